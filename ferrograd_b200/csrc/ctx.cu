@@ -1,0 +1,419 @@
+// Context, memory, plans (CUDA graphs) and the NCCL gradient exchange.
+//
+// Mirrors the reference backend's responsibilities below the GpuBackend trait
+// (crates/fused_gpu/src/dispatch/mod.rs:161-261; ROCm implementation
+// crates/fused_gpu/src/dispatch/backend/rocm/mod.rs:58-421): one device, one stream,
+// synchronous upload/download, asynchronous dispatch, schedules as captured graphs.
+#include <dlfcn.h>
+
+#include <new>
+
+#include "fg_internal.cuh"
+
+namespace {
+
+// Minimal NCCL surface, resolved with dlsym so the library loads without NCCL.
+typedef struct { char internal[FG_COMM_ID_BYTES]; } nccl_uid;
+typedef int (*pfn_ncclGetUniqueId)(nccl_uid*);
+typedef int (*pfn_ncclCommInitRank)(void**, int, nccl_uid, int);
+typedef int (*pfn_ncclAllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*pfn_ncclCommDestroy)(void*);
+typedef const char* (*pfn_ncclGetErrorString)(int);
+constexpr int kNcclFloat32 = 7;  // ncclFloat32
+constexpr int kNcclSum = 0;      // ncclSum
+
+void* open_nccl() {
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+        void* h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (h) return h;
+    }
+    return nullptr;
+}
+
+__global__ void fg_counter_increment_kernel(uint32_t* c) { *c += 1u; }
+
+}  // namespace
+
+int32_t fg_ws_alloc(fg_ctx* ctx, uint64_t bytes, void** out) {
+    uint64_t off = (ctx->ws_used + 255u) & ~uint64_t(255);
+    uint64_t need = off + bytes;
+    if (need > ctx->ws_bytes) {
+        if (ctx->capturing)
+            return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE,
+                           "scratch arena too small while recording a plan: call fg_ctx_reserve_workspace first");
+        if (ctx->ws_used != 0)
+            return fg_fail(ctx, FG_ERR_INTERNAL, "scratch arena grown in the middle of an operation");
+        // Everything that used the old arena was enqueued on this stream: drain it first.
+        FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->stream));
+        if (ctx->ws) cudaFree(ctx->ws);
+        ctx->ws = nullptr;
+        ctx->ws_bytes = 0;
+        uint64_t want = need + need / 4;
+        cudaError_t e = cudaMalloc((void**)&ctx->ws, want);
+        if (e != cudaSuccess) return fg_fail_cuda(ctx, FG_ERR_OUT_OF_MEMORY, "scratch arena", e);
+        ctx->ws_bytes = want;
+    }
+    *out = ctx->ws + off;
+    ctx->ws_used = need;
+    return FG_OK;
+}
+
+extern "C" {
+
+const char* fg_version(void) { return "ferrograd_b200 0.1 (sm_100a)"; }
+
+int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out) {
+    if (!out) return FG_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+        return FG_ERR_INVALID_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess) return FG_ERR_INVALID_DEVICE;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return FG_ERR_INVALID_DEVICE;
+    if (prop.major != 10) return FG_ERR_UNSUPPORTED_FEATURE;  // kernels are built for sm_100a only
+    fg_ctx* c = new (std::nothrow) fg_ctx();
+    if (!c) return FG_ERR_OUT_OF_MEMORY;
+    memset(c, 0, sizeof(*c));
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    if (cuda_stream) {
+        c->stream = (cudaStream_t)cuda_stream;
+        c->own_stream = false;
+    } else {
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return FG_ERR_INTERNAL; }
+        c->own_stream = true;
+    }
+    if (cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaMalloc((void**)&c->dev_status, 256) != cudaSuccess ||
+        cudaMemset(c->dev_status, 0, 256) != cudaSuccess) {
+        delete c;
+        return FG_ERR_INTERNAL;
+    }
+    cudaDriverEntryPointQueryResult qres;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+        c->tmap_encode = fn;
+    *out = c;
+    return FG_OK;
+}
+
+int32_t fg_ctx_create(int32_t device, fg_ctx** out) { return fg_ctx_create_on_stream(device, nullptr, out); }
+
+int32_t fg_ctx_destroy(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamSynchronize(ctx->comm_stream);
+    fg_comm_destroy(ctx);
+    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    cudaEventDestroy(ctx->ev_fork);
+    cudaEventDestroy(ctx->ev_join);
+    cudaStreamDestroy(ctx->comm_stream);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return FG_OK;
+}
+
+int32_t fg_sync(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->comm_stream));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->stream));
+    int status = 0;
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaMemcpy(&status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status != 0) {
+        cudaMemset(ctx->dev_status, 0, sizeof(int));
+        snprintf(ctx->err, sizeof(ctx->err), "a bounded device-side wait expired (status word 0x%x)", status);
+        return FG_ERR_TIMEOUT;
+    }
+    return FG_OK;
+}
+
+int32_t fg_ctx_device_status(fg_ctx* ctx, int32_t* status_word) {
+    if (!ctx || !status_word) return FG_ERR_INVALID_ARGUMENT;
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->stream));
+    int status = 0;
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaMemcpy(&status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (status) cudaMemset(ctx->dev_status, 0, sizeof(int));
+    *status_word = status;
+    return FG_OK;
+}
+
+int32_t fg_is_ready(fg_ctx* ctx, int32_t* ready) {
+    if (!ctx || !ready) return FG_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaStreamQuery(ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamQuery(ctx->comm_stream);
+    if (e == cudaSuccess) { *ready = 1; return FG_OK; }
+    if (e == cudaErrorNotReady) { *ready = 0; return FG_OK; }
+    return fg_fail_cuda(ctx, FG_ERR_SYNC, "cudaStreamQuery", e);
+}
+
+const char* fg_last_error(fg_ctx* ctx) { return ctx ? ctx->err : "no context"; }
+void* fg_ctx_stream(fg_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+int32_t fg_ctx_device(fg_ctx* ctx) { return ctx ? ctx->device : -1; }
+uint64_t fg_ctx_launch_count(fg_ctx* ctx) { return ctx ? ctx->launches : 0; }
+uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
+
+int32_t fg_ctx_reserve_workspace(fg_ctx* ctx, uint64_t bytes) {
+    FG_ENTER(ctx);
+    if (bytes <= ctx->ws_bytes) return FG_OK;
+    void* p;
+    int32_t s = fg_ws_alloc(ctx, bytes - 256, &p);
+    ctx->ws_used = 0;
+    return s;
+}
+
+// ---- memory ----
+int32_t fg_alloc(fg_ctx* ctx, uint64_t bytes, fg_buf** out) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, out != nullptr, "fg_alloc: out is NULL");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    fg_buf* b = new (std::nothrow) fg_buf();
+    if (!b) return fg_fail(ctx, FG_ERR_OUT_OF_MEMORY, "fg_alloc: host allocation failed");
+    b->ptr = nullptr;
+    b->bytes = bytes;
+    cudaError_t e = cudaMalloc(&b->ptr, bytes ? bytes : 1);
+    if (e != cudaSuccess) { delete b; return fg_fail_cuda(ctx, FG_ERR_OUT_OF_MEMORY, "cudaMalloc", e); }
+    *out = b;
+    return FG_OK;
+}
+
+int32_t fg_alloc_zeroed(fg_ctx* ctx, uint64_t bytes, fg_buf** out) {
+    int32_t s = fg_alloc(ctx, bytes, out);
+    if (s != FG_OK) return s;
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaMemsetAsync((*out)->ptr, 0, bytes, ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_alloc_init(fg_ctx* ctx, const void* data, uint64_t bytes, fg_buf** out) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, data != nullptr || bytes == 0, "fg_alloc_init: data is NULL");
+    int32_t s = fg_alloc(ctx, bytes, out);
+    if (s != FG_OK) return s;
+    return fg_upload(ctx, *out, data, bytes, 0);
+}
+
+int32_t fg_free(fg_ctx* ctx, fg_buf* buf) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (!buf) return FG_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(buf->ptr);
+    delete buf;
+    return FG_OK;
+}
+
+uint64_t fg_buf_size_bytes(const fg_buf* buf) { return buf ? buf->bytes : 0; }
+void* fg_buf_device_ptr(const fg_buf* buf) { return buf ? buf->ptr : nullptr; }
+
+int32_t fg_upload(fg_ctx* ctx, fg_buf* dst, const void* src, uint64_t bytes, uint64_t dst_off) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, dst && (src || bytes == 0), "fg_upload: NULL argument");
+    FG_REQUIRE(ctx, dst_off <= dst->bytes && bytes <= dst->bytes - dst_off, "fg_upload: range exceeds the buffer");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    if (bytes == 0) return FG_OK;
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync((char*)dst->ptr + dst_off, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaStreamSynchronize(ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_download(fg_ctx* ctx, const fg_buf* src, void* dst, uint64_t bytes, uint64_t src_off) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, src && (dst || bytes == 0), "fg_download: NULL argument");
+    FG_REQUIRE(ctx, src_off <= src->bytes && bytes <= src->bytes - src_off, "fg_download: range exceeds the buffer");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    if (bytes == 0) return FG_OK;
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync(dst, (const char*)src->ptr + src_off, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaStreamSynchronize(ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_copy(fg_ctx* ctx, const fg_buf* src, fg_buf* dst) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, src && dst, "fg_copy: NULL argument");
+    FG_REQUIRE(ctx, src->bytes <= dst->bytes, "fg_copy: destination smaller than source");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync(dst->ptr, src->ptr, src->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_upload_async(fg_ctx* ctx, void* dst_dev, const void* src_pinned, uint64_t bytes) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, dst_dev && src_pinned, "fg_upload_async: NULL argument");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync(dst_dev, src_pinned, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_download_async(fg_ctx* ctx, void* dst_pinned, const void* src_dev, uint64_t bytes) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, dst_pinned && src_dev, "fg_download_async: NULL argument");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync(dst_pinned, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_host_alloc_pinned(uint64_t bytes, void** out) {
+    if (!out) return FG_ERR_INVALID_ARGUMENT;
+    return cudaMallocHost(out, bytes ? bytes : 1) == cudaSuccess ? FG_OK : FG_ERR_OUT_OF_MEMORY;
+}
+
+int32_t fg_host_free_pinned(void* p) { return cudaFreeHost(p) == cudaSuccess ? FG_OK : FG_ERR_INVALID_ARGUMENT; }
+
+int32_t fg_memset_zero(fg_ctx* ctx, void* dev, uint64_t bytes) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, dev != nullptr, "fg_memset_zero: NULL pointer");
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaMemsetAsync(dev, 0, bytes, ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_counter_increment(fg_ctx* ctx, uint32_t* counter_dev) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, counter_dev != nullptr, "fg_counter_increment: NULL pointer");
+    fg_counter_increment_kernel<<<1, 1, 0, ctx->stream>>>(counter_dev);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+// ---- plans ----
+int32_t fg_plan_begin(fg_ctx* ctx) {
+    FG_ENTER(ctx);
+    if (ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "fg_plan_begin: already recording");
+    FG_CUDA(ctx, FG_ERR_INCONSISTENT_CAPTURE, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    ctx->capture_launches = 0;
+    return FG_OK;
+}
+
+int32_t fg_plan_end(fg_ctx* ctx, fg_plan** out) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (!ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "fg_plan_end: not recording");
+    if (ctx->comm_pending) {
+        int32_t s = fg_comm_join(ctx);
+        if (s != FG_OK) return s;
+    }
+    ctx->capturing = false;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess || !graph) return fg_fail_cuda(ctx, FG_ERR_INCONSISTENT_CAPTURE, "cudaStreamEndCapture", e);
+    if (!out) { cudaGraphDestroy(graph); return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_plan_end: out is NULL"); }
+    fg_plan* p = new (std::nothrow) fg_plan();
+    if (!p) { cudaGraphDestroy(graph); return fg_fail(ctx, FG_ERR_OUT_OF_MEMORY, "fg_plan_end"); }
+    p->graph = graph;
+    p->launches = ctx->capture_launches;
+    e = cudaGraphInstantiate(&p->exec, graph, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(graph); delete p; return fg_fail_cuda(ctx, FG_ERR_INTERNAL, "cudaGraphInstantiate", e); }
+    *out = p;
+    return FG_OK;
+}
+
+int32_t fg_plan_launch(fg_ctx* ctx, fg_plan* plan) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, plan != nullptr, "fg_plan_launch: plan is NULL");
+    if (ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "fg_plan_launch while recording");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_LAUNCH_FAILURE, cudaGraphLaunch(plan->exec, ctx->stream));
+    ctx->launches += plan->launches;
+    return FG_OK;
+}
+
+int32_t fg_plan_destroy(fg_plan* plan) {
+    if (!plan) return FG_OK;
+    cudaGraphExecDestroy(plan->exec);
+    cudaGraphDestroy(plan->graph);
+    delete plan;
+    return FG_OK;
+}
+
+// ---- NCCL ----
+int32_t fg_comm_unique_id(uint8_t id_out[FG_COMM_ID_BYTES]) {
+    if (!id_out) return FG_ERR_INVALID_ARGUMENT;
+    void* h = open_nccl();
+    if (!h) return FG_ERR_UNSUPPORTED_FEATURE;
+    auto get = (pfn_ncclGetUniqueId)dlsym(h, "ncclGetUniqueId");
+    if (!get) return FG_ERR_UNSUPPORTED_FEATURE;
+    nccl_uid uid;
+    if (get(&uid) != 0) return FG_ERR_INTERNAL;
+    memcpy(id_out, uid.internal, FG_COMM_ID_BYTES);
+    return FG_OK;
+}
+
+int32_t fg_comm_init(fg_ctx* ctx, int32_t nranks, int32_t rank, const uint8_t id[FG_COMM_ID_BYTES]) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, id != nullptr, "fg_comm_init: id is NULL");
+    FG_REQUIRE(ctx, nranks >= 1 && rank >= 0 && rank < nranks, "fg_comm_init: rank outside [0, nranks)");
+    if (ctx->comm) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_comm_init: communicator already initialised");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    ctx->nccl_lib = open_nccl();
+    if (!ctx->nccl_lib) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "fg_comm_init: libnccl.so.2 not found");
+    auto init = (pfn_ncclCommInitRank)dlsym(ctx->nccl_lib, "ncclCommInitRank");
+    if (!init) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "fg_comm_init: ncclCommInitRank missing");
+    nccl_uid uid;
+    memcpy(uid.internal, id, FG_COMM_ID_BYTES);
+    int r = init(&ctx->comm, nranks, uid, rank);
+    if (r != 0) {
+        auto es = (pfn_ncclGetErrorString)dlsym(ctx->nccl_lib, "ncclGetErrorString");
+        snprintf(ctx->err, sizeof(ctx->err), "ncclCommInitRank: %s", es ? es(r) : "error");
+        ctx->comm = nullptr;
+        return FG_ERR_PEER_ACCESS;
+    }
+    ctx->nranks = nranks;
+    ctx->rank = rank;
+    return FG_OK;
+}
+
+int32_t fg_allreduce_sum_f32(fg_ctx* ctx, float* buf, uint64_t count) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, buf != nullptr, "fg_allreduce_sum_f32: buf is NULL");
+    if (!ctx->comm) return fg_fail(ctx, FG_ERR_NOT_INITIALIZED, "fg_allreduce_sum_f32: call fg_comm_init first");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    if (count == 0) return FG_OK;
+    auto ar = (pfn_ncclAllReduce)dlsym(ctx->nccl_lib, "ncclAllReduce");
+    if (!ar) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "ncclAllReduce missing");
+    // Fork: the exchange starts once everything enqueued so far on the compute stream is done.
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_fork, ctx->stream));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_fork, 0));
+    int r = ar(buf, buf, (size_t)count, kNcclFloat32, kNcclSum, ctx->comm, ctx->comm_stream);
+    if (r != 0) {
+        auto es = (pfn_ncclGetErrorString)dlsym(ctx->nccl_lib, "ncclGetErrorString");
+        snprintf(ctx->err, sizeof(ctx->err), "ncclAllReduce: %s", es ? es(r) : "error");
+        return FG_ERR_PEER_ACCESS;
+    }
+    ctx->comm_pending = true;
+    if (ctx->capturing) ctx->capture_launches++; else ctx->launches++;
+    return FG_OK;
+}
+
+int32_t fg_comm_join(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (!ctx->comm_pending) return FG_OK;
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_join, ctx->comm_stream));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    ctx->comm_pending = false;
+    return FG_OK;
+}
+
+int32_t fg_comm_destroy(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (ctx->comm && ctx->nccl_lib) {
+        auto d = (pfn_ncclCommDestroy)dlsym(ctx->nccl_lib, "ncclCommDestroy");
+        if (d) d(ctx->comm);
+    }
+    ctx->comm = nullptr;
+    return FG_OK;
+}
+
+}  // extern "C"

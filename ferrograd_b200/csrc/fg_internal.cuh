@@ -1,0 +1,136 @@
+// Internal definitions shared by the translation units of libferrograd_b200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/ferrograd_b200.h"
+
+// Device error word bits, set by kernels whose bounded waits ran out.
+#define FG_DEVERR_TMA_WAIT 1
+#define FG_DEVERR_MMA_WAIT 2
+#define FG_DEVERR_EPI_WAIT 4
+
+struct fg_buf {
+    void* ptr;
+    uint64_t bytes;
+};
+
+struct fg_plan {
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    uint64_t launches;  // kernels recorded in the graph
+};
+
+struct fg_ctx {
+    int device;
+    cudaStream_t stream;
+    bool own_stream;
+    cudaStream_t comm_stream;
+    cudaEvent_t ev_fork, ev_join;
+    bool comm_pending;
+    char err[512];
+    uint64_t launches;          // kernels launched so far (eager + replayed plans)
+    bool capturing;
+    uint64_t capture_launches;  // kernels recorded since fg_plan_begin
+    // Scratch arena: operand planes of the tensor-core GEMM, reduction partials.
+    char* ws;
+    uint64_t ws_bytes;
+    uint64_t ws_used;           // bump pointer, reset at the start of every entry point
+    int* dev_status;            // device error word (see FG_DEVERR_*)
+    void* tmap_encode;          // cuTensorMapEncodeTiled, resolved at context creation
+    int sm_count;
+    // NCCL (loaded at run time)
+    void* nccl_lib;
+    void* comm;
+    int nranks, rank;
+};
+
+inline int32_t fg_fail(fg_ctx* ctx, int32_t code, const char* msg) {
+    if (ctx) {
+        strncpy(ctx->err, msg, sizeof(ctx->err) - 1);
+        ctx->err[sizeof(ctx->err) - 1] = 0;
+    }
+    return code;
+}
+
+inline int32_t fg_fail_cuda(fg_ctx* ctx, int32_t code, const char* what, cudaError_t e) {
+    if (ctx) snprintf(ctx->err, sizeof(ctx->err), "%s: %s", what, cudaGetErrorString(e));
+    return code;
+}
+
+#define FG_REQUIRE(ctx, cond, msg) \
+    do { if (!(cond)) return fg_fail((ctx), FG_ERR_INVALID_ARGUMENT, msg); } while (0)
+
+#define FG_CUDA(ctx, code, call) \
+    do { cudaError_t _e = (call); if (_e != cudaSuccess) return fg_fail_cuda((ctx), (code), #call, _e); } while (0)
+
+// Every compute entry point starts with this: valid context, right device, fresh scratch.
+#define FG_ENTER(ctx) \
+    do { if (!(ctx)) return FG_ERR_NOT_INITIALIZED; \
+         FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice((ctx)->device)); \
+         (ctx)->ws_used = 0; } while (0)
+
+// After a kernel launch: count it and surface launch-configuration errors.
+#define FG_LAUNCHED(ctx) \
+    do { cudaError_t _e = cudaGetLastError(); \
+         if (_e != cudaSuccess) return fg_fail_cuda((ctx), FG_ERR_LAUNCH_FAILURE, "kernel launch", _e); \
+         if ((ctx)->capturing) (ctx)->capture_launches++; else (ctx)->launches++; } while (0)
+
+inline bool fg_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Returns a 256-byte aligned slice of the scratch arena, growing it when allowed.
+int32_t fg_ws_alloc(fg_ctx* ctx, uint64_t bytes, void** out);
+
+// Grid for a bandwidth-bound grid-stride kernel: a multiple of the SM count.
+inline int fg_stream_grid(const fg_ctx* ctx, uint64_t work_items, int threads, int per_sm) {
+    uint64_t need = (work_items + threads - 1) / threads;
+    uint64_t cap = (uint64_t)ctx->sm_count * per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+// ---- activation maths shared by the GEMM epilogue and the elementwise kernels ----
+// Constants of the reference's tanh-approximated GELU (op/unary.rs:493-494).
+#define FG_GELU_A 0.044715f
+#define FG_GELU_B 0.7978846f
+
+__device__ __forceinline__ float fg_gelu_fwd(float x, float* t_out) {
+    float xx = x * x;
+    float u = FG_GELU_B * (x + (xx * x) * FG_GELU_A);
+    float t = tanhf(u);
+    if (t_out) *t_out = t;
+    return (0.5f * x) * (1.0f + t);
+}
+
+__device__ __forceinline__ float fg_act_fwd(int act, float z) {
+    switch (act) {
+        case FG_ACT_RELU: return z > 0.0f ? z : 0.0f;
+        case FG_ACT_TANH: return tanhf(z);
+        case FG_ACT_GELU: return fg_gelu_fwd(z, nullptr);
+        default: return z;
+    }
+}
+
+// d act / d z given the saved value (output y for relu/tanh, pre-activation z for gelu).
+__device__ __forceinline__ float fg_act_grad(int act, float saved) {
+    switch (act) {
+        case FG_ACT_RELU: return saved > 0.0f ? 1.0f : 0.0f;
+        case FG_ACT_TANH: return 1.0f - saved * saved;
+        case FG_ACT_GELU: {
+            float t;
+            fg_gelu_fwd(saved, &t);
+            float du = FG_GELU_B * (1.0f + (FG_GELU_A * 3.0f) * (saved * saved));
+            return 0.5f * ((1.0f + t) + (1.0f - t * t) * (saved * du));
+        }
+        default: return 1.0f;
+    }
+}
+
+// ---- internal launchers used across translation units ----
+int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uint32_t N, uint32_t K,
+                            const float* A, const float* B, float* C, const float* bias, int act,
+                            float* preact_out);
+int32_t fg_act_bwd_launch(fg_ctx* ctx, uint64_t n, int act, const float* dy, const float* saved, float* dz);
+int32_t fg_colsum_launch(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* x, float* out);

@@ -1,0 +1,240 @@
+/*
+ * ferrograd_b200 -- C ABI of the B200 (sm_100a) execution backend for ferrograd.
+ *
+ * This is the boundary a ferrograd `GpuBackend` implementation binds to
+ * (reference trait: crates/fused_gpu/src/dispatch/mod.rs:161-261).  Every entry
+ * point is `extern "C"`, takes plain pointers and sizes, returns an `int32_t`
+ * status (`FG_OK` == 0) and never throws or aborts.  All compute entry points
+ * enqueue work on the context's stream and return immediately, like the
+ * reference's `dispatch_*` calls (crates/fused_gpu/src/dispatch/mod.rs:766-814);
+ * only `fg_sync`, `fg_download`, `fg_upload` (from pageable memory) block.
+ *
+ * Conventions
+ *   - tensors are dense, row-major, f32 unless stated; labels/indices are u32
+ *     (reference: crates/fused_gpu/src/tensor.rs:125-128);
+ *   - device pointers handed to compute entry points must be 16-byte aligned
+ *     (anything returned by `fg_alloc*` is 256-byte aligned);
+ *   - host-side validation failures return FG_ERR_INVALID_ARGUMENT without
+ *     launching anything; `fg_last_error` gives the message;
+ *   - there is no CPU fallback: every compute entry point runs a CUDA kernel.
+ */
+#ifndef FERROGRAD_B200_H
+#define FERROGRAD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; one per `ErrorKind` variant a backend can produce
+ * (crates/fused_gpu/src/errors.rs:105-140), plus FG_ERR_TIMEOUT for a bounded
+ * device-side wait that ran out. */
+enum fg_status {
+    FG_OK = 0,
+    FG_ERR_INVALID_ARGUMENT = 1,    /* ErrorKind::InvalidArgument    */
+    FG_ERR_OUT_OF_MEMORY = 2,       /* ErrorKind::OutOfMemory        */
+    FG_ERR_INVALID_DEVICE = 3,      /* ErrorKind::InvalidDevice      */
+    FG_ERR_LAUNCH_FAILURE = 4,      /* ErrorKind::LaunchFailure      */
+    FG_ERR_SYNC = 5,                /* ErrorKind::SyncError          */
+    FG_ERR_FAILED_BUFFER_COPY = 6,  /* ErrorKind::FailedBufferCopy   */
+    FG_ERR_UNSUPPORTED_FEATURE = 7, /* ErrorKind::UnsupportedFeature */
+    FG_ERR_NOT_INITIALIZED = 8,     /* ErrorKind::NotInitialized     */
+    FG_ERR_INTERNAL = 9,            /* ErrorKind::InternalError      */
+    FG_ERR_PEER_ACCESS = 10,        /* ErrorKind::PeerAccessError    */
+    FG_ERR_TIMEOUT = 11,            /* (new) bounded wait expired    */
+    FG_ERR_INCONSISTENT_CAPTURE = 12 /* ErrorKind::InconsistentCapture */
+};
+
+/* Activations fused into the GEMM epilogue / backward prologue.
+ * Reference ops: crates/ferrograd-nn/src/op/unary.rs tanh :270-327,
+ * relu :436-490, gelu :492-733 (tanh approximation, constants :493-494). */
+enum fg_act { FG_ACT_NONE = 0, FG_ACT_RELU = 1, FG_ACT_TANH = 2, FG_ACT_GELU = 3 };
+
+/* How the f32 GEMM is computed. */
+enum fg_gemm_mode {
+    FG_GEMM_AUTO = 0,   /* tensor cores when the shape is large enough, else SIMT */
+    FG_GEMM_SIMT = 1,   /* sequential-k fmaf, bit-identical to the reference kernel body
+                           (crates/ferrograd-nn/src/op/matmul/generic.rs:98-319) */
+    FG_GEMM_3XTF32 = 2  /* tcgen05 kind::tf32, hi/lo split, three MMAs per k-step */
+};
+
+typedef struct fg_ctx fg_ctx;   /* one device + one stream (rocm/mod.rs:58-78)   */
+typedef struct fg_buf fg_buf;   /* GpuBackend::Buffer                            */
+typedef struct fg_plan fg_plan; /* GpuBackend::Schedule: a captured CUDA graph   */
+
+/* ---- context (GpuContext::new, sync, is_ready: dispatch/mod.rs:352-367,:505) ---- */
+int32_t fg_ctx_create(int32_t device, fg_ctx** out);
+/* Use an existing CUDA stream (e.g. one owned by a host framework); 0 = a new one. */
+int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out);
+int32_t fg_ctx_destroy(fg_ctx* ctx);
+int32_t fg_sync(fg_ctx* ctx);                    /* GpuBackend::sync     :253 */
+int32_t fg_is_ready(fg_ctx* ctx, int32_t* ready);/* GpuBackend::is_ready :260 */
+const char* fg_last_error(fg_ctx* ctx);          /* Error::msg (errors.rs:15-19) */
+void* fg_ctx_stream(fg_ctx* ctx);                /* the cudaStream_t, for host plumbing */
+int32_t fg_ctx_device(fg_ctx* ctx);
+/* Number of kernels this context has launched (eager launches and kernels inside
+ * replayed plans); lets a benchmark report its own launch count. */
+uint64_t fg_ctx_launch_count(fg_ctx* ctx);
+/* Pre-size the scratch arena the tensor-core GEMM uses for its hi/lo operand
+ * planes, so that no allocation happens later (required before fg_plan_begin). */
+int32_t fg_ctx_reserve_workspace(fg_ctx* ctx, uint64_t bytes);
+uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
+/* Reads and clears the device-side error word (bounded waits that expired). */
+int32_t fg_ctx_device_status(fg_ctx* ctx, int32_t* status_word);
+
+/* ---- memory (GpuBackend::alloc/alloc_zeroed/alloc_init/upload/copy/download :171-207) ---- */
+int32_t fg_alloc(fg_ctx* ctx, uint64_t bytes, fg_buf** out);
+int32_t fg_alloc_zeroed(fg_ctx* ctx, uint64_t bytes, fg_buf** out);
+int32_t fg_alloc_init(fg_ctx* ctx, const void* data, uint64_t bytes, fg_buf** out);
+int32_t fg_free(fg_ctx* ctx, fg_buf* buf);
+uint64_t fg_buf_size_bytes(const fg_buf* buf);   /* GpuBufferBackend::size_bytes :150 */
+void* fg_buf_device_ptr(const fg_buf* buf);
+int32_t fg_upload(fg_ctx* ctx, fg_buf* dst, const void* src, uint64_t bytes, uint64_t dst_off);
+int32_t fg_download(fg_ctx* ctx, const fg_buf* src, void* dst, uint64_t bytes, uint64_t src_off);
+int32_t fg_copy(fg_ctx* ctx, const fg_buf* src, fg_buf* dst);
+/* Asynchronous copies from/to PINNED host memory on the context stream. */
+int32_t fg_upload_async(fg_ctx* ctx, void* dst_dev, const void* src_pinned, uint64_t bytes);
+int32_t fg_download_async(fg_ctx* ctx, void* dst_pinned, const void* src_dev, uint64_t bytes);
+int32_t fg_host_alloc_pinned(uint64_t bytes, void** out);
+int32_t fg_host_free_pinned(void* p);
+int32_t fg_memset_zero(fg_ctx* ctx, void* dev, uint64_t bytes);
+
+/* ---- GEMM with fused epilogue (matmul: op/matmul/mod.rs:17-188,:190-296;
+ *      epilogue fusion rule: kernel/forward.rs:373-457) ----
+ * C[M,N] = act( op(A)·op(B) + bias ), op(X) = X or Xᵀ.  A is [M,K] (or [K,M] when
+ * transA), B is [K,N] (or [N,K] when transB).  bias is [N] broadcast over rows or
+ * NULL.  preact_out (NULL or [M,N]) receives op(A)·op(B)+bias before the activation
+ * (needed by the GELU backward). */
+int32_t fg_gemm_f32(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB,
+                    uint32_t M, uint32_t N, uint32_t K,
+                    const float* A, const float* B, float* C,
+                    const float* bias, int32_t act, float* preact_out);
+
+/* Backward of Y = act(A·B + bias) for A[M,K], B[K,N]  (matmul backward edges:
+ * op/matmul/mod.rs:75-101; activation backward: op/unary.rs:281-309,:453-472,:588-714).
+ *   dZ = dY ⊙ act'(saved)        saved = Y for NONE/RELU/TANH, pre-activation Z for GELU
+ *   dA = dZ·Bᵀ  [M,K]   (skipped when dA == NULL)
+ *   dB = Aᵀ·dZ  [K,N]   (skipped when dB == NULL)
+ *   dbias = column sums of dZ [N] (skipped when NULL)
+ *   dZ_out (NULL or [M,N]) receives dZ.
+ * The ReLU mask is saved > 0 (the standard mask). */
+int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K,
+                        const float* A, const float* B, const float* dY,
+                        int32_t act, const float* saved,
+                        float* dA, float* dB, float* dbias, float* dZ_out);
+
+/* ---- activations standalone (op/unary.rs) ---- */
+int32_t fg_bias_act_fwd(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* z,
+                        const float* bias, int32_t act, float* y);
+int32_t fg_act_bwd(fg_ctx* ctx, uint64_t n, int32_t act, const float* dy,
+                   const float* saved, float* dz);
+
+/* ---- softmax (op/softmax.rs:112-446 forward, :448-688 backward) ---- */
+int32_t fg_softmax_fwd(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* x, float* y);
+/* dx = y ⊙ (dy − Σ_row dy·y); accumulate != 0 adds into dx like the reference's `+=`. */
+int32_t fg_softmax_bwd(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* y,
+                       const float* dy, float* dx, int32_t accumulate);
+
+/* ---- fused softmax + cross-entropy forward and backward
+ *      (CROSS_ENTROPY: loss/basic_loss.rs:91-133; loss kernel: kernel/loss.rs:12-165) ----
+ * loss_row[r] = −log softmax(logits[r])[labels[r]];  loss_mean = Σ loss_row / rows;
+ * dlogits = (softmax − onehot) · grad_scale.  loss_row_out, loss_mean_out, probs_out
+ * may be NULL.  argmax_out (NULL or u32[rows]) receives the index of the first
+ * maximum of each row. */
+int32_t fg_softmax_ce_fwd_bwd(fg_ctx* ctx, const float* logits, const uint32_t* labels,
+                              uint32_t rows, uint32_t cols, float grad_scale,
+                              float* loss_row_out, float* loss_mean_out,
+                              float* dlogits_out, float* probs_out, uint32_t* argmax_out);
+/* The reference's unfused per-element CE on probabilities (loss/basic_loss.rs:91-133):
+ * loss[r,c] = −log p at c == label[r] else 0; grad[r,c] = p − 1 at the label else p. */
+int32_t fg_ce_loss_grad(fg_ctx* ctx, const float* probs, const uint32_t* labels,
+                        uint32_t rows, uint32_t cols, float* loss_out, float* grad_out);
+
+/* ---- MSE (MEAN_SQUARED_ERROR: loss/basic_loss.rs:3-27) ----
+ * loss[i] = (p−t)², grad[i] = 2(p−t)·grad_scale.  loss_elem_out and loss_sum_out
+ * (one float: Σ loss[i], reduced in a fixed order) may be NULL. */
+int32_t fg_mse_loss_grad(fg_ctx* ctx, const float* pred, const float* target, uint64_t n,
+                         float grad_scale, float* loss_elem_out, float* loss_sum_out,
+                         float* grad_out);
+
+/* ---- optimizers ----
+ * SGD (STOCHASTIC_GRADIENT_DESCENT: optim/basic_optim.rs:3-31; lr plumbing
+ * kernel/optim.rs:119-146): w −= lr·(g·grad_scale); g = 0 when zero_grad != 0
+ * (the reference always zeroes). */
+int32_t fg_sgd_step(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr,
+                    float grad_scale, int32_t zero_grad);
+
+typedef struct fg_adamw_hyper {
+    float lr, beta1, beta2, eps, weight_decay;
+} fg_adamw_hyper;
+/* AdamW (absent from the reference; decoupled weight decay, bias-corrected):
+ *   g' = g·grad_scale; m = β1 m + (1−β1) g'; v = β2 v + (1−β2) g'²;
+ *   w = w − lr·( (m/(1−β1^t)) / (sqrt(v/(1−β2^t)) + eps) + wd·w ).
+ * t = *step_dev when step_dev != NULL (a device counter, so a captured plan can be
+ * replayed with a moving step), else `step` (1-based). */
+int32_t fg_adamw_step(fg_ctx* ctx, float* w, float* g, float* m, float* v, uint64_t n,
+                      const fg_adamw_hyper* hyper, uint32_t step, const uint32_t* step_dev,
+                      float grad_scale, int32_t zero_grad);
+int32_t fg_counter_increment(fg_ctx* ctx, uint32_t* counter_dev);
+
+/* ---- fused elementwise chains (op/binary.rs add :74, mul :236, sub :449, div :644;
+ *      op/unary.rs; inlining rule kernel/forward.rs:298-464) ----
+ * A chain is a straight-line program over per-element values.  Instruction i
+ * defines value i.  FG_EW_INPUT loads inputs[a][idx]; FG_EW_CONST is `imm`;
+ * binary ops read values a and b; unary ops read value a.  The last value is the
+ * output.  At most FG_EW_MAX_INSTR instructions and FG_EW_MAX_INPUTS inputs. */
+enum fg_ew_op {
+    FG_EW_INPUT = 0, FG_EW_CONST = 1, FG_EW_ADD = 2, FG_EW_SUB = 3, FG_EW_MUL = 4,
+    FG_EW_DIV = 5, FG_EW_NEG = 6, FG_EW_ABS = 7, FG_EW_EXP = 8, FG_EW_LOG = 9,
+    FG_EW_TANH = 10, FG_EW_RELU = 11, FG_EW_GELU = 12, FG_EW_ELU = 13
+};
+#define FG_EW_MAX_INSTR 24
+#define FG_EW_MAX_INPUTS 8
+typedef struct fg_ew_instr {
+    int32_t op, a, b;
+    float imm;
+} fg_ew_instr;
+/* out[i] = chain(inputs[0][i], ...).  saved_out (NULL or array of ninstr pointers,
+ * each NULL or a buffer of n floats) receives intermediate values, the analogue of
+ * the reference's forward_saved tensors. */
+int32_t fg_eltwise_chain_fwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
+                             const float* const* inputs, int32_t ninputs, float* out,
+                             float* const* saved_out);
+/* One kernel recomputes the chain and back-propagates `seed` (dL/dout, [n]) to every
+ * input: grads[k][i] (+)= dL/dinputs[k][i]; grads[k] may be NULL. */
+int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
+                             const float* const* inputs, int32_t ninputs, const float* seed,
+                             float* const* grads, int32_t accumulate);
+
+/* ---- plans: a captured CUDA graph, the analogue of GpuBackend::schedule /
+ *      dispatch_schedule (dispatch/mod.rs:218-250; rocm/mod.rs:324-389 captures a
+ *      hipGraph the same way) ----
+ * Between fg_plan_begin and fg_plan_end every compute entry point on this context is
+ * recorded instead of executed.  No allocation may happen in between: reserve the
+ * workspace first. */
+int32_t fg_plan_begin(fg_ctx* ctx);
+int32_t fg_plan_end(fg_ctx* ctx, fg_plan** out);
+int32_t fg_plan_launch(fg_ctx* ctx, fg_plan* plan);
+int32_t fg_plan_destroy(fg_plan* plan);
+
+/* ---- data-parallel gradient exchange (no counterpart in the reference, which is
+ *      single-device: rocm/mod.rs:58-78).  NCCL is loaded at run time. ---- */
+#define FG_COMM_ID_BYTES 128
+int32_t fg_comm_unique_id(uint8_t id_out[FG_COMM_ID_BYTES]);
+int32_t fg_comm_init(fg_ctx* ctx, int32_t nranks, int32_t rank, const uint8_t id[FG_COMM_ID_BYTES]);
+/* In-place sum over ranks.  Runs on the context's communication stream: it starts
+ * after everything enqueued so far on the compute stream and overlaps with what is
+ * enqueued afterwards, until fg_comm_join. */
+int32_t fg_allreduce_sum_f32(fg_ctx* ctx, float* buf, uint64_t count);
+int32_t fg_comm_join(fg_ctx* ctx);
+int32_t fg_comm_destroy(fg_ctx* ctx);
+
+/* Library / build information. */
+const char* fg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERROGRAD_B200_H */

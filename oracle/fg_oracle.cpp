@@ -1,0 +1,472 @@
+// CPU oracle -- TEST INFRASTRUCTURE, NOT PRODUCT (see fg_oracle.h for the parity status).
+//
+// Every function restates, in plain f32 C++, what the reference's generated kernels
+// compute.  The generated HIP source is ordinary C++ apart from thread indices and
+// shared memory (crates/fused_gpu/src/dispatch/backend/rocm/generate.rs:102-667), is
+// compiled with fast-math off (rocm/mod.rs:148-156), and the IR optimiser contracts
+// a*b+c to fma (kernel/optimize.rs:31-117); this file therefore uses fmaf where the
+// reference's kernel body does and plain f32 operations elsewhere.
+#include "fg_oracle.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+constexpr float kGeluA = 0.044715f;    // op/unary.rs:493
+constexpr float kGeluB = 0.7978846f;   // op/unary.rs:494
+
+inline float gelu_fwd(float x, float* t_out) {
+    // op/unary.rs:501-587: 0.5*x * (1 + tanh(b*(x + a*x^3)))
+    float xx = x * x;
+    float xxx = xx * x;
+    float u = kGeluB * (x + xxx * kGeluA);
+    float t = std::tanh(u);
+    if (t_out) *t_out = t;
+    return (0.5f * x) * (1.0f + t);
+}
+
+inline float gelu_grad(float x, float t_for_x /*quirk: value used as x*/, float t) {
+    // op/unary.rs:588-714: 0.5*((1+t) + (1-t^2) * x * b*(1 + 3a*x^2)); the reference feeds
+    // the saved tanh where x is meant, reproduced when t_for_x != x.
+    float xv = t_for_x;
+    float c = kGeluA * 3.0f;
+    float du = kGeluB * (1.0f + c * (xv * xv));
+    float two = (1.0f + t) + (1.0f - t * t) * (xv * du);
+    return 0.5f * two;
+}
+
+inline float act_fwd(int act, float z) {
+    switch (act) {
+        case REF_ACT_RELU: return z > 0.0f ? z : 0.0f;   // op/unary.rs:442-451 max(x, 0)
+        case REF_ACT_TANH: return std::tanh(z);           // op/unary.rs:276
+        case REF_ACT_GELU: return gelu_fwd(z, nullptr);
+        default: return z;
+    }
+}
+
+inline float act_grad(int act, float saved, int quirks) {
+    switch (act) {
+        case REF_ACT_RELU:
+            if (quirks & REF_QUIRK_RELU_MASK_GE0) return saved >= 0.0f ? 1.0f : 0.0f;
+            return saved > 0.0f ? 1.0f : 0.0f;
+        case REF_ACT_TANH: return 1.0f - saved * saved;    // op/unary.rs:281-309, saved = y
+        case REF_ACT_GELU: {
+            float t;
+            gelu_fwd(saved, &t);                            // saved = pre-activation
+            if (quirks & REF_QUIRK_GELU_BWD_T) return gelu_grad(saved, t, t);
+            return gelu_grad(saved, saved, t);
+        }
+        default: return 1.0f;
+    }
+}
+
+// 4 x 64 register block, k strictly sequential, one fmaf per (i, j, k).
+__attribute__((target_clones("arch=skylake-avx512", "arch=haswell", "default")))
+void gemm_block_f32(uint32_t ib, uint32_t jn, uint32_t K, const float* A, uint32_t lda,
+                    const float* B, uint32_t ldb, float* C, uint32_t ldc) {
+    constexpr uint32_t JB = 64;
+    float acc[4][JB];
+    for (uint32_t i = 0; i < 4; ++i)
+        for (uint32_t j = 0; j < JB; ++j) acc[i][j] = 0.0f;
+    if (ib == 4 && jn == JB) {
+        for (uint32_t k = 0; k < K; ++k) {
+            const float* b = B + (size_t)k * ldb;
+            const float a0 = A[k], a1 = A[lda + k], a2 = A[2 * (size_t)lda + k], a3 = A[3 * (size_t)lda + k];
+#pragma omp simd
+            for (uint32_t j = 0; j < JB; ++j) {
+                float bv = b[j];
+                acc[0][j] = __builtin_fmaf(a0, bv, acc[0][j]);
+                acc[1][j] = __builtin_fmaf(a1, bv, acc[1][j]);
+                acc[2][j] = __builtin_fmaf(a2, bv, acc[2][j]);
+                acc[3][j] = __builtin_fmaf(a3, bv, acc[3][j]);
+            }
+        }
+    } else {
+        for (uint32_t k = 0; k < K; ++k) {
+            const float* b = B + (size_t)k * ldb;
+            for (uint32_t i = 0; i < ib; ++i) {
+                const float a = A[(size_t)i * lda + k];
+                for (uint32_t j = 0; j < jn; ++j) acc[i][j] = __builtin_fmaf(a, b[j], acc[i][j]);
+            }
+        }
+    }
+    for (uint32_t i = 0; i < ib; ++i)
+        for (uint32_t j = 0; j < jn; ++j) C[(size_t)i * ldc + j] = acc[i][j];
+}
+
+void transpose(uint32_t R, uint32_t Cn, const float* x, float* y) {
+    // y[Cn, R] = x[R, Cn]^T
+#pragma omp parallel for schedule(static)
+    for (int64_t rb = 0; rb < (int64_t)((R + 31) / 32); ++rb)
+        for (uint32_t cb = 0; cb < Cn; cb += 32)
+            for (uint32_t r = rb * 32; r < std::min<uint32_t>(R, rb * 32 + 32); ++r)
+                for (uint32_t c = cb; c < std::min(Cn, cb + 32); ++c)
+                    y[(size_t)c * R + r] = x[(size_t)r * Cn + c];
+}
+
+// The reference reduces a row with 256 threads: thread t folds columns t, t+256, ... and
+// a shared-memory tree then halves the stride from 128 to 1 (op/softmax.rs:121-257 for max,
+// :259-397 for the sum, :529-588 for the backward dot product).
+template <typename F>
+inline float tree256_sum(uint32_t cols, F term) {
+    float part[256];
+    for (uint32_t t = 0; t < 256; ++t) {
+        float s = 0.0f;
+        for (uint32_t c = t; c < cols; c += 256) s += term(c);
+        part[t] = s;
+    }
+    for (uint32_t stride = 128; stride >= 1; stride >>= 1)
+        for (uint32_t t = 0; t < stride; ++t) part[t] += part[t + stride];
+    return part[0];
+}
+
+}  // namespace
+
+extern "C" {
+
+int ref_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+void ref_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+void ref_gemm_f32(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A,
+                  const float* B, float* C, int accumulate_f64) {
+    // op/matmul/mod.rs:75-101 selects the transposes for the backward edges
+    // (dA = dC·B^T via transpose_b, dB = A^T·dC via transpose_a).
+    std::vector<float> At, Bt;
+    const float* a = A;
+    const float* b = B;
+    if (transA) { At.resize((size_t)M * K); transpose(K, M, A, At.data()); a = At.data(); }
+    if (transB) { Bt.resize((size_t)K * N); transpose(N, K, B, Bt.data()); b = Bt.data(); }
+    if (accumulate_f64) {
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < (int64_t)M; ++i) {
+            std::vector<double> acc(N, 0.0);
+            for (uint32_t k = 0; k < K; ++k) {
+                double av = a[(size_t)i * K + k];
+                const float* br = b + (size_t)k * N;
+                for (uint32_t j = 0; j < N; ++j) acc[j] += av * (double)br[j];
+            }
+            for (uint32_t j = 0; j < N; ++j) C[(size_t)i * N + j] = (float)acc[j];
+        }
+        return;
+    }
+    const int64_t mb = (M + 3) / 4, nb = (N + 63) / 64;
+#pragma omp parallel for schedule(dynamic, 4) collapse(2)
+    for (int64_t bi = 0; bi < mb; ++bi)
+        for (int64_t bj = 0; bj < nb; ++bj) {
+            uint32_t i0 = (uint32_t)bi * 4, j0 = (uint32_t)bj * 64;
+            gemm_block_f32(std::min<uint32_t>(4, M - i0), std::min<uint32_t>(64, N - j0), K,
+                           a + (size_t)i0 * K, K, b + j0, N, C + (size_t)i0 * N + j0, N);
+        }
+}
+
+void ref_bias_act_fwd(uint32_t rows, uint32_t cols, const float* z, const float* bias, int act,
+                      float* y, float* preact_out) {
+    // add: op/binary.rs:74-234 (the build broadcasts bias[N] over rows); activations op/unary.rs.
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)rows; ++r)
+        for (uint32_t c = 0; c < cols; ++c) {
+            size_t i = (size_t)r * cols + c;
+            float p = bias ? z[i] + bias[c] : z[i];
+            if (preact_out) preact_out[i] = p;
+            y[i] = act_fwd(act, p);
+        }
+}
+
+void ref_act_bwd(uint64_t n, int act, const float* dy, const float* saved, float* dz, int quirks) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i)
+        dz[i] = act == REF_ACT_NONE ? dy[i] : dy[i] * act_grad(act, saved[i], quirks);
+}
+
+void ref_colsum(uint32_t rows, uint32_t cols, const float* x, float* out) {
+    // Bias gradient of a row-broadcast bias: sum over rows, accumulated in double.
+#pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < (int64_t)cols; ++c) {
+        double s = 0.0;
+        for (uint32_t r = 0; r < rows; ++r) s += x[(size_t)r * cols + c];
+        out[c] = (float)s;
+    }
+}
+
+void ref_softmax_fwd(uint32_t rows, uint32_t cols, const float* x, float* y) {
+    // op/softmax.rs:112-446.
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)rows; ++r) {
+        const float* xr = x + (size_t)r * cols;
+        float* yr = y + (size_t)r * cols;
+        float mx = -INFINITY;
+        for (uint32_t c = 0; c < cols; ++c) mx = std::max(mx, xr[c]);   // max is order-independent
+        for (uint32_t c = 0; c < cols; ++c) yr[c] = std::exp(xr[c] - mx);  // :318-347 stores e
+        float sum = tree256_sum(cols, [&](uint32_t c) { return yr[c]; });
+        float inv = 1.0f / sum;                                          // :408-416
+        for (uint32_t c = 0; c < cols; ++c) yr[c] *= inv;                // :436 param_mul
+    }
+}
+
+void ref_softmax_bwd(uint32_t rows, uint32_t cols, const float* y, const float* dy, float* dx,
+                     int accumulate, int quirks) {
+    // op/softmax.rs:448-688: dot = sum(dy*y); dx += y*(dy - dot).
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)rows; ++r) {
+        const float* yr = y + (size_t)r * cols;
+        const float* dr = dy + (size_t)r * cols;
+        float* xr = dx + (size_t)r * cols;
+        float dot = tree256_sum(cols, [&](uint32_t c) { return dr[c] * yr[c]; });
+        uint32_t step = (quirks & REF_QUIRK_SOFTMAX_BWD_COL0) ? 256 : 1;
+        for (uint32_t c = 0; c < cols; c += step) {
+            float g = yr[c] * (dr[c] - dot);
+            xr[c] = accumulate ? xr[c] + g : g;
+        }
+    }
+}
+
+void ref_ce_loss_grad(uint32_t rows, uint32_t cols, const float* probs, const uint32_t* labels,
+                      float* loss, float* grad) {
+    // loss/basic_loss.rs:91-133; label read by row, compared with the column (kernel/loss.rs:92-162).
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < (int64_t)rows; ++r)
+        for (uint32_t c = 0; c < cols; ++c) {
+            size_t i = (size_t)r * cols + c;
+            float p = probs[i];
+            if (labels[r] == c) { loss[i] = -std::log(p); grad[i] = p - 1.0f; }
+            else { loss[i] = 0.0f; grad[i] = p; }
+        }
+}
+
+void ref_softmax_ce_fwd_bwd(uint32_t rows, uint32_t cols, const float* logits,
+                            const uint32_t* labels, float grad_scale, float* loss_row,
+                            float* loss_mean, float* dlogits, float* probs, uint32_t* argmax) {
+    // softmax (op/softmax.rs:112-446) followed by CROSS_ENTROPY (loss/basic_loss.rs:91-133),
+    // with p - onehot used directly as dlogits (the standard fused form).
+    std::vector<float> lr(rows);
+#pragma omp parallel
+    {
+        std::vector<float> p(cols);
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < (int64_t)rows; ++r) {
+            const float* xr = logits + (size_t)r * cols;
+            ref_softmax_fwd(1, cols, xr, p.data());
+            uint32_t am = 0;
+            for (uint32_t c = 1; c < cols; ++c) if (xr[c] > xr[am]) am = c;
+            if (argmax) argmax[r] = am;
+            uint32_t lab = labels[r];
+            lr[r] = lab < cols ? -std::log(p[lab]) : 0.0f;
+            for (uint32_t c = 0; c < cols; ++c) {
+                float g = (c == lab) ? p[c] - 1.0f : p[c];
+                if (dlogits) dlogits[(size_t)r * cols + c] = g * grad_scale;
+                if (probs) probs[(size_t)r * cols + c] = p[c];
+            }
+        }
+    }
+    double s = 0.0;
+    for (uint32_t r = 0; r < rows; ++r) { s += lr[r]; if (loss_row) loss_row[r] = lr[r]; }
+    if (loss_mean) *loss_mean = (float)(s / rows);
+}
+
+void ref_mse_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,
+                       float* loss_elem, float* loss_sum, float* grad) {
+    // loss/basic_loss.rs:3-27: diff = p - t; loss = diff*diff; grad = 2*diff (unreduced).
+    double s = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : s)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        float d = pred[i] - target[i];
+        float l = d * d;
+        if (loss_elem) loss_elem[i] = l;
+        if (grad) grad[i] = (2.0f * d) * grad_scale;
+        s += l;
+    }
+    if (loss_sum) *loss_sum = (float)s;
+}
+
+void ref_sgd_step(uint64_t n, float* w, float* g, float lr, float grad_scale, int zero_grad) {
+    // optim/basic_optim.rs:3-31: scaled = g*lr; w -= scaled; g = 0.
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        float gi = grad_scale == 1.0f ? g[i] : g[i] * grad_scale;
+        float scaled = gi * lr;
+        w[i] = w[i] - scaled;
+        if (zero_grad) g[i] = 0.0f;
+    }
+}
+
+void ref_adamw_step(uint64_t n, float* w, float* g, float* m, float* v, float lr, float beta1,
+                    float beta2, float eps, float weight_decay, uint32_t step, float grad_scale,
+                    int zero_grad) {
+    // Not in the reference (optim/basic_optim.rs has SGD only): the standard decoupled form.
+    const float bc1 = 1.0f - std::pow(beta1, (float)step);
+    const float bc2 = 1.0f - std::pow(beta2, (float)step);
+    const float inv_bc1 = 1.0f / bc1, inv_bc2 = 1.0f / bc2;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        float gi = g[i] * grad_scale;
+        float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+        float vi = beta2 * v[i] + (1.0f - beta2) * (gi * gi);
+        float mhat = mi * inv_bc1;
+        float vhat = vi * inv_bc2;
+        float upd = mhat / (std::sqrt(vhat) + eps) + weight_decay * w[i];
+        w[i] = w[i] - lr * upd;
+        m[i] = mi;
+        v[i] = vi;
+        if (zero_grad) g[i] = 0.0f;
+    }
+}
+
+// ---- elementwise chains ------------------------------------------------------------
+enum { EW_INPUT = 0, EW_CONST, EW_ADD, EW_SUB, EW_MUL, EW_DIV, EW_NEG, EW_ABS, EW_EXP, EW_LOG,
+       EW_TANH, EW_RELU, EW_GELU, EW_ELU };
+
+static inline float ew_eval(const ref_ew_instr& in, const float* v, const float* const* inputs,
+                            uint64_t i) {
+    switch (in.op) {
+        case EW_INPUT: return inputs[in.a][i];
+        case EW_CONST: return in.imm;
+        case EW_ADD: return v[in.a] + v[in.b];                 // op/binary.rs:74
+        case EW_SUB: return v[in.a] - v[in.b];                 // :449
+        case EW_MUL: return v[in.a] * v[in.b];                 // :236
+        case EW_DIV: return v[in.a] / v[in.b];                 // :644
+        case EW_NEG: return -v[in.a];
+        case EW_ABS: return std::fabs(v[in.a]);
+        case EW_EXP: return std::exp(v[in.a]);                 // op/unary.rs:741-756
+        case EW_LOG: return std::log(v[in.a]);
+        case EW_TANH: return std::tanh(v[in.a]);
+        case EW_RELU: return v[in.a] > 0.0f ? v[in.a] : 0.0f;
+        case EW_GELU: return gelu_fwd(v[in.a], nullptr);
+        case EW_ELU: return v[in.a] >= 0.0f ? v[in.a] : std::exp(v[in.a]) - 1.0f;  // op/unary.rs:328-436
+        default: return 0.0f;
+    }
+}
+
+void ref_eltwise_chain_fwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
+                           const float* const* inputs, int ninputs, float* out,
+                           float* const* saved_out) {
+    (void)ninputs;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        float v[64];
+        for (int k = 0; k < ninstr; ++k) {
+            v[k] = ew_eval(prog[k], v, inputs, (uint64_t)i);
+            if (saved_out && saved_out[k]) saved_out[k][i] = v[k];
+        }
+        out[i] = v[ninstr - 1];
+    }
+}
+
+void ref_eltwise_chain_bwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
+                           const float* const* inputs, int ninputs, const float* seed,
+                           float* const* grads, int accumulate, int quirks) {
+    // Reverse sweep; derivative forms from op/binary.rs (mul :344-418, sub :557-613,
+    // div :752-851) and op/unary.rs.
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        float v[64], adj[64], gin[16];
+        for (int k = 0; k < ninstr; ++k) { v[k] = ew_eval(prog[k], v, inputs, (uint64_t)i); adj[k] = 0.0f; }
+        for (int k = 0; k < ninputs; ++k) gin[k] = 0.0f;
+        adj[ninstr - 1] = seed[i];
+        for (int k = ninstr - 1; k >= 0; --k) {
+            const ref_ew_instr& in = prog[k];
+            float g = adj[k];
+            switch (in.op) {
+                case EW_INPUT: gin[in.a] += g; break;
+                case EW_ADD: adj[in.a] += g; adj[in.b] += g; break;
+                case EW_SUB: adj[in.a] += g; adj[in.b] -= g; break;
+                case EW_MUL: adj[in.a] += g * v[in.b]; adj[in.b] += g * v[in.a]; break;
+                case EW_DIV: adj[in.a] += g / v[in.b];
+                             adj[in.b] -= (g * v[in.a]) / (v[in.b] * v[in.b]); break;
+                case EW_NEG: adj[in.a] -= g; break;
+                case EW_ABS: adj[in.a] += (v[in.a] >= 0.0f ? g : -g); break;
+                case EW_EXP: adj[in.a] += g * v[k]; break;
+                case EW_LOG: adj[in.a] += g / v[in.a]; break;
+                case EW_TANH: adj[in.a] += g * (1.0f - v[k] * v[k]); break;
+                case EW_RELU: adj[in.a] += g * act_grad(REF_ACT_RELU, v[k], quirks); break;
+                case EW_GELU: adj[in.a] += g * act_grad(REF_ACT_GELU, v[in.a], quirks); break;
+                case EW_ELU: adj[in.a] += (v[k] >= 0.0f ? g : g * (v[k] + 1.0f)); break;
+                default: break;
+            }
+        }
+        for (int k = 0; k < ninputs; ++k)
+            if (grads[k]) grads[k][i] = accumulate ? grads[k][i] + gin[k] : gin[k];
+    }
+}
+
+// ---- MLP training step --------------------------------------------------------------
+double ref_mlp_step(int nlayers, const uint32_t* dims, uint32_t batch, int hidden_act, float** W,
+                    float** b, const float* x, const void* target, int loss_kind,
+                    float grad_scale, int opt_kind, float lr, float beta1, float beta2, float eps,
+                    float weight_decay, uint32_t step, float** mW, float** vW, float** mb,
+                    float** vb, float** gW_out, float** gb_out, float* out_copy) {
+    std::vector<std::vector<float>> act(nlayers + 1), pre(nlayers);
+    act[0].assign(x, x + (size_t)batch * dims[0]);
+    for (int l = 0; l < nlayers; ++l) {
+        size_t n = (size_t)batch * dims[l + 1];
+        std::vector<float> z(n);
+        act[l + 1].resize(n);
+        pre[l].resize(n);
+        ref_gemm_f32(0, 0, batch, dims[l + 1], dims[l], act[l].data(), W[l], z.data(), 0);
+        int a = (l < nlayers - 1) ? hidden_act : REF_ACT_NONE;
+        ref_bias_act_fwd(batch, dims[l + 1], z.data(), b ? b[l] : nullptr, a, act[l + 1].data(),
+                         pre[l].data());
+    }
+    const uint32_t od = dims[nlayers];
+    size_t on = (size_t)batch * od;
+    if (out_copy) std::memcpy(out_copy, act[nlayers].data(), on * sizeof(float));
+    std::vector<float> dz(on);
+    double loss = 0.0;
+    if (loss_kind == 0) {
+        float s;
+        ref_mse_loss_grad(on, act[nlayers].data(), (const float*)target, grad_scale, nullptr, &s,
+                          dz.data());
+        loss = s;
+    } else {
+        std::vector<float> lrow(batch);
+        float mean;
+        ref_softmax_ce_fwd_bwd(batch, od, act[nlayers].data(), (const uint32_t*)target, grad_scale,
+                               lrow.data(), &mean, dz.data(), nullptr, nullptr);
+        for (uint32_t r = 0; r < batch; ++r) loss += lrow[r];
+    }
+    for (int l = nlayers - 1; l >= 0; --l) {
+        size_t wn = (size_t)dims[l] * dims[l + 1];
+        std::vector<float> gW(wn), gb(dims[l + 1]), dprev;
+        ref_gemm_f32(1, 0, dims[l], dims[l + 1], batch, act[l].data(), dz.data(), gW.data(), 0);
+        ref_colsum(batch, dims[l + 1], dz.data(), gb.data());
+        if (l > 0) {
+            dprev.resize((size_t)batch * dims[l]);
+            ref_gemm_f32(0, 1, batch, dims[l], dims[l + 1], dz.data(), W[l], dprev.data(), 0);
+            const float* saved = hidden_act == REF_ACT_GELU ? pre[l - 1].data() : act[l].data();
+            ref_act_bwd(dprev.size(), hidden_act, dprev.data(), saved, dprev.data(), 0);
+        }
+        if (gW_out && gW_out[l]) std::memcpy(gW_out[l], gW.data(), wn * sizeof(float));
+        if (gb_out && gb_out[l]) std::memcpy(gb_out[l], gb.data(), dims[l + 1] * sizeof(float));
+        if (opt_kind == 0) {
+            ref_sgd_step(wn, W[l], gW.data(), lr, 1.0f, 1);
+            if (b) ref_sgd_step(dims[l + 1], b[l], gb.data(), lr, 1.0f, 1);
+        } else if (opt_kind == 1) {
+            ref_adamw_step(wn, W[l], gW.data(), mW[l], vW[l], lr, beta1, beta2, eps, weight_decay,
+                           step, 1.0f, 1);
+            if (b) ref_adamw_step(dims[l + 1], b[l], gb.data(), mb[l], vb[l], lr, beta1, beta2, eps,
+                                  weight_decay, step, 1.0f, 1);
+        }
+        if (l > 0) dz.swap(dprev);
+    }
+    return loss;
+}
+
+}  // extern "C"

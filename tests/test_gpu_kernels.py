@@ -1,0 +1,401 @@
+"""GPU parity tests: every CUDA entry point, called through the C ABI, against the CPU
+oracle on the same seeded inputs.  Tolerances: 1e-5 for elementwise and softmax work,
+1e-4 for GEMM-bearing results, both as |x - ref| <= tol * (|ref| + rms(ref)); integer
+outputs and the exact SIMT GEMM are compared bit for bit."""
+import numpy as np
+import pytest
+
+from conftest import rel_err_ok
+
+pytestmark = pytest.mark.gpu
+
+TOL_EW = 1e-5
+TOL_GEMM = 1e-4
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from ferrograd_b200 import GpuContext
+    c = GpuContext(0)
+    yield c
+    c.sync()
+    c.destroy()
+
+
+def rng(seed):
+    return np.random.Generator(np.random.Philox(seed))
+
+
+def up(ctx, a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint32:
+        return ctx.init_tensor_u32(a.shape, a)
+    return ctx.init_tensor_f32(a.shape, a)
+
+
+def check(x, ref, tol, what=""):
+    ok, worst = rel_err_ok(x, ref, tol)
+    assert ok, f"{what}: worst error ratio {worst:.3g} x tolerance {tol}"
+
+
+# ---------------------------------------------------------------- optimizers
+def test_sgd_reference_constants(ctx):
+    # crates/ferrograd/tests/optim.rs:10-104
+    f32 = np.float32
+    for wv, gv, expect in ((3.0, 2.0, f32(3.0) - f32(2e-3)), (2.0, 3.0, f32(2.0) - f32(3e-3)),
+                           (1.0, 1.0, f32(1.0) - f32(1e-3))):
+        w, g = up(ctx, np.full(1024, wv, f32)), up(ctx, np.full(1024, gv, f32))
+        ctx.sgd_step(w, g, 1024, float(f32(1e-3)))
+        assert (ctx.to_numpy(w) == expect).all()
+        assert (ctx.to_numpy(g) == 0.0).all()
+
+
+@pytest.mark.parametrize("n", [1, 3, 1000, 4097, 1 << 20])
+def test_sgd_vs_oracle(ctx, oracle, n):
+    r = rng(10 + n)
+    w, g = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+    dw, dg = up(ctx, w), up(ctx, g)
+    ctx.sgd_step(dw, dg, n, 0.1, grad_scale=0.5, zero_grad=False)
+    oracle.sgd(w, g, 0.1, grad_scale=0.5, zero_grad=False)
+    assert np.array_equal(ctx.to_numpy(dw), w)      # same operations, same rounding
+    assert np.array_equal(ctx.to_numpy(dg), g)
+
+
+@pytest.mark.parametrize("n", [5, 4096, (1 << 20) + 3])
+def test_adamw_vs_oracle(ctx, oracle, n):
+    r = rng(20 + n)
+    w = r.standard_normal(n, np.float32)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    dw, dm, dv = up(ctx, w), up(ctx, m), up(ctx, v)
+    hp = (1e-3, 0.9, 0.999, 1e-8, 0.01)
+    for step in (1, 2, 3):
+        g = r.standard_normal(n, np.float32)
+        dg = up(ctx, g)
+        ctx.adamw_step(dw, dg, dm, dv, n, *hp, step=step, grad_scale=0.25)
+        oracle.adamw(w, g, m, v, *hp, step, grad_scale=0.25)
+        assert (ctx.to_numpy(dg) == 0.0).all()
+    check(ctx.to_numpy(dw), w, TOL_EW, "adamw w")
+    check(ctx.to_numpy(dm), m, TOL_EW, "adamw m")
+    check(ctx.to_numpy(dv), v, TOL_EW, "adamw v")
+
+
+def test_adamw_device_step_counter(ctx, oracle):
+    n = 1000
+    r = rng(33)
+    w, g = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+    m, v = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    dw, dg, dm, dv = up(ctx, w), up(ctx, g), up(ctx, m), up(ctx, v)
+    counter = up(ctx, np.array([4], np.uint32))
+    ctx.counter_increment(counter)
+    ctx.adamw_step(dw, dg, dm, dv, n, 1e-3, 0.9, 0.999, 1e-8, 0.0, step=0, step_dev=counter, zero_grad=False)
+    oracle.adamw(w, g, m, v, 1e-3, 0.9, 0.999, 1e-8, 0.0, 5, zero_grad=False)
+    check(ctx.to_numpy(dw), w, TOL_EW, "adamw w (device step)")
+
+
+# ---------------------------------------------------------------- softmax family
+SOFTMAX_SHAPES = [(1, 1), (7, 10), (64, 33), (37, 1000), (5, 4096), (300, 8192), (9, 12345), (40, 32000),
+                  (3, 40000)]
+
+
+@pytest.mark.parametrize("rows,cols", SOFTMAX_SHAPES)
+def test_softmax_fwd_bwd(ctx, oracle, rows, cols):
+    r = rng(rows * 100003 + cols)
+    x = (2.0 * r.standard_normal((rows, cols), np.float32)).astype(np.float32)
+    dx_, dy_ = up(ctx, x), ctx.new_tensor((rows, cols))
+    ctx.softmax_fwd(dx_, dy_, rows, cols)
+    y = ctx.to_numpy(dy_)
+    yref = oracle.softmax_fwd(x)
+    check(y, yref, TOL_EW, "softmax fwd")
+    dy = r.standard_normal((rows, cols), np.float32)
+    ddy, dgrad = up(ctx, dy), ctx.new_tensor((rows, cols))
+    ctx.softmax_bwd(up(ctx, yref), ddy, dgrad, rows, cols)
+    check(ctx.to_numpy(dgrad), oracle.softmax_bwd(yref, dy), TOL_EW, "softmax bwd")
+    # accumulate form (the reference's +=)
+    base = r.standard_normal((rows, cols), np.float32)
+    dacc = up(ctx, base)
+    ctx.softmax_bwd(up(ctx, yref), ddy, dacc, rows, cols, accumulate=True)
+    check(ctx.to_numpy(dacc), oracle.softmax_bwd(yref, dy, dx=base), TOL_EW, "softmax bwd accumulate")
+
+
+@pytest.mark.parametrize("rows,cols", SOFTMAX_SHAPES)
+def test_softmax_ce(ctx, oracle, rows, cols):
+    r = rng(rows * 7919 + cols)
+    x = (2.0 * r.standard_normal((rows, cols), np.float32)).astype(np.float32)
+    labels = r.integers(0, cols, rows).astype(np.uint32)
+    scale = 1.0 / rows
+    ref = oracle.softmax_ce(x, labels, grad_scale=scale, want_probs=True)
+    dlog, probs = ctx.new_tensor((rows, cols)), ctx.new_tensor((rows, cols))
+    lrow, lmean = ctx.new_tensor((rows,)), ctx.new_tensor((1,))
+    am = ctx.new_tensor((rows,), np.uint32)
+    ctx.softmax_ce(up(ctx, x), up(ctx, labels), rows, cols, grad_scale=scale, loss_row=lrow, loss_mean=lmean,
+                   dlogits=dlog, probs=probs, argmax=am)
+    check(ctx.to_numpy(lrow), ref["loss_row"], TOL_EW, "loss_row")
+    check(ctx.to_numpy(lmean), np.array([ref["loss_mean"]], np.float32), TOL_EW, "loss_mean")
+    check(ctx.to_numpy(probs), ref["probs"], TOL_EW, "probs")
+    check(ctx.to_numpy(dlog), ref["dlogits"], TOL_EW, "dlogits")
+    assert np.array_equal(ctx.to_numpy(am), ref["argmax"])          # index output: bit-exact
+    assert ctx.device_status() == 0
+
+
+def test_softmax_ce_argmax_ties_and_minimal_outputs(ctx, oracle):
+    rows, cols = 4, 16384
+    x = np.zeros((rows, cols), np.float32)
+    x[1, 5] = x[1, 9000] = 3.0       # tie: first index wins
+    x[2, cols - 1] = 1.0
+    labels = np.array([0, 5, cols - 1, 7], np.uint32)
+    ref = oracle.softmax_ce(x, labels)
+    am, dlog = ctx.new_tensor((rows,), np.uint32), ctx.new_tensor((rows, cols))
+    ctx.softmax_ce(up(ctx, x), up(ctx, labels), rows, cols, dlogits=dlog, argmax=am)
+    assert np.array_equal(ctx.to_numpy(am), ref["argmax"]) and ctx.to_numpy(am)[1] == 5
+    check(ctx.to_numpy(dlog), ref["dlogits"], TOL_EW, "dlogits")
+
+
+def test_ce_elementwise_reference_form(ctx, oracle):
+    rows, cols = 33, 48
+    r = rng(5)
+    p = oracle.softmax_fwd(r.standard_normal((rows, cols), np.float32))
+    labels = r.integers(0, cols, rows).astype(np.uint32)
+    loss, grad = ctx.new_tensor((rows, cols)), ctx.new_tensor((rows, cols))
+    ctx.ce_loss_grad(up(ctx, p), up(ctx, labels), rows, cols, loss, grad)
+    lref, gref = oracle.ce_loss_grad(p, labels)
+    check(ctx.to_numpy(loss), lref, TOL_EW, "ce loss")
+    assert np.array_equal(ctx.to_numpy(grad), gref)
+
+
+# ---------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("n", [1, 130, 100003])
+def test_mse(ctx, oracle, n):
+    r = rng(40 + n)
+    p, t = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+    loss, grad, s = ctx.new_tensor((n,)), ctx.new_tensor((n,)), ctx.new_tensor((1,))
+    ctx.mse_loss_grad(up(ctx, p), up(ctx, t), n, grad_scale=0.5, loss_elem=loss, loss_sum=s, grad=grad)
+    lref, sref, gref = oracle.mse(p, t, grad_scale=0.5)
+    assert np.array_equal(ctx.to_numpy(loss), lref) and np.array_equal(ctx.to_numpy(grad), gref)
+    check(ctx.to_numpy(s), np.array([sref], np.float32), TOL_EW, "mse sum")
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
+def test_bias_act_and_backward(ctx, oracle, act):
+    rows, cols = 67, 130
+    r = rng(50)
+    z, b = r.standard_normal((rows, cols), np.float32), r.standard_normal(cols, np.float32)
+    y = ctx.new_tensor((rows, cols))
+    ctx.bias_act_fwd(up(ctx, z), up(ctx, b), act, y, rows, cols)
+    yref, pre = oracle.bias_act_fwd(z, b, act)
+    check(ctx.to_numpy(y), yref, TOL_EW, f"bias+{act}")
+    dy = r.standard_normal((rows, cols), np.float32)
+    saved = pre if act == "gelu" else yref
+    dz = ctx.new_tensor((rows, cols))
+    ctx.act_bwd(up(ctx, dy), up(ctx, saved), dz, rows * cols, act)
+    check(ctx.to_numpy(dz), oracle.act_bwd(dy, saved, act), TOL_EW, f"{act} backward")
+
+
+def test_chain_mul_add_reference_constants(ctx):
+    # crates/ferrograd/tests/std_wgsl.rs:10-94: out = c + a*b.
+    n = 32 * 32
+    a, b, c = (up(ctx, np.full(n, v, np.float32)) for v in (3.0, 2.0, 1.0))
+    prog = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("input", 2, 0, 0.0), ("mul", 0, 1, 0.0), ("add", 2, 3, 0.0)]
+    out = ctx.new_tensor((n,))
+    ctx.eltwise_chain_fwd(prog, [a, b, c], out, n)
+    assert (ctx.to_numpy(out) == 7.0).all()
+    grads = [ctx.new_tensor((n,)) for _ in range(3)]
+    ctx.eltwise_chain_bwd(prog, [a, b, c], up(ctx, np.ones(n, np.float32)), grads, n)
+    assert [float(ctx.to_numpy(g)[0]) for g in grads] == [2.0, 3.0, 1.0]
+    assert all((ctx.to_numpy(g) == ctx.to_numpy(g)[0]).all() for g in grads)
+
+
+def test_chain_all_ops_vs_oracle(ctx, oracle):
+    n = 5000
+    r = rng(60)
+    x0 = r.standard_normal(n, np.float32)
+    x1 = (np.abs(r.standard_normal(n, np.float32)) + 0.5).astype(np.float32)
+    prog = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("const", 0, 0, 1.5), ("mul", 0, 1, 0.0),
+            ("div", 3, 1, 0.0), ("sub", 4, 2, 0.0), ("tanh", 5, 0, 0.0), ("gelu", 0, 0, 0.0), ("add", 6, 7, 0.0),
+            ("log", 1, 0, 0.0), ("exp", 6, 0, 0.0), ("mul", 9, 10, 0.0), ("neg", 11, 0, 0.0), ("abs", 0, 0, 0.0),
+            ("relu", 5, 0, 0.0), ("elu", 0, 0, 0.0), ("add", 12, 13, 0.0), ("add", 14, 15, 0.0),
+            ("add", 16, 17, 0.0), ("add", 18, 8, 0.0)]
+    out = ctx.new_tensor((n,))
+    sv = ctx.new_tensor((n,))
+    ctx.eltwise_chain_fwd(prog, [up(ctx, x0), up(ctx, x1)], out, n, saved={6: sv})
+    oref, saved = oracle.eltwise_fwd(prog, [x0, x1], save=(6,))
+    check(ctx.to_numpy(out), oref, TOL_EW, "chain fwd")
+    check(ctx.to_numpy(sv), saved[6], TOL_EW, "chain saved value")
+    seed = r.standard_normal(n, np.float32)
+    grads = [ctx.new_tensor((n,)) for _ in range(2)]
+    ctx.eltwise_chain_bwd(prog, [up(ctx, x0), up(ctx, x1)], up(ctx, seed), grads, n)
+    gref = oracle.eltwise_bwd(prog, [x0, x1], seed)
+    for g, gr in zip(grads, gref):
+        check(ctx.to_numpy(g), gr, TOL_EW, "chain bwd")
+
+
+# ---------------------------------------------------------------- GEMM
+GEMM_SHAPES = [(32, 64, 16), (1, 1, 1), (64, 2, 16), (70, 33, 45), (130, 257, 100), (256, 512, 384)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("tA,tB", [(False, False), (True, False), (False, True), (True, True)])
+def test_gemm_simt_bit_exact(ctx, oracle, M, N, K, tA, tB):
+    r = rng(M * 31 + N * 17 + K)
+    A = r.standard_normal((K, M) if tA else (M, K), np.float32)
+    B = r.standard_normal((N, K) if tB else (K, N), np.float32)
+    Cd = ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, transA=tA, transB=tB, mode="simt")
+    assert np.array_equal(ctx.to_numpy(Cd), oracle.gemm(A, B, transA=tA, transB=tB))
+
+
+TC_SHAPES = [(128, 256, 32), (128, 128, 64), (256, 512, 384), (200, 72, 100), (130, 10, 257), (1000, 300, 77),
+             (64, 48, 8), (384, 1024, 1000)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_gemm_3xtf32_vs_oracle(ctx, oracle, M, N, K):
+    r = rng(M * 131 + N * 71 + K)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
+    Cd = ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, mode="3xtf32")
+    got = ctx.to_numpy(Cd)
+    assert ctx.device_status() == 0
+    check(got, oracle.gemm(A, B), TOL_GEMM, "3xTF32 vs f32 fma chain")
+    check(got, oracle.gemm(A, B, f64=True), TOL_GEMM, "3xTF32 vs f64 accumulate")
+
+
+@pytest.mark.parametrize("tA,tB", [(True, False), (False, True), (True, True)])
+def test_gemm_3xtf32_transposes(ctx, oracle, tA, tB):
+    M, N, K = 192, 320, 200
+    r = rng(77)
+    A = r.standard_normal((K, M) if tA else (M, K), np.float32)
+    B = r.standard_normal((N, K) if tB else (K, N), np.float32)
+    Cd = ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, transA=tA, transB=tB, mode="3xtf32")
+    check(ctx.to_numpy(Cd), oracle.gemm(A, B, transA=tA, transB=tB), TOL_GEMM, "3xTF32 transposed")
+
+
+@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
+def test_gemm_epilogue(ctx, oracle, mode, act):
+    M, N, K = 256, 264, 96
+    r = rng(88)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32) * 0.2
+    bias = r.standard_normal(N, np.float32)
+    Cd, Pd = ctx.new_tensor((M, N)), ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, bias=up(ctx, bias), act=act, preact_out=Pd, mode=mode)
+    yref, pre = oracle.bias_act_fwd(oracle.gemm(A, B), bias, act)
+    check(ctx.to_numpy(Pd), pre, TOL_GEMM, "pre-activation")
+    got = ctx.to_numpy(Cd)
+    if act == "relu":
+        # the mask is an index-like output: wherever the reference is clearly non-zero it must agree
+        clear = np.abs(pre) > 1e-3
+        assert np.array_equal((got > 0)[clear], (yref > 0)[clear])
+    check(got, yref, TOL_GEMM, f"epilogue {act}")
+
+
+@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
+def test_gemm_backward(ctx, oracle, mode, act):
+    M, N, K = 192, 136, 160
+    r = rng(99)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32) * 0.2
+    bias = r.standard_normal(N, np.float32) * 0.1
+    y, pre = oracle.bias_act_fwd(oracle.gemm(A, B), bias, act)
+    saved = pre if act == "gelu" else y
+    dY = r.standard_normal((M, N), np.float32)
+    dA, dB, db, dZ = ctx.new_tensor((M, K)), ctx.new_tensor((K, N)), ctx.new_tensor((N,)), ctx.new_tensor((M, N))
+    ctx.gemm_bwd(up(ctx, A), up(ctx, B), up(ctx, dY), M, N, K, act=act, saved=up(ctx, saved), dA=dA, dB=dB,
+                 dbias=db, dZ_out=dZ, mode=mode)
+    dz_ref = oracle.act_bwd(dY, saved, act)
+    check(ctx.to_numpy(dZ), dz_ref, TOL_EW, "dZ")
+    check(ctx.to_numpy(dA), oracle.gemm(dz_ref, B, transB=True), TOL_GEMM, "dA")
+    check(ctx.to_numpy(dB), oracle.gemm(A, dz_ref, transA=True), TOL_GEMM, "dB")
+    check(ctx.to_numpy(db), oracle.colsum(dz_ref), TOL_GEMM, "dbias")
+    assert ctx.device_status() == 0
+    # partial requests
+    dA2 = ctx.new_tensor((M, K))
+    ctx.gemm_bwd(None, up(ctx, B), up(ctx, dY), M, N, K, act=act, saved=up(ctx, saved), dA=dA2, mode=mode)
+    check(ctx.to_numpy(dA2), oracle.gemm(dz_ref, B, transB=True), TOL_GEMM, "dA only")
+
+
+@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+def test_reference_matmul_known_answers(ctx, mode):
+    # crates/ferrograd/tests/std_wgsl.rs:268-373 (matmul_add) and :376-520 (matmul_chain3): constant
+    # inputs, closed-form results, compared with ==.  Small integers are exact in TF32 too.
+    def full(shape, v):
+        return up(ctx, np.full(shape, v, np.float32))
+
+    M, N, K = 32, 64, 16
+    A, B = full((M, K), 3.0), full((K, N), 2.0)
+    bias_full = np.full((M, N), 1.0, np.float32)
+    X = ctx.new_tensor((M, N))
+    ctx.gemm(A, B, X, M, N, K, mode=mode)
+    assert (ctx.to_numpy(X) + bias_full == 97.0).all()
+    dA, dB = ctx.new_tensor((M, K)), ctx.new_tensor((K, N))
+    ctx.gemm_bwd(A, B, full((M, N), 1.0), M, N, K, dA=dA, dB=dB, mode=mode)
+    assert (ctx.to_numpy(dA) == 128.0).all() and (ctx.to_numpy(dB) == 96.0).all()
+
+    M, N, K, H = 32, 64, 128, 256
+    A, B, Cc, D = full((M, K), 3.0), full((K, N), 2.0), full((H, M), 1.0), full((N, H), 0.5)
+    X, Y, Z = ctx.new_tensor((M, N)), ctx.new_tensor((H, N)), ctx.new_tensor((H, H))
+    ctx.gemm(A, B, X, M, N, K, mode=mode)
+    ctx.gemm(Cc, X, Y, H, N, M, mode=mode)
+    ctx.gemm(Y, D, Z, H, H, N, mode=mode)
+    assert (ctx.to_numpy(X) == 768.0).all() and (ctx.to_numpy(Y) == 24576.0).all()
+    assert (ctx.to_numpy(Z) == 786432.0).all()
+    dY, dD = ctx.new_tensor((H, N)), ctx.new_tensor((N, H))
+    ctx.gemm_bwd(Y, D, full((H, H), 1.0), H, H, N, dA=dY, dB=dD, mode=mode)
+    dC, dX = ctx.new_tensor((H, M)), ctx.new_tensor((M, N))
+    ctx.gemm_bwd(Cc, X, dY, H, N, M, dA=dC, dB=dX, mode=mode)
+    dA, dB = ctx.new_tensor((M, K)), ctx.new_tensor((K, N))
+    ctx.gemm_bwd(A, B, dX, M, N, K, dA=dA, dB=dB, mode=mode)
+    y_grad, x_grad = 0.5 * H, 0.5 * H * H
+    assert (ctx.to_numpy(dA) == x_grad * 2.0 * N).all() and (ctx.to_numpy(dB) == 3.0 * x_grad * M).all()
+    assert (ctx.to_numpy(dC) == y_grad * 768.0 * N).all() and (ctx.to_numpy(dD) == 24576.0 * H).all()
+
+
+def test_reference_softmax_known_answers(ctx):
+    # std_wgsl.rs:97-187: softmax(C - A@B) = 1/64 exactly, gradients 0.
+    A, B = up(ctx, np.full((16, 32), 3.0, np.float32)), up(ctx, np.full((32, 64), 2.0, np.float32))
+    X = ctx.new_tensor((16, 64))
+    ctx.gemm(A, B, X, 16, 64, 32, mode="simt")
+    prog = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("sub", 0, 1, 0.0)]
+    Q = ctx.new_tensor((16, 64))
+    ctx.eltwise_chain_fwd(prog, [up(ctx, np.ones((16, 64), np.float32)), X], Q, 16 * 64)
+    Y = ctx.new_tensor((16, 64))
+    ctx.softmax_fwd(Q, Y, 16, 64)
+    assert (ctx.to_numpy(Y) == np.float32(1.0) / np.float32(64.0)).all()
+    dQ = ctx.new_tensor((16, 64), zeroed=True)
+    ctx.softmax_bwd(Y, up(ctx, np.ones((16, 64), np.float32)), dQ, 16, 64, accumulate=True)
+    assert (ctx.to_numpy(dQ) == 0.0).all()
+
+
+# ---------------------------------------------------------------- boundary behaviour
+def test_invalid_arguments_are_rejected(ctx):
+    from ferrograd_b200 import FgError
+    t = ctx.new_tensor((16,))
+    with pytest.raises(FgError) as e:
+        ctx.gemm(t, t, t, 0, 4, 4)
+    assert e.value.kind == "FG_ERR_INVALID_ARGUMENT"
+    with pytest.raises(FgError):
+        ctx.sgd_step(t.ptr + 4, t, 3, 0.1)            # misaligned pointer
+    with pytest.raises(FgError):
+        ctx.upload(t, np.zeros(17, np.float32))        # larger than the buffer
+    with pytest.raises(FgError):
+        ctx.eltwise_chain_fwd([("add", 0, 1, 0.0)], [t], t, 16)   # operands name later values
+    ctx.sync()
+
+
+def test_plan_capture_and_replay(ctx, oracle):
+    n = 4096
+    r = rng(123)
+    w, g = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+    dw, dg = up(ctx, w), up(ctx, g)
+    before = ctx.launch_count()
+    ctx.plan_begin()
+    ctx.sgd_step(dw, dg, n, 0.01, zero_grad=False)
+    plan = ctx.plan_end()
+    assert ctx.launch_count() == before                # recorded, not executed
+    for _ in range(3):
+        plan.launch()
+        oracle.sgd(w, g, 0.01, zero_grad=False)
+    ctx.sync()
+    assert ctx.launch_count() == before + 3
+    assert np.array_equal(ctx.to_numpy(dw), w)
+    plan.destroy()
