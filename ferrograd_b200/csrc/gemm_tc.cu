@@ -51,14 +51,25 @@ struct TileCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators (ping-pong)
+    static constexpr int kColsPerThread = BN / 2;                 // each lane quarter is shared by two warps
 };
 
+constexpr int kThreads = 320;      // warp 0: loads, warp 1: MMA issue, warps 2..9: accumulate + epilogue
+constexpr int kChunkKB = 8;        // k-blocks per accumulation chunk (256 values of k)
+
+// The tensor core adds into its f32 accumulator with truncation, so a long chain of
+// tcgen05.mma drifts linearly with K (measured: 1.9e-4 relative at K = 8192).  The K loop is
+// therefore cut into chunks of kChunkKB k-blocks.  Each chunk accumulates in one of two
+// tensor-memory accumulators, starting from zero; when it completes, the eight epilogue
+// warps read it back and add it, rounding to nearest, to running sums held in registers
+// while the tensor core is already working on the next chunk in the other accumulator.
 template <int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epilogue ep) {
     using Cfg = TileCfg<BN>;
     constexpr int S = Cfg::kStages;
+    constexpr int CPT = Cfg::kColsPerThread;
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle (descriptor base offset 0).
     const uint32_t raw = smem_u32(smem_raw);
@@ -68,19 +79,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t bar0 = base + S * Cfg::kStageBytes;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
-    const uint32_t tmem_full_bar = bar0 + 8u * (2 * S);
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 1);
+    auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
+    auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const uint32_t nkb = (ep.K + BK - 1) / BK;
+    const uint32_t nchunks = (nkb + kChunkKB - 1) / kChunkKB;
 
     // A wait that expired earlier (this launch or a previous one) makes every CTA leave at once.
-    if (*reinterpret_cast<volatile int*>(ep.dev_status) != 0) return;
+    // One thread reads the word so that the whole CTA takes the same branch.
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int*>(ep.dev_status);
+    __syncthreads();
+    if (s_abort != 0) return;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(tmem_full_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
         fence_mbar_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
@@ -115,75 +132,113 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // ---- MMA issuer ----
             constexpr uint32_t idesc = make_idesc(2u /*tf32*/, BM, BN < 16 ? 16 : BN);
             bool ok = true;
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1u;
-                if (!mbar_wait_bounded(full_bar(s), ph, kWaitCycles)) {
+            for (uint32_t c = 0; c < nchunks && ok; ++c) {
+                const uint32_t buf = c & 1u;
+                // the accumulator must have been drained by the epilogue warps (two chunks ago)
+                if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1u) ^ 1u, kWaitCycles)) {
                     atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
-                    ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t sa = base + s * Cfg::kStageBytes;
-                const uint64_t a_hi = make_desc_sw128(sa);
-                const uint64_t a_lo = make_desc_sw128(sa + BM * BK * 4);
-                const uint64_t b_hi = make_desc_sw128(sa + Cfg::kABytes);
-                const uint64_t b_lo = make_desc_sw128(sa + Cfg::kABytes + BN * BK * 4);
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t kb_end = min(nkb, (c + 1) * kChunkKB);
+                for (uint32_t kb = c * kChunkKB; kb < kb_end; ++kb) {
+                    const int s = kb % S;
+                    const uint32_t ph = (kb / S) & 1u;
+                    if (!mbar_wait_bounded(full_bar(s), ph, kWaitCycles)) {
+                        atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * Cfg::kStageBytes;
+                    const uint64_t a_hi = make_desc_sw128(sa);
+                    const uint64_t a_lo = make_desc_sw128(sa + BM * BK * 4);
+                    const uint64_t b_hi = make_desc_sw128(sa + Cfg::kABytes);
+                    const uint64_t b_lo = make_desc_sw128(sa + Cfg::kABytes + BN * BK * 4);
+                    const uint32_t first = (kb == c * kChunkKB) ? 0u : 1u;   // a chunk starts from zero
 #pragma unroll
-                for (int kk = 0; kk < BK / UK; ++kk) {
-                    // advance along K inside the swizzled row: +32 bytes, i.e. +2 in the address field
-                    const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
-                    mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb | (uint32_t)kk) != 0u);
-                    mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-                    mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+                    for (int kk = 0; kk < BK / UK; ++kk) {
+                        // advance along K inside the swizzled row: +32 bytes, i.e. +2 in the address field
+                        const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                        mma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first | (uint32_t)kk);
+                        mma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                        mma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                    }
+                    mma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
                 }
-                mma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
+                if (ok) mma_commit(acc_full_bar(buf));   // this chunk's accumulator is complete
             }
-            mma_commit(tmem_full_bar);      // accumulators complete
         }
     } else {
-        // ---- epilogue: warps 2..5; warp w may touch TMEM lanes 32*(w%4) .. +31 ----
+        // ---- accumulate + epilogue: warps 2..9.  Warp w may touch TMEM lanes 32*(w%4) .. +31;
+        //      warps 2..5 take the first half of the tile's columns, warps 6..9 the second. ----
         const int q = warp & 3;
-        bool ok = mbar_wait_bounded(tmem_full_bar, 0u, kWaitCycles + kWaitCycles / 2);
-        if (!ok && lane == 0) atomicOr(ep.dev_status, FG_DEVERR_EPI_WAIT);
-        ok = __all_sync(0xffffffffu, ok) && (*reinterpret_cast<volatile int*>(ep.dev_status) == 0);
-        tc_fence_after();
-        if (ok) {
+        const int half = (warp - 2) >> 2;
+        float sum[CPT];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
+        bool ok = true;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t buf = c & 1u;
+            bool got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1u, kWaitCycles + kWaitCycles / 2);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+                if (lane == 0) atomicOr(ep.dev_status, FG_DEVERR_EPI_WAIT);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * CPT;
+            if constexpr (CPT >= 32) {
+#pragma unroll
+                for (int g = 0; g < CPT / 32; ++g) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t0 + g * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sum[g * 32 + j] += __uint_as_float(r[j]);
+                }
+            } else {
+                uint32_t r[16];
+                tmem_ld_32x16(t0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sum[j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+        }
+        if (ok && *reinterpret_cast<volatile int*>(ep.dev_status) == 0) {
             const uint32_t row = m0 + q * 32 + lane;
-            const bool row_ok = row < ep.M;
+            const uint32_t cbase = n0 + half * CPT;
             const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
                                 (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
-            float* crow = ep.C + (size_t)row * ep.N;
-            float* prow = ep.preact ? ep.preact + (size_t)row * ep.N : nullptr;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= ep.N) break;     // uniform across the warp
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                tmem_ld_wait();
-                if (row_ok) {
+            if (row < ep.M) {
+                float* crow = ep.C + (size_t)row * ep.N;
+                float* prow = ep.preact ? ep.preact + (size_t)row * ep.N : nullptr;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const uint32_t col = n0 + c0 + j;
-                        float z[4];
+                for (int j = 0; j < CPT; j += 4) {
+                    const uint32_t col = cbase + j;
+                    if (col >= ep.N) break;
+                    float z[4];
 #pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            z[t] = __uint_as_float(r[j + t]);
-                            if (ep.bias && col + t < ep.N) z[t] += ep.bias[col + t];
-                        }
-                        if (vec_ok && col + 3 < ep.N) {
-                            if (prow) *reinterpret_cast<float4*>(prow + col) = make_float4(z[0], z[1], z[2], z[3]);
-                            *reinterpret_cast<float4*>(crow + col) =
-                                make_float4(fg_act_fwd(ep.act, z[0]), fg_act_fwd(ep.act, z[1]),
-                                            fg_act_fwd(ep.act, z[2]), fg_act_fwd(ep.act, z[3]));
-                        } else {
+                    for (int t = 0; t < 4; ++t) {
+                        z[t] = sum[j + t];
+                        if (ep.bias && col + t < ep.N) z[t] += ep.bias[col + t];
+                    }
+                    if (vec_ok && col + 3 < ep.N) {
+                        if (prow) *reinterpret_cast<float4*>(prow + col) = make_float4(z[0], z[1], z[2], z[3]);
+                        *reinterpret_cast<float4*>(crow + col) =
+                            make_float4(fg_act_fwd(ep.act, z[0]), fg_act_fwd(ep.act, z[1]),
+                                        fg_act_fwd(ep.act, z[2]), fg_act_fwd(ep.act, z[3]));
+                    } else {
 #pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (col + t < ep.N) {
-                                    if (prow) prow[col + t] = z[t];
-                                    crow[col + t] = fg_act_fwd(ep.act, z[t]);
-                                }
-                        }
+                        for (int t = 0; t < 4; ++t)
+                            if (col + t < ep.N) {
+                                if (prow) prow[col + t] = z[t];
+                                crow[col + t] = fg_act_fwd(ep.act, z[t]);
+                            }
                     }
                 }
             }
@@ -301,7 +356,7 @@ int32_t launch_tc(fg_ctx* ctx, const float* a_planes, uint32_t lda, const float*
     }
     dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: M too large");
-    gemm_tc_kernel<BN><<<grid, 192, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, ep);
+    gemm_tc_kernel<BN><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, ep);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

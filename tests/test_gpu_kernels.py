@@ -244,7 +244,7 @@ def test_gemm_simt_bit_exact(ctx, oracle, M, N, K, tA, tB):
 
 
 TC_SHAPES = [(128, 256, 32), (128, 128, 64), (256, 512, 384), (200, 72, 100), (130, 10, 257), (1000, 300, 77),
-             (64, 48, 8), (384, 1024, 1000)]
+             (64, 48, 8), (384, 1024, 1000), (128, 256, 8192), (256, 130, 4100)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
