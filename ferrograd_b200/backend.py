@@ -15,6 +15,7 @@ from . import _lib
 
 ACT = {"none": 0, None: 0, "relu": 1, "tanh": 2, "gelu": 3}
 GEMM_MODE = {"auto": 0, "simt": 1, "3xtf32": 2}
+KERNEL_KIND = {"gemm_tc": 0, "softmax_ce": 1, "adamw": 2, "sgd": 3, "split": 4}
 EW = {"input": 0, "const": 1, "add": 2, "sub": 3, "mul": 4, "div": 5, "neg": 6, "abs": 7,
       "exp": 8, "log": 9, "tanh": 10, "relu": 11, "gelu": 12, "elu": 13}
 
@@ -193,6 +194,16 @@ class GpuContext:
         w = C.c_int32()
         self._check(self.lib.fg_ctx_device_status(self.handle, C.byref(w)))
         return w.value
+
+    def timing_enable(self, on=True):
+        self._check(self.lib.fg_ctx_timing_enable(self.handle, int(on)))
+
+    def timing_read(self, kind):
+        """(launches, total_ms, total_work) of one kernel kind since the last read."""
+        n, ms, work = C.c_uint64(), C.c_double(), C.c_double()
+        self._check(self.lib.fg_ctx_timing_read(self.handle, KERNEL_KIND[kind], C.byref(n), C.byref(ms),
+                                                C.byref(work)))
+        return n.value, ms.value, work.value
 
     def memset_zero(self, t, nbytes=None):
         nb = nbytes if nbytes is not None else t.size * t.dtype.itemsize

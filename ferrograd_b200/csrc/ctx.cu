@@ -112,6 +112,10 @@ int32_t fg_ctx_destroy(fg_ctx* ctx) {
     fg_comm_destroy(ctx);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->time_recs) {
+        for (int i = 0; i < ctx->time_created; ++i) { cudaEventDestroy(ctx->time_recs[i].a); cudaEventDestroy(ctx->time_recs[i].b); }
+        delete[] ctx->time_recs;
+    }
     cudaEventDestroy(ctx->ev_fork);
     cudaEventDestroy(ctx->ev_join);
     cudaStreamDestroy(ctx->comm_stream);
@@ -160,6 +164,49 @@ void* fg_ctx_stream(fg_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 int32_t fg_ctx_device(fg_ctx* ctx) { return ctx ? ctx->device : -1; }
 uint64_t fg_ctx_launch_count(fg_ctx* ctx) { return ctx ? ctx->launches : 0; }
 uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx) { return ctx ? ctx->ws_bytes : 0; }
+
+int32_t fg_ctx_timing_enable(fg_ctx* ctx, int32_t on) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "timing cannot change while a plan is recorded");
+    if (on && !ctx->time_recs) {
+        ctx->time_recs = new (std::nothrow) fg_time_rec[FG_TIME_MAX_RECS];
+        if (!ctx->time_recs) return fg_fail(ctx, FG_ERR_OUT_OF_MEMORY, "timing records");
+        ctx->time_count = ctx->time_created = 0;
+    }
+    ctx->timing_on = on != 0;
+    return FG_OK;
+}
+
+int32_t fg_ctx_timing_read(fg_ctx* ctx, int32_t kind, uint64_t* launches, double* total_ms, double* total_work) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, launches && total_ms && total_work, "fg_ctx_timing_read: NULL output");
+    *launches = 0; *total_ms = 0.0; *total_work = 0.0;
+    if (!ctx->time_recs) return FG_OK;
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->stream));
+    // Sum and drop the records of this kind; keep the others (and their events) packed at the front.
+    int keep = 0;
+    for (int i = 0; i < ctx->time_count; ++i) {
+        fg_time_rec r = ctx->time_recs[i];
+        if (r.kind == kind) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+                *launches += 1; *total_ms += ms; *total_work += r.work;
+            }
+            // recycle the events: swap this slot to the end of the used range later
+            ctx->time_recs[i].kind = -1;
+        }
+    }
+    // compact: stable partition so used records stay in front; events of dropped records are reused
+    for (int i = 0; i < ctx->time_count; ++i) {
+        if (ctx->time_recs[i].kind != -1) {
+            if (i != keep) { fg_time_rec t = ctx->time_recs[keep]; ctx->time_recs[keep] = ctx->time_recs[i]; ctx->time_recs[i] = t; }
+            keep++;
+        }
+    }
+    ctx->time_count = keep;
+    return FG_OK;
+}
 
 int32_t fg_ctx_reserve_workspace(fg_ctx* ctx, uint64_t bytes) {
     FG_ENTER(ctx);

@@ -23,6 +23,14 @@ struct fg_plan {
     uint64_t launches;  // kernels recorded in the graph
 };
 
+// One timed launch: events on the launching stream around a single kernel.
+struct fg_time_rec {
+    cudaEvent_t a, b;
+    int kind;
+    double work;   // flop for GEMMs, bytes for bandwidth-bound kernels
+};
+#define FG_TIME_MAX_RECS 8192
+
 struct fg_ctx {
     int device;
     cudaStream_t stream;
@@ -41,6 +49,11 @@ struct fg_ctx {
     int* dev_status;            // device error word (see FG_DEVERR_*)
     void* tmap_encode;          // cuTensorMapEncodeTiled, resolved at context creation
     int sm_count;
+    // Optional per-kernel timing (eager mode only)
+    bool timing_on;
+    fg_time_rec* time_recs;
+    int time_count;       // records in use
+    int time_created;     // records whose events exist
     // NCCL (loaded at run time)
     void* nccl_lib;
     void* comm;
@@ -77,6 +90,24 @@ inline int32_t fg_fail_cuda(fg_ctx* ctx, int32_t code, const char* what, cudaErr
     do { cudaError_t _e = cudaGetLastError(); \
          if (_e != cudaSuccess) return fg_fail_cuda((ctx), FG_ERR_LAUNCH_FAILURE, "kernel launch", _e); \
          if ((ctx)->capturing) (ctx)->capture_launches++; else (ctx)->launches++; } while (0)
+
+// Brackets one kernel launch with events when timing is enabled (never while capturing).
+inline fg_time_rec* fg_time_begin(fg_ctx* ctx, int kind, double work) {
+    if (!ctx->timing_on || ctx->capturing || !ctx->time_recs || ctx->time_count >= FG_TIME_MAX_RECS) return nullptr;
+    fg_time_rec* r = &ctx->time_recs[ctx->time_count];
+    if (ctx->time_count >= ctx->time_created) {
+        if (cudaEventCreate(&r->a) != cudaSuccess || cudaEventCreate(&r->b) != cudaSuccess) return nullptr;
+        ctx->time_created = ctx->time_count + 1;
+    }
+    r->kind = kind;
+    r->work = work;
+    cudaEventRecord(r->a, ctx->stream);
+    ctx->time_count++;
+    return r;
+}
+inline void fg_time_end(fg_ctx* ctx, fg_time_rec* r) {
+    if (r) cudaEventRecord(r->b, ctx->stream);
+}
 
 inline bool fg_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

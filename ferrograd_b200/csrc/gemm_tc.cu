@@ -312,7 +312,11 @@ inline uint64_t planes_bytes(uint32_t rows, uint32_t contraction) { return 2ull 
 int32_t launch_split(fg_ctx* ctx, const SplitArgs& a) {
     dim3 grid((a.C + 31) / 32, (a.R + 31) / 32), block(32, 8);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM operand has too many rows");
+    double bytes = 4.0 * a.R * a.C * (1.0 + (a.saved ? 1.0 : 0.0) + (a.value_out ? 1.0 : 0.0) +
+                                      (a.planes_n ? 2.0 : 0.0) + (a.planes_t ? 2.0 : 0.0));
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SPLIT, bytes);
     split_kernel<<<grid, block, 0, ctx->stream>>>(a);
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
@@ -356,7 +360,9 @@ int32_t launch_tc(fg_ctx* ctx, const float* a_planes, uint32_t lda, const float*
     }
     dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: M too large");
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
     gemm_tc_kernel<BN><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, ep);
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

@@ -101,8 +101,10 @@ int32_t fg_sgd_step(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr, float
     FG_REQUIRE(ctx, fg_aligned16(w) && fg_aligned16(g), "fg_sgd_step: pointers must be 16-byte aligned");
     if (n == 0) return FG_OK;
     int grid = fg_stream_grid(ctx, (n + 3) / 4, 256, 8);
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SGD, (zero_grad ? 16.0 : 12.0) * n);
     if (zero_grad) sgd_kernel<true><<<grid, 256, 0, ctx->stream>>>(w, g, n, lr, grad_scale);
     else sgd_kernel<false><<<grid, 256, 0, ctx->stream>>>(w, g, n, lr, grad_scale);
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
@@ -120,8 +122,10 @@ int32_t fg_adamw_step(fg_ctx* ctx, float* w, float* g, float* m, float* v, uint6
     if (n == 0) return FG_OK;
     AdamConsts c{h->lr, h->beta1, h->beta2, h->eps, h->weight_decay, grad_scale};
     int grid = fg_stream_grid(ctx, (n + 3) / 4, 256, 8);
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_ADAMW, (zero_grad ? 32.0 : 28.0) * n);
     if (zero_grad) adamw_kernel<true><<<grid, 256, 0, ctx->stream>>>(w, g, m, v, n, c, step, step_dev);
     else adamw_kernel<false><<<grid, 256, 0, ctx->stream>>>(w, g, m, v, n, c, step, step_dev);
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

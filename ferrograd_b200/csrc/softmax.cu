@@ -388,6 +388,12 @@ __global__ void mean_kernel(const float* __restrict__ x, uint32_t n, float* __re
     if (threadIdx.x == 0) *out = s / (float)n;
 }
 
+// Algorithmic HBM bytes of the fused CE kernel: logits in, dlogits (and probs) out.
+double ce_bytes(const CeArgs& a) {
+    double mat = 4.0 * a.rows * a.cols;
+    return mat * (1.0 + (a.dlogits ? 1.0 : 0.0) + (a.probs ? 1.0 : 0.0)) + 8.0 * a.rows;
+}
+
 int pick_threads(uint32_t cols) {
     if (cols <= 128) return 32;
     if (cols <= 2048) return 128;
@@ -409,15 +415,19 @@ int32_t launch_rows(fg_ctx* ctx, const CeArgs& a) {
             attr_done |= 1ull << (ctx->device & 63);
         }
         int grid = (int)(a.rows < (uint32_t)ctx->sm_count ? a.rows : (uint32_t)ctx->sm_count);
+        fg_time_rec* tr = MODE == 1 ? fg_time_begin(ctx, FG_KERNEL_SOFTMAX_CE, ce_bytes(a)) : nullptr;
         softmax_rowreg_kernel<MODE><<<grid, kRowT, smem, ctx->stream>>>(a, ctx->dev_status);
+        fg_time_end(ctx, tr);
         FG_LAUNCHED(ctx);
         return FG_OK;
     }
     int threads = pick_threads(a.cols);
     uint64_t cap = (uint64_t)ctx->sm_count * (2048 / threads);
     int grid = (int)(a.rows < cap ? a.rows : cap);
+    fg_time_rec* tr = MODE == 1 ? fg_time_begin(ctx, FG_KERNEL_SOFTMAX_CE, ce_bytes(a)) : nullptr;
     if (vec) softmax_stream_kernel<MODE, true><<<grid, threads, 0, ctx->stream>>>(a);
     else softmax_stream_kernel<MODE, false><<<grid, threads, 0, ctx->stream>>>(a);
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

@@ -1,0 +1,207 @@
+"""Data-parallel MLP training on the C ABI: forward -> loss -> backward -> gradient
+exchange -> update, the order of the reference's training loop
+(crates/ferrograd/examples/save_load_model.rs:148-156: dispatch_forward, dispatch_loss,
+dispatch_backward, dispatch_optim).
+
+Buffer roles follow the reference's `AllocTensors` (crates/fused_gpu/src/dispatch/mod.rs:835-845):
+`act[l]` / `pre[l]` are the forward_saved tensors (a matmul output is always saved,
+op/matmul/mod.rs:191-202; GELU additionally needs its pre-activation), `grads` the
+grad_tensors, `dact` the seed (dL/dout) and the intermediate gradients, `loss_row` /
+`loss_sum` the loss tensor.  Unlike the reference, all parameters live in ONE flat arena
+(W0, b0, W1, b1, ...), with gradients and optimizer moments in arenas of the same layout,
+so the update is a single fused pass and each layer's gradient is one contiguous range
+for the allreduce.
+"""
+import numpy as np
+
+from .backend import GpuContext
+
+
+def _align(n, a=64):
+    return (n + a - 1) // a * a
+
+
+class MLPTrainer:
+    def __init__(self, ctx: GpuContext, dims, batch, hidden_act="gelu", loss="ce",
+                 optimizer=("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01), grad_scale=None, world=1, rank=0,
+                 gemm_mode="auto", overlap_comm=True):
+        self.ctx = ctx
+        self.dims = [int(d) for d in dims]
+        self.L = len(self.dims) - 1
+        self.batch = int(batch)
+        self.act = hidden_act
+        self.loss_kind = loss
+        self.opt = optimizer
+        self.world, self.rank = int(world), int(rank)
+        self.mode = gemm_mode
+        self.overlap = overlap_comm
+        od = self.dims[-1]
+        if grad_scale is None:
+            # mean loss over the GLOBAL batch (and over output elements for MSE)
+            grad_scale = 1.0 / (self.batch * self.world * (od if loss == "mse" else 1))
+        self.grad_scale = float(grad_scale)
+
+        # ---- flat parameter arena: [W0 | b0 | W1 | b1 | ...], every tensor 256-byte aligned ----
+        self.w_off, self.b_off = [], []
+        off = 0
+        for l in range(self.L):
+            self.w_off.append(off)
+            off = _align(off + self.dims[l] * self.dims[l + 1])
+            self.b_off.append(off)
+            off = _align(off + self.dims[l + 1])
+        self.n_arena = off
+        self.layer_range = [(self.w_off[l], (self.w_off[l + 1] if l + 1 < self.L else off)) for l in range(self.L)]
+        self.n_params = sum(self.dims[l] * self.dims[l + 1] + self.dims[l + 1] for l in range(self.L))
+        nb = self.n_arena * 4
+        self.params = ctx.alloc_zeroed(nb)
+        self.grads = ctx.alloc_zeroed(nb)
+        self.m = ctx.alloc_zeroed(nb) if optimizer[0] == "adamw" else None
+        self.v = ctx.alloc_zeroed(nb) if optimizer[0] == "adamw" else None
+        self.step_counter = ctx.alloc_zeroed(256)
+
+        # ---- activations, saved tensors, gradients of activations ----
+        B = self.batch
+        self.x = ctx.alloc(B * self.dims[0] * 4)
+        self.act_buf = [self.x] + [ctx.alloc(B * self.dims[l + 1] * 4) for l in range(self.L)]
+        self.pre_buf = [ctx.alloc(B * self.dims[l + 1] * 4) if (hidden_act == "gelu" and l < self.L - 1) else None
+                        for l in range(self.L)]
+        self.dact = [None] + [ctx.alloc(B * self.dims[l + 1] * 4) for l in range(self.L)]
+        if loss == "ce":
+            self.target = ctx.alloc(B * 4)
+            self.loss_row = ctx.alloc(B * 4)
+        else:
+            self.target = ctx.alloc(B * od * 4)
+            self.loss_row = None
+        self.loss_out = ctx.alloc_zeroed(256)     # one float: mean CE loss, or summed squared error
+        self.plan = None
+        self.steps_done = 0
+
+    # ---- parameter access ----
+    def W(self, l):
+        return self.params.ptr + 4 * self.w_off[l]
+
+    def b(self, l):
+        return self.params.ptr + 4 * self.b_off[l]
+
+    def gW(self, l):
+        return self.grads.ptr + 4 * self.w_off[l]
+
+    def gb(self, l):
+        return self.grads.ptr + 4 * self.b_off[l]
+
+    def set_params(self, W, b):
+        arena = np.zeros(self.n_arena, np.float32)
+        for l in range(self.L):
+            arena[self.w_off[l]:self.w_off[l] + W[l].size] = np.asarray(W[l], np.float32).ravel()
+            arena[self.b_off[l]:self.b_off[l] + b[l].size] = np.asarray(b[l], np.float32).ravel()
+        self.ctx.upload(self.params, arena)
+
+    def _split(self, arena):
+        W = [arena[self.w_off[l]:self.w_off[l] + self.dims[l] * self.dims[l + 1]]
+             .reshape(self.dims[l], self.dims[l + 1]).copy() for l in range(self.L)]
+        b = [arena[self.b_off[l]:self.b_off[l] + self.dims[l + 1]].copy() for l in range(self.L)]
+        return W, b
+
+    def get_params(self):
+        return self._split(self.ctx.download(self.params, np.empty(self.n_arena, np.float32)))
+
+    def get_grads(self):
+        return self._split(self.ctx.download(self.grads, np.empty(self.n_arena, np.float32)))
+
+    def get_output(self):
+        return self.ctx.download(self.act_buf[self.L], np.empty((self.batch, self.dims[-1]), np.float32))
+
+    def get_loss(self):
+        return float(self.ctx.download(self.loss_out, np.empty(1, np.float32))[0])
+
+    @staticmethod
+    def init_params(dims, init="he_normal", seed=7):
+        """Host-side initial weights, identical on every rank (biases zero)."""
+        r = np.random.Generator(np.random.Philox(seed))
+        W, b = [], []
+        for l in range(len(dims) - 1):
+            fi, fo = dims[l], dims[l + 1]
+            if init == "he_normal":
+                w = r.standard_normal((fi, fo), np.float32) * np.float32(np.sqrt(2.0 / fi))
+            elif init == "xavier_uniform":
+                lim = np.sqrt(6.0 / (fi + fo))
+                w = r.uniform(-lim, lim, (fi, fo)).astype(np.float32)
+            else:   # "normal_fan_in": N(0, 1/sqrt(fan_in))
+                w = r.standard_normal((fi, fo), np.float32) * np.float32(1.0 / np.sqrt(fi))
+            W.append(w.astype(np.float32))
+            b.append(np.zeros(fo, np.float32))
+        return W, b
+
+    # ---- data ----
+    def upload_batch(self, x, target):
+        self.ctx.upload(self.x, np.ascontiguousarray(x, np.float32))
+        t = np.ascontiguousarray(target, np.uint32 if self.loss_kind == "ce" else np.float32)
+        self.ctx.upload(self.target, t)
+
+    def upload_batch_async(self, x_pinned, target_pinned):
+        """x_pinned / target_pinned: numpy arrays over page-locked memory (ctx.pinned_array)."""
+        self.ctx.upload_async(self.x, x_pinned.ctypes.data, x_pinned.nbytes)
+        self.ctx.upload_async(self.target, target_pinned.ctypes.data, target_pinned.nbytes)
+
+    # ---- one training step, enqueued on the context's stream ----
+    def enqueue_step(self):
+        c, B, L = self.ctx, self.batch, self.L
+        for l in range(L):
+            a = self.act if l < L - 1 else "none"
+            c.gemm(self.act_buf[l], self.W(l), self.act_buf[l + 1], B, self.dims[l + 1], self.dims[l],
+                   bias=self.b(l), act=a, preact_out=self.pre_buf[l], mode=self.mode)
+        od = self.dims[-1]
+        if self.loss_kind == "ce":
+            c.softmax_ce(self.act_buf[L], self.target, B, od, grad_scale=self.grad_scale, loss_row=self.loss_row,
+                         loss_mean=self.loss_out, dlogits=self.dact[L])
+        else:
+            c.mse_loss_grad(self.act_buf[L], self.target, B * od, grad_scale=self.grad_scale,
+                            loss_sum=self.loss_out, grad=self.dact[L])
+        for l in range(L - 1, -1, -1):
+            a = self.act if l < L - 1 else "none"
+            saved = None if a == "none" else (self.pre_buf[l] if a == "gelu" else self.act_buf[l + 1])
+            c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
+                       saved=saved, dA=self.dact[l] if l > 0 else None, dB=self.gW(l), dbias=self.gb(l),
+                       mode=self.mode)
+            if self.world > 1 and self.overlap:
+                lo, hi = self.layer_range[l]
+                c.allreduce_sum(self.grads.ptr + 4 * lo, hi - lo)   # overlaps the next layer's backward
+        if self.world > 1:
+            if not self.overlap:
+                c.allreduce_sum(self.grads, self.n_arena)
+            c.comm_join()
+        # gradients were computed with the global-mean scale, so the sum over ranks needs no further factor
+        if self.opt[0] == "adamw":
+            _, lr, b1, b2, eps, wd = self.opt
+            c.counter_increment(self.step_counter)
+            c.adamw_step(self.params, self.grads, self.m, self.v, self.n_arena, lr, b1, b2, eps, wd, step=0,
+                         step_dev=self.step_counter, zero_grad=False)
+        elif self.opt[0] == "sgd":
+            c.sgd_step(self.params, self.grads, self.n_arena, self.opt[1], zero_grad=False)
+
+    def step(self):
+        """Eager step (one launch per kernel)."""
+        self.enqueue_step()
+        self.steps_done += 1
+
+    def build_plan(self):
+        """Records one step as a CUDA graph (the reference's Schedule).  Run one eager step first so
+        that the scratch arena has its final size."""
+        self.ctx.plan_begin()
+        try:
+            self.enqueue_step()
+        finally:
+            self.plan = self.ctx.plan_end()
+        return self.plan
+
+    def step_plan(self):
+        self.plan.launch()
+        self.steps_done += 1
+
+    # flop of one step on this rank (2*M*N*K per GEMM; no dX for the first layer)
+    def flops_per_step(self):
+        f = 0
+        for l in range(self.L):
+            g = 2 * self.batch * self.dims[l] * self.dims[l + 1]
+            f += g * (3 if l > 0 else 2)
+        return f

@@ -84,6 +84,22 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
 /* Reads and clears the device-side error word (bounded waits that expired). */
 int32_t fg_ctx_device_status(fg_ctx* ctx, int32_t* status_word);
 
+/* Per-kernel timing for benchmarks (no counterpart in the reference; its examples time
+ * whole epochs on the host, examples/matmul_chain3.rs:11-44).  While enabled, each launch
+ * of the kernels below is bracketed by CUDA events on the context's stream.  Not
+ * available while a plan is being recorded.  fg_ctx_timing_read synchronises, sums the
+ * launches of one kind since the last read of that kind and forgets them. */
+enum fg_kernel_kind {
+    FG_KERNEL_GEMM_TC = 0,    /* work = 2*M*N*K flop                       */
+    FG_KERNEL_SOFTMAX_CE = 1, /* work = 2*rows*cols*4 bytes (+probs)       */
+    FG_KERNEL_ADAMW = 2,      /* work = 28 (or 32 with zero_grad) bytes/param */
+    FG_KERNEL_SGD = 3,        /* work = 12 (or 16 with zero_grad) bytes/param */
+    FG_KERNEL_SPLIT = 4       /* work = bytes read + written by the operand pre-pass */
+};
+int32_t fg_ctx_timing_enable(fg_ctx* ctx, int32_t on);
+int32_t fg_ctx_timing_read(fg_ctx* ctx, int32_t kind, uint64_t* launches, double* total_ms,
+                           double* total_work);
+
 /* ---- memory (GpuBackend::alloc/alloc_zeroed/alloc_init/upload/copy/download :171-207) ---- */
 int32_t fg_alloc(fg_ctx* ctx, uint64_t bytes, fg_buf** out);
 int32_t fg_alloc_zeroed(fg_ctx* ctx, uint64_t bytes, fg_buf** out);
