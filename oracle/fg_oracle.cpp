@@ -8,6 +8,8 @@
 // reference's kernel body does and plain f32 operations elsewhere.
 #include "fg_oracle.h"
 
+#include <immintrin.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
@@ -67,38 +69,83 @@ inline float act_grad(int act, float saved, int quirks) {
     }
 }
 
-// 4 x 64 register block, k strictly sequential, one fmaf per (i, j, k).
-__attribute__((target_clones("arch=skylake-avx512", "arch=haswell", "default")))
-void gemm_block_f32(uint32_t ib, uint32_t jn, uint32_t K, const float* A, uint32_t lda,
-                    const float* B, uint32_t ldb, float* C, uint32_t ldc) {
-    constexpr uint32_t JB = 64;
-    float acc[4][JB];
-    for (uint32_t i = 0; i < 4; ++i)
-        for (uint32_t j = 0; j < JB; ++j) acc[i][j] = 0.0f;
-    if (ib == 4 && jn == JB) {
-        for (uint32_t k = 0; k < K; ++k) {
-            const float* b = B + (size_t)k * ldb;
-            const float a0 = A[k], a1 = A[lda + k], a2 = A[2 * (size_t)lda + k], a3 = A[3 * (size_t)lda + k];
-#pragma omp simd
-            for (uint32_t j = 0; j < JB; ++j) {
-                float bv = b[j];
-                acc[0][j] = __builtin_fmaf(a0, bv, acc[0][j]);
-                acc[1][j] = __builtin_fmaf(a1, bv, acc[1][j]);
-                acc[2][j] = __builtin_fmaf(a2, bv, acc[2][j]);
-                acc[3][j] = __builtin_fmaf(a3, bv, acc[3][j]);
-            }
-        }
-    } else {
-        for (uint32_t k = 0; k < K; ++k) {
-            const float* b = B + (size_t)k * ldb;
-            for (uint32_t i = 0; i < ib; ++i) {
-                const float a = A[(size_t)i * lda + k];
-                for (uint32_t j = 0; j < jn; ++j) acc[i][j] = __builtin_fmaf(a, b[j], acc[i][j]);
-            }
+// Register-blocked tiles, k strictly sequential, one fused multiply-add (single rounding,
+// the same result as fmaf) per (i, j, k).  A tile is GEMM_MR rows by GEMM_NR columns.
+constexpr uint32_t GEMM_MR = 6, GEMM_NR = 32;
+
+// Generic / edge tile: scalar fmaf.
+void gemm_tile_scalar(uint32_t ib, uint32_t jn, uint32_t K, const float* A, uint32_t lda,
+                      const float* B, uint32_t ldb, float* C, uint32_t ldc) {
+    float acc[GEMM_MR][GEMM_NR];
+    for (uint32_t i = 0; i < ib; ++i)
+        for (uint32_t j = 0; j < jn; ++j) acc[i][j] = 0.0f;
+    for (uint32_t k = 0; k < K; ++k) {
+        const float* b = B + (size_t)k * ldb;
+        for (uint32_t i = 0; i < ib; ++i) {
+            const float a = A[(size_t)i * lda + k];
+            for (uint32_t j = 0; j < jn; ++j) acc[i][j] = __builtin_fmaf(a, b[j], acc[i][j]);
         }
     }
     for (uint32_t i = 0; i < ib; ++i)
         for (uint32_t j = 0; j < jn; ++j) C[(size_t)i * ldc + j] = acc[i][j];
+}
+
+// Full 6 x 32 tile with AVX-512: 2 vectors per row, 12 accumulators.
+__attribute__((target("avx512f")))
+void gemm_tile_avx512(uint32_t K, const float* A, uint32_t lda, const float* B, uint32_t ldb, float* C,
+                      uint32_t ldc) {
+    __m512 acc[GEMM_MR][2];
+    for (uint32_t i = 0; i < GEMM_MR; ++i) acc[i][0] = acc[i][1] = _mm512_setzero_ps();
+    for (uint32_t k = 0; k < K; ++k) {
+        const float* b = B + (size_t)k * ldb;
+        const __m512 b0 = _mm512_loadu_ps(b), b1 = _mm512_loadu_ps(b + 16);
+        for (uint32_t i = 0; i < GEMM_MR; ++i) {
+            const __m512 a = _mm512_set1_ps(A[(size_t)i * lda + k]);
+            acc[i][0] = _mm512_fmadd_ps(a, b0, acc[i][0]);
+            acc[i][1] = _mm512_fmadd_ps(a, b1, acc[i][1]);
+        }
+    }
+    for (uint32_t i = 0; i < GEMM_MR; ++i) {
+        _mm512_storeu_ps(C + (size_t)i * ldc, acc[i][0]);
+        _mm512_storeu_ps(C + (size_t)i * ldc + 16, acc[i][1]);
+    }
+}
+
+// Full 6 x 32 tile with AVX2 + FMA: two passes of 6 x 16 (2 vectors per row, 12 accumulators).
+__attribute__((target("avx2,fma")))
+void gemm_tile_avx2(uint32_t K, const float* A, uint32_t lda, const float* B, uint32_t ldb, float* C,
+                    uint32_t ldc) {
+    for (uint32_t jh = 0; jh < GEMM_NR; jh += 16) {
+        __m256 acc[GEMM_MR][2];
+        for (uint32_t i = 0; i < GEMM_MR; ++i) acc[i][0] = acc[i][1] = _mm256_setzero_ps();
+        for (uint32_t k = 0; k < K; ++k) {
+            const float* b = B + (size_t)k * ldb + jh;
+            const __m256 b0 = _mm256_loadu_ps(b), b1 = _mm256_loadu_ps(b + 8);
+            for (uint32_t i = 0; i < GEMM_MR; ++i) {
+                const __m256 a = _mm256_broadcast_ss(A + (size_t)i * lda + k);
+                acc[i][0] = _mm256_fmadd_ps(a, b0, acc[i][0]);
+                acc[i][1] = _mm256_fmadd_ps(a, b1, acc[i][1]);
+            }
+        }
+        for (uint32_t i = 0; i < GEMM_MR; ++i) {
+            _mm256_storeu_ps(C + (size_t)i * ldc + jh, acc[i][0]);
+            _mm256_storeu_ps(C + (size_t)i * ldc + jh + 8, acc[i][1]);
+        }
+    }
+}
+
+int gemm_isa() {   // 2 = AVX-512, 1 = AVX2+FMA, 0 = scalar
+    static const int isa = __builtin_cpu_supports("avx512f") ? 2
+                           : (__builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma")) ? 1 : 0;
+    return isa;
+}
+
+void gemm_block_f32(uint32_t ib, uint32_t jn, uint32_t K, const float* A, uint32_t lda,
+                    const float* B, uint32_t ldb, float* C, uint32_t ldc) {
+    const int isa = gemm_isa();
+    if (ib == GEMM_MR && jn == GEMM_NR && isa == 2) gemm_tile_avx512(K, A, lda, B, ldb, C, ldc);
+    else if (ib == GEMM_MR && jn == GEMM_NR && isa == 1) gemm_tile_avx2(K, A, lda, B, ldb, C, ldc);
+    else gemm_tile_scalar(ib, jn, K, A, lda, B, ldb, C, ldc);
 }
 
 void transpose(uint32_t R, uint32_t Cn, const float* x, float* y) {
@@ -168,12 +215,13 @@ void ref_gemm_f32(int transA, int transB, uint32_t M, uint32_t N, uint32_t K, co
         }
         return;
     }
-    const int64_t mb = (M + 3) / 4, nb = (N + 63) / 64;
-#pragma omp parallel for schedule(dynamic, 4) collapse(2)
-    for (int64_t bi = 0; bi < mb; ++bi)
-        for (int64_t bj = 0; bj < nb; ++bj) {
-            uint32_t i0 = (uint32_t)bi * 4, j0 = (uint32_t)bj * 64;
-            gemm_block_f32(std::min<uint32_t>(4, M - i0), std::min<uint32_t>(64, N - j0), K,
+    const int64_t mb = (M + GEMM_MR - 1) / GEMM_MR, nb = (N + GEMM_NR - 1) / GEMM_NR;
+    // Column panels outermost so that consecutive tiles reuse the same K x 32 panel of B from cache.
+#pragma omp parallel for schedule(dynamic, 8) collapse(2)
+    for (int64_t bj = 0; bj < nb; ++bj)
+        for (int64_t bi = 0; bi < mb; ++bi) {
+            uint32_t i0 = (uint32_t)bi * GEMM_MR, j0 = (uint32_t)bj * GEMM_NR;
+            gemm_block_f32(std::min<uint32_t>(GEMM_MR, M - i0), std::min<uint32_t>(GEMM_NR, N - j0), K,
                            a + (size_t)i0 * K, K, b + j0, N, C + (size_t)i0 * N + j0, N);
         }
 }

@@ -28,6 +28,28 @@ def check(x, ref, tol, what):
     assert ok, f"{what}: worst error ratio {worst:.3g} x tolerance {tol}"
 
 
+def param_bound(ref_p, ref_g, opt, tol):
+    """Allowed |p - p_ref| after one update when the gradient itself is only known to `tol`.
+
+    SGD is linear in g.  The first AdamW step is lr * g / (|g| + eps) (+ decay): its slope in g is
+    at most lr / (|g| + eps), so a gradient error of tol * (|g| + rms g) moves the parameter by up to
+    lr * tol * (|g| + rms g) / (|g| + eps), capped at 2 lr (the step itself is at most lr).  Where |g| is
+    far above eps this term is about lr * tol; it only opens up for gradients near zero, where the
+    Adam step is ill-conditioned by construction."""
+    p = np.abs(ref_p.astype(np.float64))
+    g = np.abs(ref_g.astype(np.float64))
+    rms_p = np.sqrt(np.mean(p * p))
+    rms_g = np.sqrt(np.mean(g * g))
+    bound = tol * (p + rms_p) + 1e-30
+    dg = tol * (g + rms_g)
+    if opt[0] == "adamw":
+        lr, eps = opt[1], opt[4]
+        bound = bound + lr * np.minimum(2.0, dg / (g + eps))
+    else:
+        bound = bound + opt[1] * dg
+    return bound
+
+
 def run_case(ctx, oracle, dims, batch, act, loss, opt, init, steps, mode, tol=TOL, workload=None):
     from ferrograd_b200 import dp
     from ferrograd_b200.mlp import MLPTrainer
@@ -43,6 +65,8 @@ def run_case(ctx, oracle, dims, batch, act, loss, opt, init, steps, mode, tol=TO
         x, t = dp.synth_batch(wl, 0, s, batch)
         tr.upload_batch(x, t)
         tr.step()
+        if s == 0:
+            W_prev, b_prev = [w.copy() for w in W], [v.copy() for v in b]
         ref_loss, gW, gb, out = oracle.mlp_step(dims, batch, act, W, b, x, t, loss, gs, opt, step=s + 1, state=state)
         if s == 0:
             check(tr.get_output(), out, tol, "forward output")
@@ -52,8 +76,19 @@ def run_case(ctx, oracle, dims, batch, act, loss, opt, init, steps, mode, tol=TO
                 check(got_gb[l], gb[l], tol, f"db[{l}]")
             got_W, got_b = tr.get_params()
             for l in range(len(dims) - 1):
-                check(got_W[l], W[l], tol, f"updated W[{l}]")
-                check(got_b[l], b[l], tol, f"updated b[{l}]")
+                # (1) the optimizer in isolation: the oracle's update applied to the GPU's own gradients
+                for prev, g, got, name in ((W_prev[l], got_gW[l], got_W[l], "W"), (b_prev[l], got_gb[l], got_b[l], "b")):
+                    p, gg = prev.copy(), g.copy()
+                    if opt[0] == "adamw":
+                        oracle.adamw(p, gg, np.zeros_like(p), np.zeros_like(p), *opt[1:], 1)
+                    else:
+                        oracle.sgd(p, gg, opt[1])
+                    check(got, p, 1e-5, f"update of {name}[{l}] from the same gradients")
+                # (2) end to end: the gradient tolerance propagated through the update
+                for ref_p, ref_g, got, name in ((W[l], gW[l], got_W[l], "W"), (b[l], gb[l], got_b[l], "b")):
+                    bound = param_bound(ref_p, ref_g, opt, tol)
+                    worst = float(np.max(np.abs(got.astype(np.float64) - ref_p) / bound))
+                    assert worst <= 1.0, f"updated {name}[{l}]: {worst:.3g} x the propagated bound"
         ref = ref_loss / batch if loss == "ce" else ref_loss
         drift.append(abs(tr.get_loss() - ref) / max(abs(ref), 1e-30))
     assert ctx.device_status() == 0
