@@ -236,6 +236,16 @@ def run_ours(args, rank, world, local_rank):
     from ferrograd_b200 import GpuContext, dp
     from ferrograd_b200.mlp import MLPTrainer
 
+    # Libraries (NCCL's version banner, for one) may write to stdout; the contract is ONE JSON line there.
+    # Keep the real stdout aside and point fd 1 at stderr until the line is printed.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
+
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -363,7 +373,7 @@ def run_ours(args, rank, world, local_rank):
             ctx.timing_enable(False)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(args.workload)
-        print(json.dumps(line), flush=True)
+        emit(line)
     barrier()
     if world > 1:
         dist.destroy_process_group()
