@@ -175,6 +175,22 @@ int32_t fg_mse_loss_grad(fg_ctx* ctx, const float* pred, const float* target, ui
                          float grad_scale, float* loss_elem_out, float* loss_sum_out,
                          float* grad_out);
 
+/* The same loss and gradient for hosts that must never cause a device allocation (a
+ * process whose own pool already owns all GPU memory, a latency-bound service, a job run
+ * against a fixed memory budget).  It has no counterpart in the reference.  The partial
+ * sums of the reduction live in a 16 KiB array built into the library instead of the
+ * context's scratch arena, so no cudaMalloc/cudaFree happens on any call.
+ *   - n must not exceed FG_MSE_NOALLOC_MAX_N; larger n returns FG_ERR_INVALID_ARGUMENT.
+ *   - The first call made on a device looks up the array's address; make it outside any
+ *     stream capture.
+ *   - Calls on the same GPU share the array: do not let two of them run concurrently.
+ * loss_sum agrees with fg_mse_loss_grad to rounding (a different, SM-count-independent
+ * summation order); loss_elem and grad are identical. */
+#define FG_MSE_NOALLOC_MAX_N 268435456ull
+int32_t fg_mse_loss_grad_noalloc(fg_ctx* ctx, const float* pred, const float* target, uint64_t n,
+                                 float grad_scale, float* loss_elem_out, float* loss_sum_out,
+                                 float* grad_out);
+
 /* ---- optimizers ----
  * SGD (STOCHASTIC_GRADIENT_DESCENT: optim/basic_optim.rs:3-31; lr plumbing
  * kernel/optim.rs:119-146): w −= lr·(g·grad_scale); g = 0 when zero_grad != 0
