@@ -23,6 +23,8 @@
 // plane 1 = lo; ld = contraction length rounded up to 4 so row pitches are 16-byte
 // multiples).  One 3-D tensor map per operand: dims {contraction, rows, 2},
 // box {32, tile rows, 2}, so one load brings the hi and the lo tile of a k-block.
+#include <cuda_bf16.h>
+
 #include "fg_internal.cuh"
 #include "ptx_sm100.cuh"
 
@@ -31,7 +33,7 @@ using namespace fgptx;
 namespace {
 
 constexpr int BM = 128;         // rows of the output tile = UMMA M
-constexpr int BK = 32;          // f32 per k-block: one 128-byte swizzled row
+// BK (template parameter): f32 per k-block = one swizzled shared-memory row: 32 (128-byte swizzle) or 16 (64-byte).
 constexpr int UK = 8;           // K of one tcgen05.mma kind::tf32
 constexpr long long kWaitCycles = 2000000000LL;   // bound on every device-side wait (about 1 s)
 
@@ -44,30 +46,39 @@ struct Epilogue {
     int* dev_status;
 };
 
-template <int BN>
+template <int BN, int BK>
 struct TileCfg {
     static constexpr int kABytes = 2 * BM * BK * 4;   // hi + lo tiles of A
     static constexpr int kBBytes = 2 * BN * BK * 4;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;
+    static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators (ping-pong)
     static constexpr int kColsPerThread = BN / 2;                 // each lane quarter is shared by two warps
 };
 
 constexpr int kThreads = 320;      // warp 0: loads, warp 1: MMA issue, warps 2..9: accumulate + epilogue
-constexpr int kChunkKB = 8;        // k-blocks per accumulation chunk (256 values of k)
+constexpr int kChunkK = 256;       // values of k per accumulation chunk
 
 // The tensor core adds into its f32 accumulator with truncation, so a long chain of
 // tcgen05.mma drifts linearly with K (measured: 1.9e-4 relative at K = 8192).  The K loop is
-// therefore cut into chunks of kChunkKB k-blocks.  Each chunk accumulates in one of two
+// therefore cut into chunks of kChunkK values of k.  Each chunk accumulates in one of two
 // tensor-memory accumulators, starting from zero; when it completes, the eight epilogue
 // warps read it back and add it, rounding to nearest, to running sums held in registers
 // while the tensor core is already working on the next chunk in the other accumulator.
-template <int BN>
+//
+// FMT selects the operand planes and the MMA sequence per k-block:
+//   0  [hi | lo] f32 planes; three kind::tf32 MMAs per 8-wide k-step (lo*hi, hi*lo, hi*hi): "3xTF32".
+//   1  hi as f32 (tf32-rounded) plus a bf16 pair [bf16(x) | bf16(x - hi)]; the dominant term hi*hi
+//      runs as kind::tf32, the two cross terms as kind::f16 (bf16) MMAs, which take half the time of a
+//      tf32 MMA per k: two tf32-units of tensor work per product instead of three.  The cross terms
+//      are 2^-12 of the product, so bf16's 2^-9 relative rounding costs ~2^-20 relative per product.
+template <int BN, int BK, int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epilogue ep) {
-    using Cfg = TileCfg<BN>;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmA16, const __grid_constant__ CUtensorMap tmB16, Epilogue ep) {
+    static_assert(FMT == 0 || BK == 32, "the bf16 planes use 64-byte rows: 32 values of k per block");
+    using Cfg = TileCfg<BN, BK>;
     constexpr int S = Cfg::kStages;
     constexpr int CPT = Cfg::kColsPerThread;
     extern __shared__ unsigned char smem_raw[];
@@ -86,6 +97,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const uint32_t nkb = (ep.K + BK - 1) / BK;
+    constexpr uint32_t kChunkKB = kChunkK / BK;   // k-blocks per accumulation chunk
     const uint32_t nchunks = (nkb + kChunkKB - 1) / kChunkKB;
 
     // A wait that expired earlier (this launch or a previous one) makes every CTA leave at once.
@@ -101,6 +113,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         fence_mbar_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
+        if (FMT == 1) { prefetch_tmap(&tmA16); prefetch_tmap(&tmB16); }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::kTmemCols);
@@ -125,6 +138,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t sa = base + s * Cfg::kStageBytes;
                 tma_load_3d(sa, &tmA, full_bar(s), (int)(kb * BK), (int)m0, 0);
                 tma_load_3d(sa + Cfg::kABytes, &tmB, full_bar(s), (int)(kb * BK), (int)n0, 0);
+                if (FMT == 1) {   // the bf16 pairs follow their operand's f32 tile
+                    tma_load_3d(sa + BM * BK * 4, &tmA16, full_bar(s), (int)(kb * BK), (int)m0, 0);
+                    tma_load_3d(sa + Cfg::kABytes + BN * BK * 4, &tmB16, full_bar(s), (int)(kb * BK), (int)n0, 0);
+                }
             }
         }
     } else if (warp == 1) {
@@ -152,18 +169,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     tc_fence_after();
                     const uint32_t sa = base + s * Cfg::kStageBytes;
-                    const uint64_t a_hi = make_desc_sw128(sa);
-                    const uint64_t a_lo = make_desc_sw128(sa + BM * BK * 4);
-                    const uint64_t b_hi = make_desc_sw128(sa + Cfg::kABytes);
-                    const uint64_t b_lo = make_desc_sw128(sa + Cfg::kABytes + BN * BK * 4);
+                    const uint64_t a_hi = make_desc_kmajor<BK * 4>(sa);
+                    const uint64_t a_lo = make_desc_kmajor<BK * 4>(sa + BM * BK * 4);
+                    const uint64_t b_hi = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes);
+                    const uint64_t b_lo = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes + BN * BK * 4);
                     const uint32_t first = (kb == c * kChunkKB) ? 0u : 1u;   // a chunk starts from zero
+                    if (FMT == 0) {
 #pragma unroll
-                    for (int kk = 0; kk < BK / UK; ++kk) {
-                        // advance along K inside the swizzled row: +32 bytes, i.e. +2 in the address field
-                        const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
-                        mma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first | (uint32_t)kk);
-                        mma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
-                        mma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        for (int kk = 0; kk < BK / UK; ++kk) {
+                            // advance along K inside the swizzled row: +32 bytes, i.e. +2 in the address field
+                            const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                            mma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, first | (uint32_t)kk);
+                            mma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            mma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                    } else {
+                        // bf16 tiles: rows of 64 bytes (32 values of k), two 16-wide k-steps of 32 bytes each
+                        constexpr uint32_t idesc16 = make_idesc(1u /*bf16*/, BM, BN < 16 ? 16 : BN);
+                        const uint32_t a16 = sa + BM * BK * 4, b16 = sa + Cfg::kABytes + BN * BK * 4;
+                        const uint64_t a_h16 = make_desc_kmajor<64>(a16), a_l16 = make_desc_kmajor<64>(a16 + BM * BK * 2);
+                        const uint64_t b_h16 = make_desc_kmajor<64>(b16), b_l16 = make_desc_kmajor<64>(b16 + BN * BK * 2);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk) {
+                            const uint64_t adv = (uint64_t)(kk * 16 * 2 >> 4);
+                            mma_f16(d_tmem, a_l16 + adv, b_h16 + adv, idesc16, first | (uint32_t)kk);
+                            mma_f16(d_tmem, a_h16 + adv, b_l16 + adv, idesc16, 1u);
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < BK / UK; ++kk) {
+                            const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                            mma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
                     }
                     mma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
                 }
@@ -253,69 +289,417 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------
-// Pre-pass: hi/lo planes of X [R, C] (row-major), optionally of dY * act'(saved).
-//   planes_n: [2][R][ldn]   (same orientation; contraction index = column)
-//   planes_t: [2][C][ldt]   (transposed;       contraction index = row)
-// 32x32 tiles, 32x8 threads.
+// CTA-pair kernel (cta_group::2): two CTAs on neighbouring SMs compute one 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and HALF of the B tile (128 of its 256 rows); the
+// pair's MMA reads both halves, so the bytes each SM pulls from L2 per k-block drop from
+// 96 KiB to 64 KiB.  (The single-CTA kernel is limited by exactly that stream: it takes the
+// same time with two thirds of the tensor work.)  CTA 0 of the pair issues all MMAs; both
+// CTAs keep their 128 rows of the accumulators in their own tensor memory and run their own
+// epilogue.  Loads carry no multicast; the only cross-CTA traffic is signalling
+// (load-completion bytes counted on the leader's mbarrier, commit arrivals on both CTAs'
+// mbarriers, accumulator-drained arrivals on the leader's mbarrier).
 // ------------------------------------------------------------------------------------
+constexpr long long kPairWaitCycles = 400000000LL;   // about 0.2 s
+
+template <int BK>
+struct PairCfg {
+    static constexpr int kBN = 256;
+    static constexpr int kABytes = 2 * BM * BK * 4;          // this CTA's 128 rows of A: hi + lo (or f32 + bf16 pair)
+    static constexpr int kBBytes = 2 * (kBN / 2) * BK * 4;   // this CTA's half of the B tile
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kTmemCols = 512;                     // two 256-column accumulators
+};
+
+template <int BK, int FMT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA16, const __grid_constant__ CUtensorMap tmB16, Epilogue ep) {
+    static_assert(FMT == 0 || BK == 32, "the bf16 planes use 64-byte rows: 32 values of k per block");
+    using Cfg = PairCfg<BK>;
+    constexpr int BN = Cfg::kBN, HB = BN / 2;
+    constexpr int S = Cfg::kStages;
+    constexpr int CPT = BN / 2;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_raw + (base - raw);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(base_ptr + S * Cfg::kStageBytes);
+    const uint32_t bar0 = base + S * Cfg::kStageBytes;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+    auto acc_full_bar = [&](int b) { return bar0 + 8u * (2 * S + b); };
+    auto acc_empty_bar = [&](int b) { return bar0 + 8u * (2 * S + 2 + b); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars + 2 * S + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const uint32_t m0 = (blockIdx.x >> 1) * (2 * BM) + rank * BM;   // this CTA's rows of A and C
+    const uint32_t n0 = blockIdx.y * BN;                            // the pair's columns of C
+    const uint32_t nb0 = n0 + rank * HB;                            // the rows of B this CTA loads
+    const uint32_t nkb = (ep.K + BK - 1) / BK;
+    constexpr uint32_t kChunkKB = kChunkK / BK;
+    const uint32_t nchunks = (nkb + kChunkKB - 1) / kChunkKB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 16); }
+        fence_mbar_init();
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+        if (FMT == 1) { prefetch_tmap(&tmA16); prefetch_tmap(&tmB16); }
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // the peer's barriers exist before anything is signalled across CTAs
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer (both CTAs): own rows of A, own half of B; completion counted on the leader ----
+            for (uint32_t kb = 0; kb < nkb; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (kb / S) & 1u;
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, kPairWaitCycles)) {
+                    atomicOr(ep.dev_status, FG_DEVERR_TMA_WAIT);
+                    break;
+                }
+                if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
+                const uint32_t lf = map_to_cta(full_bar(s), 0);
+                const uint32_t sa = base + s * Cfg::kStageBytes;
+                tma_load_3d_pair(sa, &tmA, lf, (int)(kb * BK), (int)m0, 0);
+                tma_load_3d_pair(sa + Cfg::kABytes, &tmB, lf, (int)(kb * BK), (int)nb0, 0);
+                if (FMT == 1) {
+                    tma_load_3d_pair(sa + BM * BK * 4, &tmA16, lf, (int)(kb * BK), (int)m0, 0);
+                    tma_load_3d_pair(sa + Cfg::kABytes + HB * BK * 4, &tmB16, lf, (int)(kb * BK), (int)nb0, 0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---- MMA issuer (leader CTA only): M = 256 across the pair, N = 256 ----
+            constexpr uint32_t idesc = make_idesc(2u /*tf32*/, 2 * BM, BN);
+            bool ok = true;
+            for (uint32_t c = 0; c < nchunks && ok; ++c) {
+                const uint32_t buf = c & 1u;
+                if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1u) ^ 1u, kPairWaitCycles)) {
+                    atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t kb_end = min(nkb, (c + 1) * kChunkKB);
+                for (uint32_t kb = c * kChunkKB; kb < kb_end; ++kb) {
+                    const int s = kb % S;
+                    const uint32_t ph = (kb / S) & 1u;
+                    if (!mbar_wait_bounded(full_bar(s), ph, kPairWaitCycles)) {
+                        atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * Cfg::kStageBytes;
+                    const uint64_t a_hi = make_desc_kmajor<BK * 4>(sa);
+                    const uint64_t b_hi = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes);
+                    const uint32_t first = (kb == c * kChunkKB) ? 0u : 1u;
+                    if (FMT == 0) {
+                        const uint64_t a_lo = make_desc_kmajor<BK * 4>(sa + BM * BK * 4);
+                        const uint64_t b_lo = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes + HB * BK * 4);
+#pragma unroll
+                        for (int kk = 0; kk < BK / UK; ++kk) {
+                            const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                            mma_tf32_pair(d_tmem, a_lo + adv, b_hi + adv, idesc, first | (uint32_t)kk);
+                            mma_tf32_pair(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                            mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                    } else {
+                        constexpr uint32_t idesc16 = make_idesc(1u /*bf16*/, 2 * BM, BN);
+                        const uint32_t a16 = sa + BM * BK * 4, b16 = sa + Cfg::kABytes + HB * BK * 4;
+                        const uint64_t a_h16 = make_desc_kmajor<64>(a16), a_l16 = make_desc_kmajor<64>(a16 + BM * BK * 2);
+                        const uint64_t b_h16 = make_desc_kmajor<64>(b16), b_l16 = make_desc_kmajor<64>(b16 + HB * BK * 2);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; ++kk) {
+                            const uint64_t adv = (uint64_t)(kk * 16 * 2 >> 4);
+                            mma_f16_pair(d_tmem, a_l16 + adv, b_h16 + adv, idesc16, first | (uint32_t)kk);
+                            mma_f16_pair(d_tmem, a_h16 + adv, b_l16 + adv, idesc16, 1u);
+                        }
+#pragma unroll
+                        for (int kk = 0; kk < BK / UK; ++kk) {
+                            const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                            mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                    }
+                    mma_commit_pair(empty_bar(s), 3);        // frees this stage in both CTAs
+                }
+                if (ok) mma_commit_pair(acc_full_bar(buf), 3);   // both CTAs may drain their half
+            }
+        }
+    } else {
+        // ---- accumulate + epilogue (both CTAs, own 128 rows); see gemm_tc_kernel ----
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        float sum[CPT];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
+        bool ok = true;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t buf = c & 1u;
+            bool got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1u, kPairWaitCycles + kPairWaitCycles / 2);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+                if (lane == 0) atomicOr(ep.dev_status, FG_DEVERR_EPI_WAIT);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * CPT;
+#pragma unroll
+            for (int g = 0; g < CPT / 32; ++g) {
+                uint32_t r[32];
+                tmem_ld_32x32(t0 + g * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sum[g * 32 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(buf), 0));   // 16 warps report to the leader
+        }
+        if (ok && *reinterpret_cast<volatile int*>(ep.dev_status) == 0) {
+            const uint32_t row = m0 + q * 32 + lane;
+            const uint32_t cbase = n0 + half * CPT;
+            const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
+                                (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
+            if (row < ep.M) {
+                float* crow = ep.C + (size_t)row * ep.N;
+                float* prow = ep.preact ? ep.preact + (size_t)row * ep.N : nullptr;
+#pragma unroll
+                for (int j = 0; j < CPT; j += 4) {
+                    const uint32_t col = cbase + j;
+                    if (col >= ep.N) break;
+                    float z[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        z[t] = sum[j + t];
+                        if (ep.bias && col + t < ep.N) z[t] += ep.bias[col + t];
+                    }
+                    if (vec_ok && col + 3 < ep.N) {
+                        if (prow) *reinterpret_cast<float4*>(prow + col) = make_float4(z[0], z[1], z[2], z[3]);
+                        *reinterpret_cast<float4*>(crow + col) =
+                            make_float4(fg_act_fwd(ep.act, z[0]), fg_act_fwd(ep.act, z[1]),
+                                        fg_act_fwd(ep.act, z[2]), fg_act_fwd(ep.act, z[3]));
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            if (col + t < ep.N) {
+                                if (prow) prow[col + t] = z[t];
+                                crow[col + t] = fg_act_fwd(ep.act, z[t]);
+                            }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // neither CTA retires while the peer may still read its shared memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Pre-pass: operand planes of X [R, C] (row-major), optionally of dY * act'(saved).
+// Orientation n keeps X's layout (contraction index = column): rows R, pitch ld*.
+// Orientation t is transposed (contraction index = row): rows C.
+// Plane formats (FMT):
+//   0  p32 = [2][rows][ld32] f32: hi = tf32(x), lo = tf32(x - hi)
+//   1  p32 = [rows][ld32] f32: hi;  p16 = [2][rows][ld16] bf16: bf16(x), bf16(x - hi)
+// ------------------------------------------------------------------------------------
+struct PlaneSet {
+    float* p32;
+    __nv_bfloat16* p16;
+    uint32_t ld32, ld16;
+};
+
 struct SplitArgs {
     const float* x;
     const float* saved;    // non-NULL: value = x * act'(saved)
     int act;
     uint32_t R, C;
-    float* planes_n; uint32_t ldn;
-    float* planes_t; uint32_t ldt;
+    PlaneSet n, t;         // p32 == NULL: orientation not wanted
     float* value_out;      // optional copy of the (fused) value, [R, C]
 };
 
+template <int FMT>
+__device__ __forceinline__ void store_planes(const PlaneSet& ps, size_t rows, size_t r, size_t c, float hi, float lo,
+                                             float v) {
+    ps.p32[r * ps.ld32 + c] = hi;
+    if (FMT == 0) {
+        ps.p32[rows * ps.ld32 + r * ps.ld32 + c] = lo;
+    } else {
+        ps.p16[r * ps.ld16 + c] = __float2bfloat16_rn(v);
+        ps.p16[rows * ps.ld16 + r * ps.ld16 + c] = __float2bfloat16_rn(lo);
+    }
+}
+
+// Any shape and alignment: 32x32 tiles, 32x8 threads, scalar accesses.
+template <int FMT>
 __global__ void __launch_bounds__(256) split_kernel(SplitArgs a) {
-    __shared__ float thi[32][33];
-    __shared__ float tlo[32][33];
+    __shared__ float tv[32][33];
     const uint32_t c = blockIdx.x * 32 + threadIdx.x;
     const uint32_t r0 = blockIdx.y * 32;
-    const size_t plane_n = (size_t)a.R * a.ldn, plane_t = (size_t)a.C * a.ldt;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t r = r0 + threadIdx.y + i * 8;
-        float hi = 0.0f, lo = 0.0f;
+        float v = 0.0f;
         if (r < a.R && c < a.C) {
             const size_t idx = (size_t)r * a.C + c;
-            float v = a.x[idx];
+            v = a.x[idx];
             if (a.saved) v = v * fg_act_grad(a.act, a.saved[idx]);
             if (a.value_out) a.value_out[idx] = v;
-            hi = __uint_as_float(cvt_tf32(v));
-            lo = __uint_as_float(cvt_tf32(v - hi));
-            if (a.planes_n) {
-                a.planes_n[(size_t)r * a.ldn + c] = hi;
-                a.planes_n[plane_n + (size_t)r * a.ldn + c] = lo;
+            if (a.n.p32) {
+                const float hi = __uint_as_float(cvt_tf32(v));
+                const float lo = v - hi;
+                store_planes<FMT>(a.n, a.R, r, c, hi, FMT == 0 ? __uint_as_float(cvt_tf32(lo)) : lo, v);
             }
         }
-        thi[threadIdx.y + i * 8][threadIdx.x] = hi;
-        tlo[threadIdx.y + i * 8][threadIdx.x] = lo;
+        tv[threadIdx.y + i * 8][threadIdx.x] = v;
     }
-    if (!a.planes_t) return;
+    if (!a.t.p32) return;
     __syncthreads();
     const uint32_t tr = r0 + threadIdx.x;          // source row -> destination column
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t tc = blockIdx.x * 32 + threadIdx.y + i * 8;   // source column -> destination row
         if (tc < a.C && tr < a.R) {
-            a.planes_t[(size_t)tc * a.ldt + tr] = thi[threadIdx.x][threadIdx.y + i * 8];
-            a.planes_t[plane_t + (size_t)tc * a.ldt + tr] = tlo[threadIdx.x][threadIdx.y + i * 8];
+            const float v = tv[threadIdx.x][threadIdx.y + i * 8];
+            const float hi = __uint_as_float(cvt_tf32(v));
+            const float lo = v - hi;
+            store_planes<FMT>(a.t, a.C, tc, tr, hi, FMT == 0 ? __uint_as_float(cvt_tf32(lo)) : lo, v);
         }
     }
 }
 
-inline uint32_t round4(uint32_t v) { return (v + 3u) & ~3u; }
-inline uint64_t planes_bytes(uint32_t rows, uint32_t contraction) { return 2ull * rows * round4(contraction) * 4ull; }
+struct Split4 {
+    float4 hi, lo;
+};
+template <int FMT>
+__device__ __forceinline__ Split4 split4(float4 v) {
+    Split4 o;
+    o.hi = make_float4(__uint_as_float(cvt_tf32(v.x)), __uint_as_float(cvt_tf32(v.y)),
+                       __uint_as_float(cvt_tf32(v.z)), __uint_as_float(cvt_tf32(v.w)));
+    o.lo = make_float4(v.x - o.hi.x, v.y - o.hi.y, v.z - o.hi.z, v.w - o.hi.w);
+    if (FMT == 0)
+        o.lo = make_float4(__uint_as_float(cvt_tf32(o.lo.x)), __uint_as_float(cvt_tf32(o.lo.y)),
+                           __uint_as_float(cvt_tf32(o.lo.z)), __uint_as_float(cvt_tf32(o.lo.w)));
+    return o;
+}
+__device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    return u;
+}
+// Four consecutive elements of one plane row (c a multiple of 4, pitches multiples of 4 / 8).
+template <int FMT>
+__device__ __forceinline__ void store_planes4(const PlaneSet& ps, size_t rows, size_t r, size_t c, float4 v) {
+    const Split4 s = split4<FMT>(v);
+    *reinterpret_cast<float4*>(ps.p32 + r * ps.ld32 + c) = s.hi;
+    if (FMT == 0) {
+        *reinterpret_cast<float4*>(ps.p32 + rows * ps.ld32 + r * ps.ld32 + c) = s.lo;
+    } else {
+        *reinterpret_cast<uint2*>(ps.p16 + r * ps.ld16 + c) = pack_bf16x4(v);
+        *reinterpret_cast<uint2*>(ps.p16 + rows * ps.ld16 + r * ps.ld16 + c) = pack_bf16x4(s.lo);
+    }
+}
 
-int32_t launch_split(fg_ctx* ctx, const SplitArgs& a) {
-    dim3 grid((a.C + 31) / 32, (a.R + 31) / 32), block(32, 8);
+// 128-bit accesses, for R % 4 == 0 and C % 4 == 0 (every group of four is wholly inside or outside)
+// and 16-byte aligned pointers.  64x64 tiles, 256 threads: thread t handles column group t%16
+// (4 columns) of rows t/16 + 16*i, then writes 4 consecutive source rows of source column t/16 + 16*i.
+template <int FMT>
+__global__ void __launch_bounds__(256) split_vec_kernel(SplitArgs a) {
+    __shared__ float tv[64][65];
+    const uint32_t cg = threadIdx.x & 15, rl = threadIdx.x >> 4;
+    const uint32_t c = blockIdx.x * 64 + cg * 4;
+    const uint32_t r0 = blockIdx.y * 64;
+    const bool want_t = a.t.p32 != nullptr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lr = rl + 16 * i, r = r0 + lr;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < a.R && c < a.C) {
+            const size_t idx = (size_t)r * a.C + c;
+            v = __ldcs(reinterpret_cast<const float4*>(a.x + idx));
+            if (a.saved) {
+                const float4 s = __ldcs(reinterpret_cast<const float4*>(a.saved + idx));
+                v.x *= fg_act_grad(a.act, s.x); v.y *= fg_act_grad(a.act, s.y);
+                v.z *= fg_act_grad(a.act, s.z); v.w *= fg_act_grad(a.act, s.w);
+            }
+            if (a.value_out) *reinterpret_cast<float4*>(a.value_out + idx) = v;
+            if (a.n.p32) store_planes4<FMT>(a.n, a.R, r, c, v);
+        }
+        if (want_t) {
+            tv[lr][cg * 4 + 0] = v.x; tv[lr][cg * 4 + 1] = v.y; tv[lr][cg * 4 + 2] = v.z; tv[lr][cg * 4 + 3] = v.w;
+        }
+    }
+    if (!want_t) return;
+    __syncthreads();
+    const uint32_t tr = r0 + cg * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lc = rl + 16 * i, tc = blockIdx.x * 64 + lc;
+        if (tc < a.C && tr < a.R)
+            store_planes4<FMT>(a.t, a.C, tc, tr,
+                               make_float4(tv[cg * 4 + 0][lc], tv[cg * 4 + 1][lc], tv[cg * 4 + 2][lc], tv[cg * 4 + 3][lc]));
+    }
+}
+
+inline uint32_t round4(uint32_t v) { return (v + 3u) & ~3u; }
+inline uint32_t round8(uint32_t v) { return (v + 7u) & ~7u; }
+inline uint64_t align256(uint64_t v) { return (v + 255u) & ~uint64_t(255); }
+// Scratch bytes of one operand's planes (rows x contraction k), including internal alignment.
+inline uint64_t planes_bytes(int fmt, uint32_t rows, uint32_t k) {
+    if (fmt == 0) return 2ull * rows * round4(k) * 4ull + 256;
+    return align256((uint64_t)rows * round4(k) * 4ull) + 2ull * rows * round8(k) * 2ull + 512;
+}
+int32_t alloc_planes(fg_ctx* ctx, int fmt, uint32_t rows, uint32_t k, PlaneSet* out) {
+    void* p;
+    int32_t s = fg_ws_alloc(ctx, planes_bytes(fmt, rows, k), &p);
+    if (s != FG_OK) return s;
+    out->p32 = (float*)p;
+    out->ld32 = round4(k);
+    out->ld16 = round8(k);
+    out->p16 = fmt == 0 ? nullptr
+                        : (__nv_bfloat16*)((char*)p + align256((uint64_t)rows * round4(k) * 4ull));
+    return FG_OK;
+}
+
+int32_t launch_split(fg_ctx* ctx, int fmt, const SplitArgs& a) {
+    auto ok16 = [](const PlaneSet& ps) { return !ps.p32 || (fg_aligned16(ps.p32) && (!ps.p16 || fg_aligned16(ps.p16))); };
+    const bool vec = (a.R % 4 == 0) && (a.C % 4 == 0) && fg_aligned16(a.x) && (!a.saved || fg_aligned16(a.saved)) &&
+                     (!a.value_out || fg_aligned16(a.value_out)) && ok16(a.n) && ok16(a.t);
+    const uint32_t tile = vec ? 64 : 32;
+    dim3 grid((a.C + tile - 1) / tile, (a.R + tile - 1) / tile);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM operand has too many rows");
     double bytes = 4.0 * a.R * a.C * (1.0 + (a.saved ? 1.0 : 0.0) + (a.value_out ? 1.0 : 0.0) +
-                                      (a.planes_n ? 2.0 : 0.0) + (a.planes_t ? 2.0 : 0.0));
+                                      (a.n.p32 ? 2.0 : 0.0) + (a.t.p32 ? 2.0 : 0.0));
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SPLIT, bytes);
-    split_kernel<<<grid, block, 0, ctx->stream>>>(a);
+    if (fmt == 0) {
+        if (vec) split_vec_kernel<0><<<grid, 256, 0, ctx->stream>>>(a);
+        else split_kernel<0><<<grid, dim3(32, 8), 0, ctx->stream>>>(a);
+    } else {
+        if (vec) split_vec_kernel<1><<<grid, 256, 0, ctx->stream>>>(a);
+        else split_kernel<1><<<grid, dim3(32, 8), 0, ctx->stream>>>(a);
+    }
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
@@ -325,17 +709,20 @@ typedef CUresult (*pfn_encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, vo
                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Tensor map over planes [2][rows][ld] with contraction extent `kdim`; box {32, box_rows, 2}.
-int32_t make_tmap(fg_ctx* ctx, CUtensorMap* out, const float* planes, uint32_t rows, uint32_t kdim, uint32_t ld,
-                  uint32_t box_rows) {
+// Tensor map over planes [nplanes][rows][ld] with contraction extent `kdim`; box {bk, box_rows, nplanes}.
+// The swizzle span equals the box's inner extent in bytes: 128 or 64.
+int32_t make_tmap(fg_ctx* ctx, CUtensorMap* out, const void* planes, bool bf16, uint32_t nplanes, uint32_t rows,
+                  uint32_t kdim, uint32_t ld, uint32_t box_rows, uint32_t bk) {
     if (!ctx->tmap_encode) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "cuTensorMapEncodeTiled unavailable");
-    cuuint64_t dims[3] = {kdim, rows, 2};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)rows * ld * 4};
-    cuuint32_t box[3] = {BK, box_rows, 2};
+    const uint32_t esz = bf16 ? 2 : 4;
+    cuuint64_t dims[3] = {kdim, rows, nplanes};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * esz, (cuuint64_t)rows * ld * esz};
+    cuuint32_t box[3] = {bk, box_rows, nplanes};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = ((pfn_encode)ctx->tmap_encode)(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)planes, dims, strides,
-                                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUtensorMapSwizzle swz = bk * esz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    CUresult r = ((pfn_encode)ctx->tmap_encode)(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                                3, (void*)planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         snprintf(ctx->err, sizeof(ctx->err), "cuTensorMapEncodeTiled failed with code %d", (int)r);
         return FG_ERR_INTERNAL;
@@ -343,47 +730,112 @@ int32_t make_tmap(fg_ctx* ctx, CUtensorMap* out, const float* planes, uint32_t r
     return FG_OK;
 }
 
-template <int BN>
-int32_t launch_tc(fg_ctx* ctx, const float* a_planes, uint32_t lda, const float* b_planes, uint32_t ldb,
-                  const Epilogue& ep) {
-    using Cfg = TileCfg<BN>;
-    CUtensorMap tmA, tmB;
-    int32_t s = make_tmap(ctx, &tmA, a_planes, ep.M, ep.K, lda, BM);
-    if (s != FG_OK) return s;
-    s = make_tmap(ctx, &tmB, b_planes, ep.N, ep.K, ldb, BN);
-    if (s != FG_OK) return s;
+template <int BN, int BK, int FMT>
+int32_t launch_tc(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilogue& ep) {
+    using Cfg = TileCfg<BN, BK>;
+    CUtensorMap tmA, tmB, tmA16, tmB16;
+    int32_t s;
+    if ((s = make_tmap(ctx, &tmA, a.p32, false, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
+    if ((s = make_tmap(ctx, &tmB, b.p32, false, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, BN, BK)) != FG_OK) return s;
+    if (FMT == 1) {
+        if ((s = make_tmap(ctx, &tmA16, a.p16, true, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
+        if ((s = make_tmap(ctx, &tmB16, b.p16, true, 2, ep.N, ep.K, b.ld16, BN, BK)) != FG_OK) return s;
+    } else {
+        tmA16 = tmA;
+        tmB16 = tmB;
+    }
     static uint64_t attr_done = 0;   // one bit per device
     if (!(attr_done >> (ctx->device & 63) & 1ull)) {
         FG_CUDA(ctx, FG_ERR_INTERNAL,
-                cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+                cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_done |= 1ull << (ctx->device & 63);
     }
     dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: M too large");
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
-    gemm_tc_kernel<BN><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, ep);
+    gemm_tc_kernel<BN, BK, FMT><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
 
-// C[M,N] = act(Aop·Bopᵀ + bias) where Aop planes are [2][M][lda] and Bop planes [2][N][ldb].
-int32_t tc_gemm(fg_ctx* ctx, const float* a_planes, uint32_t lda, const float* b_planes, uint32_t ldb, uint32_t M,
-                uint32_t N, uint32_t K, float* C, const float* bias, int act, float* preact) {
-    Epilogue ep{C, bias, preact, M, N, K, act, ctx->dev_status};
-    // Widest tile that still fills the machine; narrow N gets a narrow tile.
-    const uint64_t tiles256 = (uint64_t)((M + BM - 1) / BM) * ((N + 255) / 256);
-    if (N > 128 && tiles256 >= (uint64_t)ctx->sm_count) return launch_tc<256>(ctx, a_planes, lda, b_planes, ldb, ep);
-    if (N > 64) return launch_tc<128>(ctx, a_planes, lda, b_planes, ldb, ep);
-    if (N > 32) return launch_tc<64>(ctx, a_planes, lda, b_planes, ldb, ep);
-    return launch_tc<32>(ctx, a_planes, lda, b_planes, ldb, ep);
+template <int BK, int FMT>
+int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilogue& ep) {
+    using Cfg = PairCfg<BK>;
+    CUtensorMap tmA, tmB, tmA16, tmB16;
+    int32_t s;
+    if ((s = make_tmap(ctx, &tmA, a.p32, false, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
+    if ((s = make_tmap(ctx, &tmB, b.p32, false, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, Cfg::kBN / 2, BK)) != FG_OK) return s;
+    if (FMT == 1) {
+        if ((s = make_tmap(ctx, &tmA16, a.p16, true, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
+        if ((s = make_tmap(ctx, &tmB16, b.p16, true, 2, ep.N, ep.K, b.ld16, Cfg::kBN / 2, BK)) != FG_OK) return s;
+    } else {
+        tmA16 = tmA;
+        tmB16 = tmB;
+    }
+    static uint64_t attr_done = 0;   // one bit per device
+    if (!(attr_done >> (ctx->device & 63) & 1ull)) {
+        FG_CUDA(ctx, FG_ERR_INTERNAL,
+                cudaFuncSetAttribute(gemm_tc_pair_kernel<BK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+        attr_done |= 1ull << (ctx->device & 63);
+    }
+    dim3 grid(2 * ((ep.M + 2 * BM - 1) / (2 * BM)), (ep.N + Cfg::kBN - 1) / Cfg::kBN);   // x: CTA pairs along M
+    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: N too large");
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
+    gemm_tc_pair_kernel<BK, FMT><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
+    fg_time_end(ctx, tr);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
 }
 
-bool use_tensor_cores(const fg_ctx* ctx, int mode, uint32_t M, uint32_t N, uint32_t K) {
-    if (mode == FG_GEMM_SIMT) return false;
-    if (mode == FG_GEMM_3XTF32) return true;
-    if (!ctx->tmap_encode) return false;
-    return M >= 64 && (uint64_t)M * N * K >= (1ull << 22);
+// C[M,N] = act(Aop·Bopᵀ + bias) where the A operand's planes have M rows and the B operand's N rows.
+int32_t tc_gemm(fg_ctx* ctx, int fmt, const PlaneSet& a, const PlaneSet& b, uint32_t M, uint32_t N, uint32_t K, float* C,
+                const float* bias, int act, float* preact) {
+    Epilogue ep{C, bias, preact, M, N, K, act, ctx->dev_status};
+    // Tile choice: one output tile per CTA (or per CTA pair), so the last wave is often part empty.
+    // Each candidate is scored by machine fill times its measured relative throughput at 8192^3
+    // (hybrid planes: pair 316, 128x256 248, 128x128 ~215 TFLOP/s; hi/lo planes: 262, 260, 217).
+    const uint64_t sms = (uint64_t)ctx->sm_count, mt = (M + BM - 1) / BM;
+    auto fill = [](uint64_t tiles, uint64_t slots) { return (double)tiles / (double)(((tiles + slots - 1) / slots) * slots); };
+    const uint64_t t256 = mt * ((N + 255) / 256), t128 = mt * ((N + 127) / 128);
+    const uint64_t tpair = (uint64_t)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    const double s_pair = (N > 128 && M > BM) ? fill(tpair, sms / 2) * 1.0 : 0.0;
+    const double s_256 = N > 128 ? fill(t256, sms) * (fmt == 1 ? 0.78 : 0.98) : 0.0;
+    const double s_128 = N > 64 ? fill(t128, sms) * (fmt == 1 ? 0.68 : 0.83) : 0.0;
+    int bn = N > 128 ? (s_256 >= s_128 ? 256 : 128) : N > 64 ? 128 : N > 32 ? 64 : 32;
+    int bk = (fmt == 0 && bn == 256) ? 16 : 32;
+    bool pair = s_pair > 0.0 && s_pair >= s_256 && s_pair >= s_128;
+    // Tuning override for experiments: FG_GEMM_TILE="pair" or "<BN>x<BK>", e.g. "256x16".
+    if (const char* e = getenv("FG_GEMM_TILE")) {
+        int x = 0, y = 0;
+        if (strcmp(e, "pair") == 0) pair = N > 128;
+        else if (sscanf(e, "%dx%d", &x, &y) == 2 && (x == 256 || x == 128) && (y == 32 || (y == 16 && fmt == 0))) {
+            bn = x; bk = y; pair = false;
+        }
+    }
+    if (pair) return fmt == 1 ? launch_tc_pair<32, 1>(ctx, a, b, ep) : launch_tc_pair<32, 0>(ctx, a, b, ep);
+    if (fmt == 1) {
+        if (bn == 256) return launch_tc<256, 32, 1>(ctx, a, b, ep);
+        if (bn == 128) return launch_tc<128, 32, 1>(ctx, a, b, ep);
+        if (bn == 64) return launch_tc<64, 32, 1>(ctx, a, b, ep);
+        return launch_tc<32, 32, 1>(ctx, a, b, ep);
+    }
+    if (bn == 256 && bk == 16) return launch_tc<256, 16, 0>(ctx, a, b, ep);
+    if (bn == 128 && bk == 16) return launch_tc<128, 16, 0>(ctx, a, b, ep);
+    if (bn == 256) return launch_tc<256, 32, 0>(ctx, a, b, ep);
+    if (bn == 128) return launch_tc<128, 32, 0>(ctx, a, b, ep);
+    if (bn == 64) return launch_tc<64, 32, 0>(ctx, a, b, ep);
+    return launch_tc<32, 32, 0>(ctx, a, b, ep);
+}
+
+// Which path a request takes: 0 = SIMT, otherwise the plane format + 1.
+int pick_path(const fg_ctx* ctx, int mode, uint32_t M, uint32_t N, uint32_t K) {
+    if (mode == FG_GEMM_SIMT) return 0;
+    if (mode == FG_GEMM_3XTF32) return 1;
+    if (mode == FG_GEMM_TF32_BF16X2) return 2;
+    if (!ctx->tmap_encode) return 0;
+    if (!(M >= 64 && (uint64_t)M * N * K >= (1ull << 22))) return 0;
+    return 2;   // AUTO: tf32 main term + bf16 cross terms (same accuracy class, two thirds of the tensor work)
 }
 
 }  // namespace
@@ -395,38 +847,36 @@ int32_t fg_gemm_f32(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB, u
     FG_ENTER(ctx);
     FG_REQUIRE(ctx, A && B && C, "fg_gemm_f32: NULL operand");
     FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_f32: dimensions must be >= 1");
-    FG_REQUIRE(ctx, mode >= FG_GEMM_AUTO && mode <= FG_GEMM_3XTF32, "fg_gemm_f32: unknown mode");
+    FG_REQUIRE(ctx, mode >= FG_GEMM_AUTO && mode <= FG_GEMM_TF32_BF16X2, "fg_gemm_f32: unknown mode");
     FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_f32: unknown activation");
     FG_REQUIRE(ctx, (uint64_t)M * N < (1ull << 40) && (uint64_t)M * K < (1ull << 40) && (uint64_t)N * K < (1ull << 40),
                "fg_gemm_f32: operand too large");
-    if (!use_tensor_cores(ctx, mode, M, N, K))
-        return fg_gemm_simt_launch(ctx, transA, transB, M, N, K, A, B, C, bias, act, preact_out);
-    const uint32_t ld = round4(K);
-    void *pa, *pb;
+    const int path = pick_path(ctx, mode, M, N, K);
+    if (path == 0) return fg_gemm_simt_launch(ctx, transA, transB, M, N, K, A, B, C, bias, act, preact_out);
+    const int fmt = path - 1;
     // Size the arena for both operands before carving it.
-    if (ctx->ws_bytes < planes_bytes(M, K) + planes_bytes(N, K) + 512) {
-        int32_t s0 = fg_ctx_reserve_workspace(ctx, planes_bytes(M, K) + planes_bytes(N, K) + 512);
+    const uint64_t need = planes_bytes(fmt, M, K) + planes_bytes(fmt, N, K) + 1024;
+    if (ctx->ws_bytes < need) {
+        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
         if (s0 != FG_OK) return s0;
     }
-    int32_t s = fg_ws_alloc(ctx, planes_bytes(M, K), &pa);
-    if (s != FG_OK) return s;
-    s = fg_ws_alloc(ctx, planes_bytes(N, K), &pb);
-    if (s != FG_OK) return s;
+    PlaneSet pa{}, pb{};
+    int32_t s;
+    if ((s = alloc_planes(ctx, fmt, M, K, &pa)) != FG_OK) return s;
+    if ((s = alloc_planes(ctx, fmt, N, K, &pb)) != FG_OK) return s;
     // A operand: [M, K] with K contiguous.
     SplitArgs sa{};
     sa.x = A;
-    if (!transA) { sa.R = M; sa.C = K; sa.planes_n = (float*)pa; sa.ldn = ld; }
-    else         { sa.R = K; sa.C = M; sa.planes_t = (float*)pa; sa.ldt = ld; }
-    s = launch_split(ctx, sa);
-    if (s != FG_OK) return s;
+    if (!transA) { sa.R = M; sa.C = K; sa.n = pa; }
+    else         { sa.R = K; sa.C = M; sa.t = pa; }
+    if ((s = launch_split(ctx, fmt, sa)) != FG_OK) return s;
     // B operand: [N, K] with K contiguous.
     SplitArgs sb{};
     sb.x = B;
-    if (!transB) { sb.R = K; sb.C = N; sb.planes_t = (float*)pb; sb.ldt = ld; }
-    else         { sb.R = N; sb.C = K; sb.planes_n = (float*)pb; sb.ldn = ld; }
-    s = launch_split(ctx, sb);
-    if (s != FG_OK) return s;
-    return tc_gemm(ctx, (const float*)pa, ld, (const float*)pb, ld, M, N, K, C, bias, act, preact_out);
+    if (!transB) { sb.R = K; sb.C = N; sb.t = pb; }
+    else         { sb.R = N; sb.C = K; sb.n = pb; }
+    if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
+    return tc_gemm(ctx, fmt, pa, pb, M, N, K, C, bias, act, preact_out);
 }
 
 int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
@@ -435,16 +885,16 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     FG_ENTER(ctx);
     FG_REQUIRE(ctx, dY != nullptr, "fg_gemm_bwd_f32: dY is NULL");
     FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_bwd_f32: dimensions must be >= 1");
-    FG_REQUIRE(ctx, mode >= FG_GEMM_AUTO && mode <= FG_GEMM_3XTF32, "fg_gemm_bwd_f32: unknown mode");
+    FG_REQUIRE(ctx, mode >= FG_GEMM_AUTO && mode <= FG_GEMM_TF32_BF16X2, "fg_gemm_bwd_f32: unknown mode");
     FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_bwd_f32: unknown activation");
     FG_REQUIRE(ctx, act == FG_ACT_NONE || saved, "fg_gemm_bwd_f32: the activation backward needs the saved tensor");
     FG_REQUIRE(ctx, !dA || B, "fg_gemm_bwd_f32: dA needs B");
     FG_REQUIRE(ctx, !dB || A, "fg_gemm_bwd_f32: dB needs A");
     const bool fuse = act != FG_ACT_NONE;
-    const bool tc = use_tensor_cores(ctx, mode, M, N, K);
+    const int path = pick_path(ctx, mode, M, N, K);
     const uint64_t mn = (uint64_t)M * N;
 
-    if (!tc) {
+    if (path == 0) {
         // Exact path: materialise dZ, then two SIMT GEMMs.
         const float* dz = dY;
         {
@@ -479,48 +929,50 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
 
     // Tensor-core path.  Scratch: dZ planes in both orientations, B planes, Aᵀ planes, dZ itself
     // when a bias gradient is wanted, and the column-sum partials.
-    const uint32_t ld_n = round4(N), ld_m = round4(M);
-    uint64_t need = 1024;
-    if (dA) need += planes_bytes(M, N) + planes_bytes(K, N) + 512;
-    if (dB) need += planes_bytes(N, M) + planes_bytes(K, M) + 512;
+    const int fmt = path - 1;
+    uint64_t need = 2048;
+    if (dA) need += planes_bytes(fmt, M, N) + planes_bytes(fmt, K, N);
+    if (dB) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M);
     if (dbias && !dZ_out) need += mn * 4 + 256;
     if (dbias) need += (uint64_t)((M + 255) / 256) * N * 4 + 256;
     if (ctx->ws_bytes < need) {
         int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
         if (s0 != FG_OK) return s0;
     }
-    void *dz_n = nullptr, *dz_t = nullptr, *b_n = nullptr, *a_t = nullptr, *dz_val = dZ_out;
+    PlaneSet dz_n{}, dz_t{}, b_n{}, a_t{};
+    void* dz_val = dZ_out;
     int32_t s;
     if (dA) {
-        if ((s = fg_ws_alloc(ctx, planes_bytes(M, N), &dz_n)) != FG_OK) return s;
-        if ((s = fg_ws_alloc(ctx, planes_bytes(K, N), &b_n)) != FG_OK) return s;
+        if ((s = alloc_planes(ctx, fmt, M, N, &dz_n)) != FG_OK) return s;
+        if ((s = alloc_planes(ctx, fmt, K, N, &b_n)) != FG_OK) return s;
     }
     if (dB) {
-        if ((s = fg_ws_alloc(ctx, planes_bytes(N, M), &dz_t)) != FG_OK) return s;
-        if ((s = fg_ws_alloc(ctx, planes_bytes(K, M), &a_t)) != FG_OK) return s;
+        if ((s = alloc_planes(ctx, fmt, N, M, &dz_t)) != FG_OK) return s;
+        if ((s = alloc_planes(ctx, fmt, K, M, &a_t)) != FG_OK) return s;
     }
     if (dbias && !dz_val) {
         if ((s = fg_ws_alloc(ctx, mn * 4, &dz_val)) != FG_OK) return s;
     }
     SplitArgs sz{};
     sz.x = dY; sz.saved = fuse ? saved : nullptr; sz.act = act; sz.R = M; sz.C = N;
-    sz.planes_n = (float*)dz_n; sz.ldn = ld_n;
-    sz.planes_t = (float*)dz_t; sz.ldt = ld_m;
+    sz.n = dz_n; sz.t = dz_t;
     sz.value_out = (float*)dz_val;
-    if ((s = launch_split(ctx, sz)) != FG_OK) return s;
+    if (dA || dB || dz_val) {
+        if ((s = launch_split(ctx, fmt, sz)) != FG_OK) return s;
+    }
     if (dA) {
         // dA[M,K] = dZ[M,N] · Bᵀ: contraction over N; B [K,N] is already "rows = K, contraction contiguous".
         SplitArgs sb{};
-        sb.x = B; sb.R = K; sb.C = N; sb.planes_n = (float*)b_n; sb.ldn = ld_n;
-        if ((s = launch_split(ctx, sb)) != FG_OK) return s;
-        if ((s = tc_gemm(ctx, (const float*)dz_n, ld_n, (const float*)b_n, ld_n, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
+        sb.x = B; sb.R = K; sb.C = N; sb.n = b_n;
+        if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
+        if ((s = tc_gemm(ctx, fmt, dz_n, b_n, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
     }
     if (dB) {
         // dB[K,N] = Aᵀ · dZ: contraction over M; operands are Aᵀ [K,M] and dZᵀ [N,M].
         SplitArgs sa{};
-        sa.x = A; sa.R = M; sa.C = K; sa.planes_t = (float*)a_t; sa.ldt = ld_m;
-        if ((s = launch_split(ctx, sa)) != FG_OK) return s;
-        if ((s = tc_gemm(ctx, (const float*)a_t, ld_m, (const float*)dz_t, ld_m, K, N, M, dB, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
+        sa.x = A; sa.R = M; sa.C = K; sa.t = a_t;
+        if ((s = launch_split(ctx, fmt, sa)) != FG_OK) return s;
+        if ((s = tc_gemm(ctx, fmt, a_t, dz_t, K, N, M, dB, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
     }
     if (dbias) {
         if ((s = fg_colsum_launch(ctx, M, N, (const float*)dz_val, dbias)) != FG_OK) return s;

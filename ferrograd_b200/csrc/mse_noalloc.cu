@@ -30,7 +30,8 @@
 
 #define FG_MSE_NOALLOC_CHUNK 65536u
 #define FG_MSE_NOALLOC_MAX_PARTIALS 4096u
-#define FG_MSE_NOALLOC_MAX_N ((uint64_t)FG_MSE_NOALLOC_CHUNK * FG_MSE_NOALLOC_MAX_PARTIALS)
+static_assert(FG_MSE_NOALLOC_MAX_N == (uint64_t)FG_MSE_NOALLOC_CHUNK * FG_MSE_NOALLOC_MAX_PARTIALS,
+              "the limit declared in the header must match the static scratch");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
 static __device__ __align__(256) float g_mse_partials[FG_MSE_NOALLOC_MAX_PARTIALS];

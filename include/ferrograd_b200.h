@@ -57,7 +57,10 @@ enum fg_gemm_mode {
     FG_GEMM_AUTO = 0,   /* tensor cores when the shape is large enough, else SIMT */
     FG_GEMM_SIMT = 1,   /* sequential-k fmaf, bit-identical to the reference kernel body
                            (crates/ferrograd-nn/src/op/matmul/generic.rs:98-319) */
-    FG_GEMM_3XTF32 = 2  /* tcgen05 kind::tf32, hi/lo split, three MMAs per k-step */
+    FG_GEMM_3XTF32 = 2, /* tcgen05 kind::tf32, hi/lo split, three MMAs per k-step */
+    FG_GEMM_TF32_BF16X2 = 3 /* the dominant hi*hi term as kind::tf32, the two cross terms
+                               (lo*hi, hi*lo: 2^-12 of the product) as bf16 MMAs: two
+                               tf32-units of tensor work per product instead of three */
 };
 
 typedef struct fg_ctx fg_ctx;   /* one device + one stream (rocm/mod.rs:58-78)   */

@@ -244,33 +244,55 @@ def test_gemm_simt_bit_exact(ctx, oracle, M, N, K, tA, tB):
 
 
 TC_SHAPES = [(128, 256, 32), (128, 128, 64), (256, 512, 384), (200, 72, 100), (130, 10, 257), (1000, 300, 77),
-             (64, 48, 8), (384, 1024, 1000), (128, 256, 8192), (256, 130, 4100)]
+             (64, 48, 8), (384, 1024, 1000), (128, 256, 8192), (256, 130, 4100),
+             # shapes that take the CTA-pair kernel (M > 128, N > 128), with ragged edges and long K
+             (256, 256, 64), (300, 520, 1000), (512, 768, 8192), (1100, 257, 333)]
+TC_MODES = ["3xtf32", "tf32_bf16x2", "auto"]
 
 
+@pytest.mark.parametrize("mode", TC_MODES)
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
-def test_gemm_3xtf32_vs_oracle(ctx, oracle, M, N, K):
+def test_gemm_tensor_core_vs_oracle(ctx, oracle, M, N, K, mode):
     r = rng(M * 131 + N * 71 + K)
     A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
     Cd = ctx.new_tensor((M, N))
-    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, mode="3xtf32")
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, mode=mode)
     got = ctx.to_numpy(Cd)
     assert ctx.device_status() == 0
-    check(got, oracle.gemm(A, B), TOL_GEMM, "3xTF32 vs f32 fma chain")
-    check(got, oracle.gemm(A, B, f64=True), TOL_GEMM, "3xTF32 vs f64 accumulate")
+    check(got, oracle.gemm(A, B), TOL_GEMM, f"{mode} vs f32 fma chain")
+    check(got, oracle.gemm(A, B, f64=True), TOL_GEMM, f"{mode} vs f64 accumulate")
 
 
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32_bf16x2"])
+@pytest.mark.parametrize("tile", ["128x32", "256x32", "pair"])
+def test_gemm_every_tile_kernel(ctx, oracle, monkeypatch, mode, tile):
+    # The tile heuristic picks one kernel per shape; force each of them on the same ragged problem.
+    monkeypatch.setenv("FG_GEMM_TILE", tile)
+    M, N, K = 400, 600, 700
+    r = rng(4242)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
+    bias = r.standard_normal(N, np.float32)
+    Cd, Pd = ctx.new_tensor((M, N)), ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, bias=up(ctx, bias), act="tanh", preact_out=Pd, mode=mode)
+    yref, pre = oracle.bias_act_fwd(oracle.gemm(A, B), bias, "tanh")
+    assert ctx.device_status() == 0
+    check(ctx.to_numpy(Pd), pre, TOL_GEMM, f"{mode}/{tile} pre-activation")
+    check(ctx.to_numpy(Cd), yref, TOL_GEMM, f"{mode}/{tile} output")
+
+
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32_bf16x2"])
 @pytest.mark.parametrize("tA,tB", [(True, False), (False, True), (True, True)])
-def test_gemm_3xtf32_transposes(ctx, oracle, tA, tB):
+def test_gemm_tensor_core_transposes(ctx, oracle, tA, tB, mode):
     M, N, K = 192, 320, 200
     r = rng(77)
     A = r.standard_normal((K, M) if tA else (M, K), np.float32)
     B = r.standard_normal((N, K) if tB else (K, N), np.float32)
     Cd = ctx.new_tensor((M, N))
-    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, transA=tA, transB=tB, mode="3xtf32")
-    check(ctx.to_numpy(Cd), oracle.gemm(A, B, transA=tA, transB=tB), TOL_GEMM, "3xTF32 transposed")
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, transA=tA, transB=tB, mode=mode)
+    check(ctx.to_numpy(Cd), oracle.gemm(A, B, transA=tA, transB=tB), TOL_GEMM, f"{mode} transposed")
 
 
-@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 @pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
 def test_gemm_epilogue(ctx, oracle, mode, act):
     M, N, K = 256, 264, 96
@@ -289,7 +311,7 @@ def test_gemm_epilogue(ctx, oracle, mode, act):
     check(got, yref, TOL_GEMM, f"epilogue {act}")
 
 
-@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 @pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
 def test_gemm_backward(ctx, oracle, mode, act):
     M, N, K = 192, 136, 160
@@ -314,7 +336,7 @@ def test_gemm_backward(ctx, oracle, mode, act):
     check(ctx.to_numpy(dA2), oracle.gemm(dz_ref, B, transB=True), TOL_GEMM, "dA only")
 
 
-@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_reference_matmul_known_answers(ctx, mode):
     # crates/ferrograd/tests/std_wgsl.rs:268-373 (matmul_add) and :376-520 (matmul_chain3): constant
     # inputs, closed-form results, compared with ==.  Small integers are exact in TF32 too.

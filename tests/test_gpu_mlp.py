@@ -126,7 +126,7 @@ def test_c1_tiny_mlp_1000_steps(ctx, oracle):
     assert last < first      # it trains
 
 
-@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_c4_reduced(ctx, oracle, mode):
     # BASELINE config 4 at reduced width: GELU hidden layers, softmax-CE, AdamW.
     opt = ("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01)
@@ -134,7 +134,7 @@ def test_c4_reduced(ctx, oracle, mode):
     assert max(drift) < 1e-4, f"loss drift over 5 steps: {drift}"
 
 
-@pytest.mark.parametrize("mode", ["simt", "3xtf32"])
+@pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_c5_reduced(ctx, oracle, mode):
     # BASELINE config 5 at reduced width/depth: tanh, MSE, AdamW.
     opt = ("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01)
