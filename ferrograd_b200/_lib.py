@@ -77,6 +77,29 @@ SIGNATURES = {
                                    C.POINTER(C.c_void_p)]),
     "fg_eltwise_chain_bwd": (i32, [c_ctx, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
                                    C.POINTER(C.c_void_p), i32]),
+    "fg_graph_create": (i32, [i32, i32, C.POINTER(C.c_void_p)]),
+    "fg_graph_destroy": (i32, [C.c_void_p]),
+    "fg_graph_node_count": (i32, [C.c_void_p]),
+    "fg_graph_input": (i32, [C.c_void_p, C.POINTER(u32), u32, C.POINTER(i32)]),
+    "fg_graph_constant_f32": (i32, [C.c_void_p, f32, C.POINTER(i32)]),
+    "fg_graph_op": (i32, [C.c_void_p, i32, i32, i32, C.POINTER(i32)]),
+    "fg_exec_create": (i32, [c_ctx, C.c_void_p, C.POINTER(u32), u32, i32, C.POINTER(C.c_void_p)]),
+    "fg_exec_destroy": (i32, [C.c_void_p]),
+    "fg_exec_set_adamw": (i32, [C.c_void_p, C.POINTER(AdamWHyper)]),
+    "fg_exec_bind": (i32, [C.c_void_p, C.POINTER(c_buf), u32, C.c_char_p]),
+    "fg_exec_dispatch_forward": (i32, [C.c_void_p]),
+    "fg_exec_dispatch_backward": (i32, [C.c_void_p]),
+    "fg_exec_dispatch_loss": (i32, [C.c_void_p, c_buf]),
+    "fg_exec_dispatch_optim": (i32, [C.c_void_p]),
+    "fg_exec_dispatch_single_optim": (i32, [C.c_void_p, c_buf, u32]),
+    "fg_exec_forward_out": (c_buf, [C.c_void_p]),
+    "fg_exec_seed": (c_buf, [C.c_void_p]),
+    "fg_exec_loss_t": (c_buf, [C.c_void_p]),
+    "fg_exec_num_saved": (u32, [C.c_void_p]),
+    "fg_exec_saved": (c_buf, [C.c_void_p, u32, C.POINTER(i32)]),
+    "fg_exec_num_grads": (u32, [C.c_void_p]),
+    "fg_exec_grad": (c_buf, [C.c_void_p, u32, C.POINTER(i32)]),
+    "fg_exec_forward_steps": (u32, [C.c_void_p]),
     "fg_plan_begin": (i32, [c_ctx]),
     "fg_plan_end": (i32, [c_ctx, C.POINTER(c_plan)]),
     "fg_plan_launch": (i32, [c_ctx, c_plan]),

@@ -1,0 +1,583 @@
+// Graph engine: ferrograd graphs executed with the hand-written kernels.
+//
+// What it stands in for.  In the reference a user builds a `Graph` of nodes
+// (crates/fused_gpu/src/dispatch/backend/mod.rs:500-506, :978-1316; ops from
+// crates/ferrograd/src/graph.rs:111-158), `compute_saved_nodes` decides what persists between
+// forward and backward (backend/mod.rs:1189-1208), `alloc_tensors` creates forward_saved /
+// grad_tensors / forward_out / seed / loss_t (dispatch/mod.rs:509-575), the lowering drivers turn the
+// graph into fused kernels (kernel/forward.rs:19-281, kernel/backward.rs:19-227, kernel/loss.rs,
+// kernel/optim.rs) and `schedule` binds buffers (dispatch/mod.rs:664-764).  Here the same graph is
+// lowered to calls of this library's entry points instead of generated code:
+//   * matmul, optionally followed by `+ bias[N]` and tanh/relu/gelu with single consumers, becomes
+//     one fg_gemm_f32 with a fused epilogue (the reference fuses trailing elementwise ops into the
+//     matmul kernel the same way: kernel/forward.rs:373-457); its backward is one fg_gemm_bwd_f32;
+//   * every maximal region of elementwise nodes becomes one fg_eltwise_chain_fwd and one
+//     fg_eltwise_chain_bwd (the reference inlines elementwise producers into their consumer:
+//     kernel/forward.rs:298-464);
+//   * softmax is fg_softmax_fwd / fg_softmax_bwd.
+// A node is materialised (gets a buffer) when it is a matmul/softmax/fused-GEMM result, the graph
+// output, has more than one consumer, or feeds a matmul/softmax; everything else lives in registers
+// inside a chain kernel.
+//
+// Deviations from the reference, by design: a softmax that ends the graph under the CROSS_ENTROPY
+// loss is not differentiated a second time (the loss kernel's p - onehot already is dL/dlogits;
+// the reference pushes it through the softmax backward again, dispatch/mod.rs:713-718); shapes
+// need not be multiples of 16; `add` accepts a bias of shape [N] or [1,N] after a matmul.
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "fg_internal.cuh"
+
+namespace {
+
+enum { OP_MATMUL = FG_GRAPH_MATMUL, OP_SOFTMAX = FG_GRAPH_SOFTMAX };
+
+struct GNode {
+    int op, a, b;
+    float imm;
+    std::vector<uint32_t> fields;   // INPUT: one metadata field id per dimension
+};
+
+inline bool is_ew(int op) { return op >= FG_EW_ADD && op <= FG_EW_ELU; }
+inline bool is_binary(int op) { return op >= FG_EW_ADD && op <= FG_EW_DIV; }
+
+}  // namespace
+
+struct fg_graph {
+    std::vector<GNode> nodes;
+    int loss, optim;
+};
+
+namespace {
+
+struct ENode {
+    std::vector<uint32_t> dims;
+    uint64_t numel = 0;
+    int consumers = 0;
+    bool materialized = false;   // has a value buffer
+    bool absorbed = false;       // computed inside a fused GEMM epilogue, never stored on its own
+    bool bias_bcast = false;     // ADD whose second operand is a [N] bias (legal only after a matmul)
+    fg_buf* value = nullptr;     // owned, or the bound input tensor
+    bool own_value = false;
+    fg_buf* grad = nullptr;      // owned
+    int input_slot = -1;         // index among the graph's inputs
+};
+
+struct GemmStep {
+    int mm, a, b, bias, act, out;   // node ids; bias = -1 when absent; out = node whose buffer receives the result
+    fg_buf* preact;                 // GELU needs the pre-activation
+};
+struct ChainStep {
+    int root;
+    std::vector<fg_ew_instr> prog;
+    std::vector<int> inputs;        // node ids of the loaded values
+};
+struct Step {
+    int kind;   // 0 gemm, 1 chain, 2 softmax
+    int idx;    // index into gemms / chains, or the softmax node id
+};
+
+}  // namespace
+
+struct fg_exec {
+    fg_ctx* ctx;
+    fg_graph g;
+    std::vector<uint32_t> meta;
+    int gemm_mode;
+    std::vector<ENode> n;
+    std::vector<GemmStep> gemms;
+    std::vector<ChainStep> chains;
+    std::vector<Step> fwd;          // in execution order; backward walks it in reverse
+    std::vector<int> inputs;        // node ids of INPUT nodes, in order
+    std::vector<int> saved;         // materialised non-input nodes except the output, in node order
+    std::vector<int> grads;         // nodes that own a gradient buffer, in node order
+    std::vector<uint8_t> trainable;
+    fg_buf *seed = nullptr, *loss_t = nullptr, *tmp = nullptr;
+    std::vector<fg_buf*> m, v;      // AdamW moments per input
+    fg_buf* step_counter = nullptr;
+    fg_adamw_hyper hyper{1e-3f, 0.9f, 0.999f, 1e-8f, 0.01f};
+    bool bound = false;
+    int last;                       // output node
+    bool ce_softmax_tail = false;   // graph ends in softmax and the loss is cross-entropy
+};
+
+namespace {
+
+int32_t fail(fg_exec* e, int32_t code, const char* msg) { return fg_fail(e->ctx, code, msg); }
+
+float* vptr(fg_exec* e, int node) { return (float*)e->n[node].value->ptr; }
+float* gptr(fg_exec* e, int node) { return (float*)e->n[node].grad->ptr; }
+
+// Emits the straight-line program that computes `node` from materialised values.
+int emit(fg_exec* e, ChainStep& c, int node, int root, int32_t* status) {
+    if (*status != FG_OK) return 0;
+    const GNode& gn = e->g.nodes[node];
+    auto push = [&](int op, int a, int b, float imm) -> int {
+        if ((int)c.prog.size() >= FG_EW_MAX_INSTR) { *status = FG_ERR_UNSUPPORTED_FEATURE; return 0; }
+        c.prog.push_back(fg_ew_instr{op, a, b, imm});
+        return (int)c.prog.size() - 1;
+    };
+    if (gn.op == FG_EW_CONST) return push(FG_EW_CONST, 0, 0, gn.imm);
+    if (node != root && (e->n[node].materialized || gn.op == FG_EW_INPUT)) {
+        int slot = -1;
+        for (size_t k = 0; k < c.inputs.size(); ++k) if (c.inputs[k] == node) slot = (int)k;
+        if (slot < 0) {
+            if ((int)c.inputs.size() >= FG_EW_MAX_INPUTS) { *status = FG_ERR_UNSUPPORTED_FEATURE; return 0; }
+            c.inputs.push_back(node);
+            slot = (int)c.inputs.size() - 1;
+        }
+        return push(FG_EW_INPUT, slot, 0, 0.0f);
+    }
+    int va = emit(e, c, gn.a, root, status);
+    int vb = is_binary(gn.op) ? emit(e, c, gn.b, root, status) : 0;
+    return push(gn.op, va, vb, 0.0f);
+}
+
+int32_t alloc_buf(fg_exec* e, uint64_t numel, bool zero, fg_buf** out) {
+    return zero ? fg_alloc_zeroed(e->ctx, numel * 4, out) : fg_alloc(e->ctx, numel * 4, out);
+}
+
+int act_of(int op) { return op == FG_EW_TANH ? FG_ACT_TANH : op == FG_EW_RELU ? FG_ACT_RELU : op == FG_EW_GELU ? FG_ACT_GELU : -1; }
+
+// The single consumer of `node`, or -1.
+int sole_consumer(const fg_exec* e, int node) {
+    if (e->n[node].consumers != 1) return -1;
+    for (size_t k = node + 1; k < e->g.nodes.size(); ++k) {
+        const GNode& c = e->g.nodes[k];
+        if (c.op == FG_EW_INPUT || c.op == FG_EW_CONST) continue;
+        if (c.a == node || ((is_binary(c.op) || c.op == OP_MATMUL) && c.b == node)) return (int)k;
+    }
+    return -1;
+}
+
+int32_t lower(fg_exec* e) {
+    fg_graph& g = e->g;
+    const int N = (int)g.nodes.size();
+    e->n.assign(N, ENode());
+    e->last = N - 1;
+    // ---- shapes (the reference's validate: backend/mod.rs:854-975) ----
+    for (int i = 0; i < N; ++i) {
+        const GNode& gn = g.nodes[i];
+        ENode& en = e->n[i];
+        if (gn.op == FG_EW_INPUT) {
+            for (uint32_t f : gn.fields) {
+                if (f >= e->meta.size()) return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: shape names a metadata field that is not bound");
+                en.dims.push_back(e->meta[f]);
+            }
+            en.input_slot = (int)e->inputs.size();
+            e->inputs.push_back(i);
+        } else if (gn.op == FG_EW_CONST) {
+            en.dims.clear();
+        } else if (gn.op == OP_MATMUL) {
+            const auto &da = e->n[gn.a].dims, &db = e->n[gn.b].dims;
+            if (da.size() != 2 || db.size() != 2 || da[1] != db[0])
+                return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: matmul needs [M,K] x [K,N]");
+            en.dims = {da[0], db[1]};
+        } else if (gn.op == OP_SOFTMAX) {
+            en.dims = e->n[gn.a].dims;
+            if (en.dims.empty()) return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: softmax of a scalar");
+        } else if (is_binary(gn.op)) {
+            const auto &da = e->n[gn.a].dims, &db = e->n[gn.b].dims;
+            const bool ca = g.nodes[gn.a].op == FG_EW_CONST, cb = g.nodes[gn.b].op == FG_EW_CONST;
+            if (ca && cb) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: operation on two constants");
+            if (ca) en.dims = db;
+            else if (cb) en.dims = da;
+            else if (da == db) en.dims = da;
+            else if (gn.op == FG_EW_ADD && da.size() == 2 && g.nodes[gn.b].op == FG_EW_INPUT &&
+                     ((db.size() == 1 && db[0] == da[1]) || (db.size() == 2 && db[0] == 1 && db[1] == da[1]))) {
+                en.dims = da;
+                en.bias_bcast = true;
+            } else return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: elementwise operands must have identical shapes");
+        } else if (is_ew(gn.op)) {
+            if (g.nodes[gn.a].op == FG_EW_CONST) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: unary op of a constant");
+            en.dims = e->n[gn.a].dims;
+        } else return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: unknown op");
+        en.numel = 1;
+        for (uint32_t d : en.dims) en.numel *= d;
+        if (gn.op != FG_EW_INPUT && gn.op != FG_EW_CONST) {
+            e->n[gn.a].consumers++;
+            if (is_binary(gn.op) || gn.op == OP_MATMUL) e->n[gn.b].consumers++;
+        }
+    }
+    if (g.nodes[e->last].op == FG_EW_INPUT || g.nodes[e->last].op == FG_EW_CONST)
+        return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: the last node must be an operation");
+    e->ce_softmax_tail = g.loss == FG_LOSS_CROSS_ENTROPY && g.nodes[e->last].op == OP_SOFTMAX;
+
+    // ---- fused GEMM patterns ----
+    std::vector<int> gemm_of_out(N, -1);
+    for (int i = 0; i < N; ++i) {
+        if (g.nodes[i].op != OP_MATMUL) continue;
+        if (g.nodes[g.nodes[i].a].op == FG_EW_CONST || g.nodes[g.nodes[i].b].op == FG_EW_CONST)
+            return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: matmul of a constant");
+        GemmStep s{i, g.nodes[i].a, g.nodes[i].b, -1, FG_ACT_NONE, i, nullptr};
+        int c = sole_consumer(e, s.out);
+        if (c >= 0 && e->n[c].bias_bcast && g.nodes[c].a == s.out) {
+            s.bias = g.nodes[c].b;
+            e->n[s.out].absorbed = true;
+            s.out = c;
+            c = sole_consumer(e, s.out);
+        }
+        if (c >= 0 && act_of(g.nodes[c].op) >= 0) {
+            s.act = act_of(g.nodes[c].op);
+            e->n[s.out].absorbed = true;
+            s.out = c;
+        }
+        gemm_of_out[s.out] = (int)e->gemms.size();
+        e->gemms.push_back(s);
+    }
+    for (int i = 0; i < N; ++i)
+        if (e->n[i].bias_bcast && !(i > 0 && e->n[g.nodes[i].a].absorbed))
+            return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: a broadcast bias is only supported directly after a matmul");
+
+    // ---- materialisation ----
+    for (int i = 0; i < N; ++i) {
+        const GNode& gn = g.nodes[i];
+        ENode& en = e->n[i];
+        if (gn.op == FG_EW_INPUT || gn.op == FG_EW_CONST || en.absorbed) continue;
+        if (gemm_of_out[i] >= 0 || gn.op == OP_SOFTMAX || i == e->last || en.consumers != 1) { en.materialized = true; continue; }
+        const int c = sole_consumer(e, i);
+        const int cop = g.nodes[c].op;
+        if (cop == OP_MATMUL || cop == OP_SOFTMAX) en.materialized = true;
+    }
+    // ---- buffers (alloc_tensors) ----
+    int32_t s;
+    for (int i = 0; i < N; ++i) {
+        ENode& en = e->n[i];
+        const bool is_input = g.nodes[i].op == FG_EW_INPUT;
+        if (en.materialized) {
+            if ((s = alloc_buf(e, en.numel, false, &en.value)) != FG_OK) return s;
+            en.own_value = true;
+            if (i != e->last) e->saved.push_back(i);
+        }
+        if ((is_input || en.materialized) && i != e->last) {
+            if ((s = alloc_buf(e, en.numel, true, &en.grad)) != FG_OK) return s;   // zeroed like the reference
+            e->grads.push_back(i);
+        }
+    }
+    const uint64_t on = e->n[e->last].numel;
+    if ((s = alloc_buf(e, on, true, &e->seed)) != FG_OK) return s;
+    if ((s = alloc_buf(e, on, true, &e->loss_t)) != FG_OK) return s;
+    uint64_t biggest = 1;
+    for (int i = 0; i < N; ++i) biggest = std::max(biggest, e->n[i].numel);
+    if ((s = alloc_buf(e, biggest, false, &e->tmp)) != FG_OK) return s;
+    for (GemmStep& gs : e->gemms)
+        if (gs.act == FG_ACT_GELU && (s = alloc_buf(e, e->n[gs.out].numel, false, &gs.preact)) != FG_OK) return s;
+    if (g.optim == FG_OPTIM_ADAMW) {
+        for (int id : e->inputs) {
+            fg_buf *m = nullptr, *v = nullptr;
+            if ((s = alloc_buf(e, e->n[id].numel, true, &m)) != FG_OK) return s;
+            if ((s = alloc_buf(e, e->n[id].numel, true, &v)) != FG_OK) return s;
+            e->m.push_back(m);
+            e->v.push_back(v);
+        }
+        if ((s = fg_alloc_zeroed(e->ctx, 256, &e->step_counter)) != FG_OK) return s;
+    }
+    // ---- forward step list ----
+    for (int i = 0; i < N; ++i) {
+        const GNode& gn = g.nodes[i];
+        if (!e->n[i].materialized) continue;
+        if (gemm_of_out[i] >= 0) { e->fwd.push_back(Step{0, gemm_of_out[i]}); continue; }
+        if (gn.op == OP_SOFTMAX) { e->fwd.push_back(Step{2, i}); continue; }
+        ChainStep c;
+        c.root = i;
+        int32_t st = FG_OK;
+        emit(e, c, i, i, &st);
+        if (st != FG_OK) return fail(e, st, "graph: an elementwise region exceeds the chain limits (24 instructions, 8 inputs)");
+        for (int in : c.inputs)
+            if (e->n[in].numel != e->n[i].numel) return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: elementwise operands must have identical shapes");
+        e->fwd.push_back(Step{1, (int)e->chains.size()});
+        e->chains.push_back(c);
+    }
+    // operands of matmul / softmax must have buffers
+    for (const GemmStep& gs : e->gemms)
+        if (!(e->n[gs.a].materialized || g.nodes[gs.a].op == FG_EW_INPUT) || !(e->n[gs.b].materialized || g.nodes[gs.b].op == FG_EW_INPUT))
+            return fail(e, FG_ERR_INTERNAL, "graph: matmul operand without a buffer");
+    return FG_OK;
+}
+
+// Adds `src` into grad[node] (used when a gradient gets a second contribution from a GEMM).
+int32_t accumulate_into(fg_exec* e, int node, const float* src) {
+    fg_ew_instr prog[3] = {{FG_EW_INPUT, 0, 0, 0.f}, {FG_EW_INPUT, 1, 0, 0.f}, {FG_EW_ADD, 0, 1, 0.f}};
+    const float* in[2] = {gptr(e, node), src};
+    return fg_eltwise_chain_fwd(e->ctx, e->n[node].numel, prog, 3, in, 2, gptr(e, node), nullptr);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fg_graph_create(int32_t loss, int32_t optim, fg_graph** out) {
+    if (!out || loss < FG_LOSS_MSE || loss > FG_LOSS_CROSS_ENTROPY || optim < FG_OPTIM_SGD || optim > FG_OPTIM_ADAMW)
+        return FG_ERR_INVALID_ARGUMENT;
+    fg_graph* g = new (std::nothrow) fg_graph();
+    if (!g) return FG_ERR_OUT_OF_MEMORY;
+    g->loss = loss;
+    g->optim = optim;
+    *out = g;
+    return FG_OK;
+}
+
+int32_t fg_graph_destroy(fg_graph* g) { delete g; return FG_OK; }
+
+int32_t fg_graph_node_count(const fg_graph* g) { return g ? (int32_t)g->nodes.size() : -1; }
+
+int32_t fg_graph_input(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t* node) {
+    if (!g || !shape_fields || !node || ndim < 1 || ndim > 4) return FG_ERR_INVALID_ARGUMENT;
+    GNode n{FG_EW_INPUT, -1, -1, 0.f, std::vector<uint32_t>(shape_fields, shape_fields + ndim)};
+    g->nodes.push_back(n);
+    *node = (int32_t)g->nodes.size() - 1;
+    return FG_OK;
+}
+
+int32_t fg_graph_constant_f32(fg_graph* g, float value, int32_t* node) {
+    if (!g || !node) return FG_ERR_INVALID_ARGUMENT;
+    g->nodes.push_back(GNode{FG_EW_CONST, -1, -1, value, {}});
+    *node = (int32_t)g->nodes.size() - 1;
+    return FG_OK;
+}
+
+int32_t fg_graph_op(fg_graph* g, int32_t op, int32_t a, int32_t b, int32_t* node) {
+    if (!g || !node) return FG_ERR_INVALID_ARGUMENT;
+    const int n = (int)g->nodes.size();
+    const bool two = is_binary(op) || op == OP_MATMUL;
+    if (!(is_ew(op) || op == OP_MATMUL || op == OP_SOFTMAX)) return FG_ERR_INVALID_ARGUMENT;
+    if (a < 0 || a >= n || (two && (b < 0 || b >= n))) return FG_ERR_INVALID_ARGUMENT;   // UnresolvedInput
+    g->nodes.push_back(GNode{op, a, two ? b : -1, 0.f, {}});
+    *node = n;
+    return FG_OK;
+}
+
+int32_t fg_exec_create(fg_ctx* ctx, const fg_graph* graph, const uint32_t* meta, uint32_t nmeta, int32_t gemm_mode,
+                       fg_exec** out) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, graph && meta && out && nmeta >= 1, "fg_exec_create: NULL argument");
+    FG_REQUIRE(ctx, !graph->nodes.empty(), "fg_exec_create: the graph is empty");   // ErrorKind::GraphEmpty
+    FG_REQUIRE(ctx, gemm_mode >= FG_GEMM_AUTO && gemm_mode <= FG_GEMM_TF32_BF16X2, "fg_exec_create: unknown GEMM mode");
+    fg_exec* e = new (std::nothrow) fg_exec();
+    if (!e) return fg_fail(ctx, FG_ERR_OUT_OF_MEMORY, "fg_exec_create");
+    e->ctx = ctx;
+    e->g = *graph;
+    e->meta.assign(meta, meta + nmeta);
+    e->gemm_mode = gemm_mode;
+    int32_t s = lower(e);
+    if (s != FG_OK) { fg_exec_destroy(e); return s; }
+    *out = e;
+    return FG_OK;
+}
+
+int32_t fg_exec_destroy(fg_exec* e) {
+    if (!e) return FG_OK;
+    for (ENode& en : e->n) {
+        if (en.own_value && en.value) fg_free(e->ctx, en.value);
+        if (en.grad) fg_free(e->ctx, en.grad);
+    }
+    for (GemmStep& gs : e->gemms) if (gs.preact) fg_free(e->ctx, gs.preact);
+    for (fg_buf* b : e->m) fg_free(e->ctx, b);
+    for (fg_buf* b : e->v) fg_free(e->ctx, b);
+    for (fg_buf* b : {e->seed, e->loss_t, e->tmp, e->step_counter}) if (b) fg_free(e->ctx, b);
+    delete e;
+    return FG_OK;
+}
+
+int32_t fg_exec_set_adamw(fg_exec* e, const fg_adamw_hyper* h) {
+    if (!e || !h) return FG_ERR_INVALID_ARGUMENT;
+    e->hyper = *h;
+    return FG_OK;
+}
+
+// schedule(): binds the user's tensors to the graph's inputs, in input order.
+int32_t fg_exec_bind(fg_exec* e, fg_buf* const* in_tensors, uint32_t count, const uint8_t* trainable) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(e->ctx, in_tensors && count == e->inputs.size(), "fg_exec_bind: one tensor per graph input is required");
+    for (uint32_t k = 0; k < count; ++k) {
+        FG_REQUIRE(e->ctx, in_tensors[k] != nullptr, "fg_exec_bind: NULL tensor");
+        FG_REQUIRE(e->ctx, in_tensors[k]->bytes >= e->n[e->inputs[k]].numel * 4, "fg_exec_bind: tensor smaller than the input's shape");
+        e->n[e->inputs[k]].value = in_tensors[k];
+    }
+    e->trainable.assign(count, 1);
+    if (trainable) e->trainable.assign(trainable, trainable + count);
+    e->bound = true;
+    return FG_OK;
+}
+
+int32_t fg_exec_dispatch_forward(fg_exec* e) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_forward: bind the input tensors first");
+    int32_t s;
+    for (const Step& st : e->fwd) {
+        if (st.kind == 0) {
+            const GemmStep& gs = e->gemms[st.idx];
+            const auto& da = e->n[gs.a].dims;
+            const auto& db = e->n[gs.b].dims;
+            s = fg_gemm_f32(e->ctx, e->gemm_mode, 0, 0, da[0], db[1], da[1], vptr(e, gs.a), vptr(e, gs.b), vptr(e, gs.out),
+                            gs.bias >= 0 ? vptr(e, gs.bias) : nullptr, gs.act, gs.preact ? (float*)gs.preact->ptr : nullptr);
+        } else if (st.kind == 1) {
+            const ChainStep& c = e->chains[st.idx];
+            const float* in[FG_EW_MAX_INPUTS];
+            for (size_t k = 0; k < c.inputs.size(); ++k) in[k] = vptr(e, c.inputs[k]);
+            s = fg_eltwise_chain_fwd(e->ctx, e->n[c.root].numel, c.prog.data(), (int)c.prog.size(), in,
+                                     (int)c.inputs.size(), vptr(e, c.root), nullptr);
+        } else {
+            const auto& d = e->n[st.idx].dims;
+            const uint32_t cols = d.back();
+            s = fg_softmax_fwd(e->ctx, (uint32_t)(e->n[st.idx].numel / cols), cols, vptr(e, e->g.nodes[st.idx].a), vptr(e, st.idx));
+        }
+        if (s != FG_OK) return s;
+    }
+    return FG_OK;
+}
+
+int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(e->ctx, target != nullptr, "dispatch_loss: target is NULL");
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_loss: bind the input tensors first");
+    const ENode& o = e->n[e->last];
+    if (e->g.loss == FG_LOSS_MSE) {
+        FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
+        return fg_mse_loss_grad(e->ctx, vptr(e, e->last), (const float*)target->ptr, o.numel, 1.0f, (float*)e->loss_t->ptr,
+                                nullptr, (float*)e->seed->ptr);
+    }
+    const uint32_t cols = o.dims.back();
+    const uint32_t rows = (uint32_t)(o.numel / cols);
+    FG_REQUIRE(e->ctx, target->bytes >= (uint64_t)rows * 4, "dispatch_loss: one u32 label per row is required");
+    return fg_ce_loss_grad(e->ctx, vptr(e, e->last), (const uint32_t*)target->ptr, rows, cols, (float*)e->loss_t->ptr,
+                           (float*)e->seed->ptr);
+}
+
+int32_t fg_exec_dispatch_backward(fg_exec* e) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_backward: bind the input tensors first");
+    const int N = (int)e->n.size();
+    std::vector<uint8_t> written(N, 0);
+    auto grad_of = [&](int node) -> float* { return node == e->last ? (float*)e->seed->ptr : gptr(e, node); };
+    int32_t s;
+    for (int k = (int)e->fwd.size() - 1; k >= 0; --k) {
+        const Step& st = e->fwd[k];
+        if (st.kind == 0) {
+            const GemmStep& gs = e->gemms[st.idx];
+            if (gs.out != e->last && !written[gs.out]) continue;   // does not reach the output
+            const auto& da = e->n[gs.a].dims;
+            const auto& db = e->n[gs.b].dims;
+            const uint32_t M = da[0], K = da[1], Nn = db[1];
+            // destinations: the gradient buffer itself for a first contribution, the scratch tensor otherwise
+            float* dA = written[gs.a] ? (float*)e->tmp->ptr : gptr(e, gs.a);
+            const float* saved = gs.act == FG_ACT_NONE ? nullptr : gs.act == FG_ACT_GELU ? (float*)gs.preact->ptr : vptr(e, gs.out);
+            float* dbias = nullptr;
+            if (gs.bias >= 0) dbias = written[gs.bias] ? nullptr : gptr(e, gs.bias);
+            if (gs.bias >= 0 && written[gs.bias]) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: a bias used by two layers");
+            if (!written[gs.a] && !written[gs.b] && gs.a != gs.b) {
+                // the common case: one call computes dZ once and both products from it
+                s = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act,
+                                    saved, gptr(e, gs.a), gptr(e, gs.b), dbias, nullptr);
+                if (s != FG_OK) return s;
+                written[gs.a] = written[gs.b] = 1;
+                if (gs.bias >= 0) written[gs.bias] = 1;
+                continue;
+            }
+            // dA first (it may need the scratch tensor), then dB
+            s = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved,
+                                dA, nullptr, dbias, nullptr);
+            if (s != FG_OK) return s;
+            if (written[gs.a] && (s = accumulate_into(e, gs.a, dA)) != FG_OK) return s;
+            written[gs.a] = 1;
+            if (gs.bias >= 0) written[gs.bias] = 1;
+            float* dB = written[gs.b] ? (float*)e->tmp->ptr : gptr(e, gs.b);
+            s = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved,
+                                nullptr, dB, nullptr, nullptr);
+            if (s != FG_OK) return s;
+            if (written[gs.b] && (s = accumulate_into(e, gs.b, dB)) != FG_OK) return s;
+            written[gs.b] = 1;
+        } else if (st.kind == 1) {
+            const ChainStep& c = e->chains[st.idx];
+            if (c.root != e->last && !written[c.root]) continue;
+            const float* in[FG_EW_MAX_INPUTS];
+            float* gr[FG_EW_MAX_INPUTS];
+            bool any_written = false;
+            for (size_t j = 0; j < c.inputs.size(); ++j) any_written |= written[c.inputs[j]] != 0;
+            for (size_t j = 0; j < c.inputs.size(); ++j) {
+                in[j] = vptr(e, c.inputs[j]);
+                gr[j] = gptr(e, c.inputs[j]);
+                if (any_written && !written[c.inputs[j]] &&
+                    (s = fg_memset_zero(e->ctx, gr[j], e->n[c.inputs[j]].numel * 4)) != FG_OK) return s;
+            }
+            s = fg_eltwise_chain_bwd(e->ctx, e->n[c.root].numel, c.prog.data(), (int)c.prog.size(), in, (int)c.inputs.size(),
+                                     grad_of(c.root), gr, any_written ? 1 : 0);
+            if (s != FG_OK) return s;
+            for (int id : c.inputs) written[id] = 1;
+        } else {
+            const int node = st.idx, src = e->g.nodes[node].a;
+            if (node != e->last && !written[node]) continue;
+            const auto& d = e->n[node].dims;
+            const uint32_t cols = d.back(), rows = (uint32_t)(e->n[node].numel / cols);
+            if (node == e->last && e->ce_softmax_tail) {
+                // the loss kernel's p - onehot is already dL/dlogits
+                if (written[src]) s = accumulate_into(e, src, (const float*)e->seed->ptr);
+                else {
+                    cudaError_t ce = cudaMemcpyAsync(gptr(e, src), e->seed->ptr, e->n[src].numel * 4, cudaMemcpyDeviceToDevice, e->ctx->stream);
+                    s = ce == cudaSuccess ? FG_OK : fg_fail_cuda(e->ctx, FG_ERR_FAILED_BUFFER_COPY, "seed copy", ce);
+                }
+            } else {
+                s = fg_softmax_bwd(e->ctx, rows, cols, vptr(e, node), grad_of(node), gptr(e, src), written[src] ? 1 : 0);
+            }
+            if (s != FG_OK) return s;
+            written[src] = 1;
+        }
+    }
+    return FG_OK;
+}
+
+static int32_t optim_one(fg_exec* e, uint32_t slot, fg_buf* weight) {
+    const int node = e->inputs[slot];
+    float lr;
+    memcpy(&lr, &e->meta[0], 4);   // field 0 holds the learning rate's bits (kernel/optim.rs:119-131)
+    if (e->g.optim == FG_OPTIM_SGD)
+        return fg_sgd_step(e->ctx, (float*)weight->ptr, gptr(e, node), e->n[node].numel, lr, 1.0f, 1);
+    fg_adamw_hyper h = e->hyper;
+    h.lr = lr;
+    return fg_adamw_step(e->ctx, (float*)weight->ptr, gptr(e, node), (float*)e->m[slot]->ptr, (float*)e->v[slot]->ptr,
+                         e->n[node].numel, &h, 0, (const uint32_t*)e->step_counter->ptr, 1.0f, 1);
+}
+
+// Updates every bound tensor that is marked trainable (the reference updates all of them:
+// dispatch/mod.rs:735-748) and zeroes its gradient.
+int32_t fg_exec_dispatch_optim(fg_exec* e) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_optim: bind the input tensors first");
+    int32_t s;
+    if (e->g.optim == FG_OPTIM_ADAMW && (s = fg_counter_increment(e->ctx, (uint32_t*)e->step_counter->ptr)) != FG_OK) return s;
+    for (uint32_t k = 0; k < e->inputs.size(); ++k)
+        if (e->trainable[k] && (s = optim_one(e, k, e->n[e->inputs[k]].value)) != FG_OK) return s;
+    return FG_OK;
+}
+
+// dispatch_single_optim (dispatch/mod.rs:790-814): one weight, its gradient chosen by index.
+int32_t fg_exec_dispatch_single_optim(fg_exec* e, fg_buf* weight, uint32_t grad_index) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(e->ctx, weight != nullptr, "dispatch_single_optim: weight is NULL");
+    FG_REQUIRE(e->ctx, grad_index < e->grads.size() && e->n[e->grads[grad_index]].input_slot >= 0,
+               "dispatch_single_optim: grad index does not name an input's gradient");
+    const uint32_t slot = (uint32_t)e->n[e->grads[grad_index]].input_slot;
+    FG_REQUIRE(e->ctx, weight->bytes >= e->n[e->inputs[slot]].numel * 4, "dispatch_single_optim: weight smaller than its gradient");
+    return optim_one(e, slot, weight);
+}
+
+fg_buf* fg_exec_forward_out(fg_exec* e) { return e ? e->n[e->last].value : nullptr; }
+fg_buf* fg_exec_seed(fg_exec* e) { return e ? e->seed : nullptr; }
+fg_buf* fg_exec_loss_t(fg_exec* e) { return e ? e->loss_t : nullptr; }
+uint32_t fg_exec_num_saved(fg_exec* e) { return e ? (uint32_t)e->saved.size() : 0; }
+fg_buf* fg_exec_saved(fg_exec* e, uint32_t i, int32_t* node) {
+    if (!e || i >= e->saved.size()) return nullptr;
+    if (node) *node = e->saved[i];
+    return e->n[e->saved[i]].value;
+}
+uint32_t fg_exec_num_grads(fg_exec* e) { return e ? (uint32_t)e->grads.size() : 0; }
+fg_buf* fg_exec_grad(fg_exec* e, uint32_t i, int32_t* node) {
+    if (!e || i >= e->grads.size()) return nullptr;
+    if (node) *node = e->grads[i];
+    return e->n[e->grads[i]].grad;
+}
+// Number of kernels the forward pass launches per dispatch (how much was fused).
+uint32_t fg_exec_forward_steps(fg_exec* e) { return e ? (uint32_t)e->fwd.size() : 0; }
+
+}  // extern "C"

@@ -243,6 +243,51 @@ int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, i
                              const float* const* inputs, int32_t ninputs, const float* seed,
                              float* const* grads, int32_t accumulate);
 
+/* ---- graphs: the reference's Graph -> alloc_tensors -> schedule -> dispatch_* flow ----
+ * A graph is a list of nodes in definition order (Graph::push_node,
+ * crates/fused_gpu/src/dispatch/backend/mod.rs:1224; ops: crates/ferrograd/src/graph.rs:111-158).
+ * Elementwise ops use the fg_ew_op codes; matmul and softmax have the two codes below.  An input's
+ * shape is a list of metadata FIELD ids (Metadata::new_field, backend/mod.rs:585-596); field 0 is
+ * reserved for the learning rate's f32 bits, the bound metadata array gives every field its value. */
+enum fg_graph_op { FG_GRAPH_MATMUL = 14, FG_GRAPH_SOFTMAX = 15 };
+enum fg_loss { FG_LOSS_MSE = 0, FG_LOSS_CROSS_ENTROPY = 1 };   /* loss/basic_loss.rs:3-27, :91-133 */
+enum fg_optim { FG_OPTIM_SGD = 0, FG_OPTIM_ADAMW = 1 };        /* optim/basic_optim.rs:3-31; AdamW is new */
+typedef struct fg_graph fg_graph;   /* ferrograd::Graph (crates/ferrograd/src/graph.rs:15-98)        */
+typedef struct fg_exec fg_exec;     /* AllocTensors + compiled kernels + Schedule of one graph        */
+
+int32_t fg_graph_create(int32_t loss, int32_t optim, fg_graph** out);            /* Graph::new        */
+int32_t fg_graph_destroy(fg_graph* g);
+int32_t fg_graph_node_count(const fg_graph* g);
+int32_t fg_graph_input(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t* node); /* DefineOps::input */
+int32_t fg_graph_constant_f32(fg_graph* g, float value, int32_t* node);          /* constant_f32      */
+/* op: FG_EW_ADD..FG_EW_ELU, FG_GRAPH_MATMUL, FG_GRAPH_SOFTMAX; b is ignored for unary ops.          */
+int32_t fg_graph_op(fg_graph* g, int32_t op, int32_t a, int32_t b, int32_t* node);
+/* compute_saved_nodes + validate + alloc_tensors + lower + compile, for one metadata binding
+ * (backend/mod.rs:1172-1208; dispatch/mod.rs:369-455, :509-575).  The graph is copied. */
+int32_t fg_exec_create(fg_ctx* ctx, const fg_graph* g, const uint32_t* meta, uint32_t nmeta,
+                       int32_t gemm_mode, fg_exec** out);
+int32_t fg_exec_destroy(fg_exec* e);
+int32_t fg_exec_set_adamw(fg_exec* e, const fg_adamw_hyper* hyper);   /* lr is taken from meta[0] */
+/* schedule (dispatch/mod.rs:664-764): one tensor per graph input, in input order.  trainable
+ * (NULL = all, as in the reference) selects which of them dispatch_optim updates. */
+int32_t fg_exec_bind(fg_exec* e, fg_buf* const* in_tensors, uint32_t count, const uint8_t* trainable);
+int32_t fg_exec_dispatch_forward(fg_exec* e);                         /* dispatch/mod.rs:766 */
+int32_t fg_exec_dispatch_backward(fg_exec* e);                        /* :770                */
+int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target);      /* :774-788            */
+int32_t fg_exec_dispatch_optim(fg_exec* e);                           /* :790                */
+int32_t fg_exec_dispatch_single_optim(fg_exec* e, fg_buf* weight, uint32_t grad_index); /* :794-814 */
+/* AllocTensors (dispatch/mod.rs:835-845).  Saved tensors are the materialised intermediate nodes
+ * in node order (a matmul result is always one); gradients exist for every input and every
+ * materialised intermediate node, in node order.  `node` (may be NULL) receives the node id. */
+fg_buf* fg_exec_forward_out(fg_exec* e);
+fg_buf* fg_exec_seed(fg_exec* e);
+fg_buf* fg_exec_loss_t(fg_exec* e);
+uint32_t fg_exec_num_saved(fg_exec* e);
+fg_buf* fg_exec_saved(fg_exec* e, uint32_t i, int32_t* node);
+uint32_t fg_exec_num_grads(fg_exec* e);
+fg_buf* fg_exec_grad(fg_exec* e, uint32_t i, int32_t* node);
+uint32_t fg_exec_forward_steps(fg_exec* e);   /* kernels-level steps of one forward dispatch */
+
 /* ---- plans: a captured CUDA graph, the analogue of GpuBackend::schedule /
  *      dispatch_schedule (dispatch/mod.rs:218-250; rocm/mod.rs:324-389 captures a
  *      hipGraph the same way) ----
