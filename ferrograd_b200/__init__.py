@@ -8,3 +8,4 @@ mirrors its graph API (Graph / define_ops / alloc_tensors / schedule / dispatch_
 from .backend import Buffer, FgError, GpuContext, Plan, Tensor  # noqa: F401
 from .graph import (CROSS_ENTROPY, MEAN_SQUARED_ERROR, Graph, Metadata, Optim, SimpleDType,  # noqa: F401
                     f32_bits)
+from . import bpat  # noqa: F401,E402

@@ -100,6 +100,14 @@ SIGNATURES = {
     "fg_exec_num_grads": (u32, [C.c_void_p]),
     "fg_exec_grad": (c_buf, [C.c_void_p, u32, C.POINTER(i32)]),
     "fg_exec_forward_steps": (u32, [C.c_void_p]),
+    "fg_bpat_save": (i32, [c_ctx, C.c_char_p, i32, u32, C.POINTER(c_buf), C.POINTER(u32),
+                           C.POINTER(C.POINTER(u32))]),
+    "fg_bpat_open": (i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "fg_bpat_close": (i32, [C.c_void_p]),
+    "fg_bpat_format": (i32, [C.c_void_p]),
+    "fg_bpat_count": (u32, [C.c_void_p]),
+    "fg_bpat_shape": (i32, [C.c_void_p, u32, C.POINTER(u32), C.POINTER(u32)]),
+    "fg_bpat_load_tensor": (i32, [c_ctx, C.c_void_p, u32, C.POINTER(c_buf)]),
     "fg_plan_begin": (i32, [c_ctx]),
     "fg_plan_end": (i32, [c_ctx, C.POINTER(c_plan)]),
     "fg_plan_launch": (i32, [c_ctx, c_plan]),

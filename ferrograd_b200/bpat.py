@@ -1,0 +1,62 @@
+"""`.bpat` checkpoints through the C ABI: the reference's `save_tensors` / `load_tensors`
+(crates/fused_gpu/src/io/mod.rs:98-159, exposed on GpuContext at crates/fused_gpu/src/dispatch/mod.rs:816-833).
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from .backend import Buffer, FgError, GpuContext, Tensor
+
+# BpatHeader of the reference (crates/fused_gpu/src/io/mod.rs): the formats this backend can write / read
+V0, V1, V1_MICRO, V2_F32 = 0, 1, 2, 3
+
+
+def inspect(path):
+    """Header, shapes (and checksum verification) without a device: [(shape...)], format."""
+    lib = _lib.load()
+    h = C.c_void_p()
+    code = lib.fg_bpat_open(str(path).encode(), C.byref(h))
+    if code != 0:
+        raise FgError(code, f"cannot read {path}: missing, truncated, or a checksum does not match")
+    try:
+        shapes = []
+        for i in range(lib.fg_bpat_count(h)):
+            nd, dims = C.c_uint32(), (C.c_uint32 * 8)()
+            lib.fg_bpat_shape(h, i, C.byref(nd), dims)
+            shapes.append(tuple(dims[d] for d in range(nd.value)))
+        return shapes, lib.fg_bpat_format(h)
+    finally:
+        lib.fg_bpat_close(h)
+
+
+def save_tensors(ctx, path, tensors, header=V2_F32):
+    n = len(tensors)
+    bufs = (C.c_void_p * n)(*[t.as_buffer().handle for t in tensors])
+    ndims = (C.c_uint32 * n)(*[len(t.shape) for t in tensors])
+    shape_arrays = [(C.c_uint32 * len(t.shape))(*t.shape) for t in tensors]
+    shapes = (C.POINTER(C.c_uint32) * n)(*[C.cast(a, C.POINTER(C.c_uint32)) for a in shape_arrays])
+    ctx._check(ctx.lib.fg_bpat_save(ctx.handle, str(path).encode(), int(header), n, bufs, ndims, shapes))
+
+
+def load_tensors(ctx, path):
+    lib = ctx.lib
+    h = C.c_void_p()
+    code = lib.fg_bpat_open(str(path).encode(), C.byref(h))
+    if code != 0:
+        raise FgError(code, f"cannot read {path}: missing, truncated, or a checksum does not match")
+    try:
+        out = []
+        for i in range(lib.fg_bpat_count(h)):
+            nd, dims = C.c_uint32(), (C.c_uint32 * 8)()
+            lib.fg_bpat_shape(h, i, C.byref(nd), dims)
+            b = C.c_void_p()
+            ctx._check(lib.fg_bpat_load_tensor(ctx.handle, h, i, C.byref(b)))
+            out.append(Tensor(tuple(dims[d] for d in range(nd.value)), Buffer(ctx, b), np.float32))
+        return out
+    finally:
+        lib.fg_bpat_close(h)
+
+
+GpuContext.save_tensors = lambda self, path, tensors, header=V2_F32: save_tensors(self, path, tensors, header)
+GpuContext.load_tensors = lambda self, path: load_tensors(self, path)

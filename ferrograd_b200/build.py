@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libferrograd_b200.so")
-SOURCES = ["ctx.cu", "optim.cu", "softmax.cu", "eltwise.cu", "gemm_simt.cu", "gemm_tc.cu", "mse_noalloc.cu", "graph.cu"]
+SOURCES = ["ctx.cu", "optim.cu", "softmax.cu", "eltwise.cu", "gemm_simt.cu", "gemm_tc.cu", "mse_noalloc.cu", "graph.cu", "bpat.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--fmad=false", "-Xcompiler", "-fPIC", "-cudart", "static"]
 

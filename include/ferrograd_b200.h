@@ -288,6 +288,21 @@ uint32_t fg_exec_num_grads(fg_exec* e);
 fg_buf* fg_exec_grad(fg_exec* e, uint32_t i, int32_t* node);
 uint32_t fg_exec_forward_steps(fg_exec* e);   /* kernels-level steps of one forward dispatch */
 
+/* ---- .bpat tensor files (crates/fused_gpu/src/io/headers.rs:16-117; save_tensors / load_tensors:
+ *      crates/fused_gpu/src/io/mod.rs:98-159) ----
+ * Reading accepts v0, v1, v1m and v2-f32 and verifies the CRC-32s of v1/v1m; writing produces
+ * v2-f32 or v1m.  Tensors are f32 on the device; f64 files are narrowed on load. */
+enum fg_bpat_format { FG_BPAT_V0 = 0, FG_BPAT_V1 = 1, FG_BPAT_V1_MICRO = 2, FG_BPAT_V2_F32 = 3 };
+typedef struct fg_bpat_file fg_bpat_file;
+int32_t fg_bpat_save(fg_ctx* ctx, const char* path, int32_t format, uint32_t count, fg_buf* const* tensors,
+                     const uint32_t* ndims, const uint32_t* const* shapes);
+int32_t fg_bpat_open(const char* path, fg_bpat_file** out);   /* no device needed */
+int32_t fg_bpat_close(fg_bpat_file* f);
+int32_t fg_bpat_format(const fg_bpat_file* f);
+uint32_t fg_bpat_count(const fg_bpat_file* f);
+int32_t fg_bpat_shape(const fg_bpat_file* f, uint32_t index, uint32_t* ndim, uint32_t dims_out[8]);
+int32_t fg_bpat_load_tensor(fg_ctx* ctx, const fg_bpat_file* f, uint32_t index, fg_buf** out);
+
 /* ---- plans: a captured CUDA graph, the analogue of GpuBackend::schedule /
  *      dispatch_schedule (dispatch/mod.rs:218-250; rocm/mod.rs:324-389 captures a
  *      hipGraph the same way) ----
