@@ -18,6 +18,7 @@ def main():
     ap.add_argument("case", choices=["gemm", "gemm_bwd", "softmax_ce", "adamw", "sgd", "mlp"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--n", type=int, default=0, help="override the problem size")
+    ap.add_argument("--mode", default="auto", choices=["auto", "simt", "3xtf32", "tf32_bf16x2"], help="GEMM mode")
     a = ap.parse_args()
     ctx = GpuContext(0)
     r = np.random.Generator(np.random.Philox(1))
@@ -29,13 +30,13 @@ def main():
         Cm = ctx.new_tensor((n, n))
         if a.case == "gemm":
             for _ in range(a.iters):
-                ctx.gemm(A, B, Cm, n, n, n, bias=bias, act="relu", mode="3xtf32")
+                ctx.gemm(A, B, Cm, n, n, n, bias=bias, act="relu", mode=a.mode)
         else:
             dY = ctx.init_tensor_f32((n, n), r.standard_normal((n, n), np.float32))
-            ctx.gemm(A, B, Cm, n, n, n, bias=bias, act="relu", mode="3xtf32")
+            ctx.gemm(A, B, Cm, n, n, n, bias=bias, act="relu", mode=a.mode)
             dA, dB = ctx.new_tensor((n, n)), ctx.new_tensor((n, n))
             for _ in range(a.iters):
-                ctx.gemm_bwd(A, B, dY, n, n, n, act="relu", saved=Cm, dA=dA, dB=dB, mode="3xtf32")
+                ctx.gemm_bwd(A, B, dY, n, n, n, act="relu", saved=Cm, dA=dA, dB=dB, mode=a.mode)
     elif a.case == "softmax_ce":
         rows, cols = a.n or 2048, 32000
         x = ctx.init_tensor_f32((rows, cols), 2.0 * r.standard_normal((rows, cols), np.float32))

@@ -336,8 +336,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
-    const uint32_t m0 = (blockIdx.x >> 1) * (2 * BM) + rank * BM;   // this CTA's rows of A and C
-    const uint32_t n0 = blockIdx.y * BN;                            // the pair's columns of C
+    // Tile order: pairs are numbered so that eight consecutive pair-rows sweep all columns before the
+    // next eight start.  A wave of 74 pairs then covers a squarish block of C and re-uses both its A rows
+    // and its B rows from L2 (with rows-fastest order every wave streamed all of A again: 7.7x the
+    // operand bytes from DRAM at 8192^3).
+    const uint32_t pairs_m = (ep.M + 2 * BM - 1) / (2 * BM), pairs_n = (ep.N + BN - 1) / BN;
+    constexpr uint32_t kGroup = 8;
+    const uint32_t pid = blockIdx.x >> 1;
+    const uint32_t grp = pid / (kGroup * pairs_n);
+    const uint32_t grp_rows = min(kGroup, pairs_m - grp * kGroup);
+    const uint32_t rem = pid - grp * kGroup * pairs_n;
+    const uint32_t pm = grp * kGroup + rem % grp_rows, pn = rem / grp_rows;
+    (void)pairs_n;
+    const uint32_t m0 = pm * (2 * BM) + rank * BM;                  // this CTA's rows of A and C
+    const uint32_t n0 = pn * BN;                                    // the pair's columns of C
     const uint32_t nb0 = n0 + rank * HB;                            // the rows of B this CTA loads
     const uint32_t nkb = (ep.K + BK - 1) / BK;
     constexpr uint32_t kChunkKB = kChunkK / BK;
@@ -779,8 +791,9 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
                 cudaFuncSetAttribute(gemm_tc_pair_kernel<BK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_done |= 1ull << (ctx->device & 63);
     }
-    dim3 grid(2 * ((ep.M + 2 * BM - 1) / (2 * BM)), (ep.N + Cfg::kBN - 1) / Cfg::kBN);   // x: CTA pairs along M
-    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: N too large");
+    const uint64_t npairs = (uint64_t)((ep.M + 2 * BM - 1) / (2 * BM)) * ((ep.N + Cfg::kBN - 1) / Cfg::kBN);
+    if (npairs > (1ull << 30)) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: too many tiles");
+    dim3 grid((unsigned)(2 * npairs));   // two CTAs per pair; the kernel maps pair ids to tiles
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
     gemm_tc_pair_kernel<BK, FMT><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
     fg_time_end(ctx, tr);
