@@ -57,6 +57,10 @@ SIGNATURES = {
     "fg_copy": (i32, [c_ctx, c_buf, c_buf]),
     "fg_upload_async": (i32, [c_ctx, c_dev, C.c_void_p, u64]),
     "fg_download_async": (i32, [c_ctx, C.c_void_p, c_dev, u64]),
+    "fg_upload_prefetch": (i32, [c_ctx, c_dev, C.c_void_p, u64]),
+    "fg_prefetch_wait": (i32, [c_ctx]),
+    "fg_prefetch_mark": (i32, [c_ctx]),
+    "fg_copy_dev_async": (i32, [c_ctx, c_dev, c_dev, u64]),
     "fg_host_alloc_pinned": (i32, [u64, C.POINTER(C.c_void_p)]),
     "fg_host_free_pinned": (i32, [C.c_void_p]),
     "fg_memset_zero": (i32, [c_ctx, c_dev, u64]),

@@ -215,6 +215,18 @@ class GpuContext:
     def download_async(self, pinned_ptr, src, nbytes):
         self._check(self.lib.fg_download_async(self.handle, pinned_ptr, _ptr(src), int(nbytes)))
 
+    def upload_prefetch(self, dst, pinned_ptr, nbytes):
+        self._check(self.lib.fg_upload_prefetch(self.handle, _ptr(dst), pinned_ptr, int(nbytes)))
+
+    def prefetch_wait(self):
+        self._check(self.lib.fg_prefetch_wait(self.handle))
+
+    def prefetch_mark(self):
+        self._check(self.lib.fg_prefetch_mark(self.handle))
+
+    def copy_dev_async(self, dst, src, nbytes):
+        self._check(self.lib.fg_copy_dev_async(self.handle, _ptr(dst), _ptr(src), int(nbytes)))
+
     def pinned_array(self, shape, dtype=np.float32):
         """A numpy array over page-locked host memory (kept alive by the returned array)."""
         n = int(np.prod(shape)) * np.dtype(dtype).itemsize

@@ -86,6 +86,9 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
         c->own_stream = true;
     }
     if (cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_copy_done, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_main_mark, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
         cudaMalloc((void**)&c->dev_status, 256) != cudaSuccess ||
@@ -119,6 +122,10 @@ int32_t fg_ctx_destroy(fg_ctx* ctx) {
     cudaEventDestroy(ctx->ev_fork);
     cudaEventDestroy(ctx->ev_join);
     cudaStreamDestroy(ctx->comm_stream);
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+    cudaEventDestroy(ctx->ev_copy_done);
+    cudaEventDestroy(ctx->ev_main_mark);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return FG_OK;
@@ -128,6 +135,7 @@ int32_t fg_sync(fg_ctx* ctx) {
     if (!ctx) return FG_ERR_NOT_INITIALIZED;
     FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
     FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->comm_stream));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->copy_stream));
     FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamSynchronize(ctx->stream));
     int status = 0;
     FG_CUDA(ctx, FG_ERR_SYNC, cudaMemcpy(&status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
@@ -309,6 +317,44 @@ int32_t fg_download_async(fg_ctx* ctx, void* dst_pinned, const void* src_dev, ui
     FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
     FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
             cudaMemcpyAsync(dst_pinned, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return FG_OK;
+}
+
+// ---- input prefetch: host->device copies on a side stream, overlapped with compute ----
+int32_t fg_upload_prefetch(fg_ctx* ctx, void* dst_dev, const void* src_pinned, uint64_t bytes) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, dst_dev && src_pinned, "fg_upload_prefetch: NULL argument");
+    if (ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "fg_upload_prefetch while recording a plan");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    // do not overwrite the destination before the compute stream has passed the last fg_prefetch_mark
+    if (ctx->mark_valid) FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_main_mark, 0));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync(dst_dev, src_pinned, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
+    return FG_OK;
+}
+
+int32_t fg_prefetch_wait(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->stream, ctx->ev_copy_done, 0));
+    return FG_OK;
+}
+
+int32_t fg_prefetch_mark(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_main_mark, ctx->stream));
+    ctx->mark_valid = true;
+    return FG_OK;
+}
+
+int32_t fg_copy_dev_async(fg_ctx* ctx, void* dst_dev, const void* src_dev, uint64_t bytes) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, dst_dev && src_dev, "fg_copy_dev_async: NULL argument");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
+            cudaMemcpyAsync(dst_dev, src_dev, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return FG_OK;
 }
 

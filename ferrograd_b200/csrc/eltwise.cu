@@ -210,6 +210,12 @@ int32_t fg_act_bwd_launch(fg_ctx* ctx, uint64_t n, int act, const float* dy, con
     return FG_OK;
 }
 
+int32_t fg_colsum_fold_launch(fg_ctx* ctx, uint32_t cols, uint32_t nchunks, const float* part, float* out) {
+    colsum_fold_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(cols, nchunks, part, out);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
 int32_t fg_colsum_launch(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* x, float* out) {
     const uint32_t chunk = 256;
     const uint32_t nchunks = (rows + chunk - 1) / chunk;

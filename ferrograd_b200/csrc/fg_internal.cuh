@@ -38,6 +38,9 @@ struct fg_ctx {
     cudaStream_t comm_stream;
     cudaEvent_t ev_fork, ev_join;
     bool comm_pending;
+    cudaStream_t copy_stream;           // host->device prefetches that overlap compute
+    cudaEvent_t ev_copy_done, ev_main_mark;
+    bool mark_valid;
     char err[512];
     uint64_t launches;          // kernels launched so far (eager + replayed plans)
     bool capturing;
@@ -165,3 +168,4 @@ int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uin
                             float* preact_out);
 int32_t fg_act_bwd_launch(fg_ctx* ctx, uint64_t n, int act, const float* dy, const float* saved, float* dz);
 int32_t fg_colsum_launch(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* x, float* out);
+int32_t fg_colsum_fold_launch(fg_ctx* ctx, uint32_t cols, uint32_t nchunks, const float* part, float* out);

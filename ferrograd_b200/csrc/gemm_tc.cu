@@ -548,6 +548,7 @@ struct SplitArgs {
     uint32_t R, C;
     PlaneSet n, t;         // p32 == NULL: orientation not wanted
     float* value_out;      // optional copy of the (fused) value, [R, C]
+    float* colsum_part;    // optional [gridDim.y][C]: column sums of the value over each tile's rows (bias gradient)
 };
 
 template <int FMT>
@@ -566,8 +567,10 @@ __device__ __forceinline__ void store_planes(const PlaneSet& ps, size_t rows, si
 template <int FMT>
 __global__ void __launch_bounds__(256) split_kernel(SplitArgs a) {
     __shared__ float tv[32][33];
+    __shared__ float cs[8][33];
     const uint32_t c = blockIdx.x * 32 + threadIdx.x;
     const uint32_t r0 = blockIdx.y * 32;
+    float csum = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t r = r0 + threadIdx.y + i * 8;
@@ -584,9 +587,18 @@ __global__ void __launch_bounds__(256) split_kernel(SplitArgs a) {
             }
         }
         tv[threadIdx.y + i * 8][threadIdx.x] = v;
+        csum += v;
+    }
+    if (a.colsum_part) cs[threadIdx.y][threadIdx.x] = csum;
+    if (!a.t.p32 && !a.colsum_part) return;
+    __syncthreads();
+    if (a.colsum_part && threadIdx.y == 0 && c < a.C) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += cs[k][threadIdx.x];
+        a.colsum_part[(size_t)blockIdx.y * a.C + c] = t;
     }
     if (!a.t.p32) return;
-    __syncthreads();
     const uint32_t tr = r0 + threadIdx.x;          // source row -> destination column
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -640,10 +652,12 @@ __device__ __forceinline__ void store_planes4(const PlaneSet& ps, size_t rows, s
 template <int FMT>
 __global__ void __launch_bounds__(256) split_vec_kernel(SplitArgs a) {
     __shared__ float tv[64][65];
+    __shared__ float cs[16][64];
     const uint32_t cg = threadIdx.x & 15, rl = threadIdx.x >> 4;
     const uint32_t c = blockIdx.x * 64 + cg * 4;
     const uint32_t r0 = blockIdx.y * 64;
     const bool want_t = a.t.p32 != nullptr;
+    float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t lr = rl + 16 * i, r = r0 + lr;
@@ -662,9 +676,20 @@ __global__ void __launch_bounds__(256) split_vec_kernel(SplitArgs a) {
         if (want_t) {
             tv[lr][cg * 4 + 0] = v.x; tv[lr][cg * 4 + 1] = v.y; tv[lr][cg * 4 + 2] = v.z; tv[lr][cg * 4 + 3] = v.w;
         }
+        csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w;
+    }
+    if (a.colsum_part) {
+        cs[rl][cg * 4 + 0] = csum.x; cs[rl][cg * 4 + 1] = csum.y; cs[rl][cg * 4 + 2] = csum.z; cs[rl][cg * 4 + 3] = csum.w;
+    }
+    if (!want_t && !a.colsum_part) return;
+    __syncthreads();
+    if (a.colsum_part && threadIdx.x < 64 && blockIdx.x * 64 + threadIdx.x < a.C) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) t += cs[k][threadIdx.x];
+        a.colsum_part[(size_t)blockIdx.y * a.C + blockIdx.x * 64 + threadIdx.x] = t;
     }
     if (!want_t) return;
-    __syncthreads();
     const uint32_t tr = r0 + cg * 4;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -695,13 +720,15 @@ int32_t alloc_planes(fg_ctx* ctx, int fmt, uint32_t rows, uint32_t k, PlaneSet* 
     return FG_OK;
 }
 
-int32_t launch_split(fg_ctx* ctx, int fmt, const SplitArgs& a) {
+// `chunks_out` (may be NULL) receives the number of row tiles = rows of a.colsum_part that get written.
+int32_t launch_split(fg_ctx* ctx, int fmt, const SplitArgs& a, uint32_t* chunks_out = nullptr) {
     auto ok16 = [](const PlaneSet& ps) { return !ps.p32 || (fg_aligned16(ps.p32) && (!ps.p16 || fg_aligned16(ps.p16))); };
     const bool vec = (a.R % 4 == 0) && (a.C % 4 == 0) && fg_aligned16(a.x) && (!a.saved || fg_aligned16(a.saved)) &&
                      (!a.value_out || fg_aligned16(a.value_out)) && ok16(a.n) && ok16(a.t);
     const uint32_t tile = vec ? 64 : 32;
     dim3 grid((a.C + tile - 1) / tile, (a.R + tile - 1) / tile);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM operand has too many rows");
+    if (chunks_out) *chunks_out = grid.y;
     double bytes = 4.0 * a.R * a.C * (1.0 + (a.saved ? 1.0 : 0.0) + (a.value_out ? 1.0 : 0.0) +
                                       (a.n.p32 ? 2.0 : 0.0) + (a.t.p32 ? 2.0 : 0.0));
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SPLIT, bytes);
@@ -946,8 +973,7 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     uint64_t need = 2048;
     if (dA) need += planes_bytes(fmt, M, N) + planes_bytes(fmt, K, N);
     if (dB) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M);
-    if (dbias && !dZ_out) need += mn * 4 + 256;
-    if (dbias) need += (uint64_t)((M + 255) / 256) * N * 4 + 256;
+    if (dbias) need += (uint64_t)((M + 31) / 32) * N * 4 + 256;   // per-tile column sums from the pre-pass
     if (ctx->ws_bytes < need) {
         int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
         if (s0 != FG_OK) return s0;
@@ -963,15 +989,16 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
         if ((s = alloc_planes(ctx, fmt, N, M, &dz_t)) != FG_OK) return s;
         if ((s = alloc_planes(ctx, fmt, K, M, &a_t)) != FG_OK) return s;
     }
-    if (dbias && !dz_val) {
-        if ((s = fg_ws_alloc(ctx, mn * 4, &dz_val)) != FG_OK) return s;
-    }
+    void* cs_part = nullptr;
+    if (dbias && (s = fg_ws_alloc(ctx, (uint64_t)((M + 31) / 32) * N * 4, &cs_part)) != FG_OK) return s;
     SplitArgs sz{};
     sz.x = dY; sz.saved = fuse ? saved : nullptr; sz.act = act; sz.R = M; sz.C = N;
     sz.n = dz_n; sz.t = dz_t;
     sz.value_out = (float*)dz_val;
-    if (dA || dB || dz_val) {
-        if ((s = launch_split(ctx, fmt, sz)) != FG_OK) return s;
+    sz.colsum_part = (float*)cs_part;
+    uint32_t cs_chunks = 0;
+    if (dA || dB || dz_val || dbias) {
+        if ((s = launch_split(ctx, fmt, sz, &cs_chunks)) != FG_OK) return s;
     }
     if (dA) {
         // dA[M,K] = dZ[M,N] · Bᵀ: contraction over N; B [K,N] is already "rows = K, contraction contiguous".
@@ -988,7 +1015,8 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
         if ((s = tc_gemm(ctx, fmt, a_t, dz_t, K, N, M, dB, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
     }
     if (dbias) {
-        if ((s = fg_colsum_launch(ctx, M, N, (const float*)dz_val, dbias)) != FG_OK) return s;
+        // the pre-pass left one row of column sums per row tile: fold them in a fixed order
+        if ((s = fg_colsum_fold_launch(ctx, N, cs_chunks, (const float*)cs_part, dbias)) != FG_OK) return s;
     }
     return FG_OK;
 }

@@ -143,6 +143,23 @@ class MLPTrainer:
         self.ctx.upload_async(self.x, x_pinned.ctypes.data, x_pinned.nbytes)
         self.ctx.upload_async(self.target, target_pinned.ctypes.data, target_pinned.nbytes)
 
+    def prefetch_batch(self, x_pinned, target_pinned):
+        """Starts copying the NEXT batch into staging buffers on the copy stream; it overlaps the step that
+        is running.  take_prefetched() then moves it into place at device speed."""
+        if not hasattr(self, "stage_x"):
+            self.stage_x = self.ctx.alloc(x_pinned.nbytes)
+            self.stage_t = self.ctx.alloc(target_pinned.nbytes)
+        self.ctx.upload_prefetch(self.stage_x, x_pinned.ctypes.data, x_pinned.nbytes)
+        self.ctx.upload_prefetch(self.stage_t, target_pinned.ctypes.data, target_pinned.nbytes)
+        self._staged = (x_pinned.nbytes, target_pinned.nbytes)
+
+    def take_prefetched(self):
+        nx, nt = self._staged
+        self.ctx.prefetch_wait()
+        self.ctx.copy_dev_async(self.x, self.stage_x, nx)
+        self.ctx.copy_dev_async(self.target, self.stage_t, nt)
+        self.ctx.prefetch_mark()
+
     # ---- one training step, enqueued on the context's stream ----
     def enqueue_step(self):
         c, B, L = self.ctx, self.batch, self.L
@@ -160,6 +177,15 @@ class MLPTrainer:
         for l in range(L - 1, -1, -1):
             a = self.act if l < L - 1 else "none"
             saved = None if a == "none" else (self.pre_buf[l] if a == "gelu" else self.act_buf[l + 1])
+            if self.world > 1 and self.overlap and l > 0:
+                # weight and bias gradients first, so that their exchange also overlaps this layer's dX GEMM
+                c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
+                           saved=saved, dA=None, dB=self.gW(l), dbias=self.gb(l), mode=self.mode)
+                lo, hi = self.layer_range[l]
+                c.allreduce_sum(self.grads.ptr + 4 * lo, hi - lo)
+                c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
+                           saved=saved, dA=self.dact[l], dB=None, dbias=None, mode=self.mode)
+                continue
             c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
                        saved=saved, dA=self.dact[l] if l > 0 else None, dB=self.gW(l), dbias=self.gb(l),
                        mode=self.mode)

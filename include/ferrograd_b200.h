@@ -116,6 +116,15 @@ int32_t fg_copy(fg_ctx* ctx, const fg_buf* src, fg_buf* dst);
 /* Asynchronous copies from/to PINNED host memory on the context stream. */
 int32_t fg_upload_async(fg_ctx* ctx, void* dst_dev, const void* src_pinned, uint64_t bytes);
 int32_t fg_download_async(fg_ctx* ctx, void* dst_pinned, const void* src_dev, uint64_t bytes);
+/* Input prefetch (no counterpart in the reference, whose uploads are synchronous:
+ * rocm/mod.rs:184-205).  fg_upload_prefetch copies from pinned host memory on a side stream, so it
+ * overlaps whatever the context's stream is computing; fg_prefetch_wait makes the context's stream
+ * wait for the prefetches issued so far; fg_prefetch_mark records that the stream is done reading the
+ * prefetch destination, and the next fg_upload_prefetch will not start before that point. */
+int32_t fg_upload_prefetch(fg_ctx* ctx, void* dst_dev, const void* src_pinned, uint64_t bytes);
+int32_t fg_prefetch_wait(fg_ctx* ctx);
+int32_t fg_prefetch_mark(fg_ctx* ctx);
+int32_t fg_copy_dev_async(fg_ctx* ctx, void* dst_dev, const void* src_dev, uint64_t bytes);
 int32_t fg_host_alloc_pinned(uint64_t bytes, void** out);
 int32_t fg_host_free_pinned(void* p);
 int32_t fg_memset_zero(fg_ctx* ctx, void* dev, uint64_t bytes);
