@@ -46,6 +46,13 @@ struct Epilogue {
     int* dev_status;
 };
 
+// One shared copy of the activation code.  fg_act_fwd inlines tanhf and the GELU polynomial at every call
+// site; an epilogue that is unrolled over a thread's 128 accumulators would carry 128 copies and run out
+// of instruction cache (measured on the pair kernel: 45,000 cycles for ~1,000 useful instructions).
+__device__ __noinline__ float4 act_fwd4(int act, float4 z) {
+    return make_float4(fg_act_fwd(act, z.x), fg_act_fwd(act, z.y), fg_act_fwd(act, z.z), fg_act_fwd(act, z.w));
+}
+
 template <int BN, int BK>
 struct TileCfg {
     static constexpr int kABytes = 2 * BM * BK * 4;   // hi + lo tiles of A
@@ -263,17 +270,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         z[t] = sum[j + t];
                         if (ep.bias && col + t < ep.N) z[t] += ep.bias[col + t];
                     }
+                    const float4 o = ep.act == FG_ACT_NONE ? make_float4(z[0], z[1], z[2], z[3])
+                                                           : act_fwd4(ep.act, make_float4(z[0], z[1], z[2], z[3]));
                     if (vec_ok && col + 3 < ep.N) {
                         if (prow) *reinterpret_cast<float4*>(prow + col) = make_float4(z[0], z[1], z[2], z[3]);
-                        *reinterpret_cast<float4*>(crow + col) =
-                            make_float4(fg_act_fwd(ep.act, z[0]), fg_act_fwd(ep.act, z[1]),
-                                        fg_act_fwd(ep.act, z[2]), fg_act_fwd(ep.act, z[3]));
+                        *reinterpret_cast<float4*>(crow + col) = o;
                     } else {
+                        const float ov[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
                         for (int t = 0; t < 4; ++t)
                             if (col + t < ep.N) {
                                 if (prow) prow[col + t] = z[t];
-                                crow[col + t] = fg_act_fwd(ep.act, z[t]);
+                                crow[col + t] = ov[t];
                             }
                     }
                 }
@@ -308,10 +316,17 @@ struct PairCfg {
     static constexpr int kBBytes = 2 * (kBN / 2) * BK * 4;   // this CTA's half of the B tile
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kStoreBytes = 8 * 32 * 33 * 4;       // the epilogue warps' transpose buffers
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kStoreBytes;
+    static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
     static constexpr int kTmemCols = 512;                     // two 256-column accumulators
 };
 
+// Persistent: the grid is one CTA pair per SM pair (or fewer); pair p computes tiles p, p + P, p + 2P, ...
+// The load ring, the MMA issue and the accumulator ping-pong run straight across tile boundaries, so
+// while the epilogue warps apply bias/activation and store tile t from their registers, the loads and
+// MMAs of tile t+1 are already under way (per-tile set-up, fill and store cost 20-55 us per wave when
+// every tile was its own CTA pair: 17 % of a 4096^3 GEMM, more than half of a K = 784 one).
 template <int BK, int FMT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -336,21 +351,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
-    // Tile order: pairs are numbered so that eight consecutive pair-rows sweep all columns before the
-    // next eight start.  A wave of 74 pairs then covers a squarish block of C and re-uses both its A rows
-    // and its B rows from L2 (with rows-fastest order every wave streamed all of A again: 7.7x the
-    // operand bytes from DRAM at 8192^3).
+    // Tile order: tiles are numbered so that eight consecutive pair-rows sweep all columns before the
+    // next eight start.  The pairs working at the same time then cover a squarish block of C and re-use
+    // both its A rows and its B rows from L2 (with rows-fastest order every wave streamed all of A
+    // again: 7.7x the operand bytes from DRAM at 8192^3).
     const uint32_t pairs_m = (ep.M + 2 * BM - 1) / (2 * BM), pairs_n = (ep.N + BN - 1) / BN;
+    const uint32_t ntiles = pairs_m * pairs_n;
+    const uint32_t npairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
     constexpr uint32_t kGroup = 8;
-    const uint32_t pid = blockIdx.x >> 1;
-    const uint32_t grp = pid / (kGroup * pairs_n);
-    const uint32_t grp_rows = min(kGroup, pairs_m - grp * kGroup);
-    const uint32_t rem = pid - grp * kGroup * pairs_n;
-    const uint32_t pm = grp * kGroup + rem % grp_rows, pn = rem / grp_rows;
-    (void)pairs_n;
-    const uint32_t m0 = pm * (2 * BM) + rank * BM;                  // this CTA's rows of A and C
-    const uint32_t n0 = pn * BN;                                    // the pair's columns of C
-    const uint32_t nb0 = n0 + rank * HB;                            // the rows of B this CTA loads
+    auto tile_origin = [&](uint32_t tile, uint32_t& m0, uint32_t& n0) {
+        const uint32_t grp = tile / (kGroup * pairs_n);
+        const uint32_t grp_rows = min(kGroup, pairs_m - grp * kGroup);
+        const uint32_t rem = tile - grp * kGroup * pairs_n;
+        m0 = (grp * kGroup + rem % grp_rows) * (2 * BM) + rank * BM;   // this CTA's rows of A and C
+        n0 = (rem / grp_rows) * BN;                                    // the pair's columns of C
+    };
     const uint32_t nkb = (ep.K + BK - 1) / BK;
     constexpr uint32_t kChunkKB = kChunkK / BK;
     const uint32_t nchunks = (nkb + kChunkKB - 1) / kChunkKB;
@@ -376,21 +391,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer (both CTAs): own rows of A, own half of B; completion counted on the leader ----
-            for (uint32_t kb = 0; kb < nkb; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1u;
-                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, kPairWaitCycles)) {
-                    atomicOr(ep.dev_status, FG_DEVERR_TMA_WAIT);
-                    break;
-                }
-                if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
-                const uint32_t lf = map_to_cta(full_bar(s), 0);
-                const uint32_t sa = base + s * Cfg::kStageBytes;
-                tma_load_3d_pair(sa, &tmA, lf, (int)(kb * BK), (int)m0, 0);
-                tma_load_3d_pair(sa + Cfg::kABytes, &tmB, lf, (int)(kb * BK), (int)nb0, 0);
-                if (FMT == 1) {
-                    tma_load_3d_pair(sa + BM * BK * 4, &tmA16, lf, (int)(kb * BK), (int)m0, 0);
-                    tma_load_3d_pair(sa + Cfg::kABytes + HB * BK * 4, &tmB16, lf, (int)(kb * BK), (int)nb0, 0);
+            uint32_t g = 0;      // k-blocks issued so far, across tiles: ring position and phase
+            bool ok = true;
+            for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
+                uint32_t m0, n0;
+                tile_origin(tile, m0, n0);
+                const uint32_t nb0 = n0 + rank * HB;                    // the rows of B this CTA loads
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t ph = (g / S) & 1u;
+                    if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, kPairWaitCycles)) {
+                        atomicOr(ep.dev_status, FG_DEVERR_TMA_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
+                    const uint32_t lf = map_to_cta(full_bar(s), 0);
+                    const uint32_t sa = base + s * Cfg::kStageBytes;
+                    tma_load_3d_pair(sa, &tmA, lf, (int)(kb * BK), (int)m0, 0);
+                    tma_load_3d_pair(sa + Cfg::kABytes, &tmB, lf, (int)(kb * BK), (int)nb0, 0);
+                    if (FMT == 1) {
+                        tma_load_3d_pair(sa + BM * BK * 4, &tmA16, lf, (int)(kb * BK), (int)m0, 0);
+                        tma_load_3d_pair(sa + Cfg::kABytes + HB * BK * 4, &tmB16, lf, (int)(kb * BK), (int)nb0, 0);
+                    }
                 }
             }
         }
@@ -399,122 +422,150 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // ---- MMA issuer (leader CTA only): M = 256 across the pair, N = 256 ----
             constexpr uint32_t idesc = make_idesc(2u /*tf32*/, 2 * BM, BN);
             bool ok = true;
-            for (uint32_t c = 0; c < nchunks && ok; ++c) {
-                const uint32_t buf = c & 1u;
-                if (!mbar_wait_bounded(acc_empty_bar(buf), ((c >> 1) & 1u) ^ 1u, kPairWaitCycles)) {
-                    atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                const uint32_t kb_end = min(nkb, (c + 1) * kChunkKB);
-                for (uint32_t kb = c * kChunkKB; kb < kb_end; ++kb) {
-                    const int s = kb % S;
-                    const uint32_t ph = (kb / S) & 1u;
-                    if (!mbar_wait_bounded(full_bar(s), ph, kPairWaitCycles)) {
+            uint32_t g = 0, gc = 0;     // k-blocks and chunks consumed so far, across tiles
+            for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
+                for (uint32_t c = 0; c < nchunks && ok; ++c, ++gc) {
+                    const uint32_t buf = gc & 1u;
+                    // the accumulator must have been drained by both CTAs' epilogue warps (two chunks ago)
+                    if (!mbar_wait_bounded(acc_empty_bar(buf), ((gc >> 1) & 1u) ^ 1u, kPairWaitCycles)) {
                         atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sa = base + s * Cfg::kStageBytes;
-                    const uint64_t a_hi = make_desc_kmajor<BK * 4>(sa);
-                    const uint64_t b_hi = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes);
-                    const uint32_t first = (kb == c * kChunkKB) ? 0u : 1u;
-                    if (FMT == 0) {
-                        const uint64_t a_lo = make_desc_kmajor<BK * 4>(sa + BM * BK * 4);
-                        const uint64_t b_lo = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes + HB * BK * 4);
-#pragma unroll
-                        for (int kk = 0; kk < BK / UK; ++kk) {
-                            const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
-                            mma_tf32_pair(d_tmem, a_lo + adv, b_hi + adv, idesc, first | (uint32_t)kk);
-                            mma_tf32_pair(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
-                            mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    const uint32_t kb_end = min(nkb, (c + 1) * kChunkKB);
+                    for (uint32_t kb = c * kChunkKB; kb < kb_end; ++kb, ++g) {
+                        const int s = g % S;
+                        const uint32_t ph = (g / S) & 1u;
+                        if (!mbar_wait_bounded(full_bar(s), ph, kPairWaitCycles)) {
+                            atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
+                            ok = false;
+                            break;
                         }
-                    } else {
-                        constexpr uint32_t idesc16 = make_idesc(1u /*bf16*/, 2 * BM, BN);
-                        const uint32_t a16 = sa + BM * BK * 4, b16 = sa + Cfg::kABytes + HB * BK * 4;
-                        const uint64_t a_h16 = make_desc_kmajor<64>(a16), a_l16 = make_desc_kmajor<64>(a16 + BM * BK * 2);
-                        const uint64_t b_h16 = make_desc_kmajor<64>(b16), b_l16 = make_desc_kmajor<64>(b16 + HB * BK * 2);
+                        tc_fence_after();
+                        const uint32_t sa = base + s * Cfg::kStageBytes;
+                        const uint64_t a_hi = make_desc_kmajor<BK * 4>(sa);
+                        const uint64_t b_hi = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes);
+                        const uint32_t first = (kb == c * kChunkKB) ? 0u : 1u;   // a chunk starts from zero
+                        if (FMT == 0) {
+                            const uint64_t a_lo = make_desc_kmajor<BK * 4>(sa + BM * BK * 4);
+                            const uint64_t b_lo = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes + HB * BK * 4);
 #pragma unroll
-                        for (int kk = 0; kk < BK / 16; ++kk) {
-                            const uint64_t adv = (uint64_t)(kk * 16 * 2 >> 4);
-                            mma_f16_pair(d_tmem, a_l16 + adv, b_h16 + adv, idesc16, first | (uint32_t)kk);
-                            mma_f16_pair(d_tmem, a_h16 + adv, b_l16 + adv, idesc16, 1u);
-                        }
+                            for (int kk = 0; kk < BK / UK; ++kk) {
+                                const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                                mma_tf32_pair(d_tmem, a_lo + adv, b_hi + adv, idesc, first | (uint32_t)kk);
+                                mma_tf32_pair(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                                mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                            }
+                        } else {
+                            constexpr uint32_t idesc16 = make_idesc(1u /*bf16*/, 2 * BM, BN);
+                            const uint32_t a16 = sa + BM * BK * 4, b16 = sa + Cfg::kABytes + HB * BK * 4;
+                            const uint64_t a_h16 = make_desc_kmajor<64>(a16), a_l16 = make_desc_kmajor<64>(a16 + BM * BK * 2);
+                            const uint64_t b_h16 = make_desc_kmajor<64>(b16), b_l16 = make_desc_kmajor<64>(b16 + HB * BK * 2);
 #pragma unroll
-                        for (int kk = 0; kk < BK / UK; ++kk) {
-                            const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
-                            mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                            for (int kk = 0; kk < BK / 16; ++kk) {
+                                const uint64_t adv = (uint64_t)(kk * 16 * 2 >> 4);
+                                mma_f16_pair(d_tmem, a_l16 + adv, b_h16 + adv, idesc16, first | (uint32_t)kk);
+                                mma_f16_pair(d_tmem, a_h16 + adv, b_l16 + adv, idesc16, 1u);
+                            }
+#pragma unroll
+                            for (int kk = 0; kk < BK / UK; ++kk) {
+                                const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
+                                mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                            }
                         }
+                        mma_commit_pair(empty_bar(s), 3);        // frees this stage in both CTAs
                     }
-                    mma_commit_pair(empty_bar(s), 3);        // frees this stage in both CTAs
+                    if (ok) mma_commit_pair(acc_full_bar(buf), 3);   // both CTAs may drain their half
                 }
-                if (ok) mma_commit_pair(acc_full_bar(buf), 3);   // both CTAs may drain their half
             }
         }
     } else {
         // ---- accumulate + epilogue (both CTAs, own 128 rows); see gemm_tc_kernel ----
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;
+        const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
+                            (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
+        const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
+        float* tbuf = reinterpret_cast<float*>(base_ptr + S * Cfg::kStageBytes + 256);   // 8 warps x 32x33 floats
         float sum[CPT];
-#pragma unroll
-        for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
         bool ok = true;
-        for (uint32_t c = 0; c < nchunks; ++c) {
-            const uint32_t buf = c & 1u;
-            bool got = mbar_wait_bounded(acc_full_bar(buf), (c >> 1) & 1u, kPairWaitCycles + kPairWaitCycles / 2);
-            got = __all_sync(0xffffffffu, got);
-            if (!got) {
-                if (lane == 0) atomicOr(ep.dev_status, FG_DEVERR_EPI_WAIT);
-                ok = false;
-                break;
+        uint32_t gc = 0;
+        for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
+            uint32_t m0, n0;
+            tile_origin(tile, m0, n0);
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
+            for (uint32_t c = 0; c < nchunks; ++c, ++gc) {
+                const uint32_t buf = gc & 1u;
+                bool got = mbar_wait_bounded(acc_full_bar(buf), (gc >> 1) & 1u, kPairWaitCycles + kPairWaitCycles / 2);
+                got = __all_sync(0xffffffffu, got);
+                if (!got) {
+                    if (lane == 0) atomicOr(ep.dev_status, FG_DEVERR_EPI_WAIT);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * CPT;
+#pragma unroll
+                for (int g4 = 0; g4 < CPT / 32; ++g4) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t0 + g4 * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sum[g4 * 32 + j] += __uint_as_float(r[j]);
+                }
+                tc_fence_before();
+                if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * buf);   // 16 warps report to the leader
             }
-            tc_fence_after();
-            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * CPT;
+            if (!ok) break;
+            // Store this tile from registers; the tensor core is already working on the next one.  A thread
+            // owns one row, so storing directly would touch 32 different lines per instruction; instead each
+            // warp passes 32x32 blocks through a padded shared-memory buffer and writes 4 rows x 128 bytes
+            // per instruction (bias and activation are applied on the way out).
+            float* tb = tbuf + (warp - 2) * (32 * 33);
+            const uint32_t rsub = lane >> 3, c4 = (lane & 7) * 4;
 #pragma unroll
-            for (int g = 0; g < CPT / 32; ++g) {
-                uint32_t r[32];
-                tmem_ld_32x32(t0 + g * 32, r);
-                tmem_ld_wait();
+            for (int g4 = 0; g4 < CPT / 32; ++g4) {
+                const uint32_t col = n0 + half * CPT + g4 * 32 + c4;     // this lane's 4 columns on the way out
 #pragma unroll
-                for (int j = 0; j < 32; ++j) sum[g * 32 + j] += __uint_as_float(r[j]);
-            }
-            tc_fence_before();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty_bar(buf), 0));   // 16 warps report to the leader
-        }
-        if (ok && *reinterpret_cast<volatile int*>(ep.dev_status) == 0) {
-            const uint32_t row = m0 + q * 32 + lane;
-            const uint32_t cbase = n0 + half * CPT;
-            const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
-                                (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
-            if (row < ep.M) {
-                float* crow = ep.C + (size_t)row * ep.N;
-                float* prow = ep.preact ? ep.preact + (size_t)row * ep.N : nullptr;
+                for (int j = 0; j < 32; ++j) tb[lane * 33 + j] = sum[g4 * 32 + j];
+                __syncwarp();
+                float bz[4] = {0.f, 0.f, 0.f, 0.f};
+                if (ep.bias) {
 #pragma unroll
-                for (int j = 0; j < CPT; j += 4) {
-                    const uint32_t col = cbase + j;
-                    if (col >= ep.N) break;
+                    for (int t = 0; t < 4; ++t) if (col + t < ep.N) bz[t] = ep.bias[col + t];
+                }
+                // rolled on purpose: the activation code (tanhf, GELU) is inlined at every call site, and
+                // 128 copies of it per thread made this section miss the instruction cache on every line
+                // (measured: 45,000 cycles per tile for ~1,000 useful instructions)
+#pragma unroll 1
+                for (int r = 0; r < 8; ++r) {
+                    const uint32_t lr = r * 4 + rsub;
+                    const uint32_t row = m0 + q * 32 + lr;
                     float z[4];
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        z[t] = sum[j + t];
-                        if (ep.bias && col + t < ep.N) z[t] += ep.bias[col + t];
-                    }
-                    if (vec_ok && col + 3 < ep.N) {
-                        if (prow) *reinterpret_cast<float4*>(prow + col) = make_float4(z[0], z[1], z[2], z[3]);
-                        *reinterpret_cast<float4*>(crow + col) =
-                            make_float4(fg_act_fwd(ep.act, z[0]), fg_act_fwd(ep.act, z[1]),
-                                        fg_act_fwd(ep.act, z[2]), fg_act_fwd(ep.act, z[3]));
-                    } else {
+                    for (int t = 0; t < 4; ++t) z[t] = tb[lr * 33 + c4 + t] + bz[t];
+                    if (row < ep.M && col < ep.N) {
+                        float* crow = ep.C + (size_t)row * ep.N + col;
+                        float* prow = ep.preact ? ep.preact + (size_t)row * ep.N + col : nullptr;
+                        if (vec_ok && col + 3 < ep.N) {
+                            const float4 o = ep.act == FG_ACT_NONE ? make_float4(z[0], z[1], z[2], z[3])
+                                                                   : act_fwd4(ep.act, make_float4(z[0], z[1], z[2], z[3]));
+                            if (prow) *reinterpret_cast<float4*>(prow) = make_float4(z[0], z[1], z[2], z[3]);
+                            *reinterpret_cast<float4*>(crow) = o;
+                        } else {
 #pragma unroll
-                        for (int t = 0; t < 4; ++t)
-                            if (col + t < ep.N) {
-                                if (prow) prow[col + t] = z[t];
-                                crow[col + t] = fg_act_fwd(ep.act, z[t]);
-                            }
+                            for (int t = 0; t < 4; ++t)
+                                if (col + t < ep.N) {
+                                    if (prow) prow[t] = z[t];
+                                    crow[t] = fg_act_fwd(ep.act, z[t]);
+                                }
+                        }
                     }
                 }
+                __syncwarp();
             }
         }
     }
@@ -818,9 +869,30 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
                 cudaFuncSetAttribute(gemm_tc_pair_kernel<BK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
         attr_done |= 1ull << (ctx->device & 63);
     }
-    const uint64_t npairs = (uint64_t)((ep.M + 2 * BM - 1) / (2 * BM)) * ((ep.N + Cfg::kBN - 1) / Cfg::kBN);
-    if (npairs > (1ull << 30)) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: too many tiles");
-    dim3 grid((unsigned)(2 * npairs));   // two CTAs per pair; the kernel maps pair ids to tiles
+    const uint64_t ntiles = (uint64_t)((ep.M + 2 * BM - 1) / (2 * BM)) * ((ep.N + Cfg::kBN - 1) / Cfg::kBN);
+    if (ntiles > (1ull << 30)) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: too many tiles");
+    // persistent: one CTA pair per SM pair, each walking tiles pair, pair + P, ...
+    // How many pairs can be resident at once is asked of the runtime (not every SM need be pairable).
+    static int max_clusters[64] = {0};
+    if (max_clusters[ctx->device & 63] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)ctx->sm_count & ~1u);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BK, FMT>, &cfg) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = ctx->sm_count / 2;
+        }
+        max_clusters[ctx->device & 63] = n;
+    }
+    const uint64_t slots = (uint64_t)max_clusters[ctx->device & 63];
+    dim3 grid((unsigned)(2 * (ntiles < slots ? ntiles : slots)));
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
     gemm_tc_pair_kernel<BK, FMT><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
     fg_time_end(ctx, tr);
