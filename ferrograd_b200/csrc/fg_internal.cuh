@@ -166,6 +166,13 @@ __device__ __forceinline__ float fg_act_grad(int act, float saved) {
 int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uint32_t N, uint32_t K,
                             const float* A, const float* B, float* C, const float* bias, int act,
                             float* preact_out);
+uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K);   // enough for any one skinny launch
+int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
+                                const float* bias, int act, float* preact_out);
+int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N, const float* dZ, const float* B,
+                                 float* dA);
+int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t N, const float* A, const float* dZ,
+                                 float* dB);
 int32_t fg_act_bwd_launch(fg_ctx* ctx, uint64_t n, int act, const float* dy, const float* saved, float* dz);
 int32_t fg_colsum_launch(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* x, float* out);
 int32_t fg_colsum_fold_launch(fg_ctx* ctx, uint32_t cols, uint32_t nchunks, const float* part, float* out);

@@ -85,7 +85,266 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(uint32_t M, uint32_t N, 
     }
 }
 
+// ---- skinny outputs (N <= 16, e.g. a 10-class output layer) ----
+// A 128-row tensor-core tile would leave most SMs idle for such shapes (32 CTAs for M = 4096) and the
+// operand pre-pass would cost more than the product.  These kernels are bandwidth-bound on streaming the
+// large operand once, and use plain f32 FMAs.  NT is N rounded up to a multiple of four; the small operand
+// is zero-padded to NT so that the inner loops carry no predicates.
+constexpr int SKN = 16;
+
+// Bt[n][k] = B[k][n], zero for n >= N or k >= K   (Bt is [NT][Kp]).
+__global__ void __launch_bounds__(256) skinny_transpose_kernel(uint32_t K, uint32_t N, uint32_t Kp, uint32_t NT,
+                                                               const float* __restrict__ B, float* __restrict__ Bt) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= NT * Kp) return;
+    const uint32_t n = i / Kp, k = i % Kp;
+    Bt[i] = (n < N && k < K) ? B[(size_t)k * N + n] : 0.0f;
+}
+
+// C[M,N] = act(A[M,K]·B[K,N] + bias) from the transposed copy Bt: one warp per 2 rows, lanes split k.
+template <int NT, bool VEC>
+__global__ void __launch_bounds__(256) gemm_skinny_n_kernel(uint32_t M, uint32_t N, uint32_t K, uint32_t Kp,
+                                                            const float* __restrict__ A, const float* __restrict__ Bt,
+                                                            float* __restrict__ C, const float* __restrict__ bias, int act,
+                                                            float* __restrict__ preact) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t row0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
+    if (row0 >= M) return;
+    const uint32_t row1 = min(row0 + 1, M - 1);
+    float acc0[NT], acc1[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) acc0[n] = acc1[n] = 0.0f;
+    const float* a0 = A + (size_t)row0 * K;
+    const float* a1 = A + (size_t)row1 * K;
+    if (VEC) {
+#pragma unroll 2
+        for (uint32_t k = lane * 4; k < K; k += 128) {
+            const float4 x0 = *reinterpret_cast<const float4*>(a0 + k);
+            const float4 x1 = *reinterpret_cast<const float4*>(a1 + k);
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const float4 w = *reinterpret_cast<const float4*>(Bt + (size_t)n * Kp + k);
+                acc0[n] = fmaf(x0.w, w.w, fmaf(x0.z, w.z, fmaf(x0.y, w.y, fmaf(x0.x, w.x, acc0[n]))));
+                acc1[n] = fmaf(x1.w, w.w, fmaf(x1.z, w.z, fmaf(x1.y, w.y, fmaf(x1.x, w.x, acc1[n]))));
+            }
+        }
+    } else {
+#pragma unroll 4
+        for (uint32_t k = lane; k < K; k += 32) {
+            const float x0 = a0[k], x1 = a1[k];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const float w = Bt[(size_t)n * Kp + k];
+                acc0[n] = fmaf(x0, w, acc0[n]);
+                acc1[n] = fmaf(x1, w, acc1[n]);
+            }
+        }
+    }
+    float z0 = 0.0f, z1 = 0.0f;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        float u = acc0[n], v = acc1[n];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            u += __shfl_xor_sync(0xffffffffu, u, o);
+            v += __shfl_xor_sync(0xffffffffu, v, o);
+        }
+        if (lane == n) { z0 = u; z1 = v; }
+    }
+    if (lane < (int)N) {
+        const float bb = bias ? bias[lane] : 0.0f;
+        size_t o = (size_t)row0 * N + lane;
+        z0 += bb;
+        if (preact) preact[o] = z0;
+        C[o] = fg_act_fwd(act, z0);
+        if (row0 + 1 < M) {
+            o += N;
+            z1 += bb;
+            if (preact) preact[o] = z1;
+            C[o] = fg_act_fwd(act, z1);
+        }
+    }
+}
+
+constexpr int TN_ROWS = 64;   // rows of A per partial sum in the dB kernel
+
+// part[chunk][j][n] = sum over the chunk's rows m of A[m][j] * dZ[m][n]   (A is [M, Kd], dZ is [M, N]).
+// A thread owns four consecutive j; the chunk's rows of dZ sit in shared memory and are broadcast.
+template <int NT, bool VEC>
+__global__ void __launch_bounds__(128) gemm_skinny_tn_partial_kernel(uint32_t M, uint32_t Kd, uint32_t N,
+                                                                     const float* __restrict__ A,
+                                                                     const float* __restrict__ dZ,
+                                                                     float* __restrict__ part) {
+    __shared__ float zs[TN_ROWS][NT];
+    const uint32_t m0 = blockIdx.y * TN_ROWS, rows = min((uint32_t)TN_ROWS, M - m0);
+    for (uint32_t e = threadIdx.x; e < TN_ROWS * NT; e += 128) {
+        const uint32_t r = e / NT, n = e % NT;
+        zs[r][n] = (r < rows && n < N) ? dZ[(size_t)(m0 + r) * N + n] : 0.0f;
+    }
+    __syncthreads();
+    const uint32_t j0 = (blockIdx.x * 128 + threadIdx.x) * 4;
+    if (j0 >= Kd) return;
+    float acc[4][NT];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) acc[q][n] = 0.0f;
+    const float* a = A + (size_t)m0 * Kd + j0;
+    for (uint32_t r0 = 0; r0 < rows; r0 += 8) {
+        float x[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint32_t r = min(r0 + u, rows - 1);     // rows past the end reload the last one; their dZ is zero
+            if (VEC) {
+                const float4 t = *reinterpret_cast<const float4*>(a + (size_t)r * Kd);
+                x[u][0] = t.x; x[u][1] = t.y; x[u][2] = t.z; x[u][3] = t.w;
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) x[u][q] = (j0 + q < Kd) ? a[(size_t)r * Kd + q] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (r0 + u < rows) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const float z = zs[r0 + u][n];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) acc[q][n] = fmaf(x[u][q], z, acc[q][n]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        if (j0 + q < Kd) {
+            float* p = part + ((size_t)blockIdx.y * Kd + j0 + q) * N;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                if (n < (int)N) p[n] = acc[q][n];
+        }
+    }
+}
+
+// dA[m][k] = sum_n dZ[m][n] * B[k][n]   (dZ is [M, N], B is [K, N]): bound by writing dA once.
+// A thread owns four consecutive k and keeps their rows of B in registers while it walks 32 rows of dZ.
+template <int NT>
+__global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_t K, uint32_t N,
+                                                             const float* __restrict__ dZ, const float* __restrict__ B,
+                                                             float* __restrict__ dA) {
+    __shared__ float zs[32][NT];
+    const uint32_t m0 = blockIdx.y * 32, rows = min(32u, M - m0);
+    for (uint32_t e = threadIdx.x; e < 32 * NT; e += 128) {
+        const uint32_t r = e / NT, n = e % NT;
+        zs[r][n] = (r < rows && n < N) ? dZ[(size_t)(m0 + r) * N + n] : 0.0f;
+    }
+    __syncthreads();
+    const uint32_t k0 = (blockIdx.x * 128 + threadIdx.x) * 4;
+    if (k0 >= K) return;
+    float b[4][NT];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) b[q][n] = (n < (int)N && k0 + q < K) ? B[(size_t)(k0 + q) * N + n] : 0.0f;
+    const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15u) == 0);
+#pragma unroll 4
+    for (uint32_t r = 0; r < rows; ++r) {
+        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const float z = zs[r][n];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) o[q] = fmaf(z, b[q][n], o[q]);
+        }
+        float* dst = dA + (size_t)(m0 + r) * K + k0;
+        if (vec) {
+            *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) if (k0 + q < K) dst[q] = o[q];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) fold_chunks_kernel(uint64_t n, uint32_t nchunks, const float* __restrict__ part,
+                                                          float* __restrict__ out) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        float s = 0.0f;
+#pragma unroll 8
+        for (uint32_t c = 0; c < nchunks; ++c) s += part[(size_t)c * n + i];
+        out[i] = s;
+    }
+}
+
+// Runs the statement with NT = N rounded up to a multiple of four.
+#define FG_SKINNY_DISPATCH(N, ...)                                  \
+    do {                                                            \
+        if ((N) <= 4) { constexpr int NT = 4; __VA_ARGS__; }        \
+        else if ((N) <= 8) { constexpr int NT = 8; __VA_ARGS__; }   \
+        else if ((N) <= 12) { constexpr int NT = 12; __VA_ARGS__; } \
+        else { constexpr int NT = 16; __VA_ARGS__; }                \
+    } while (0)
+
 }  // namespace
+
+uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K) {
+    const uint64_t kp = (K + 3) / 4 * 4;
+    const uint64_t fwd = 16 * kp * 4 + 256;                                              // transposed B
+    const uint64_t bwd = (uint64_t)((M + TN_ROWS - 1) / TN_ROWS) * K * N * 4 + 256;      // dB partials
+    return fwd > bwd ? fwd : bwd;
+}
+
+int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
+                                const float* bias, int act, float* preact_out) {
+    if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
+    const uint32_t Kp = (K + 3) / 4 * 4, NTr = (N + 3) / 4 * 4;
+    void* bt;
+    int32_t s = fg_ws_alloc(ctx, (uint64_t)NTr * Kp * 4, &bt);
+    if (s != FG_OK) return s;
+    skinny_transpose_kernel<<<(NTr * Kp + 255) / 256, 256, 0, ctx->stream>>>(K, N, Kp, NTr, B, (float*)bt);
+    FG_LAUNCHED(ctx);
+    const uint32_t blocks = (M + 15) / 16;
+    const bool vec = (K % 4 == 0) && fg_aligned16(A);
+    FG_SKINNY_DISPATCH(N, {
+        if (vec) gemm_skinny_n_kernel<NT, true><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);
+        else gemm_skinny_n_kernel<NT, false><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);
+    });
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+// dA[M, K] = dZ · B^T with dZ [M, N], B [K, N], N <= 16.
+int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N, const float* dZ, const float* B,
+                                 float* dA) {
+    if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
+    dim3 grid((K + 511) / 512, (M + 31) / 32);
+    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
+    FG_SKINNY_DISPATCH(N, (gemm_skinny_nt_kernel<NT><<<grid, 128, 0, ctx->stream>>>(M, K, N, dZ, B, dA)));
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+// dB[Kd, N] = A^T · dZ with A [M, Kd], dZ [M, N], N <= 16.  Uses the scratch arena for the per-chunk partials.
+int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t N, const float* A, const float* dZ,
+                                 float* dB) {
+    if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
+    const uint32_t nchunks = (M + TN_ROWS - 1) / TN_ROWS;
+    void* part;
+    int32_t s = fg_ws_alloc(ctx, (uint64_t)nchunks * Kd * N * 4, &part);
+    if (s != FG_OK) return s;
+    dim3 grid((Kd + 511) / 512, nchunks);
+    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
+    const bool vec = (Kd % 4 == 0) && fg_aligned16(A);
+    FG_SKINNY_DISPATCH(N, {
+        if (vec) gemm_skinny_tn_partial_kernel<NT, true><<<grid, 128, 0, ctx->stream>>>(M, Kd, N, A, dZ, (float*)part);
+        else gemm_skinny_tn_partial_kernel<NT, false><<<grid, 128, 0, ctx->stream>>>(M, Kd, N, A, dZ, (float*)part);
+    });
+    FG_LAUNCHED(ctx);
+    const uint64_t n = (uint64_t)Kd * N;
+    fold_chunks_kernel<<<fg_stream_grid(ctx, n, 256, 8), 256, 0, ctx->stream>>>(n, nchunks, (const float*)part, dB);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
 
 int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A,
                             const float* B, float* C, const float* bias, int act, float* preact_out) {

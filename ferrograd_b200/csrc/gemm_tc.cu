@@ -965,6 +965,15 @@ int32_t fg_gemm_f32(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB, u
                "fg_gemm_f32: operand too large");
     const int path = pick_path(ctx, mode, M, N, K);
     if (path == 0) return fg_gemm_simt_launch(ctx, transA, transB, M, N, K, A, B, C, bias, act, preact_out);
+    // A skinny output (say 10 classes) is bandwidth-bound on reading A once: no pre-pass, no tensor cores.
+    if (mode == FG_GEMM_AUTO && N <= 16 && !transA && !transB) {
+        const uint64_t need = fg_gemm_skinny_scratch_bytes(M, N, K) + 1024;
+        if (ctx->ws_bytes < need) {
+            int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
+            if (s0 != FG_OK) return s0;
+        }
+        return fg_gemm_skinny_n_launch(ctx, M, N, K, A, B, C, bias, act, preact_out);
+    }
     const int fmt = path - 1;
     // Size the arena for both operands before carving it.
     const uint64_t need = planes_bytes(fmt, M, K) + planes_bytes(fmt, N, K) + 1024;
@@ -1042,9 +1051,15 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     // Tensor-core path.  Scratch: dZ planes in both orientations, B planes, Aᵀ planes, dZ itself
     // when a bias gradient is wanted, and the column-sum partials.
     const int fmt = path - 1;
+    // A skinny layer (N <= 16, say 10 classes): dA is bound by writing it once and dB by reading A once, so
+    // both run as plain-FMA kernels on dZ itself; the operand pre-passes and a tensor-core GEMM that could
+    // only fill M/128 CTAs would cost several times more.
+    const bool skinny = mode == FG_GEMM_AUTO && N <= 16;
+    const bool tc_da = dA && !skinny, tc_db = dB && !skinny;
     uint64_t need = 2048;
-    if (dA) need += planes_bytes(fmt, M, N) + planes_bytes(fmt, K, N);
-    if (dB) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M);
+    if (tc_da) need += planes_bytes(fmt, M, N) + planes_bytes(fmt, K, N);
+    if (tc_db) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M);
+    if (skinny) need += mn * 4 + 256 + fg_gemm_skinny_scratch_bytes(M, N, K);
     if (dbias) need += (uint64_t)((M + 31) / 32) * N * 4 + 256;   // per-tile column sums from the pre-pass
     if (ctx->ws_bytes < need) {
         int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
@@ -1053,13 +1068,16 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     PlaneSet dz_n{}, dz_t{}, b_n{}, a_t{};
     void* dz_val = dZ_out;
     int32_t s;
-    if (dA) {
+    if (tc_da) {
         if ((s = alloc_planes(ctx, fmt, M, N, &dz_n)) != FG_OK) return s;
         if ((s = alloc_planes(ctx, fmt, K, N, &b_n)) != FG_OK) return s;
     }
-    if (dB) {
+    if (tc_db) {
         if ((s = alloc_planes(ctx, fmt, N, M, &dz_t)) != FG_OK) return s;
         if ((s = alloc_planes(ctx, fmt, K, M, &a_t)) != FG_OK) return s;
+    }
+    if (skinny && fuse && !dz_val && (dA || dB)) {      // the skinny kernels read dZ itself
+        if ((s = fg_ws_alloc(ctx, mn * 4, &dz_val)) != FG_OK) return s;
     }
     void* cs_part = nullptr;
     if (dbias && (s = fg_ws_alloc(ctx, (uint64_t)((M + 31) / 32) * N * 4, &cs_part)) != FG_OK) return s;
@@ -1069,17 +1087,20 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     sz.value_out = (float*)dz_val;
     sz.colsum_part = (float*)cs_part;
     uint32_t cs_chunks = 0;
-    if (dA || dB || dz_val || dbias) {
+    if (tc_da || tc_db || dz_val || dbias) {
         if ((s = launch_split(ctx, fmt, sz, &cs_chunks)) != FG_OK) return s;
     }
-    if (dA) {
+    const float* dz_src = dz_val ? (const float*)dz_val : dY;   // dZ == dY when there is no activation
+    if (tc_da) {
         // dA[M,K] = dZ[M,N] · Bᵀ: contraction over N; B [K,N] is already "rows = K, contraction contiguous".
         SplitArgs sb{};
         sb.x = B; sb.R = K; sb.C = N; sb.n = b_n;
         if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
         if ((s = tc_gemm(ctx, fmt, dz_n, b_n, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
     }
-    if (dB) {
+    if (skinny && dA && (s = fg_gemm_skinny_nt_launch(ctx, M, K, N, dz_src, B, dA)) != FG_OK) return s;
+    if (skinny && dB && (s = fg_gemm_skinny_tn_launch(ctx, M, K, N, A, dz_src, dB)) != FG_OK) return s;
+    if (tc_db) {
         // dB[K,N] = Aᵀ · dZ: contraction over M; operands are Aᵀ [K,M] and dZᵀ [N,M].
         SplitArgs sa{};
         sa.x = A; sa.R = M; sa.C = K; sa.t = a_t;

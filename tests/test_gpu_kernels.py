@@ -336,6 +336,33 @@ def test_gemm_backward(ctx, oracle, mode, act):
     check(ctx.to_numpy(dA2), oracle.gemm(dz_ref, B, transB=True), TOL_GEMM, "dA only")
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 10, 1024), (1001, 16, 517), (300, 3, 4800), (4096, 1, 1030)])
+@pytest.mark.parametrize("act", ["none", "tanh"])
+def test_gemm_skinny_output_layer(ctx, oracle, M, N, K, act):
+    # N <= 16 in auto mode runs on plain-FMA kernels (forward, dA and dB) instead of tensor-core tiles.
+    r = rng(M + 7 * N + K)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32) * 0.1
+    bias = r.standard_normal(N, np.float32)
+    Cd, Pd = ctx.new_tensor((M, N)), ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, bias=up(ctx, bias), act=act, preact_out=Pd, mode="auto")
+    y, pre = oracle.bias_act_fwd(oracle.gemm(A, B), bias, act)
+    check(ctx.to_numpy(Pd), pre, TOL_GEMM, "skinny pre-activation")
+    check(ctx.to_numpy(Cd), y, TOL_GEMM, "skinny output")
+    dY = r.standard_normal((M, N), np.float32)
+    dz_ref = oracle.act_bwd(dY, y, act)
+    dA, dB, db = ctx.new_tensor((M, K)), ctx.new_tensor((K, N)), ctx.new_tensor((N,))
+    ctx.gemm_bwd(up(ctx, A), up(ctx, B), up(ctx, dY), M, N, K, act=act, saved=up(ctx, y), dA=dA, dB=dB, dbias=db,
+                 mode="auto")
+    check(ctx.to_numpy(dA), oracle.gemm(dz_ref, B, transB=True), TOL_GEMM, "skinny dA")
+    check(ctx.to_numpy(dB), oracle.gemm(A, dz_ref, transA=True), TOL_GEMM, "skinny dB")
+    check(ctx.to_numpy(db), oracle.colsum(dz_ref), TOL_GEMM, "skinny dbias")
+    # dB alone, no activation: dZ is dY itself and no pre-pass runs
+    dB2 = ctx.new_tensor((K, N))
+    ctx.gemm_bwd(up(ctx, A), None, up(ctx, dY), M, N, K, dB=dB2, mode="auto")
+    check(ctx.to_numpy(dB2), oracle.gemm(A, dY, transA=True), TOL_GEMM, "skinny dB only")
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_reference_matmul_known_answers(ctx, mode):
     # crates/ferrograd/tests/std_wgsl.rs:268-373 (matmul_add) and :376-520 (matmul_chain3): constant
