@@ -44,7 +44,26 @@ struct Epilogue {
     uint32_t M, N, K;
     int act;
     int* dev_status;
+    // Split-K tail of the pair kernel: tiles [0, t_full) are whole; each later tile is computed as `split`
+    // partial sums over equal shares of the K chunks, written raw to `partial` and folded by a second kernel.
+    float* partial;
+    uint32_t t_full, split;
 };
+
+// Origin of pair tile `tile`: tiles are numbered so that eight consecutive pair-rows sweep all columns
+// before the next eight start.  The pairs working at the same time then cover a squarish block of C and
+// re-use both its A rows and its B rows from L2 (with rows-fastest order every wave streamed all of A
+// again: 7.7x the operand bytes from DRAM at 8192^3).
+__host__ __device__ __forceinline__ void pair_tile_origin(uint32_t tile, uint32_t pairs_m, uint32_t pairs_n,
+                                                          uint32_t tile_m, uint32_t tile_n, uint32_t& m0, uint32_t& n0) {
+    constexpr uint32_t kGroup = 8;
+    const uint32_t grp = tile / (kGroup * pairs_n);
+    const uint32_t left = pairs_m - grp * kGroup;
+    const uint32_t grp_rows = left < kGroup ? left : kGroup;
+    const uint32_t rem = tile - grp * kGroup * pairs_n;
+    m0 = (grp * kGroup + rem % grp_rows) * tile_m;
+    n0 = (rem / grp_rows) * tile_n;
+}
 
 // One shared copy of the activation code.  fg_act_fwd inlines tanhf and the GELU polynomial at every call
 // site; an epilogue that is unrolled over a thread's 128 accumulators would carry 128 copies and run out
@@ -351,24 +370,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
-    // Tile order: tiles are numbered so that eight consecutive pair-rows sweep all columns before the
-    // next eight start.  The pairs working at the same time then cover a squarish block of C and re-use
-    // both its A rows and its B rows from L2 (with rows-fastest order every wave streamed all of A
-    // again: 7.7x the operand bytes from DRAM at 8192^3).
     const uint32_t pairs_m = (ep.M + 2 * BM - 1) / (2 * BM), pairs_n = (ep.N + BN - 1) / BN;
     const uint32_t ntiles = pairs_m * pairs_n;
     const uint32_t npairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
-    constexpr uint32_t kGroup = 8;
     auto tile_origin = [&](uint32_t tile, uint32_t& m0, uint32_t& n0) {
-        const uint32_t grp = tile / (kGroup * pairs_n);
-        const uint32_t grp_rows = min(kGroup, pairs_m - grp * kGroup);
-        const uint32_t rem = tile - grp * kGroup * pairs_n;
-        m0 = (grp * kGroup + rem % grp_rows) * (2 * BM) + rank * BM;   // this CTA's rows of A and C
-        n0 = (rem / grp_rows) * BN;                                    // the pair's columns of C
+        pair_tile_origin(tile, pairs_m, pairs_n, 2 * BM, BN, m0, n0);
+        m0 += rank * BM;                                               // this CTA's rows of A and C
     };
     const uint32_t nkb = (ep.K + BK - 1) / BK;
     constexpr uint32_t kChunkKB = kChunkK / BK;
     const uint32_t nchunks = (nkb + kChunkKB - 1) / kChunkKB;
+    // Work units: whole tiles first, then the tail tiles in `split` K-shares each (the host sizes the
+    // tail so that it fills one last wave instead of leaving most pairs idle for a whole tile time).
+    const uint32_t nunits = ep.t_full + (ntiles - ep.t_full) * ep.split;
+    auto unit_at = [&](uint32_t u, uint32_t& tile, uint32_t& c0, uint32_t& c1, uint32_t& slot) -> bool {
+        if (u < ep.t_full) { tile = u; c0 = 0; c1 = nchunks; slot = 0; return false; }
+        const uint32_t v = u - ep.t_full, p = v % ep.split;
+        tile = ep.t_full + v / ep.split;
+        c0 = p * nchunks / ep.split;
+        c1 = (p + 1) * nchunks / ep.split;
+        slot = v;
+        return true;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -393,11 +416,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // ---- producer (both CTAs): own rows of A, own half of B; completion counted on the leader ----
             uint32_t g = 0;      // k-blocks issued so far, across tiles: ring position and phase
             bool ok = true;
-            for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
-                uint32_t m0, n0;
+            for (uint32_t u = pair; u < nunits && ok; u += npairs) {
+                uint32_t tile, c0, c1, slot, m0, n0;
+                unit_at(u, tile, c0, c1, slot);
                 tile_origin(tile, m0, n0);
                 const uint32_t nb0 = n0 + rank * HB;                    // the rows of B this CTA loads
-                for (uint32_t kb = 0; kb < nkb; ++kb, ++g) {
+                const uint32_t kb_last = min(nkb, c1 * kChunkKB);
+                for (uint32_t kb = c0 * kChunkKB; kb < kb_last; ++kb, ++g) {
                     const int s = g % S;
                     const uint32_t ph = (g / S) & 1u;
                     if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, kPairWaitCycles)) {
@@ -423,8 +448,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             constexpr uint32_t idesc = make_idesc(2u /*tf32*/, 2 * BM, BN);
             bool ok = true;
             uint32_t g = 0, gc = 0;     // k-blocks and chunks consumed so far, across tiles
-            for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
-                for (uint32_t c = 0; c < nchunks && ok; ++c, ++gc) {
+            for (uint32_t u = pair; u < nunits && ok; u += npairs) {
+                uint32_t tile, c0, c1, slot;
+                unit_at(u, tile, c0, c1, slot);
+                for (uint32_t c = c0; c < c1 && ok; ++c, ++gc) {
                     const uint32_t buf = gc & 1u;
                     // the accumulator must have been drained by both CTAs' epilogue warps (two chunks ago)
                     if (!mbar_wait_bounded(acc_empty_bar(buf), ((gc >> 1) & 1u) ^ 1u, kPairWaitCycles)) {
@@ -492,12 +519,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float sum[CPT];
         bool ok = true;
         uint32_t gc = 0;
-        for (uint32_t tile = pair; tile < ntiles && ok; tile += npairs) {
-            uint32_t m0, n0;
+        for (uint32_t u = pair; u < nunits && ok; u += npairs) {
+            uint32_t tile, c0, c1, slot, m0, n0;
+            const bool part = unit_at(u, tile, c0, c1, slot);
             tile_origin(tile, m0, n0);
 #pragma unroll
             for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
-            for (uint32_t c = 0; c < nchunks; ++c, ++gc) {
+            for (uint32_t c = c0; c < c1; ++c, ++gc) {
                 const uint32_t buf = gc & 1u;
                 bool got = mbar_wait_bounded(acc_full_bar(buf), (gc >> 1) & 1u, kPairWaitCycles + kPairWaitCycles / 2);
                 got = __all_sync(0xffffffffu, got);
@@ -524,18 +552,25 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // owns one row, so storing directly would touch 32 different lines per instruction; instead each
             // warp passes 32x32 blocks through a padded shared-memory buffer and writes 4 rows x 128 bytes
             // per instruction (bias and activation are applied on the way out).
+            // A K-share of a tail tile goes out raw (no bias, no activation) into its 256x256 slot.
             float* tb = tbuf + (warp - 2) * (32 * 33);
             const uint32_t rsub = lane >> 3, c4 = (lane & 7) * 4;
+            float* const out = part ? ep.partial + (size_t)slot * (2 * BM * BN) : ep.C;
+            float* const pre = part ? nullptr : ep.preact;
+            const uint32_t out_ld = part ? BN : ep.N, row_lim = part ? 2 * BM : ep.M, col_lim = part ? BN : ep.N;
+            const uint32_t row_base = part ? rank * BM : m0, col_base = part ? 0u : n0;
+            const int act = part ? FG_ACT_NONE : ep.act;
+            const bool vec = part || vec_ok;
 #pragma unroll
             for (int g4 = 0; g4 < CPT / 32; ++g4) {
-                const uint32_t col = n0 + half * CPT + g4 * 32 + c4;     // this lane's 4 columns on the way out
+                const uint32_t col = col_base + half * CPT + g4 * 32 + c4;     // this lane's 4 columns on the way out
 #pragma unroll
                 for (int j = 0; j < 32; ++j) tb[lane * 33 + j] = sum[g4 * 32 + j];
                 __syncwarp();
                 float bz[4] = {0.f, 0.f, 0.f, 0.f};
-                if (ep.bias) {
+                if (ep.bias && !part) {
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) if (col + t < ep.N) bz[t] = ep.bias[col + t];
+                    for (int t = 0; t < 4; ++t) if (col + t < col_lim) bz[t] = ep.bias[col + t];
                 }
                 // rolled on purpose: the activation code (tanhf, GELU) is inlined at every call site, and
                 // 128 copies of it per thread made this section miss the instruction cache on every line
@@ -543,24 +578,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll 1
                 for (int r = 0; r < 8; ++r) {
                     const uint32_t lr = r * 4 + rsub;
-                    const uint32_t row = m0 + q * 32 + lr;
+                    const uint32_t row = row_base + q * 32 + lr;
                     float z[4];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) z[t] = tb[lr * 33 + c4 + t] + bz[t];
-                    if (row < ep.M && col < ep.N) {
-                        float* crow = ep.C + (size_t)row * ep.N + col;
-                        float* prow = ep.preact ? ep.preact + (size_t)row * ep.N + col : nullptr;
-                        if (vec_ok && col + 3 < ep.N) {
-                            const float4 o = ep.act == FG_ACT_NONE ? make_float4(z[0], z[1], z[2], z[3])
-                                                                   : act_fwd4(ep.act, make_float4(z[0], z[1], z[2], z[3]));
+                    if (row < row_lim && col < col_lim) {
+                        float* crow = out + (size_t)row * out_ld + col;
+                        float* prow = pre ? pre + (size_t)row * out_ld + col : nullptr;
+                        if (vec && col + 3 < col_lim) {
+                            const float4 o = act == FG_ACT_NONE ? make_float4(z[0], z[1], z[2], z[3])
+                                                                : act_fwd4(act, make_float4(z[0], z[1], z[2], z[3]));
                             if (prow) *reinterpret_cast<float4*>(prow) = make_float4(z[0], z[1], z[2], z[3]);
                             *reinterpret_cast<float4*>(crow) = o;
                         } else {
 #pragma unroll
                             for (int t = 0; t < 4; ++t)
-                                if (col + t < ep.N) {
+                                if (col + t < col_lim) {
                                     if (prow) prow[t] = z[t];
-                                    crow[t] = fg_act_fwd(ep.act, z[t]);
+                                    crow[t] = fg_act_fwd(act, z[t]);
                                 }
                         }
                     }
@@ -575,6 +610,46 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// Folds the K-shares of the pair kernel's tail tiles in a fixed order, then bias, activation and store.
+// 64 blocks of 256 threads per tile; a thread owns four consecutive columns of one row.
+__global__ void __launch_bounds__(256) gemm_tc_pair_fold_kernel(Epilogue ep) {
+    constexpr uint32_t TM = 2 * BM, TN = 256;
+    const uint32_t pairs_m = (ep.M + TM - 1) / TM, pairs_n = (ep.N + TN - 1) / TN;
+    const uint32_t tail = blockIdx.x >> 6;
+    uint32_t m0, n0;
+    pair_tile_origin(ep.t_full + tail, pairs_m, pairs_n, TM, TN, m0, n0);
+    const uint32_t e = ((blockIdx.x & 63u) * 256 + threadIdx.x) * 4;        // element of the 256x256 tile
+    const uint32_t row = m0 + e / TN, col = n0 + e % TN;
+    if (row >= ep.M || col >= ep.N) return;
+    const float* p = ep.partial + (size_t)tail * ep.split * (TM * TN) + e;
+    float4 z = *reinterpret_cast<const float4*>(p);
+    for (uint32_t k = 1; k < ep.split; ++k) {
+        const float4 t = *reinterpret_cast<const float4*>(p + (size_t)k * (TM * TN));
+        z.x += t.x; z.y += t.y; z.z += t.z; z.w += t.w;
+    }
+    float zz[4] = {z.x, z.y, z.z, z.w};
+    if (ep.bias) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) if (col + t < ep.N) zz[t] += ep.bias[col + t];
+    }
+    float* crow = ep.C + (size_t)row * ep.N + col;
+    float* prow = ep.preact ? ep.preact + (size_t)row * ep.N + col : nullptr;
+    const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
+                        (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
+    if (vec_ok && col + 3 < ep.N) {
+        const float4 zin = make_float4(zz[0], zz[1], zz[2], zz[3]);
+        if (prow) *reinterpret_cast<float4*>(prow) = zin;
+        *reinterpret_cast<float4*>(crow) = ep.act == FG_ACT_NONE ? zin : act_fwd4(ep.act, zin);
+    } else {
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            if (col + t < ep.N) {
+                if (prow) prow[t] = zz[t];
+                crow[t] = fg_act_fwd(ep.act, zz[t]);
+            }
     }
 }
 
@@ -849,8 +924,12 @@ int32_t launch_tc(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilo
     return FG_OK;
 }
 
+// Scratch the pair kernel's split-K tail may need: at most one 256x256 f32 slot per resident pair.
+constexpr uint64_t kPairPartialBytes = 80ull * (2 * BM) * 256 * 4 + 256;
+
 template <int BK, int FMT>
-int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilogue& ep) {
+int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilogue& ep_in) {
+    Epilogue ep = ep_in;
     using Cfg = PairCfg<BK>;
     CUtensorMap tmA, tmB, tmA16, tmB16;
     int32_t s;
@@ -892,11 +971,35 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
         max_clusters[ctx->device & 63] = n;
     }
     const uint64_t slots = (uint64_t)max_clusters[ctx->device & 63];
-    dim3 grid((unsigned)(2 * (ntiles < slots ? ntiles : slots)));
+    // The last wave: `rem` tiles for `slots` pairs.  When at least two pairs are free per tile, each tail
+    // tile is cut into K-shares (whole accumulation chunks, at least two per share) so that the wave
+    // lasts a fraction of a tile time; the shares are folded by a second, bandwidth-bound kernel.
+    const uint32_t nchunks = (uint32_t)(((ep.K + BK - 1) / BK + kChunkK / BK - 1) / (kChunkK / BK));
+    const uint64_t rem = ntiles % slots;
+    uint64_t split = rem ? slots / rem : 1;
+    if (split > nchunks / 2) split = nchunks / 2;
+    if (split > 4) split = 4;
+    if (getenv("FG_GEMM_NO_SPLITK")) split = 1;
+    ep.partial = nullptr;
+    ep.t_full = (uint32_t)ntiles;
+    ep.split = 1;
+    if (split >= 2 && rem * split * (2 * BM) * 256 * 4 + 256 <= kPairPartialBytes) {
+        void* part;
+        if ((s = fg_ws_alloc(ctx, rem * split * (2 * BM) * 256 * 4, &part)) != FG_OK) return s;
+        ep.partial = (float*)part;
+        ep.t_full = (uint32_t)(ntiles - rem);
+        ep.split = (uint32_t)split;
+    }
+    const uint64_t nunits = ep.t_full + (ntiles - ep.t_full) * ep.split;
+    dim3 grid((unsigned)(2 * (nunits < slots ? nunits : slots)));
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
     gemm_tc_pair_kernel<BK, FMT><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
-    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
+    if (ep.split > 1) {
+        gemm_tc_pair_fold_kernel<<<(unsigned)((ntiles - ep.t_full) * 64), 256, 0, ctx->stream>>>(ep);
+        FG_LAUNCHED(ctx);
+    }
+    fg_time_end(ctx, tr);
     return FG_OK;
 }
 
@@ -976,7 +1079,7 @@ int32_t fg_gemm_f32(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB, u
     }
     const int fmt = path - 1;
     // Size the arena for both operands before carving it.
-    const uint64_t need = planes_bytes(fmt, M, K) + planes_bytes(fmt, N, K) + 1024;
+    const uint64_t need = planes_bytes(fmt, M, K) + planes_bytes(fmt, N, K) + kPairPartialBytes + 1024;
     if (ctx->ws_bytes < need) {
         int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
         if (s0 != FG_OK) return s0;
@@ -1057,8 +1160,8 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     const bool skinny = mode == FG_GEMM_AUTO && N <= 16;
     const bool tc_da = dA && !skinny, tc_db = dB && !skinny;
     uint64_t need = 2048;
-    if (tc_da) need += planes_bytes(fmt, M, N) + planes_bytes(fmt, K, N);
-    if (tc_db) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M);
+    if (tc_da) need += planes_bytes(fmt, M, N) + planes_bytes(fmt, K, N) + kPairPartialBytes;
+    if (tc_db) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M) + kPairPartialBytes;
     if (skinny) need += mn * 4 + 256 + fg_gemm_skinny_scratch_bytes(M, N, K);
     if (dbias) need += (uint64_t)((M + 31) / 32) * N * 4 + 256;   // per-tile column sums from the pre-pass
     if (ctx->ws_bytes < need) {
