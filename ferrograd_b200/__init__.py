@@ -6,6 +6,6 @@ mirrors its graph API (Graph / define_ops / alloc_tensors / schedule / dispatch_
 `mlp` drives data-parallel MLP training steps through the same entry points.
 """
 from .backend import Buffer, FgError, GpuContext, Plan, Tensor  # noqa: F401
-from .graph import (CROSS_ENTROPY, MEAN_SQUARED_ERROR, Graph, Metadata, Optim, SimpleDType,  # noqa: F401
+from .graph import (BINARY_CROSS_ENTROPY, CROSS_ENTROPY, MEAN_SQUARED_ERROR, Graph, Metadata, Optim, SimpleDType,  # noqa: F401
                     f32_bits)
 from . import bpat  # noqa: F401,E402

@@ -73,6 +73,7 @@ SIGNATURES = {
     "fg_softmax_ce_fwd_bwd": (i32, [c_ctx, c_dev, c_dev, u32, u32, f32, c_dev, c_dev, c_dev, c_dev, c_dev]),
     "fg_ce_loss_grad": (i32, [c_ctx, c_dev, c_dev, u32, u32, c_dev, c_dev]),
     "fg_mse_loss_grad": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
+    "fg_bce_loss_grad": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
     "fg_mse_loss_grad_noalloc": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
     "fg_sgd_step": (i32, [c_ctx, c_dev, c_dev, u64, f32, f32, i32]),
     "fg_adamw_step": (i32, [c_ctx, c_dev, c_dev, c_dev, c_dev, u64, C.POINTER(AdamWHyper), u32, c_dev, f32, i32]),

@@ -275,6 +275,10 @@ class GpuContext:
         self._check(self.lib.fg_mse_loss_grad(self.handle, _ptr(pred), _ptr(target), n, grad_scale,
                                               _ptr(loss_elem), _ptr(loss_sum), _ptr(grad)))
 
+    def bce_loss_grad(self, pred, target, n, grad_scale=1.0, loss_elem=None, loss_sum=None, grad=None):
+        self._check(self.lib.fg_bce_loss_grad(self.handle, _ptr(pred), _ptr(target), n, grad_scale,
+                                              _ptr(loss_elem), _ptr(loss_sum), _ptr(grad)))
+
     def mse_loss_grad_noalloc(self, pred, target, n, grad_scale=1.0, loss_elem=None, loss_sum=None, grad=None):
         """fg_mse_loss_grad for hosts that must not allocate device memory: the reduction scratch is a
         fixed array inside the library (n <= 268,435,456; calls on one GPU must not overlap)."""

@@ -63,6 +63,31 @@ __global__ void __launch_bounds__(256) mse_kernel(const float* __restrict__ pred
     }
 }
 
+// BCE on probabilities: loss = -(t*log(p) + (1-t)*log(1-p)), grad = (p - t)*scale.
+__global__ void __launch_bounds__(256) bce_kernel(const float* __restrict__ pred, const float* __restrict__ target,
+                                                  uint64_t n, float scale, float* __restrict__ loss_elem,
+                                                  float* __restrict__ grad, float* __restrict__ partials) {
+    __shared__ float red[8];
+    float s = 0.0f;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float p = pred[i], t = target[i];
+        const float l = -(t * logf(p) + (1.0f - t) * logf(1.0f - p));
+        if (loss_elem) loss_elem[i] = l;
+        if (grad) grad[i] = (p - t) * scale;
+        s += l;
+    }
+    if (partials) {
+        s = warp_sum(s);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.0f;
+            for (int w = 0; w < 8; ++w) t += red[w];
+            partials[blockIdx.x] = t;
+        }
+    }
+}
+
 // One CTA folds the partials in a fixed order.
 __global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restrict__ partials, int n,
                                                             float* __restrict__ out) {
@@ -271,6 +296,32 @@ int32_t fg_mse_loss_grad(fg_ctx* ctx, const float* pred, const float* target, ui
         partials = (float*)p;
     }
     mse_kernel<<<grid, 256, 0, ctx->stream>>>(pred, target, n, grad_scale, loss_elem_out, grad_out, partials);
+    FG_LAUNCHED(ctx);
+    if (loss_sum_out) {
+        fold_partials_kernel<<<1, 256, 0, ctx->stream>>>(partials, grid, loss_sum_out);
+        FG_LAUNCHED(ctx);
+    }
+    return FG_OK;
+}
+
+int32_t fg_bce_loss_grad(fg_ctx* ctx, const float* pred, const float* target, uint64_t n, float grad_scale,
+                         float* loss_elem_out, float* loss_sum_out, float* grad_out) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, pred && target, "fg_bce_loss_grad: NULL pointer");
+    FG_REQUIRE(ctx, loss_elem_out || loss_sum_out || grad_out, "fg_bce_loss_grad: no output requested");
+    if (n == 0) {
+        if (loss_sum_out) FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaMemsetAsync(loss_sum_out, 0, 4, ctx->stream));
+        return FG_OK;
+    }
+    int grid = fg_stream_grid(ctx, n, 256, 8);
+    float* partials = nullptr;
+    if (loss_sum_out) {
+        void* p;
+        int32_t s = fg_ws_alloc(ctx, (uint64_t)grid * sizeof(float), &p);
+        if (s != FG_OK) return s;
+        partials = (float*)p;
+    }
+    bce_kernel<<<grid, 256, 0, ctx->stream>>>(pred, target, n, grad_scale, loss_elem_out, grad_out, partials);
     FG_LAUNCHED(ctx);
     if (loss_sum_out) {
         fold_partials_kernel<<<1, 256, 0, ctx->stream>>>(partials, grid, loss_sum_out);

@@ -101,67 +101,75 @@ __global__ void __launch_bounds__(256) skinny_transpose_kernel(uint32_t K, uint3
     Bt[i] = (n < N && k < K) ? B[(size_t)k * N + n] : 0.0f;
 }
 
-// C[M,N] = act(A[M,K]·B[K,N] + bias) from the transposed copy Bt: one warp per 2 rows, lanes split k.
+// C[M,N] = act(A[M,K]·B[K,N] + bias) from the transposed copy Bt.  A block of 8 warps owns 8 rows: warp w
+// works on rows 4*(w/4) .. +3 and on every fourth 128-wide slice of k (lanes split the slice), so each
+// Bt value fetched from L1 feeds four rows, and the four k-quarters of a row meet in shared memory.
 template <int NT, bool VEC>
-__global__ void __launch_bounds__(256) gemm_skinny_n_kernel(uint32_t M, uint32_t N, uint32_t K, uint32_t Kp,
+__global__ void __launch_bounds__(256, 2) gemm_skinny_n_kernel(uint32_t M, uint32_t N, uint32_t K, uint32_t Kp,
                                                             const float* __restrict__ A, const float* __restrict__ Bt,
                                                             float* __restrict__ C, const float* __restrict__ bias, int act,
                                                             float* __restrict__ preact) {
-    const int lane = threadIdx.x & 31;
-    const uint32_t row0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * 2;
-    if (row0 >= M) return;
-    const uint32_t row1 = min(row0 + 1, M - 1);
-    float acc0[NT], acc1[NT];
+    __shared__ float red[8][4][NT];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ks = warp & 3;
+    const uint32_t row0 = blockIdx.x * 8 + (warp >> 2) * 4;
+    float acc[4][NT];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) acc0[n] = acc1[n] = 0.0f;
-    const float* a0 = A + (size_t)row0 * K;
-    const float* a1 = A + (size_t)row1 * K;
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) acc[r][n] = 0.0f;
+    const float* a[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) a[r] = A + (size_t)min(row0 + r, M - 1) * K;     // rows past the end are not stored
     if (VEC) {
-#pragma unroll 2
-        for (uint32_t k = lane * 4; k < K; k += 128) {
-            const float4 x0 = *reinterpret_cast<const float4*>(a0 + k);
-            const float4 x1 = *reinterpret_cast<const float4*>(a1 + k);
+#pragma unroll 1
+        for (uint32_t k = (ks * 32 + lane) * 4; k < K; k += 512) {
+            float4 x[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) x[r] = *reinterpret_cast<const float4*>(a[r] + k);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const float4 w = *reinterpret_cast<const float4*>(Bt + (size_t)n * Kp + k);
-                acc0[n] = fmaf(x0.w, w.w, fmaf(x0.z, w.z, fmaf(x0.y, w.y, fmaf(x0.x, w.x, acc0[n]))));
-                acc1[n] = fmaf(x1.w, w.w, fmaf(x1.z, w.z, fmaf(x1.y, w.y, fmaf(x1.x, w.x, acc1[n]))));
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    acc[r][n] = fmaf(x[r].w, w.w, fmaf(x[r].z, w.z, fmaf(x[r].y, w.y, fmaf(x[r].x, w.x, acc[r][n]))));
             }
         }
     } else {
-#pragma unroll 4
-        for (uint32_t k = lane; k < K; k += 32) {
-            const float x0 = a0[k], x1 = a1[k];
+#pragma unroll 2
+        for (uint32_t k = ks * 32 + lane; k < K; k += 128) {
+            float x[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) x[r] = a[r][k];
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const float w = Bt[(size_t)n * Kp + k];
-                acc0[n] = fmaf(x0, w, acc0[n]);
-                acc1[n] = fmaf(x1, w, acc1[n]);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[r][n] = fmaf(x[r], w, acc[r][n]);
             }
         }
     }
-    float z0 = 0.0f, z1 = 0.0f;
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-        float u = acc0[n], v = acc1[n];
+    for (int r = 0; r < 4; ++r)
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            u += __shfl_xor_sync(0xffffffffu, u, o);
-            v += __shfl_xor_sync(0xffffffffu, v, o);
+        for (int n = 0; n < NT; ++n) {
+            float v = acc[r][n];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) red[warp][r][n] = v;
         }
-        if (lane == n) { z0 = u; z1 = v; }
-    }
-    if (lane < (int)N) {
-        const float bb = bias ? bias[lane] : 0.0f;
-        size_t o = (size_t)row0 * N + lane;
-        z0 += bb;
-        if (preact) preact[o] = z0;
-        C[o] = fg_act_fwd(act, z0);
-        if (row0 + 1 < M) {
-            o += N;
-            z1 += bb;
-            if (preact) preact[o] = z1;
-            C[o] = fg_act_fwd(act, z1);
+    __syncthreads();
+    // thread t < 8*N: row t / N of the block, column t % N
+    const uint32_t t = threadIdx.x;
+    if (t < 8 * N) {
+        const uint32_t rr = t / N, n = t % N, row = blockIdx.x * 8 + rr;
+        if (row < M) {
+            const int w0 = (rr >> 2) * 4, r = rr & 3;
+            float z = (red[w0][r][n] + red[w0 + 1][r][n]) + (red[w0 + 2][r][n] + red[w0 + 3][r][n]);
+            if (bias) z += bias[n];
+            const size_t o = (size_t)row * N + n;
+            if (preact) preact[o] = z;
+            C[o] = fg_act_fwd(act, z);
         }
     }
 }
@@ -303,7 +311,7 @@ int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K,
     if (s != FG_OK) return s;
     skinny_transpose_kernel<<<(NTr * Kp + 255) / 256, 256, 0, ctx->stream>>>(K, N, Kp, NTr, B, (float*)bt);
     FG_LAUNCHED(ctx);
-    const uint32_t blocks = (M + 15) / 16;
+    const uint32_t blocks = (M + 7) / 8;
     const bool vec = (K % 4 == 0) && fg_aligned16(A);
     FG_SKINNY_DISPATCH(N, {
         if (vec) gemm_skinny_n_kernel<NT, true><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);

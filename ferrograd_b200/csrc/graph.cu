@@ -308,7 +308,7 @@ int32_t accumulate_into(fg_exec* e, int node, const float* src) {
 extern "C" {
 
 int32_t fg_graph_create(int32_t loss, int32_t optim, fg_graph** out) {
-    if (!out || loss < FG_LOSS_MSE || loss > FG_LOSS_CROSS_ENTROPY || optim < FG_OPTIM_SGD || optim > FG_OPTIM_ADAMW)
+    if (!out || loss < FG_LOSS_MSE || loss > FG_LOSS_BINARY_CROSS_ENTROPY || optim < FG_OPTIM_SGD || optim > FG_OPTIM_ADAMW)
         return FG_ERR_INVALID_ARGUMENT;
     fg_graph* g = new (std::nothrow) fg_graph();
     if (!g) return FG_ERR_OUT_OF_MEMORY;
@@ -436,6 +436,11 @@ int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
     if (e->g.loss == FG_LOSS_MSE) {
         FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
         return fg_mse_loss_grad(e->ctx, vptr(e, e->last), (const float*)target->ptr, o.numel, 1.0f, (float*)e->loss_t->ptr,
+                                nullptr, (float*)e->seed->ptr);
+    }
+    if (e->g.loss == FG_LOSS_BINARY_CROSS_ENTROPY) {
+        FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
+        return fg_bce_loss_grad(e->ctx, vptr(e, e->last), (const float*)target->ptr, o.numel, 1.0f, (float*)e->loss_t->ptr,
                                 nullptr, (float*)e->seed->ptr);
     }
     const uint32_t cols = o.dims.back();

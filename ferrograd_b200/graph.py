@@ -29,6 +29,7 @@ from .backend import Buffer, FgError, Tensor
 
 MEAN_SQUARED_ERROR = 0      # ferrograd_nn::loss::MEAN_SQUARED_ERROR
 CROSS_ENTROPY = 1           # ferrograd_nn::loss::CROSS_ENTROPY
+BINARY_CROSS_ENTROPY = 2    # ferrograd_nn::loss::BINARY_CROSS_ENTROPY
 _OPS = {"add": 2, "sub": 3, "mul": 4, "div": 5, "neg": 6, "abs": 7, "exp": 8, "log": 9, "tanh": 10, "relu": 11,
         "gelu": 12, "elu": 13, "matmul": 14, "softmax": 15}
 

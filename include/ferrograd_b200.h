@@ -187,6 +187,16 @@ int32_t fg_mse_loss_grad(fg_ctx* ctx, const float* pred, const float* target, ui
                          float grad_scale, float* loss_elem_out, float* loss_sum_out,
                          float* grad_out);
 
+/* ---- BCE (BINARY_CROSS_ENTROPY: loss/basic_loss.rs:29-89), on probabilities p in (0,1) ----
+ * loss[i] = −(t·log p + (1−t)·log(1−p)); grad[i] = (p − t)·grad_scale, which is the reference's
+ * gradient expression (:81-85: the derivative with respect to the logit of a sigmoid output).
+ * The reference's loss expression differs from the definition above in two places (:47-51 takes
+ * 1 − target where 1 − pred is meant, and :75-79 subtracts the terms in the opposite order); the
+ * standard definition is computed here.  Outputs as for fg_mse_loss_grad. */
+int32_t fg_bce_loss_grad(fg_ctx* ctx, const float* pred, const float* target, uint64_t n,
+                         float grad_scale, float* loss_elem_out, float* loss_sum_out,
+                         float* grad_out);
+
 /* The same loss and gradient for hosts that must never cause a device allocation (a
  * process whose own pool already owns all GPU memory, a latency-bound service, a job run
  * against a fixed memory budget).  It has no counterpart in the reference.  The partial
@@ -259,7 +269,8 @@ int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, i
  * shape is a list of metadata FIELD ids (Metadata::new_field, backend/mod.rs:585-596); field 0 is
  * reserved for the learning rate's f32 bits, the bound metadata array gives every field its value. */
 enum fg_graph_op { FG_GRAPH_MATMUL = 14, FG_GRAPH_SOFTMAX = 15 };
-enum fg_loss { FG_LOSS_MSE = 0, FG_LOSS_CROSS_ENTROPY = 1 };   /* loss/basic_loss.rs:3-27, :91-133 */
+enum fg_loss { FG_LOSS_MSE = 0, FG_LOSS_CROSS_ENTROPY = 1,     /* loss/basic_loss.rs:3-27, :91-133 */
+               FG_LOSS_BINARY_CROSS_ENTROPY = 2 };             /* loss/basic_loss.rs:29-89         */
 enum fg_optim { FG_OPTIM_SGD = 0, FG_OPTIM_ADAMW = 1 };        /* optim/basic_optim.rs:3-31; AdamW is new */
 typedef struct fg_graph fg_graph;   /* ferrograd::Graph (crates/ferrograd/src/graph.rs:15-98)        */
 typedef struct fg_exec fg_exec;     /* AllocTensors + compiled kernels + Schedule of one graph        */

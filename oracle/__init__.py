@@ -143,6 +143,16 @@ def mse(pred, target, grad_scale=1.0):
     return loss, float(s[0]), grad
 
 
+def bce(pred, target, grad_scale=1.0, reference_formula=False):
+    pred, target = _f(pred), _f(target)
+    loss = np.empty_like(pred)
+    grad = np.empty_like(pred)
+    s = np.empty(1, np.float32)
+    lib().ref_bce_loss_grad(C.c_uint64(pred.size), _p(pred), _p(target), C.c_float(grad_scale),
+                            int(reference_formula), _p(loss), _p(s), _p(grad))
+    return loss, float(s[0]), grad
+
+
 def sgd(w, g, lr, grad_scale=1.0, zero_grad=True):
     """In place on w and g (float32 contiguous arrays)."""
     assert w.dtype == np.float32 and g.dtype == np.float32

@@ -345,6 +345,30 @@ void ref_mse_loss_grad(uint64_t n, const float* pred, const float* target, float
     if (loss_sum) *loss_sum = (float)s;
 }
 
+void ref_bce_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,
+                       int reference_formula, float* loss_elem, float* loss_sum, float* grad) {
+    // loss/basic_loss.rs:29-89.  grad = pred - target (:81-85).  The loss there is
+    // (1-t)*log(1-t) - t*log(p): `one_minus_pred` is built from the target (:47-51) and the terms
+    // are subtracted as term2 - term1 (:75-79).  reference_formula != 0 reproduces exactly that;
+    // 0 gives the definition -(t*log(p) + (1-t)*log(1-p)).
+    double s = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : s)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        const float p = pred[i], t = target[i];
+        float l;
+        if (reference_formula) {
+            const float omt = 1.0f - t;
+            l = omt * logf(omt) - t * logf(p);
+        } else {
+            l = -(t * logf(p) + (1.0f - t) * logf(1.0f - p));
+        }
+        if (loss_elem) loss_elem[i] = l;
+        if (grad) grad[i] = (p - t) * grad_scale;
+        s += l;
+    }
+    if (loss_sum) *loss_sum = (float)s;
+}
+
 void ref_sgd_step(uint64_t n, float* w, float* g, float lr, float grad_scale, int zero_grad) {
     // optim/basic_optim.rs:3-31: scaled = g*lr; w -= scaled; g = 0.
 #pragma omp parallel for schedule(static)

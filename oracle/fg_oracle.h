@@ -55,6 +55,8 @@ void ref_softmax_ce_fwd_bwd(uint32_t rows, uint32_t cols, const float* logits,
                             float* loss_mean, float* dlogits, float* probs, uint32_t* argmax);
 void ref_mse_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,
                        float* loss_elem, float* loss_sum, float* grad);
+void ref_bce_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,
+                       int reference_formula, float* loss_elem, float* loss_sum, float* grad);
 
 void ref_sgd_step(uint64_t n, float* w, float* g, float lr, float grad_scale, int zero_grad);
 void ref_adamw_step(uint64_t n, float* w, float* g, float* m, float* v, float lr, float beta1,

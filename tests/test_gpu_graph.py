@@ -259,6 +259,44 @@ def test_mlp_graph_matches_oracle(ctx, oracle, act, loss_name):
     t.destroy()
 
 
+def test_binary_cross_entropy_graph(ctx, oracle):
+    """p = 1 / (1 + exp(-x)) built from graph ops, BINARY_CROSS_ENTROPY against soft and hard targets:
+    loss_t holds the per-element loss, the seed is p - t (loss/basic_loss.rs:81-85), and the backward
+    pass carries it through the sigmoid's own derivative."""
+    from ferrograd_b200 import BINARY_CROSS_ENTROPY
+    R, Cn = 64, 48
+    r = np.random.Generator(np.random.Philox(21))
+    x = (r.standard_normal((R, Cn)) * 1.5).astype(np.float32)
+    tgt = (r.random((R, Cn)) < 0.4).astype(np.float32)
+    tgt[:8] = r.random((8, Cn)).astype(np.float32)
+
+    def define(g, fr, fc):
+        xi = g.input([fr, fc])
+        g.div(g.constant_f32(1.0), g.add(g.constant_f32(1.0), g.exp(g.neg(xi))))
+    graph, t, kernels, binding = build(ctx, define, [R, Cn], loss=BINARY_CROSS_ENTROPY)
+    ins = [ctx.init_tensor_f32(x.shape, x)]
+    sch = ctx.schedule(kernels, binding, ins, t, [], ())
+    target = ctx.init_tensor_f32(tgt.shape, tgt)
+    ctx.dispatch_forward(sch)
+    ctx.dispatch_loss(sch, target)
+    ctx.dispatch_backward(sch)
+    ctx.sync()
+    x64, t64 = x.astype(np.float64), tgt.astype(np.float64)
+    p64 = 1.0 / (1.0 + np.exp(-x64))
+    got_p = dl(ctx, t.forward_out, x.size).reshape(R, Cn)
+    ok, worst = rel_err_ok(got_p, p64, 1e-5)
+    assert ok, f"sigmoid: {worst:.3g} x 1e-5"
+    lref, _, gref = oracle.bce(got_p, tgt)
+    ok, worst = rel_err_ok(ctx.to_numpy(t.loss_t).reshape(R, Cn), lref, 1e-5)
+    assert ok, f"loss: {worst:.3g} x 1e-5"
+    ok, worst = rel_err_ok(ctx.to_numpy(t.loss_t).reshape(R, Cn), -(t64 * np.log(p64) + (1 - t64) * np.log1p(-p64)), 1e-5)
+    assert ok, f"loss vs float64: {worst:.3g} x 1e-5"
+    assert np.array_equal(dl(ctx, t.seed, x.size).reshape(R, Cn), gref)
+    ok, worst = rel_err_ok(dl(ctx, t.grad_tensors[0], x.size).reshape(R, Cn), (p64 - t64) * p64 * (1 - p64), 1e-5)
+    assert ok, f"dx: {worst:.3g} x 1e-5"
+    t.destroy()
+
+
 def test_fan_out_accumulates_gradients(ctx, oracle):
     """y = (a @ b) * tanh(a @ b): the matmul result has two consumers, a is used by one matmul only; and
     z = a @ a (both operands the same tensor) takes the accumulate path."""

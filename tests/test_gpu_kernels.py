@@ -174,6 +174,24 @@ def test_mse(ctx, oracle, n):
     check(ctx.to_numpy(s), np.array([sref], np.float32), TOL_EW, "mse sum")
 
 
+@pytest.mark.parametrize("n", [1, 130, 100003])
+def test_bce(ctx, oracle, n):
+    r = rng(45 + n)
+    p = (1.0 / (1.0 + np.exp(-r.standard_normal(n) * 2.0))).astype(np.float32)
+    t = (r.random(n) < 0.5).astype(np.float32)
+    if n > 100:
+        t[:50] = r.random(50).astype(np.float32)        # soft targets too
+    loss, grad, s = ctx.new_tensor((n,)), ctx.new_tensor((n,)), ctx.new_tensor((1,))
+    ctx.bce_loss_grad(up(ctx, p), up(ctx, t), n, grad_scale=0.25, loss_elem=loss, loss_sum=s, grad=grad)
+    lref, sref, gref = oracle.bce(p, t, grad_scale=0.25)
+    assert np.array_equal(ctx.to_numpy(grad), gref)
+    check(ctx.to_numpy(loss), lref, TOL_EW, "bce loss")
+    check(ctx.to_numpy(s), np.array([sref], np.float32), TOL_EW, "bce sum")
+    # float64 closed form
+    p64, t64 = p.astype(np.float64), t.astype(np.float64)
+    check(ctx.to_numpy(loss), -(t64 * np.log(p64) + (1 - t64) * np.log1p(-p64)), TOL_EW, "bce vs float64")
+
+
 @pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
 def test_bias_act_and_backward(ctx, oracle, act):
     rows, cols = 67, 130

@@ -94,6 +94,19 @@ def test_div_const_softmax(oracle):
     assert (dx == 0.0).all()
 
 
+def test_bce_formulas(oracle):
+    # loss/basic_loss.rs:29-89.  Hard targets at p = 1/2: the definition gives log 2 per element and the
+    # gradient is p - t.  With reference_formula the loss is (1-t)*log(1-t) - t*log(p) as the file has it:
+    # at t = 1/2, p = 1/4 that is 0.5*log(0.5) - 0.5*log(0.25) = 0.5*log 2.
+    p, t = full(64, 0.5), np.concatenate([full(32, 0.0), full(32, 1.0)])
+    loss, s, grad = oracle.bce(p, t)
+    assert np.allclose(loss, np.log(2.0), rtol=1e-6) and abs(s - 64 * np.log(2.0)) < 1e-4
+    assert (grad == p - t).all()
+    loss_q, _, grad_q = oracle.bce(full(8, 0.25), full(8, 0.5), reference_formula=True)
+    assert np.allclose(loss_q, 0.5 * np.log(2.0), rtol=1e-6)
+    assert (grad_q == f32(-0.25)).all()
+
+
 def test_mul_add_optim(oracle):
     # tests/optim.rs:10-104: SGD with lr = 1e-3 after mul_add; grads are zeroed.
     a, b, c = full(1024, 3.0), full(1024, 2.0), full(1024, 1.0)
