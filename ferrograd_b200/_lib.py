@@ -66,6 +66,9 @@ SIGNATURES = {
     "fg_memset_zero": (i32, [c_ctx, c_dev, u64]),
     "fg_gemm_f32": (i32, [c_ctx, i32, i32, i32, u32, u32, u32, c_dev, c_dev, c_dev, c_dev, i32, c_dev]),
     "fg_gemm_bwd_f32": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, i32, c_dev, c_dev, c_dev, c_dev, c_dev]),
+    "fg_gemm_batched_f32": (i32, [c_ctx, i32, u32, u32, u32, u32, c_dev, u64, c_dev, u64, c_dev, u64, c_dev, i32, c_dev]),
+    "fg_gemm_batched_bwd_f32": (i32, [c_ctx, i32, u32, u32, u32, u32, c_dev, u64, c_dev, u64, c_dev, u64, i32, c_dev,
+                                      c_dev, c_dev]),
     "fg_bias_act_fwd": (i32, [c_ctx, u32, u32, c_dev, c_dev, i32, c_dev]),
     "fg_act_bwd": (i32, [c_ctx, u64, i32, c_dev, c_dev, c_dev]),
     "fg_softmax_fwd": (i32, [c_ctx, u32, u32, c_dev, c_dev]),

@@ -249,6 +249,19 @@ class GpuContext:
         self._check(self.lib.fg_gemm_bwd_f32(self.handle, GEMM_MODE[mode], M, N, K, _ptr(A), _ptr(B), _ptr(dY),
                                              ACT[act], _ptr(saved), _ptr(dA), _ptr(dB), _ptr(dbias), _ptr(dZ_out)))
 
+    def gemm_batched(self, A, B, Cout, batch, M, N, K, bias=None, act="none", preact_out=None, mode="auto",
+                     strides=None):
+        sa, sb, sc = strides or (M * K, K * N, M * N)
+        self._check(self.lib.fg_gemm_batched_f32(self.handle, GEMM_MODE[mode], batch, M, N, K, _ptr(A), sa, _ptr(B), sb,
+                                                 _ptr(Cout), sc, _ptr(bias), ACT[act], _ptr(preact_out)))
+
+    def gemm_batched_bwd(self, A, B, dY, batch, M, N, K, act="none", saved=None, dA=None, dB=None, mode="auto",
+                         strides=None):
+        sa, sb, sc = strides or (M * K, K * N, M * N)
+        self._check(self.lib.fg_gemm_batched_bwd_f32(self.handle, GEMM_MODE[mode], batch, M, N, K, _ptr(A), sa,
+                                                     _ptr(B), sb, _ptr(dY), sc, ACT[act], _ptr(saved), _ptr(dA),
+                                                     _ptr(dB)))
+
     def bias_act_fwd(self, z, bias, act, y, rows, cols):
         self._check(self.lib.fg_bias_act_fwd(self.handle, rows, cols, _ptr(z), _ptr(bias), ACT[act], _ptr(y)))
 

@@ -1217,4 +1217,36 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
     return FG_OK;
 }
 
+// Batched forms: `batch` independent products, operand t at base + t*stride (strides in elements).
+// The reference steps A, B and C by one matrix per Z index of a rank-3 matmul (kernel/forward.rs:159-190).
+int32_t fg_gemm_batched_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t M, uint32_t N, uint32_t K, const float* A,
+                            uint64_t strideA, const float* B, uint64_t strideB, float* C, uint64_t strideC,
+                            const float* bias, int32_t act, float* preact_out) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, strideA >= (uint64_t)M * K && strideB >= (uint64_t)K * N && strideC >= (uint64_t)M * N,
+               "fg_gemm_batched_f32: a stride is smaller than its matrix (for one B shared by all products, "
+               "call fg_gemm_f32 with batch*M rows)");
+    for (uint32_t t = 0; t < batch; ++t) {
+        int32_t s = fg_gemm_f32(ctx, mode, 0, 0, M, N, K, A + t * strideA, B + t * strideB, C + t * strideC, bias, act,
+                                preact_out ? preact_out + t * strideC : nullptr);
+        if (s != FG_OK) return s;
+    }
+    return FG_OK;
+}
+
+int32_t fg_gemm_batched_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t M, uint32_t N, uint32_t K,
+                                const float* A, uint64_t strideA, const float* B, uint64_t strideB, const float* dY,
+                                uint64_t strideC, int32_t act, const float* saved, float* dA, float* dB) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, strideA >= (uint64_t)M * K && strideB >= (uint64_t)K * N && strideC >= (uint64_t)M * N,
+               "fg_gemm_batched_bwd_f32: a stride is smaller than its matrix");
+    for (uint32_t t = 0; t < batch; ++t) {
+        int32_t s = fg_gemm_bwd_f32(ctx, mode, M, N, K, A ? A + t * strideA : nullptr, B ? B + t * strideB : nullptr,
+                                    dY + t * strideC, act, saved ? saved + t * strideC : nullptr,
+                                    dA ? dA + t * strideA : nullptr, dB ? dB + t * strideB : nullptr, nullptr, nullptr);
+        if (s != FG_OK) return s;
+    }
+    return FG_OK;
+}
+
 }  // extern "C"

@@ -67,6 +67,10 @@ struct ENode {
 struct GemmStep {
     int mm, a, b, bias, act, out;   // node ids; bias = -1 when absent; out = node whose buffer receives the result
     fg_buf* preact;                 // GELU needs the pre-activation
+    // batch products of [M,K] x [K,N].  [T,M,K] x [T,K,N] is T products (the reference steps both operands
+    // and the result by one matrix per Z index: kernel/forward.rs:159-190); [T,M,K] x [K,N] is one product
+    // with T*M rows.
+    uint32_t batch, M, K, N;
 };
 struct ChainStep {
     int root;
@@ -171,9 +175,10 @@ int32_t lower(fg_exec* e) {
             en.dims.clear();
         } else if (gn.op == OP_MATMUL) {
             const auto &da = e->n[gn.a].dims, &db = e->n[gn.b].dims;
-            if (da.size() != 2 || db.size() != 2 || da[1] != db[0])
-                return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: matmul needs [M,K] x [K,N]");
-            en.dims = {da[0], db[1]};
+            if (da.size() == 2 && db.size() == 2 && da[1] == db[0]) en.dims = {da[0], db[1]};
+            else if (da.size() == 3 && db.size() == 3 && da[0] == db[0] && da[2] == db[1]) en.dims = {da[0], da[1], db[2]};
+            else if (da.size() == 3 && db.size() == 2 && da[2] == db[0]) en.dims = {da[0], da[1], db[1]};
+            else return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: matmul needs [M,K] x [K,N], [T,M,K] x [T,K,N] or [T,M,K] x [K,N]");
         } else if (gn.op == OP_SOFTMAX) {
             en.dims = e->n[gn.a].dims;
             if (en.dims.empty()) return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: softmax of a scalar");
@@ -210,7 +215,16 @@ int32_t lower(fg_exec* e) {
         if (g.nodes[i].op != OP_MATMUL) continue;
         if (g.nodes[g.nodes[i].a].op == FG_EW_CONST || g.nodes[g.nodes[i].b].op == FG_EW_CONST)
             return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: matmul of a constant");
-        GemmStep s{i, g.nodes[i].a, g.nodes[i].b, -1, FG_ACT_NONE, i, nullptr};
+        GemmStep s{i, g.nodes[i].a, g.nodes[i].b, -1, FG_ACT_NONE, i, nullptr, 1, 0, 0, 0};
+        {
+            const auto &da = e->n[s.a].dims, &db = e->n[s.b].dims;
+            if (da.size() == 2) { s.M = da[0]; s.K = da[1]; s.N = db[1]; }
+            else if (db.size() == 3) { s.batch = da[0]; s.M = da[1]; s.K = da[2]; s.N = db[2]; }
+            else {
+                if ((uint64_t)da[0] * da[1] > 0xffffffffull) return fail(e, FG_ERR_INVALID_ARGUMENT, "graph: matmul has too many rows");
+                s.M = da[0] * da[1]; s.K = da[2]; s.N = db[1];
+            }
+        }
         int c = sole_consumer(e, s.out);
         if (c >= 0 && e->n[c].bias_bcast && g.nodes[c].a == s.out) {
             s.bias = g.nodes[c].b;
@@ -408,10 +422,12 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
     for (const Step& st : e->fwd) {
         if (st.kind == 0) {
             const GemmStep& gs = e->gemms[st.idx];
-            const auto& da = e->n[gs.a].dims;
-            const auto& db = e->n[gs.b].dims;
-            s = fg_gemm_f32(e->ctx, e->gemm_mode, 0, 0, da[0], db[1], da[1], vptr(e, gs.a), vptr(e, gs.b), vptr(e, gs.out),
-                            gs.bias >= 0 ? vptr(e, gs.bias) : nullptr, gs.act, gs.preact ? (float*)gs.preact->ptr : nullptr);
+            const size_t sa = (size_t)gs.M * gs.K, sb = (size_t)gs.K * gs.N, sc = (size_t)gs.M * gs.N;
+            s = FG_OK;
+            for (uint32_t t = 0; t < gs.batch && s == FG_OK; ++t)
+                s = fg_gemm_f32(e->ctx, e->gemm_mode, 0, 0, gs.M, gs.N, gs.K, vptr(e, gs.a) + t * sa, vptr(e, gs.b) + t * sb,
+                                vptr(e, gs.out) + t * sc, gs.bias >= 0 ? vptr(e, gs.bias) : nullptr, gs.act,
+                                gs.preact ? (float*)gs.preact->ptr + t * sc : nullptr);
         } else if (st.kind == 1) {
             const ChainStep& c = e->chains[st.idx];
             const float* in[FG_EW_MAX_INPUTS];
@@ -462,12 +478,37 @@ int32_t fg_exec_dispatch_backward(fg_exec* e) {
         if (st.kind == 0) {
             const GemmStep& gs = e->gemms[st.idx];
             if (gs.out != e->last && !written[gs.out]) continue;   // does not reach the output
-            const auto& da = e->n[gs.a].dims;
-            const auto& db = e->n[gs.b].dims;
-            const uint32_t M = da[0], K = da[1], Nn = db[1];
+            const uint32_t M = gs.M, K = gs.K, Nn = gs.N;
+            const size_t sa = (size_t)M * K, sb = (size_t)K * Nn, sc = (size_t)M * Nn;
             // destinations: the gradient buffer itself for a first contribution, the scratch tensor otherwise
             float* dA = written[gs.a] ? (float*)e->tmp->ptr : gptr(e, gs.a);
             const float* saved = gs.act == FG_ACT_NONE ? nullptr : gs.act == FG_ACT_GELU ? (float*)gs.preact->ptr : vptr(e, gs.out);
+            if (gs.batch > 1) {
+                // one product per Z index: every operand, gradient and saved tensor is stepped by one matrix
+                auto run = [&](float* da_dst, float* db_dst) -> int32_t {
+                    for (uint32_t t = 0; t < gs.batch; ++t) {
+                        int32_t r = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a) + t * sa, vptr(e, gs.b) + t * sb,
+                                                    grad_of(gs.out) + t * sc, gs.act, saved ? saved + t * sc : nullptr,
+                                                    da_dst ? da_dst + t * sa : nullptr, db_dst ? db_dst + t * sb : nullptr,
+                                                    nullptr, nullptr);
+                        if (r != FG_OK) return r;
+                    }
+                    return FG_OK;
+                };
+                if (!written[gs.a] && !written[gs.b] && gs.a != gs.b) {
+                    if ((s = run(gptr(e, gs.a), gptr(e, gs.b))) != FG_OK) return s;
+                    written[gs.a] = written[gs.b] = 1;
+                    continue;
+                }
+                if ((s = run(dA, nullptr)) != FG_OK) return s;
+                if (written[gs.a] && (s = accumulate_into(e, gs.a, dA)) != FG_OK) return s;
+                written[gs.a] = 1;
+                float* dBt = written[gs.b] ? (float*)e->tmp->ptr : gptr(e, gs.b);
+                if ((s = run(nullptr, dBt)) != FG_OK) return s;
+                if (written[gs.b] && (s = accumulate_into(e, gs.b, dBt)) != FG_OK) return s;
+                written[gs.b] = 1;
+                continue;
+            }
             float* dbias = nullptr;
             if (gs.bias >= 0) dbias = written[gs.bias] ? nullptr : gptr(e, gs.bias);
             if (gs.bias >= 0 && written[gs.bias]) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: a bias used by two layers");

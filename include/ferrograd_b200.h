@@ -153,6 +153,19 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
                         int32_t act, const float* saved,
                         float* dA, float* dB, float* dbias, float* dZ_out);
 
+/* Rank-3 matmul: `batch` independent products; product t uses A + t*strideA, B + t*strideB and
+ * C (or dY, saved, preact_out) + t*strideC, strides in elements.  The reference steps every operand
+ * by one matrix per Z index (kernel/forward.rs:159-190, op/matmul/generic.rs:131,194).  Each stride
+ * must be at least its matrix; one B shared by all products is fg_gemm_f32 with batch*M rows. */
+int32_t fg_gemm_batched_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t M, uint32_t N, uint32_t K,
+                            const float* A, uint64_t strideA, const float* B, uint64_t strideB,
+                            float* C, uint64_t strideC, const float* bias, int32_t act,
+                            float* preact_out);
+int32_t fg_gemm_batched_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t M, uint32_t N,
+                                uint32_t K, const float* A, uint64_t strideA, const float* B,
+                                uint64_t strideB, const float* dY, uint64_t strideC, int32_t act,
+                                const float* saved, float* dA, float* dB);
+
 /* ---- activations standalone (op/unary.rs) ---- */
 int32_t fg_bias_act_fwd(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float* z,
                         const float* bias, int32_t act, float* y);

@@ -297,6 +297,41 @@ def test_binary_cross_entropy_graph(ctx, oracle):
     t.destroy()
 
 
+@pytest.mark.parametrize("shared_b", [False, True])
+def test_rank3_matmul_graph(ctx, oracle, shared_b):
+    """[T,M,K] x [T,K,N] runs one product per leading index; [T,M,K] x [K,N] is one product with T*M rows.
+    Forward and both gradients against the oracle, followed by an elementwise consumer."""
+    T, M, K, Nn = 3, 48, 40, 56
+    r = np.random.Generator(np.random.Philox(33))
+    A = r.standard_normal((T, M, K), np.float32)
+    B = (r.standard_normal((K, Nn) if shared_b else (T, K, Nn), np.float32) * 0.3).astype(np.float32)
+
+    def define(g, ft, fm, fk, fn):
+        a = g.input([ft, fm, fk])
+        b = g.input([fk, fn]) if shared_b else g.input([ft, fk, fn])
+        g.tanh(g.matmul(a, b))
+    graph, t, kernels, binding = build(ctx, define, [T, M, K, Nn], gemm_mode="simt")
+    ins = [ctx.init_tensor_f32(A.shape, A), ctx.init_tensor_f32(B.shape, B)]
+    seed = r.standard_normal((T, M, Nn), np.float32)
+    ctx.upload(t.seed, seed)
+    sch = ctx.schedule(kernels, binding, ins, t, [], ())
+    ctx.dispatch_forward(sch)
+    ctx.dispatch_backward(sch)
+    ctx.sync()
+    Bt = [B if shared_b else B[i] for i in range(T)]
+    Y = np.stack([np.tanh(oracle.gemm(A[i], Bt[i])) for i in range(T)])
+    dZ = seed * (1.0 - Y * Y)
+    dA = np.stack([oracle.gemm(dZ[i], Bt[i], transB=True) for i in range(T)])
+    dB = [oracle.gemm(A[i], dZ[i], transA=True) for i in range(T)]
+    dB = sum(dB) if shared_b else np.stack(dB)
+    for got, ref, what in ((dl(ctx, t.forward_out, Y.size).reshape(Y.shape), Y, "output"),
+                           (dl(ctx, t.grad_tensors[0], A.size).reshape(A.shape), dA, "dA"),
+                           (dl(ctx, t.grad_tensors[1], B.size).reshape(B.shape), dB, "dB")):
+        ok, worst = rel_err_ok(got, ref, 1e-4)
+        assert ok, f"{what}: {worst:.3g} x 1e-4"
+    t.destroy()
+
+
 def test_fan_out_accumulates_gradients(ctx, oracle):
     """y = (a @ b) * tanh(a @ b): the matmul result has two consumers, a is used by one matmul only; and
     z = a @ a (both operands the same tensor) takes the accumulate path."""

@@ -407,6 +407,29 @@ def test_gemm_skinny_output_layer(ctx, oracle, M, N, K, act):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("mode", ["simt", "auto"])
+def test_gemm_batched(ctx, oracle, mode):
+    # rank-3 matmul: T independent products, every tensor stepped by one matrix per product
+    T, M, N, K = 3, 136, 200, 168
+    r = rng(314)
+    A, B = r.standard_normal((T, M, K), np.float32), r.standard_normal((T, K, N), np.float32) * 0.2
+    bias = r.standard_normal(N, np.float32)
+    Cd, Pd = ctx.new_tensor((T, M, N)), ctx.new_tensor((T, M, N))
+    ctx.gemm_batched(up(ctx, A), up(ctx, B), Cd, T, M, N, K, bias=up(ctx, bias), act="tanh", preact_out=Pd, mode=mode)
+    got, dY = ctx.to_numpy(Cd), r.standard_normal((T, M, N), np.float32)
+    dA, dB = ctx.new_tensor((T, M, K)), ctx.new_tensor((T, K, N))
+    ctx.gemm_batched_bwd(up(ctx, A), up(ctx, B), up(ctx, dY), T, M, N, K, act="tanh", saved=Cd, dA=dA, dB=dB, mode=mode)
+    gA, gB = ctx.to_numpy(dA), ctx.to_numpy(dB)
+    for t in range(T):
+        y, _ = oracle.bias_act_fwd(oracle.gemm(A[t], B[t]), bias, "tanh")
+        check(got[t], y, TOL_GEMM, f"batched output {t}")
+        dz = oracle.act_bwd(dY[t], y, "tanh")
+        check(gA[t], oracle.gemm(dz, B[t], transB=True), TOL_GEMM, f"batched dA {t}")
+        check(gB[t], oracle.gemm(A[t], dz, transA=True), TOL_GEMM, f"batched dB {t}")
+    with pytest.raises(Exception):
+        ctx.gemm_batched(up(ctx, A), up(ctx, B), Cd, T, M, N, K, strides=(M * K, 0, M * N))
+
+
 @pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_reference_matmul_known_answers(ctx, mode):
     # crates/ferrograd/tests/std_wgsl.rs:268-373 (matmul_add) and :376-520 (matmul_chain3): constant
