@@ -20,9 +20,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes (read + write) per tensor-core GEMM launch, averaged over the eight launches of one training
-# step, from the ncu capture summarised in profiles/mlp_c4_gemm_dram_traffic.md.
-GEMM_TRAFFIC_PER_LAUNCH = {"c4": 369.0e6}
+# DRAM bytes (read + write) per tensor-core GEMM (a pair launch and its fold), averaged over the five of
+# one training step, from the ncu capture summarised in profiles/mlp_c4_gemm_dram_traffic.md.
+GEMM_TRAFFIC_PER_LAUNCH = {"c4": 505.0e6}
 
 
 def load_peaks():

@@ -66,6 +66,8 @@ SIGNATURES = {
     "fg_memset_zero": (i32, [c_ctx, c_dev, u64]),
     "fg_gemm_f32": (i32, [c_ctx, i32, i32, i32, u32, u32, u32, c_dev, c_dev, c_dev, c_dev, i32, c_dev]),
     "fg_gemm_bwd_f32": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, i32, c_dev, c_dev, c_dev, c_dev, c_dev]),
+    "fg_gemm_bwd_exchange_f32": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, i32, c_dev, c_dev, c_dev, c_dev, c_dev,
+                                       u64]),
     "fg_gemm_batched_f32": (i32, [c_ctx, i32, u32, u32, u32, u32, c_dev, u64, c_dev, u64, c_dev, u64, c_dev, i32, c_dev]),
     "fg_gemm_batched_bwd_f32": (i32, [c_ctx, i32, u32, u32, u32, u32, c_dev, u64, c_dev, u64, c_dev, u64, i32, c_dev,
                                       c_dev, c_dev]),

@@ -249,6 +249,13 @@ class GpuContext:
         self._check(self.lib.fg_gemm_bwd_f32(self.handle, GEMM_MODE[mode], M, N, K, _ptr(A), _ptr(B), _ptr(dY),
                                              ACT[act], _ptr(saved), _ptr(dA), _ptr(dB), _ptr(dbias), _ptr(dZ_out)))
 
+    def gemm_bwd_exchange(self, A, B, dY, M, N, K, exch_buf, exch_count, act="none", saved=None, dA=None, dB=None,
+                          dbias=None, mode="auto"):
+        """gemm_bwd that starts the allreduce of exch_buf once dB and dbias are done and computes dA beside it."""
+        self._check(self.lib.fg_gemm_bwd_exchange_f32(self.handle, GEMM_MODE[mode], M, N, K, _ptr(A), _ptr(B), _ptr(dY),
+                                                      ACT[act], _ptr(saved), _ptr(dA), _ptr(dB), _ptr(dbias),
+                                                      _ptr(exch_buf), exch_count))
+
     def gemm_batched(self, A, B, Cout, batch, M, N, K, bias=None, act="none", preact_out=None, mode="auto",
                      strides=None):
         sa, sb, sc = strides or (M * K, K * N, M * N)

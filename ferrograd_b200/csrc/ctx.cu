@@ -85,7 +85,10 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
         if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return FG_ERR_INTERNAL; }
         c->own_stream = true;
     }
-    if (cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+    // The exchange stream has the highest priority, so its CTAs are placed as soon as SMs are free.
+    int prio_least = 0, prio_greatest = 0;
+    cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest);
+    if (cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, prio_greatest) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_copy_done, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_main_mark, cudaEventDisableTiming) != cudaSuccess ||
@@ -453,6 +456,15 @@ int32_t fg_comm_init(fg_ctx* ctx, int32_t nranks, int32_t rank, const uint8_t id
     if (!ctx->nccl_lib) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "fg_comm_init: libnccl.so.2 not found");
     auto init = (pfn_ncclCommInitRank)dlsym(ctx->nccl_lib, "ncclCommInitRank");
     if (!init) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "fg_comm_init: ncclCommInitRank missing");
+    // An exchange CTA and a GEMM CTA cannot share an SM (registers, shared memory), and the pair GEMM is
+    // persistent: if it took every SM the exchange would start only when it ended, and if the exchange
+    // took some first the GEMM's last CTAs would start late with a full share of tiles.  So the exchange
+    // is held to 16 CTAs (unless the caller's environment says otherwise) and the GEMM leaves 20 SMs free
+    // while one is in flight.  FG_COMM_SMS overrides the number; 0 turns the reservation off.
+    setenv("NCCL_MAX_CTAS", "16", 0);
+    ctx->comm_reserved_sms = 20;
+    if (const char* e = getenv("FG_COMM_SMS")) ctx->comm_reserved_sms = atoi(e);
+    if (ctx->comm_reserved_sms < 0 || ctx->comm_reserved_sms > ctx->sm_count / 2) ctx->comm_reserved_sms = 0;
     nccl_uid uid;
     memcpy(uid.internal, id, FG_COMM_ID_BYTES);
     int r = init(&ctx->comm, nranks, uid, rank);

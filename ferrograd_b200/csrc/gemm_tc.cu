@@ -970,7 +970,12 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
         }
         max_clusters[ctx->device & 63] = n;
     }
-    const uint64_t slots = (uint64_t)max_clusters[ctx->device & 63];
+    uint64_t slots = (uint64_t)max_clusters[ctx->device & 63];
+    if (ctx->comm_pending && ctx->comm_reserved_sms > 0) {
+        // leave room for the gradient exchange that runs beside this GEMM (see fg_comm_init)
+        const uint64_t lim = (uint64_t)(ctx->sm_count - ctx->comm_reserved_sms) / 2;
+        if (lim >= 1 && lim < slots) slots = lim;
+    }
     // The last wave: `rem` tiles for `slots` pairs.  When at least two pairs are free per tile, each tail
     // tile is cut into K-shares (whole accumulation chunks, at least two per share) so that the wave
     // lasts a fraction of a tile time; the shares are folded by a second, bandwidth-bound kernel.
@@ -1103,9 +1108,15 @@ int32_t fg_gemm_f32(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB, u
     return tc_gemm(ctx, fmt, pa, pb, M, N, K, C, bias, act, preact_out);
 }
 
-int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
-                        const float* dY, int32_t act, const float* saved, float* dA, float* dB, float* dbias,
-                        float* dZ_out) {
+}  // extern "C"
+
+namespace {
+
+// Backward of one layer.  With exch_buf set, dB and dbias are finished first, the sum of exch_buf over the
+// ranks is started on the exchange stream, and dA is computed while it runs.
+int32_t gemm_bwd_impl(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
+                      const float* dY, int32_t act, const float* saved, float* dA, float* dB, float* dbias,
+                      float* dZ_out, float* exch_buf, uint64_t exch_count) {
     FG_ENTER(ctx);
     FG_REQUIRE(ctx, dY != nullptr, "fg_gemm_bwd_f32: dY is NULL");
     FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_bwd_f32: dimensions must be >= 1");
@@ -1145,9 +1156,10 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
             }
             dz = buf;
         }
-        if (dA) { int32_t s = fg_gemm_simt_launch(ctx, 0, 1, M, K, N, dz, B, dA, nullptr, FG_ACT_NONE, nullptr); if (s) return s; }
         if (dB) { int32_t s = fg_gemm_simt_launch(ctx, 1, 0, K, N, M, A, dz, dB, nullptr, FG_ACT_NONE, nullptr); if (s) return s; }
         if (dbias) { int32_t s = fg_colsum_launch(ctx, M, N, dz, dbias); if (s) return s; }
+        if (exch_buf) { int32_t s = fg_allreduce_sum_f32(ctx, exch_buf, exch_count); if (s) return s; }
+        if (dA) { int32_t s = fg_gemm_simt_launch(ctx, 0, 1, M, K, N, dz, B, dA, nullptr, FG_ACT_NONE, nullptr); if (s) return s; }
         return FG_OK;
     }
 
@@ -1194,14 +1206,7 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
         if ((s = launch_split(ctx, fmt, sz, &cs_chunks)) != FG_OK) return s;
     }
     const float* dz_src = dz_val ? (const float*)dz_val : dY;   // dZ == dY when there is no activation
-    if (tc_da) {
-        // dA[M,K] = dZ[M,N] · Bᵀ: contraction over N; B [K,N] is already "rows = K, contraction contiguous".
-        SplitArgs sb{};
-        sb.x = B; sb.R = K; sb.C = N; sb.n = b_n;
-        if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
-        if ((s = tc_gemm(ctx, fmt, dz_n, b_n, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
-    }
-    if (skinny && dA && (s = fg_gemm_skinny_nt_launch(ctx, M, K, N, dz_src, B, dA)) != FG_OK) return s;
+    // weight and bias gradients first: with an exchange requested, it starts as soon as they are complete
     if (skinny && dB && (s = fg_gemm_skinny_tn_launch(ctx, M, K, N, A, dz_src, dB)) != FG_OK) return s;
     if (tc_db) {
         // dB[K,N] = Aᵀ · dZ: contraction over M; operands are Aᵀ [K,M] and dZᵀ [N,M].
@@ -1214,7 +1219,35 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
         // the pre-pass left one row of column sums per row tile: fold them in a fixed order
         if ((s = fg_colsum_fold_launch(ctx, N, cs_chunks, (const float*)cs_part, dbias)) != FG_OK) return s;
     }
+    if (exch_buf && (s = fg_allreduce_sum_f32(ctx, exch_buf, exch_count)) != FG_OK) return s;
+    if (tc_da) {
+        // dA[M,K] = dZ[M,N] · Bᵀ: contraction over N; B [K,N] is already "rows = K, contraction contiguous".
+        SplitArgs sb{};
+        sb.x = B; sb.R = K; sb.C = N; sb.n = b_n;
+        if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
+        if ((s = tc_gemm(ctx, fmt, dz_n, b_n, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
+    }
+    if (skinny && dA && (s = fg_gemm_skinny_nt_launch(ctx, M, K, N, dz_src, B, dA)) != FG_OK) return s;
     return FG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
+                        const float* dY, int32_t act, const float* saved, float* dA, float* dB, float* dbias,
+                        float* dZ_out) {
+    return gemm_bwd_impl(ctx, mode, M, N, K, A, B, dY, act, saved, dA, dB, dbias, dZ_out, nullptr, 0);
+}
+
+int32_t fg_gemm_bwd_exchange_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A,
+                                 const float* B, const float* dY, int32_t act, const float* saved, float* dA, float* dB,
+                                 float* dbias, float* exch_buf, uint64_t exch_count) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, exch_buf != nullptr && exch_count > 0, "fg_gemm_bwd_exchange_f32: nothing to exchange");
+    if (!ctx->comm) return fg_fail(ctx, FG_ERR_NOT_INITIALIZED, "fg_gemm_bwd_exchange_f32: call fg_comm_init first");
+    return gemm_bwd_impl(ctx, mode, M, N, K, A, B, dY, act, saved, dA, dB, dbias, nullptr, exch_buf, exch_count);
 }
 
 // Batched forms: `batch` independent products, operand t at base + t*stride (strides in elements).

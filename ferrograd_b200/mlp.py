@@ -35,6 +35,7 @@ class MLPTrainer:
         self.world, self.rank = int(world), int(rank)
         self.mode = gemm_mode
         self.overlap = overlap_comm
+        self.min_exchange = 1 << 20     # elements: smaller layers ride along with the next exchange
         od = self.dims[-1]
         if grad_scale is None:
             # mean loss over the GLOBAL batch (and over output elements for MSE)
@@ -174,24 +175,24 @@ class MLPTrainer:
         else:
             c.mse_loss_grad(self.act_buf[L], self.target, B * od, grad_scale=self.grad_scale,
                             loss_sum=self.loss_out, grad=self.dact[L])
+        # Gradient exchange: layers are contiguous in the arena, so consecutive layers can share one call.
+        # A layer's gradients wait for the next layer's when they are small (a 10-class head is not worth a
+        # launch, and the GEMMs give up SMs while an exchange is in flight).
+        pend_hi = self.n_arena
         for l in range(L - 1, -1, -1):
             a = self.act if l < L - 1 else "none"
             saved = None if a == "none" else (self.pre_buf[l] if a == "gelu" else self.act_buf[l + 1])
-            if self.world > 1 and self.overlap and l > 0:
-                # weight and bias gradients first, so that their exchange also overlaps this layer's dX GEMM
-                c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
-                           saved=saved, dA=None, dB=self.gW(l), dbias=self.gb(l), mode=self.mode)
-                lo, hi = self.layer_range[l]
-                c.allreduce_sum(self.grads.ptr + 4 * lo, hi - lo)
-                c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
-                           saved=saved, dA=self.dact[l], dB=None, dbias=None, mode=self.mode)
-                continue
-            c.gemm_bwd(self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l], act=a,
-                       saved=saved, dA=self.dact[l] if l > 0 else None, dB=self.gW(l), dbias=self.gb(l),
-                       mode=self.mode)
-            if self.world > 1 and self.overlap:
-                lo, hi = self.layer_range[l]
-                c.allreduce_sum(self.grads.ptr + 4 * lo, hi - lo)   # overlaps the next layer's backward
+            args = (self.act_buf[l], self.W(l), self.dact[l + 1], B, self.dims[l + 1], self.dims[l])
+            kw = dict(act=a, saved=saved, dA=self.dact[l] if l > 0 else None, dB=self.gW(l), dbias=self.gb(l),
+                      mode=self.mode)
+            lo = self.layer_range[l][0]
+            if self.world > 1 and self.overlap and (l == 0 or pend_hi - lo >= self.min_exchange):
+                # weight and bias gradients first; their exchange runs beside this layer's dX GEMM and the
+                # backward of the layers below
+                c.gemm_bwd_exchange(*args, self.grads.ptr + 4 * lo, pend_hi - lo, **kw)
+                pend_hi = lo
+            else:
+                c.gemm_bwd(*args, **kw)
         if self.world > 1:
             if not self.overlap:
                 c.allreduce_sum(self.grads, self.n_arena)

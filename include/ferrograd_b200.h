@@ -153,6 +153,18 @@ int32_t fg_gemm_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint3
                         int32_t act, const float* saved,
                         float* dA, float* dB, float* dbias, float* dZ_out);
 
+/* fg_gemm_bwd_f32 for data-parallel training (no counterpart in the reference, which is single
+ * device): dB and dbias are completed first, then the sum over all ranks of exch_buf[0..exch_count)
+ * — normally the range of the gradient arena that holds this layer's dB and dbias, plus any later
+ * layers not yet exchanged — is started on the exchange stream as by fg_allreduce_sum_f32, and dA is
+ * computed while it runs.  dZ is formed once for both products.  Needs fg_comm_init; finish with
+ * fg_comm_join before the gradients are used. */
+int32_t fg_gemm_bwd_exchange_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K,
+                                 const float* A, const float* B, const float* dY,
+                                 int32_t act, const float* saved,
+                                 float* dA, float* dB, float* dbias,
+                                 float* exch_buf, uint64_t exch_count);
+
 /* Rank-3 matmul: `batch` independent products; product t uses A + t*strideA, B + t*strideB and
  * C (or dY, saved, preact_out) + t*strideC, strides in elements.  The reference steps every operand
  * by one matrix per Z index (kernel/forward.rs:159-190, op/matmul/generic.rs:131,194).  Each stride
