@@ -21,7 +21,7 @@ sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) per tensor-core GEMM (a pair launch and its fold), averaged over the five of
-# one training step, from the ncu capture summarised in profiles/mlp_c4_gemm_dram_traffic.md.
+# one training step, from an ncu capture of one step (dram__bytes_read.sum + dram__bytes_write.sum).
 GEMM_TRAFFIC_PER_LAUNCH = {"c4": 505.0e6}
 
 
