@@ -87,10 +87,16 @@ SIGNATURES = {
                                    C.POINTER(C.c_void_p)]),
     "fg_eltwise_chain_bwd": (i32, [c_ctx, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
                                    C.POINTER(C.c_void_p), i32]),
+    "fg_eltwise_chain_fwd_dt": (i32, [c_ctx, i32, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
+                                      C.POINTER(C.c_void_p)]),
+    "fg_eltwise_chain_bwd_dt": (i32, [c_ctx, i32, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
+                                      C.POINTER(C.c_void_p), i32]),
+    "fg_convert": (i32, [c_ctx, c_dev, i32, c_dev, i32, u64]),
     "fg_graph_create": (i32, [i32, i32, C.POINTER(C.c_void_p)]),
     "fg_graph_destroy": (i32, [C.c_void_p]),
     "fg_graph_node_count": (i32, [C.c_void_p]),
     "fg_graph_input": (i32, [C.c_void_p, C.POINTER(u32), u32, C.POINTER(i32)]),
+    "fg_graph_input_dt": (i32, [C.c_void_p, C.POINTER(u32), u32, i32, C.POINTER(i32)]),
     "fg_graph_constant_f32": (i32, [C.c_void_p, f32, C.POINTER(i32)]),
     "fg_graph_op": (i32, [C.c_void_p, i32, i32, i32, C.POINTER(i32)]),
     "fg_exec_create": (i32, [c_ctx, C.c_void_p, C.POINTER(u32), u32, i32, C.POINTER(C.c_void_p)]),

@@ -93,6 +93,20 @@ class Plan:
             self.handle = None
 
 
+DTYPE = {"f32": 0, "f16": 1, "bf16": 2}
+
+
+def to_bf16_bits(x):
+    """float32 array -> uint16 bf16 bit patterns, round to nearest even."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    r = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return np.where((u & 0x7FFFFFFF) > 0x7F800000, u >> 16, r).astype(np.uint16)
+
+
+def from_bf16_bits(b):
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
 class GpuContext:
     def __init__(self, device=0, stream=None):
         self.lib = _lib.load()
@@ -163,6 +177,18 @@ class GpuContext:
         a = np.ascontiguousarray(data, dtype=np.float32)
         assert a.size == int(np.prod(shape))
         return Tensor(shape, self.alloc_init(a), np.float32)
+
+    def init_tensor_f16(self, shape, data):
+        """GpuContext::init_tensor_f16 (exercised by crates/ferrograd/tests/nonf32.rs:57-64)."""
+        a = np.ascontiguousarray(data, dtype=np.float16)
+        assert a.size == int(np.prod(shape))
+        return Tensor(shape, self.alloc_init(a), np.float16)
+
+    def init_tensor_bf16(self, shape, data):
+        """data: float values; stored as bf16 bit patterns (numpy has no bf16: the tensor's dtype is uint16)."""
+        a = to_bf16_bits(np.ascontiguousarray(data, dtype=np.float32))
+        assert a.size == int(np.prod(shape))
+        return Tensor(shape, self.alloc_init(a), np.uint16)
 
     def init_tensor_u32(self, shape, data):
         a = np.ascontiguousarray(data, dtype=np.uint32)
@@ -324,21 +350,24 @@ class GpuContext:
             arr[i] = _lib.EwInstr(EW[op] if isinstance(op, str) else op, a, b, imm)
         return arr
 
-    def eltwise_chain_fwd(self, instrs, inputs, out, n, saved=None):
+    def eltwise_chain_fwd(self, instrs, inputs, out, n, saved=None, dtype="f32"):
         prog = self._prog(instrs)
         inp = (C.c_void_p * len(inputs))(*[_ptr(x) for x in inputs])
         sv = None
         if saved:
             sv = (C.c_void_p * len(instrs))(*[_ptr(saved.get(k)) for k in range(len(instrs))])
-        self._check(self.lib.fg_eltwise_chain_fwd(self.handle, n, prog, len(instrs), inp, len(inputs), _ptr(out),
-                                                  sv))
+        self._check(self.lib.fg_eltwise_chain_fwd_dt(self.handle, DTYPE[dtype], n, prog, len(instrs), inp, len(inputs),
+                                                     _ptr(out), sv))
 
-    def eltwise_chain_bwd(self, instrs, inputs, seed, grads, n, accumulate=False):
+    def eltwise_chain_bwd(self, instrs, inputs, seed, grads, n, accumulate=False, dtype="f32"):
         prog = self._prog(instrs)
         inp = (C.c_void_p * len(inputs))(*[_ptr(x) for x in inputs])
         gp = (C.c_void_p * len(inputs))(*[_ptr(g) for g in grads])
-        self._check(self.lib.fg_eltwise_chain_bwd(self.handle, n, prog, len(instrs), inp, len(inputs), _ptr(seed),
-                                                  gp, int(accumulate)))
+        self._check(self.lib.fg_eltwise_chain_bwd_dt(self.handle, DTYPE[dtype], n, prog, len(instrs), inp, len(inputs),
+                                                     _ptr(seed), gp, int(accumulate)))
+
+    def convert(self, src, src_dtype, dst, dst_dtype, n):
+        self._check(self.lib.fg_convert(self.handle, _ptr(src), DTYPE[src_dtype], _ptr(dst), DTYPE[dst_dtype], n))
 
     # ---- plans ----
     def plan_begin(self):

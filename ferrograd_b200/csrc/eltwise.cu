@@ -10,6 +10,9 @@
 // (crates/fused_gpu/src/dispatch/backend/kernel/forward.rs:298-464); a chain here is the
 // same idea with the program interpreted per element: every input is read once, every
 // output written once.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "fg_internal.cuh"
 
 namespace {
@@ -133,79 +136,117 @@ __global__ void __launch_bounds__(256) colsum_fold_kernel(uint32_t cols, uint32_
 }
 
 // ---- chains ----
+// Storage type of a chain's tensors.  Values are held as float in registers; with 16-bit storage every
+// operation's result is rounded to the storage type (round to nearest even), which for + - * / equals
+// native half arithmetic (float carries more than twice the bits, so the double rounding is harmless).
+template <int DT> struct Stored;
+template <> struct Stored<FG_DTYPE_F32> {
+    typedef float T;
+    static __device__ __forceinline__ float ld(const void* p, uint64_t i) { return static_cast<const float*>(p)[i]; }
+    static __device__ __forceinline__ void st(void* p, uint64_t i, float v) { static_cast<float*>(p)[i] = v; }
+    static __device__ __forceinline__ float r(float v) { return v; }
+};
+template <> struct Stored<FG_DTYPE_F16> {
+    typedef __half T;
+    static __device__ __forceinline__ float ld(const void* p, uint64_t i) { return __half2float(static_cast<const __half*>(p)[i]); }
+    static __device__ __forceinline__ void st(void* p, uint64_t i, float v) { static_cast<__half*>(p)[i] = __float2half_rn(v); }
+    static __device__ __forceinline__ float r(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <> struct Stored<FG_DTYPE_BF16> {
+    typedef __nv_bfloat16 T;
+    static __device__ __forceinline__ float ld(const void* p, uint64_t i) { return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]); }
+    static __device__ __forceinline__ void st(void* p, uint64_t i, float v) { static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
 struct ChainArgs {
     fg_ew_instr prog[FG_EW_MAX_INSTR];
-    const float* in[FG_EW_MAX_INPUTS];
-    float* saved[FG_EW_MAX_INSTR];   // forward: optional stores of intermediates
-    float* grads[FG_EW_MAX_INPUTS];  // backward
-    const float* seed;
-    float* out;
+    const void* in[FG_EW_MAX_INPUTS];
+    void* saved[FG_EW_MAX_INSTR];   // forward: optional stores of intermediates
+    void* grads[FG_EW_MAX_INPUTS];  // backward
+    const void* seed;
+    void* out;
     int ninstr, ninputs, accumulate;
     uint64_t n;
 };
 
+template <int DT>
 __device__ __forceinline__ float ew_eval(const fg_ew_instr& in, const float* v, const ChainArgs& a, uint64_t i) {
+    typedef Stored<DT> S;
     switch (in.op) {
-        case FG_EW_INPUT: return a.in[in.a][i];
-        case FG_EW_CONST: return in.imm;
-        case FG_EW_ADD: return v[in.a] + v[in.b];
-        case FG_EW_SUB: return v[in.a] - v[in.b];
-        case FG_EW_MUL: return v[in.a] * v[in.b];
-        case FG_EW_DIV: return __fdiv_rn(v[in.a], v[in.b]);
+        case FG_EW_INPUT: return S::ld(a.in[in.a], i);
+        case FG_EW_CONST: return S::r(in.imm);
+        case FG_EW_ADD: return S::r(v[in.a] + v[in.b]);
+        case FG_EW_SUB: return S::r(v[in.a] - v[in.b]);
+        case FG_EW_MUL: return S::r(v[in.a] * v[in.b]);
+        case FG_EW_DIV: return S::r(__fdiv_rn(v[in.a], v[in.b]));
         case FG_EW_NEG: return -v[in.a];
         case FG_EW_ABS: return fabsf(v[in.a]);
-        case FG_EW_EXP: return expf(v[in.a]);
-        case FG_EW_LOG: return logf(v[in.a]);
-        case FG_EW_TANH: return tanhf(v[in.a]);
+        case FG_EW_EXP: return S::r(expf(v[in.a]));
+        case FG_EW_LOG: return S::r(logf(v[in.a]));
+        case FG_EW_TANH: return S::r(tanhf(v[in.a]));
         case FG_EW_RELU: return v[in.a] > 0.0f ? v[in.a] : 0.0f;
-        case FG_EW_GELU: return fg_gelu_fwd(v[in.a], nullptr);
-        case FG_EW_ELU: return v[in.a] >= 0.0f ? v[in.a] : expf(v[in.a]) - 1.0f;
+        case FG_EW_GELU: return S::r(fg_gelu_fwd(v[in.a], nullptr));
+        case FG_EW_ELU: return v[in.a] >= 0.0f ? v[in.a] : S::r(expf(v[in.a]) - 1.0f);
         default: return 0.0f;
     }
 }
 
+template <int DT>
 __global__ void __launch_bounds__(256) chain_fwd_kernel(const __grid_constant__ ChainArgs a) {
+    typedef Stored<DT> S;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
         float v[FG_EW_MAX_INSTR];
         for (int k = 0; k < a.ninstr; ++k) {
-            v[k] = ew_eval(a.prog[k], v, a, i);
-            if (a.saved[k]) a.saved[k][i] = v[k];
+            v[k] = ew_eval<DT>(a.prog[k], v, a, i);
+            if (a.saved[k]) S::st(a.saved[k], i, v[k]);
         }
-        a.out[i] = v[a.ninstr - 1];
+        S::st(a.out, i, v[a.ninstr - 1]);
     }
 }
 
+template <int DT>
 __global__ void __launch_bounds__(256) chain_bwd_kernel(const __grid_constant__ ChainArgs a) {
+    typedef Stored<DT> S;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
         float v[FG_EW_MAX_INSTR], adj[FG_EW_MAX_INSTR], gin[FG_EW_MAX_INPUTS];
-        for (int k = 0; k < a.ninstr; ++k) { v[k] = ew_eval(a.prog[k], v, a, i); adj[k] = 0.0f; }
+        for (int k = 0; k < a.ninstr; ++k) { v[k] = ew_eval<DT>(a.prog[k], v, a, i); adj[k] = 0.0f; }
         for (int k = 0; k < a.ninputs; ++k) gin[k] = 0.0f;
-        adj[a.ninstr - 1] = a.seed[i];
+        adj[a.ninstr - 1] = S::ld(a.seed, i);
         for (int k = a.ninstr - 1; k >= 0; --k) {
             const fg_ew_instr& in = a.prog[k];
             const float g = adj[k];
             switch (in.op) {
-                case FG_EW_INPUT: gin[in.a] += g; break;
-                case FG_EW_ADD: adj[in.a] += g; adj[in.b] += g; break;
-                case FG_EW_SUB: adj[in.a] += g; adj[in.b] -= g; break;
-                case FG_EW_MUL: { float va = v[in.a], vb = v[in.b]; adj[in.a] += g * vb; adj[in.b] += g * va; break; }
+                case FG_EW_INPUT: gin[in.a] = S::r(gin[in.a] + g); break;
+                case FG_EW_ADD: adj[in.a] = S::r(adj[in.a] + g); adj[in.b] = S::r(adj[in.b] + g); break;
+                case FG_EW_SUB: adj[in.a] = S::r(adj[in.a] + g); adj[in.b] = S::r(adj[in.b] - g); break;
+                case FG_EW_MUL: { float va = v[in.a], vb = v[in.b];
+                                  adj[in.a] = S::r(adj[in.a] + S::r(g * vb));
+                                  adj[in.b] = S::r(adj[in.b] + S::r(g * va)); break; }
                 case FG_EW_DIV: { float va = v[in.a], vb = v[in.b];
-                                  adj[in.a] += __fdiv_rn(g, vb);
-                                  adj[in.b] -= __fdiv_rn(g * va, vb * vb); break; }
-                case FG_EW_NEG: adj[in.a] -= g; break;
-                case FG_EW_ABS: adj[in.a] += (v[in.a] >= 0.0f ? g : -g); break;
-                case FG_EW_EXP: adj[in.a] += g * v[k]; break;
-                case FG_EW_LOG: adj[in.a] += __fdiv_rn(g, v[in.a]); break;
-                case FG_EW_TANH: adj[in.a] += g * (1.0f - v[k] * v[k]); break;
-                case FG_EW_RELU: adj[in.a] += g * fg_act_grad(FG_ACT_RELU, v[k]); break;
-                case FG_EW_GELU: adj[in.a] += g * fg_act_grad(FG_ACT_GELU, v[in.a]); break;
-                case FG_EW_ELU: adj[in.a] += (v[k] >= 0.0f ? g : g * (v[k] + 1.0f)); break;
+                                  adj[in.a] = S::r(adj[in.a] + S::r(__fdiv_rn(g, vb)));
+                                  adj[in.b] = S::r(adj[in.b] - S::r(__fdiv_rn(S::r(g * va), S::r(vb * vb)))); break; }
+                case FG_EW_NEG: adj[in.a] = S::r(adj[in.a] - g); break;
+                case FG_EW_ABS: adj[in.a] = S::r(adj[in.a] + (v[in.a] >= 0.0f ? g : -g)); break;
+                case FG_EW_EXP: adj[in.a] = S::r(adj[in.a] + S::r(g * v[k])); break;
+                case FG_EW_LOG: adj[in.a] = S::r(adj[in.a] + S::r(__fdiv_rn(g, v[in.a]))); break;
+                case FG_EW_TANH: adj[in.a] = S::r(adj[in.a] + S::r(g * S::r(1.0f - S::r(v[k] * v[k])))); break;
+                case FG_EW_RELU: adj[in.a] = S::r(adj[in.a] + g * fg_act_grad(FG_ACT_RELU, v[k])); break;
+                case FG_EW_GELU: adj[in.a] = S::r(adj[in.a] + S::r(g * S::r(fg_act_grad(FG_ACT_GELU, v[in.a])))); break;
+                case FG_EW_ELU: adj[in.a] = S::r(adj[in.a] + (v[k] >= 0.0f ? g : S::r(g * S::r(v[k] + 1.0f)))); break;
                 default: break;
             }
         }
         for (int k = 0; k < a.ninputs; ++k)
-            if (a.grads[k]) a.grads[k][i] = a.accumulate ? a.grads[k][i] + gin[k] : gin[k];
+            if (a.grads[k]) S::st(a.grads[k], i, a.accumulate ? S::r(S::ld(a.grads[k], i) + gin[k]) : gin[k]);
     }
+}
+
+// dst[i] = (type of dst) src[i], round to nearest even
+template <int DS, int DD>
+__global__ void __launch_bounds__(256) convert_kernel(const void* __restrict__ src, void* __restrict__ dst, uint64_t n) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        Stored<DD>::st(dst, i, Stored<DS>::ld(src, i));
 }
 
 int32_t check_prog(fg_ctx* ctx, const fg_ew_instr* prog, int32_t ninstr, int32_t ninputs) {
@@ -330,11 +371,12 @@ int32_t fg_bce_loss_grad(fg_ctx* ctx, const float* pred, const float* target, ui
     return FG_OK;
 }
 
-int32_t fg_eltwise_chain_fwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
-                             const float* const* inputs, int32_t ninputs, float* out, float* const* saved_out) {
+int32_t fg_eltwise_chain_fwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
+                                const void* const* inputs, int32_t ninputs, void* out, void* const* saved_out) {
     FG_ENTER(ctx);
     int32_t s = check_prog(ctx, prog, ninstr, ninputs);
     if (s != FG_OK) return s;
+    FG_REQUIRE(ctx, dtype >= FG_DTYPE_F32 && dtype <= FG_DTYPE_BF16, "fg_eltwise_chain_fwd: unknown dtype");
     FG_REQUIRE(ctx, inputs && out, "fg_eltwise_chain_fwd: NULL pointer");
     ChainArgs a;
     memset(&a, 0, sizeof(a));
@@ -346,17 +388,20 @@ int32_t fg_eltwise_chain_fwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, i
     a.out = out; a.ninstr = ninstr; a.ninputs = ninputs; a.n = n;
     if (n == 0) return FG_OK;
     int grid = fg_stream_grid(ctx, n, 256, 8);
-    chain_fwd_kernel<<<grid, 256, 0, ctx->stream>>>(a);
+    if (dtype == FG_DTYPE_F32) chain_fwd_kernel<FG_DTYPE_F32><<<grid, 256, 0, ctx->stream>>>(a);
+    else if (dtype == FG_DTYPE_F16) chain_fwd_kernel<FG_DTYPE_F16><<<grid, 256, 0, ctx->stream>>>(a);
+    else chain_fwd_kernel<FG_DTYPE_BF16><<<grid, 256, 0, ctx->stream>>>(a);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
 
-int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
-                             const float* const* inputs, int32_t ninputs, const float* seed, float* const* grads,
-                             int32_t accumulate) {
+int32_t fg_eltwise_chain_bwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
+                                const void* const* inputs, int32_t ninputs, const void* seed, void* const* grads,
+                                int32_t accumulate) {
     FG_ENTER(ctx);
     int32_t s = check_prog(ctx, prog, ninstr, ninputs);
     if (s != FG_OK) return s;
+    FG_REQUIRE(ctx, dtype >= FG_DTYPE_F32 && dtype <= FG_DTYPE_BF16, "fg_eltwise_chain_bwd: unknown dtype");
     FG_REQUIRE(ctx, inputs && seed && grads, "fg_eltwise_chain_bwd: NULL pointer");
     ChainArgs a;
     memset(&a, 0, sizeof(a));
@@ -369,7 +414,38 @@ int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, i
     a.seed = seed; a.ninstr = ninstr; a.ninputs = ninputs; a.n = n; a.accumulate = accumulate;
     if (n == 0) return FG_OK;
     int grid = fg_stream_grid(ctx, n, 256, 8);
-    chain_bwd_kernel<<<grid, 256, 0, ctx->stream>>>(a);
+    if (dtype == FG_DTYPE_F32) chain_bwd_kernel<FG_DTYPE_F32><<<grid, 256, 0, ctx->stream>>>(a);
+    else if (dtype == FG_DTYPE_F16) chain_bwd_kernel<FG_DTYPE_F16><<<grid, 256, 0, ctx->stream>>>(a);
+    else chain_bwd_kernel<FG_DTYPE_BF16><<<grid, 256, 0, ctx->stream>>>(a);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+int32_t fg_eltwise_chain_fwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
+                             const float* const* inputs, int32_t ninputs, float* out, float* const* saved_out) {
+    return fg_eltwise_chain_fwd_dt(ctx, FG_DTYPE_F32, n, prog, ninstr, reinterpret_cast<const void* const*>(inputs), ninputs,
+                                   out, reinterpret_cast<void* const*>(saved_out));
+}
+
+int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, int32_t ninstr,
+                             const float* const* inputs, int32_t ninputs, const float* seed, float* const* grads,
+                             int32_t accumulate) {
+    return fg_eltwise_chain_bwd_dt(ctx, FG_DTYPE_F32, n, prog, ninstr, reinterpret_cast<const void* const*>(inputs), ninputs,
+                                   seed, reinterpret_cast<void* const*>(grads), accumulate);
+}
+
+int32_t fg_convert(fg_ctx* ctx, const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, uint64_t n) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, src && dst, "fg_convert: NULL pointer");
+    FG_REQUIRE(ctx, src_dtype >= FG_DTYPE_F32 && src_dtype <= FG_DTYPE_BF16 && dst_dtype >= FG_DTYPE_F32 &&
+                        dst_dtype <= FG_DTYPE_BF16, "fg_convert: unknown dtype");
+    if (n == 0) return FG_OK;
+    const int grid = fg_stream_grid(ctx, n, 256, 8);
+#define FG_CONV(S, D) if (src_dtype == S && dst_dtype == D) convert_kernel<S, D><<<grid, 256, 0, ctx->stream>>>(src, dst, n)
+    FG_CONV(FG_DTYPE_F32, FG_DTYPE_F32); FG_CONV(FG_DTYPE_F32, FG_DTYPE_F16); FG_CONV(FG_DTYPE_F32, FG_DTYPE_BF16);
+    FG_CONV(FG_DTYPE_F16, FG_DTYPE_F32); FG_CONV(FG_DTYPE_F16, FG_DTYPE_F16); FG_CONV(FG_DTYPE_F16, FG_DTYPE_BF16);
+    FG_CONV(FG_DTYPE_BF16, FG_DTYPE_F32); FG_CONV(FG_DTYPE_BF16, FG_DTYPE_F16); FG_CONV(FG_DTYPE_BF16, FG_DTYPE_BF16);
+#undef FG_CONV
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

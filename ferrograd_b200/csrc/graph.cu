@@ -37,6 +37,7 @@ struct GNode {
     int op, a, b;
     float imm;
     std::vector<uint32_t> fields;   // INPUT: one metadata field id per dimension
+    int dtype = FG_DTYPE_F32;       // INPUT: storage type
 };
 
 inline bool is_ew(int op) { return op >= FG_EW_ADD && op <= FG_EW_ELU; }
@@ -103,6 +104,8 @@ struct fg_exec {
     fg_adamw_hyper hyper{1e-3f, 0.9f, 0.999f, 1e-8f, 0.01f};
     bool bound = false;
     int last;                       // output node
+    int dtype = FG_DTYPE_F32;       // storage type of every tensor of the graph
+    uint64_t esize = 4;
     bool ce_softmax_tail = false;   // graph ends in softmax and the loss is cross-entropy
 };
 
@@ -139,7 +142,7 @@ int emit(fg_exec* e, ChainStep& c, int node, int root, int32_t* status) {
 }
 
 int32_t alloc_buf(fg_exec* e, uint64_t numel, bool zero, fg_buf** out) {
-    return zero ? fg_alloc_zeroed(e->ctx, numel * 4, out) : fg_alloc(e->ctx, numel * 4, out);
+    return zero ? fg_alloc_zeroed(e->ctx, numel * e->esize, out) : fg_alloc(e->ctx, numel * e->esize, out);
 }
 
 int act_of(int op) { return op == FG_EW_TANH ? FG_ACT_TANH : op == FG_EW_RELU ? FG_ACT_RELU : op == FG_EW_GELU ? FG_ACT_GELU : -1; }
@@ -160,6 +163,22 @@ int32_t lower(fg_exec* e) {
     const int N = (int)g.nodes.size();
     e->n.assign(N, ENode());
     e->last = N - 1;
+    // ---- storage type: one per graph.  16-bit graphs run their elementwise regions in that type; ----
+    // ---- matmul, softmax, the losses and the optimizers are f32-only here.                      ----
+    {
+        int dt = -1;
+        for (const GNode& gn : g.nodes) {
+            if (gn.op != FG_EW_INPUT) continue;
+            if (dt >= 0 && gn.dtype != dt) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: inputs of different storage types");
+            dt = gn.dtype;
+        }
+        e->dtype = dt < 0 ? FG_DTYPE_F32 : dt;
+        e->esize = e->dtype == FG_DTYPE_F32 ? 4 : 2;
+        if (e->dtype != FG_DTYPE_F32)
+            for (const GNode& gn : g.nodes)
+                if (gn.op == OP_MATMUL || gn.op == OP_SOFTMAX)
+                    return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: matmul and softmax need f32 storage");
+    }
     // ---- shapes (the reference's validate: backend/mod.rs:854-975) ----
     for (int i = 0; i < N; ++i) {
         const GNode& gn = g.nodes[i];
@@ -314,7 +333,8 @@ int32_t lower(fg_exec* e) {
 int32_t accumulate_into(fg_exec* e, int node, const float* src) {
     fg_ew_instr prog[3] = {{FG_EW_INPUT, 0, 0, 0.f}, {FG_EW_INPUT, 1, 0, 0.f}, {FG_EW_ADD, 0, 1, 0.f}};
     const float* in[2] = {gptr(e, node), src};
-    return fg_eltwise_chain_fwd(e->ctx, e->n[node].numel, prog, 3, in, 2, gptr(e, node), nullptr);
+    return fg_eltwise_chain_fwd_dt(e->ctx, e->dtype, e->n[node].numel, prog, 3, (const void* const*)in, 2, gptr(e, node),
+                                   nullptr);
 }
 
 }  // namespace
@@ -336,17 +356,22 @@ int32_t fg_graph_destroy(fg_graph* g) { delete g; return FG_OK; }
 
 int32_t fg_graph_node_count(const fg_graph* g) { return g ? (int32_t)g->nodes.size() : -1; }
 
-int32_t fg_graph_input(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t* node) {
+int32_t fg_graph_input_dt(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t dtype, int32_t* node) {
     if (!g || !shape_fields || !node || ndim < 1 || ndim > 4) return FG_ERR_INVALID_ARGUMENT;
-    GNode n{FG_EW_INPUT, -1, -1, 0.f, std::vector<uint32_t>(shape_fields, shape_fields + ndim)};
+    if (dtype < FG_DTYPE_F32 || dtype > FG_DTYPE_BF16) return FG_ERR_INVALID_ARGUMENT;
+    GNode n{FG_EW_INPUT, -1, -1, 0.f, std::vector<uint32_t>(shape_fields, shape_fields + ndim), dtype};
     g->nodes.push_back(n);
     *node = (int32_t)g->nodes.size() - 1;
     return FG_OK;
 }
 
+int32_t fg_graph_input(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t* node) {
+    return fg_graph_input_dt(g, shape_fields, ndim, FG_DTYPE_F32, node);
+}
+
 int32_t fg_graph_constant_f32(fg_graph* g, float value, int32_t* node) {
     if (!g || !node) return FG_ERR_INVALID_ARGUMENT;
-    g->nodes.push_back(GNode{FG_EW_CONST, -1, -1, value, {}});
+    g->nodes.push_back(GNode{FG_EW_CONST, -1, -1, value, {}, FG_DTYPE_F32});
     *node = (int32_t)g->nodes.size() - 1;
     return FG_OK;
 }
@@ -406,7 +431,7 @@ int32_t fg_exec_bind(fg_exec* e, fg_buf* const* in_tensors, uint32_t count, cons
     FG_REQUIRE(e->ctx, in_tensors && count == e->inputs.size(), "fg_exec_bind: one tensor per graph input is required");
     for (uint32_t k = 0; k < count; ++k) {
         FG_REQUIRE(e->ctx, in_tensors[k] != nullptr, "fg_exec_bind: NULL tensor");
-        FG_REQUIRE(e->ctx, in_tensors[k]->bytes >= e->n[e->inputs[k]].numel * 4, "fg_exec_bind: tensor smaller than the input's shape");
+        FG_REQUIRE(e->ctx, in_tensors[k]->bytes >= e->n[e->inputs[k]].numel * e->esize, "fg_exec_bind: tensor smaller than the input's shape");
         e->n[e->inputs[k]].value = in_tensors[k];
     }
     e->trainable.assign(count, 1);
@@ -432,8 +457,8 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
             const ChainStep& c = e->chains[st.idx];
             const float* in[FG_EW_MAX_INPUTS];
             for (size_t k = 0; k < c.inputs.size(); ++k) in[k] = vptr(e, c.inputs[k]);
-            s = fg_eltwise_chain_fwd(e->ctx, e->n[c.root].numel, c.prog.data(), (int)c.prog.size(), in,
-                                     (int)c.inputs.size(), vptr(e, c.root), nullptr);
+            s = fg_eltwise_chain_fwd_dt(e->ctx, e->dtype, e->n[c.root].numel, c.prog.data(), (int)c.prog.size(),
+                                        (const void* const*)in, (int)c.inputs.size(), vptr(e, c.root), nullptr);
         } else {
             const auto& d = e->n[st.idx].dims;
             const uint32_t cols = d.back();
@@ -446,6 +471,7 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
 
 int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (e->dtype != FG_DTYPE_F32) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "dispatch_loss: the losses need f32 storage");
     FG_REQUIRE(e->ctx, target != nullptr, "dispatch_loss: target is NULL");
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_loss: bind the input tensors first");
     const ENode& o = e->n[e->last];
@@ -545,10 +571,11 @@ int32_t fg_exec_dispatch_backward(fg_exec* e) {
                 in[j] = vptr(e, c.inputs[j]);
                 gr[j] = gptr(e, c.inputs[j]);
                 if (any_written && !written[c.inputs[j]] &&
-                    (s = fg_memset_zero(e->ctx, gr[j], e->n[c.inputs[j]].numel * 4)) != FG_OK) return s;
+                    (s = fg_memset_zero(e->ctx, gr[j], e->n[c.inputs[j]].numel * e->esize)) != FG_OK) return s;
             }
-            s = fg_eltwise_chain_bwd(e->ctx, e->n[c.root].numel, c.prog.data(), (int)c.prog.size(), in, (int)c.inputs.size(),
-                                     grad_of(c.root), gr, any_written ? 1 : 0);
+            s = fg_eltwise_chain_bwd_dt(e->ctx, e->dtype, e->n[c.root].numel, c.prog.data(), (int)c.prog.size(),
+                                        (const void* const*)in, (int)c.inputs.size(), grad_of(c.root), (void* const*)gr,
+                                        any_written ? 1 : 0);
             if (s != FG_OK) return s;
             for (int id : c.inputs) written[id] = 1;
         } else {
@@ -577,6 +604,17 @@ static int32_t optim_one(fg_exec* e, uint32_t slot, fg_buf* weight) {
     const int node = e->inputs[slot];
     float lr;
     memcpy(&lr, &e->meta[0], 4);   // field 0 holds the learning rate's bits (kernel/optim.rs:119-131)
+    if (e->dtype != FG_DTYPE_F32) {
+        // 16-bit storage: scaled = g*lr; w -= scaled; g = 0 (optim/basic_optim.rs:3-31), each result rounded
+        // to the storage type, as a two-input elementwise program written back over w.
+        if (e->g.optim != FG_OPTIM_SGD) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "AdamW needs f32 storage");
+        const fg_ew_instr prog[5] = {{FG_EW_INPUT, 0, 0, 0.f}, {FG_EW_INPUT, 1, 0, 0.f}, {FG_EW_CONST, 0, 0, lr},
+                                     {FG_EW_MUL, 1, 2, 0.f}, {FG_EW_SUB, 0, 3, 0.f}};
+        const void* in[2] = {weight->ptr, gptr(e, node)};
+        int32_t s = fg_eltwise_chain_fwd_dt(e->ctx, e->dtype, e->n[node].numel, prog, 5, in, 2, weight->ptr, nullptr);
+        if (s != FG_OK) return s;
+        return fg_memset_zero(e->ctx, gptr(e, node), e->n[node].numel * e->esize);
+    }
     if (e->g.optim == FG_OPTIM_SGD)
         return fg_sgd_step(e->ctx, (float*)weight->ptr, gptr(e, node), e->n[node].numel, lr, 1.0f, 1);
     fg_adamw_hyper h = e->hyper;
@@ -604,7 +642,7 @@ int32_t fg_exec_dispatch_single_optim(fg_exec* e, fg_buf* weight, uint32_t grad_
     FG_REQUIRE(e->ctx, grad_index < e->grads.size() && e->n[e->grads[grad_index]].input_slot >= 0,
                "dispatch_single_optim: grad index does not name an input's gradient");
     const uint32_t slot = (uint32_t)e->n[e->grads[grad_index]].input_slot;
-    FG_REQUIRE(e->ctx, weight->bytes >= e->n[e->inputs[slot]].numel * 4, "dispatch_single_optim: weight smaller than its gradient");
+    FG_REQUIRE(e->ctx, weight->bytes >= e->n[e->inputs[slot]].numel * e->esize, "dispatch_single_optim: weight smaller than its gradient");
     return optim_one(e, slot, weight);
 }
 

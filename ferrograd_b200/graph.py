@@ -40,8 +40,14 @@ def f32_bits(x):
 
 
 class SimpleDType:
+    """crates/fused_gpu/src/dispatch/backend/mod.rs:337-345 (the storage types this backend takes)."""
     F32 = "f32"
+    F16 = "f16"
+    BF16 = "bf16"
     U32 = "u32"
+
+
+_DTYPE_CODE = {SimpleDType.F32: 0, SimpleDType.F16: 1, SimpleDType.BF16: 2}
 
 
 class Metadata:
@@ -130,7 +136,8 @@ class DefineOps:
     def input(self, shape, dtype=SimpleDType.F32):
         fields = (C.c_uint32 * len(shape))(*shape)
         node = C.c_int32()
-        self._check(self.graph.lib.fg_graph_input(self.graph.handle, fields, len(shape), C.byref(node)), "input")
+        self._check(self.graph.lib.fg_graph_input_dt(self.graph.handle, fields, len(shape), _DTYPE_CODE[dtype],
+                                                     C.byref(node)), "input")
         return node.value
 
     def constant_f32(self, value):

@@ -287,6 +287,21 @@ int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, i
                              const float* const* inputs, int32_t ninputs, const float* seed,
                              float* const* grads, int32_t accumulate);
 
+/* ---- 16-bit storage (SimpleDType::{F16,BF16}: crates/fused_gpu/src/dispatch/backend/mod.rs:337-345;
+ *      exercised by crates/ferrograd/tests/nonf32.rs:10-99) ----
+ * The _dt forms take tensors of one storage type.  With 16-bit storage every operation's result
+ * is rounded to that type (round to nearest even), as native half arithmetic does. */
+enum fg_dtype { FG_DTYPE_F32 = 0, FG_DTYPE_F16 = 1, FG_DTYPE_BF16 = 2 };
+int32_t fg_eltwise_chain_fwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg_ew_instr* prog,
+                                int32_t ninstr, const void* const* inputs, int32_t ninputs,
+                                void* out, void* const* saved_out);
+int32_t fg_eltwise_chain_bwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg_ew_instr* prog,
+                                int32_t ninstr, const void* const* inputs, int32_t ninputs,
+                                const void* seed, void* const* grads, int32_t accumulate);
+/* dst[i] = src[i] converted between storage types (round to nearest even when narrowing). */
+int32_t fg_convert(fg_ctx* ctx, const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype,
+                   uint64_t n);
+
 /* ---- graphs: the reference's Graph -> alloc_tensors -> schedule -> dispatch_* flow ----
  * A graph is a list of nodes in definition order (Graph::push_node,
  * crates/fused_gpu/src/dispatch/backend/mod.rs:1224; ops: crates/ferrograd/src/graph.rs:111-158).
@@ -304,6 +319,10 @@ int32_t fg_graph_create(int32_t loss, int32_t optim, fg_graph** out);           
 int32_t fg_graph_destroy(fg_graph* g);
 int32_t fg_graph_node_count(const fg_graph* g);
 int32_t fg_graph_input(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t* node); /* DefineOps::input */
+/* An input stored as f16 or bf16 (fg_dtype).  All inputs of a graph share one storage type; 16-bit
+ * graphs may hold elementwise operations and use SGD (matmul, softmax, the losses and AdamW are
+ * f32-only), and every tensor the engine allocates for them has that type. */
+int32_t fg_graph_input_dt(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t dtype, int32_t* node);
 int32_t fg_graph_constant_f32(fg_graph* g, float value, int32_t* node);          /* constant_f32      */
 /* op: FG_EW_ADD..FG_EW_ELU, FG_GRAPH_MATMUL, FG_GRAPH_SOFTMAX; b is ignored for unary ops.          */
 int32_t fg_graph_op(fg_graph* g, int32_t op, int32_t a, int32_t b, int32_t* node);

@@ -177,7 +177,18 @@ def make_prog(instrs):
     return arr
 
 
-def eltwise_fwd(instrs, inputs, save=()):
+DTYPES = {"f32": 0, "f16": 1, "bf16": 2}
+
+
+def round_to(x, dtype):
+    """x rounded to the nearest f16 / bf16 value (ties to even), returned as float32."""
+    x = _f(x)
+    out = np.empty_like(x)
+    lib().ref_round_to(DTYPES[dtype], C.c_uint64(x.size), _p(x), _p(out))
+    return out
+
+
+def eltwise_fwd(instrs, inputs, save=(), dtype="f32"):
     inputs = [_f(x) for x in inputs]
     n = inputs[0].size
     prog = make_prog(instrs)
@@ -186,11 +197,11 @@ def eltwise_fwd(instrs, inputs, save=()):
     saved = {k: np.empty_like(inputs[0]) for k in save}
     sv = (C.c_void_p * len(instrs))(*[saved[k].ctypes.data if k in saved else None
                                       for k in range(len(instrs))])
-    lib().ref_eltwise_chain_fwd(C.c_uint64(n), prog, len(instrs), inp, len(inputs), _p(out), sv)
+    lib().ref_eltwise_chain_fwd_dt(DTYPES[dtype], C.c_uint64(n), prog, len(instrs), inp, len(inputs), _p(out), sv)
     return out, saved
 
 
-def eltwise_bwd(instrs, inputs, seed, quirks=0):
+def eltwise_bwd(instrs, inputs, seed, quirks=0, dtype="f32"):
     inputs = [_f(x) for x in inputs]
     seed = _f(seed)
     n = inputs[0].size
@@ -198,8 +209,8 @@ def eltwise_bwd(instrs, inputs, seed, quirks=0):
     grads = [np.zeros_like(x) for x in inputs]
     inp = (C.c_void_p * len(inputs))(*[x.ctypes.data for x in inputs])
     gp = (C.c_void_p * len(inputs))(*[g.ctypes.data for g in grads])
-    lib().ref_eltwise_chain_bwd(C.c_uint64(n), prog, len(instrs), inp, len(inputs), _p(seed), gp,
-                                0, quirks)
+    lib().ref_eltwise_chain_bwd_dt(DTYPES[dtype], C.c_uint64(n), prog, len(instrs), inp, len(inputs), _p(seed), gp,
+                                   0, quirks)
     return grads
 
 

@@ -406,77 +406,114 @@ void ref_adamw_step(uint64_t n, float* w, float* g, float* m, float* v, float lr
 enum { EW_INPUT = 0, EW_CONST, EW_ADD, EW_SUB, EW_MUL, EW_DIV, EW_NEG, EW_ABS, EW_EXP, EW_LOG,
        EW_TANH, EW_RELU, EW_GELU, EW_ELU };
 
-static inline float ew_eval(const ref_ew_instr& in, const float* v, const float* const* inputs,
+// Rounding to a 16-bit storage type (round to nearest even); dtype 0 = f32 = identity.
+static inline float rnd(int dt, float x) {
+    if (dt == 1) return (float)(_Float16)x;
+    if (dt == 2) {
+        uint32_t u;
+        std::memcpy(&u, &x, 4);
+        if ((u & 0x7fffffffu) > 0x7f800000u) return x;            // NaN
+        u += 0x7fffu + ((u >> 16) & 1u);
+        u &= 0xffff0000u;
+        std::memcpy(&x, &u, 4);
+        return x;
+    }
+    return x;
+}
+
+static inline float ew_eval(int dt, const ref_ew_instr& in, const float* v, const float* const* inputs,
                             uint64_t i) {
     switch (in.op) {
         case EW_INPUT: return inputs[in.a][i];
-        case EW_CONST: return in.imm;
-        case EW_ADD: return v[in.a] + v[in.b];                 // op/binary.rs:74
-        case EW_SUB: return v[in.a] - v[in.b];                 // :449
-        case EW_MUL: return v[in.a] * v[in.b];                 // :236
-        case EW_DIV: return v[in.a] / v[in.b];                 // :644
+        case EW_CONST: return rnd(dt, in.imm);
+        case EW_ADD: return rnd(dt, v[in.a] + v[in.b]);                 // op/binary.rs:74
+        case EW_SUB: return rnd(dt, v[in.a] - v[in.b]);                 // :449
+        case EW_MUL: return rnd(dt, v[in.a] * v[in.b]);                 // :236
+        case EW_DIV: return rnd(dt, v[in.a] / v[in.b]);                 // :644
         case EW_NEG: return -v[in.a];
         case EW_ABS: return std::fabs(v[in.a]);
-        case EW_EXP: return std::exp(v[in.a]);                 // op/unary.rs:741-756
-        case EW_LOG: return std::log(v[in.a]);
-        case EW_TANH: return std::tanh(v[in.a]);
+        case EW_EXP: return rnd(dt, std::exp(v[in.a]));                 // op/unary.rs:741-756
+        case EW_LOG: return rnd(dt, std::log(v[in.a]));
+        case EW_TANH: return rnd(dt, std::tanh(v[in.a]));
         case EW_RELU: return v[in.a] > 0.0f ? v[in.a] : 0.0f;
-        case EW_GELU: return gelu_fwd(v[in.a], nullptr);
-        case EW_ELU: return v[in.a] >= 0.0f ? v[in.a] : std::exp(v[in.a]) - 1.0f;  // op/unary.rs:328-436
+        case EW_GELU: return rnd(dt, gelu_fwd(v[in.a], nullptr));
+        case EW_ELU: return v[in.a] >= 0.0f ? v[in.a] : rnd(dt, std::exp(v[in.a]) - 1.0f);  // op/unary.rs:328-436
         default: return 0.0f;
     }
 }
 
-void ref_eltwise_chain_fwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
-                           const float* const* inputs, int ninputs, float* out,
-                           float* const* saved_out) {
+// The arrays are float; with dtype 1 (f16) or 2 (bf16) they hold values of that type and every operation's
+// result is rounded to it, which is what arithmetic in the 16-bit type itself gives for + - * /
+// (the reference computes f16 graphs in the storage type: crates/ferrograd/tests/nonf32.rs:10-99).
+void ref_eltwise_chain_fwd_dt(int dt, uint64_t n, const ref_ew_instr* prog, int ninstr,
+                              const float* const* inputs, int ninputs, float* out,
+                              float* const* saved_out) {
     (void)ninputs;
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < (int64_t)n; ++i) {
         float v[64];
         for (int k = 0; k < ninstr; ++k) {
-            v[k] = ew_eval(prog[k], v, inputs, (uint64_t)i);
+            v[k] = ew_eval(dt, prog[k], v, inputs, (uint64_t)i);
             if (saved_out && saved_out[k]) saved_out[k][i] = v[k];
         }
         out[i] = v[ninstr - 1];
     }
 }
 
-void ref_eltwise_chain_bwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
-                           const float* const* inputs, int ninputs, const float* seed,
-                           float* const* grads, int accumulate, int quirks) {
+void ref_eltwise_chain_bwd_dt(int dt, uint64_t n, const ref_ew_instr* prog, int ninstr,
+                              const float* const* inputs, int ninputs, const float* seed,
+                              float* const* grads, int accumulate, int quirks) {
     // Reverse sweep; derivative forms from op/binary.rs (mul :344-418, sub :557-613,
     // div :752-851) and op/unary.rs.
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < (int64_t)n; ++i) {
         float v[64], adj[64], gin[16];
-        for (int k = 0; k < ninstr; ++k) { v[k] = ew_eval(prog[k], v, inputs, (uint64_t)i); adj[k] = 0.0f; }
+        for (int k = 0; k < ninstr; ++k) { v[k] = ew_eval(dt, prog[k], v, inputs, (uint64_t)i); adj[k] = 0.0f; }
         for (int k = 0; k < ninputs; ++k) gin[k] = 0.0f;
         adj[ninstr - 1] = seed[i];
+        auto R = [dt](float x) { return rnd(dt, x); };
         for (int k = ninstr - 1; k >= 0; --k) {
             const ref_ew_instr& in = prog[k];
             float g = adj[k];
             switch (in.op) {
-                case EW_INPUT: gin[in.a] += g; break;
-                case EW_ADD: adj[in.a] += g; adj[in.b] += g; break;
-                case EW_SUB: adj[in.a] += g; adj[in.b] -= g; break;
-                case EW_MUL: adj[in.a] += g * v[in.b]; adj[in.b] += g * v[in.a]; break;
-                case EW_DIV: adj[in.a] += g / v[in.b];
-                             adj[in.b] -= (g * v[in.a]) / (v[in.b] * v[in.b]); break;
-                case EW_NEG: adj[in.a] -= g; break;
-                case EW_ABS: adj[in.a] += (v[in.a] >= 0.0f ? g : -g); break;
-                case EW_EXP: adj[in.a] += g * v[k]; break;
-                case EW_LOG: adj[in.a] += g / v[in.a]; break;
-                case EW_TANH: adj[in.a] += g * (1.0f - v[k] * v[k]); break;
-                case EW_RELU: adj[in.a] += g * act_grad(REF_ACT_RELU, v[k], quirks); break;
-                case EW_GELU: adj[in.a] += g * act_grad(REF_ACT_GELU, v[in.a], quirks); break;
-                case EW_ELU: adj[in.a] += (v[k] >= 0.0f ? g : g * (v[k] + 1.0f)); break;
+                case EW_INPUT: gin[in.a] = R(gin[in.a] + g); break;
+                case EW_ADD: adj[in.a] = R(adj[in.a] + g); adj[in.b] = R(adj[in.b] + g); break;
+                case EW_SUB: adj[in.a] = R(adj[in.a] + g); adj[in.b] = R(adj[in.b] - g); break;
+                case EW_MUL: { float va = v[in.a], vb = v[in.b];
+                               adj[in.a] = R(adj[in.a] + R(g * vb)); adj[in.b] = R(adj[in.b] + R(g * va)); break; }
+                case EW_DIV: { float va = v[in.a], vb = v[in.b];
+                               adj[in.a] = R(adj[in.a] + R(g / vb));
+                               adj[in.b] = R(adj[in.b] - R(R(g * va) / R(vb * vb))); break; }
+                case EW_NEG: adj[in.a] = R(adj[in.a] - g); break;
+                case EW_ABS: adj[in.a] = R(adj[in.a] + (v[in.a] >= 0.0f ? g : -g)); break;
+                case EW_EXP: adj[in.a] = R(adj[in.a] + R(g * v[k])); break;
+                case EW_LOG: adj[in.a] = R(adj[in.a] + R(g / v[in.a])); break;
+                case EW_TANH: adj[in.a] = R(adj[in.a] + R(g * R(1.0f - R(v[k] * v[k])))); break;
+                case EW_RELU: adj[in.a] = R(adj[in.a] + g * act_grad(REF_ACT_RELU, v[k], quirks)); break;
+                case EW_GELU: adj[in.a] = R(adj[in.a] + R(g * R(act_grad(REF_ACT_GELU, v[in.a], quirks)))); break;
+                case EW_ELU: adj[in.a] = R(adj[in.a] + (v[k] >= 0.0f ? g : R(g * R(v[k] + 1.0f)))); break;
                 default: break;
             }
         }
         for (int k = 0; k < ninputs; ++k)
-            if (grads[k]) grads[k][i] = accumulate ? grads[k][i] + gin[k] : gin[k];
+            if (grads[k]) grads[k][i] = accumulate ? R(grads[k][i] + gin[k]) : gin[k];
     }
+}
+
+void ref_eltwise_chain_fwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
+                           const float* const* inputs, int ninputs, float* out,
+                           float* const* saved_out) {
+    ref_eltwise_chain_fwd_dt(0, n, prog, ninstr, inputs, ninputs, out, saved_out);
+}
+
+void ref_eltwise_chain_bwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
+                           const float* const* inputs, int ninputs, const float* seed,
+                           float* const* grads, int accumulate, int quirks) {
+    ref_eltwise_chain_bwd_dt(0, n, prog, ninstr, inputs, ninputs, seed, grads, accumulate, quirks);
+}
+
+void ref_round_to(int dt, uint64_t n, const float* src, float* dst) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = rnd(dt, src[i]);
 }
 
 // ---- MLP training step --------------------------------------------------------------

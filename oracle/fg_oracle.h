@@ -71,6 +71,15 @@ void ref_eltwise_chain_fwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
 void ref_eltwise_chain_bwd(uint64_t n, const ref_ew_instr* prog, int ninstr,
                            const float* const* inputs, int ninputs, const float* seed,
                            float* const* grads, int accumulate, int quirks);
+/* The same with 16-bit storage semantics: dt 0 = f32, 1 = f16, 2 = bf16.  Arrays stay float and hold
+ * values of that type; every operation's result is rounded to it. */
+void ref_eltwise_chain_fwd_dt(int dt, uint64_t n, const ref_ew_instr* prog, int ninstr,
+                              const float* const* inputs, int ninputs, float* out,
+                              float* const* saved_out);
+void ref_eltwise_chain_bwd_dt(int dt, uint64_t n, const ref_ew_instr* prog, int ninstr,
+                              const float* const* inputs, int ninputs, const float* seed,
+                              float* const* grads, int accumulate, int quirks);
+void ref_round_to(int dt, uint64_t n, const float* src, float* dst);
 
 /* One training step of a dense MLP, composed in the reference's order
  * forward -> loss -> backward -> update (examples/save_load_model.rs:148-156).

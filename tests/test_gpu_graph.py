@@ -209,6 +209,61 @@ def test_mul_add_optim(ctx, separate):
     t.destroy()
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_mul_add_f16(ctx, dtype):
+    # crates/ferrograd/tests/nonf32.rs:10-99 (f16; the same constants are exact in bf16): inputs declared
+    # with SimpleDType::F16, tensors from init_tensor_f16, the seed uploaded as f16, results compared with ==.
+    from ferrograd_b200 import SimpleDType
+    from ferrograd_b200.backend import from_bf16_bits, to_bf16_bits
+    sd = SimpleDType.F16 if dtype == "f16" else SimpleDType.BF16
+
+    def define(g, m, n):
+        a, b, c = g.input([m, n], sd), g.input([m, n], sd), g.input([m, n], sd)
+        g.add(c, g.mul(a, b))
+    graph, t, kernels, binding = build(ctx, define, [32, 32])
+    init = ctx.init_tensor_f16 if dtype == "f16" else ctx.init_tensor_bf16
+    ins = [init((32, 32), np.full((32, 32), v, np.float32)) for v in (3.0, 2.0, 1.0)]
+    ones = np.ones(1024, np.float32)
+    ctx.upload(t.seed, ones.astype(np.float16) if dtype == "f16" else to_bf16_bits(ones))
+    sch = ctx.schedule(kernels, binding, ins, t, [], ())
+    ctx.dispatch_forward(sch)
+    ctx.dispatch_backward(sch)
+    ctx.sync()
+
+    def dl16(buf):
+        raw = ctx.download(buf, np.empty(1024, np.float16 if dtype == "f16" else np.uint16))
+        return raw.astype(np.float32) if dtype == "f16" else from_bf16_bits(raw)
+    assert (dl16(t.forward_out) == 7.0).all()
+    assert (dl16(t.grad_tensors[0]) == 2.0).all()
+    assert (dl16(t.grad_tensors[1]) == 3.0).all()
+    assert (dl16(t.grad_tensors[2]) == 1.0).all()
+    # SGD in the storage type: w -= lr*g with every result rounded; gradients zeroed
+    ctx.dispatch_optim(sch)
+    ctx.sync()
+    lr = np.float32(1e-3)
+    for i, (w, g) in enumerate(((3.0, 2.0), (2.0, 3.0), (1.0, 1.0))):
+        if dtype == "f16":
+            expect = np.float32(np.float16(w) - np.float16(np.float16(g) * np.float16(lr)))
+            got = ctx.to_numpy(ins[i]).astype(np.float32)
+        else:
+            rb = lambda x: from_bf16_bits(to_bf16_bits(np.array([x], np.float32)))[0]
+            expect = rb(np.float32(w) - rb(np.float32(g) * rb(lr)))
+            got = from_bf16_bits(ctx.to_numpy(ins[i]))
+        assert (got == expect).all(), (i, got.ravel()[0], expect)
+        assert (dl16(t.grad_tensors[i]) == 0.0).all()
+    t.destroy()
+
+
+def test_16bit_graph_rejects_matmul(ctx):
+    from ferrograd_b200 import FgError, SimpleDType
+
+    def define(g, m):
+        a = g.input([m, m], SimpleDType.F16)
+        g.matmul(a, a)
+    with pytest.raises(FgError):
+        build(ctx, define, [32])
+
+
 # ---------------------------------------------------------------- beyond the reference's tests
 @pytest.mark.parametrize("act,loss_name", [("tanh", "mse"), ("gelu", "ce"), ("relu", "ce")])
 def test_mlp_graph_matches_oracle(ctx, oracle, act, loss_name):

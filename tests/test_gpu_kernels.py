@@ -246,6 +246,80 @@ def test_chain_all_ops_vs_oracle(ctx, oracle):
         check(ctx.to_numpy(g), gr, TOL_EW, "chain bwd")
 
 
+# ---------------------------------------------------------------- 16-bit storage
+def up16(ctx, x, dtype):
+    """x (float32, already representable in dtype) as a device tensor of that storage type."""
+    return ctx.init_tensor_f16(x.shape, x) if dtype == "f16" else ctx.init_tensor_bf16(x.shape, x)
+
+
+def down16(ctx, t, dtype):
+    from ferrograd_b200.backend import from_bf16_bits
+    a = ctx.to_numpy(t)
+    return a.astype(np.float32) if dtype == "f16" else from_bf16_bits(a)
+
+
+def new16(ctx, n, dtype):
+    return ctx.new_tensor((n,), np.float16 if dtype == "f16" else np.uint16)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_convert_round_trip(ctx, oracle, dtype):
+    n = 70001
+    x = (rng(70).standard_normal(n) * 37.0).astype(np.float32)
+    x[:4] = [0.0, -0.0, 65504.0, 1e-7]
+    d32, d16, back = up(ctx, x), new16(ctx, n, dtype), ctx.new_tensor((n,))
+    ctx.convert(d32, "f32", d16, dtype, n)
+    ctx.convert(d16, dtype, back, "f32", n)
+    assert np.array_equal(ctx.to_numpy(back), oracle.round_to(x, dtype))        # round to nearest even, bit for bit
+    assert np.array_equal(down16(ctx, d16, dtype), oracle.round_to(x, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_chain_16bit_arithmetic_bit_exact(ctx, oracle, dtype):
+    # + - * / with every result rounded to the storage type: identical to the oracle's, bit for bit
+    n = 20011
+    r = rng(71)
+    x0 = oracle.round_to(r.standard_normal(n, np.float32), dtype)
+    x1 = oracle.round_to(np.abs(r.standard_normal(n, np.float32)) + 0.5, dtype)
+    prog = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("const", 0, 0, 1.7), ("mul", 0, 1, 0.0), ("div", 3, 2, 0.0),
+            ("sub", 4, 1, 0.0), ("add", 5, 0, 0.0), ("div", 6, 1, 0.0), ("neg", 7, 0, 0.0), ("abs", 8, 0, 0.0),
+            ("mul", 9, 7, 0.0)]
+    a, b, out = up16(ctx, x0, dtype), up16(ctx, x1, dtype), new16(ctx, n, dtype)
+    ctx.eltwise_chain_fwd(prog, [a, b], out, n, dtype=dtype)
+    oref, _ = oracle.eltwise_fwd(prog, [x0, x1], dtype=dtype)
+    assert np.array_equal(down16(ctx, out, dtype), oref)
+    seed = oracle.round_to(r.standard_normal(n, np.float32), dtype)
+    grads = [new16(ctx, n, dtype) for _ in range(2)]
+    ctx.eltwise_chain_bwd(prog, [a, b], up16(ctx, seed, dtype), grads, n, dtype=dtype)
+    for g, gr in zip(grads, oracle.eltwise_bwd(prog, [x0, x1], seed, dtype=dtype)):
+        assert np.array_equal(down16(ctx, g, dtype), gr)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_chain_16bit_all_ops(ctx, oracle, dtype):
+    # exp/log/tanh/gelu go through float libm on both sides; a last-bit difference there can land on the
+    # other side of a 16-bit rounding boundary, so the bar is one unit of the storage type's precision
+    n = 5000
+    tol = 2.0 ** -10 if dtype == "f16" else 2.0 ** -7
+    r = rng(72)
+    x0 = oracle.round_to(r.standard_normal(n, np.float32), dtype)
+    x1 = oracle.round_to(np.abs(r.standard_normal(n, np.float32)) + 0.5, dtype)
+    prog = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("const", 0, 0, 1.5), ("mul", 0, 1, 0.0),
+            ("div", 3, 1, 0.0), ("sub", 4, 2, 0.0), ("tanh", 5, 0, 0.0), ("gelu", 0, 0, 0.0), ("add", 6, 7, 0.0),
+            ("log", 1, 0, 0.0), ("exp", 6, 0, 0.0), ("mul", 9, 10, 0.0), ("neg", 11, 0, 0.0), ("abs", 0, 0, 0.0),
+            ("relu", 5, 0, 0.0), ("elu", 0, 0, 0.0), ("add", 12, 13, 0.0), ("add", 14, 15, 0.0),
+            ("add", 16, 17, 0.0), ("add", 18, 8, 0.0)]
+    a, b, out = up16(ctx, x0, dtype), up16(ctx, x1, dtype), new16(ctx, n, dtype)
+    ctx.eltwise_chain_fwd(prog, [a, b], out, n, dtype=dtype)
+    oref, _ = oracle.eltwise_fwd(prog, [x0, x1], dtype=dtype)
+    check(down16(ctx, out, dtype), oref, tol, f"{dtype} chain fwd")
+    seed = oracle.round_to(r.standard_normal(n, np.float32), dtype)
+    grads = [new16(ctx, n, dtype) for _ in range(2)]
+    ctx.eltwise_chain_bwd(prog, [a, b], up16(ctx, seed, dtype), grads, n, dtype=dtype)
+    for g, gr in zip(grads, oracle.eltwise_bwd(prog, [x0, x1], seed, dtype=dtype)):
+        check(down16(ctx, g, dtype), gr, 4 * tol, f"{dtype} chain bwd")
+
+
 # ---------------------------------------------------------------- GEMM
 GEMM_SHAPES = [(32, 64, 16), (1, 1, 1), (64, 2, 16), (70, 33, 45), (130, 257, 100), (256, 512, 384)]
 

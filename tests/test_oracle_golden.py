@@ -94,6 +94,31 @@ def test_div_const_softmax(oracle):
     assert (dx == 0.0).all()
 
 
+def test_mul_add_f16(oracle):
+    # crates/ferrograd/tests/nonf32.rs:10-99: c + a*b in f16 with a, b, c = 3, 2, 1 -> 7; grads 2, 3, 1.
+    prog = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("input", 2, 0, 0.0), ("mul", 0, 1, 0.0), ("add", 2, 3, 0.0)]
+    for dtype in ("f16", "bf16"):
+        out, _ = oracle.eltwise_fwd(prog, [full(1024, 3.0), full(1024, 2.0), full(1024, 1.0)], dtype=dtype)
+        assert (out == 7.0).all()
+        ga, gb, gc = oracle.eltwise_bwd(prog, [full(1024, 3.0), full(1024, 2.0), full(1024, 1.0)], full(1024, 1.0), dtype=dtype)
+        assert (ga == 2.0).all() and (gb == 3.0).all() and (gc == 1.0).all()
+
+
+def test_16bit_rounding(oracle):
+    # the oracle's rounding against numpy's float16 cast and a bit-level bf16 rounding; and one f16 product
+    # that differs from the f32 one: 0.1 * 0.3 in f16 arithmetic
+    r = np.random.Generator(np.random.Philox(3))
+    x = (r.standard_normal(100000) * 50).astype(np.float32)
+    assert np.array_equal(oracle.round_to(x, "f16"), x.astype(np.float16).astype(np.float32))
+    u = x.view(np.uint32)
+    bf = (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+    assert np.array_equal(oracle.round_to(x, "bf16"), bf)
+    a, b = np.float16(0.1), np.float16(0.3)
+    out, _ = oracle.eltwise_fwd([("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("mul", 0, 1, 0.0)],
+                                [np.full(4, a, np.float32), np.full(4, b, np.float32)], dtype="f16")
+    assert (out == np.float32(a * b)).all() and np.float32(a * b) != np.float32(a) * np.float32(b)
+
+
 def test_bce_formulas(oracle):
     # loss/basic_loss.rs:29-89.  Hard targets at p = 1/2: the definition gives log 2 per element and the
     # gradient is p - t.  With reference_formula the loss is (1-t)*log(1-t) - t*log(p) as the file has it:
