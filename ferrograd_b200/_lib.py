@@ -91,6 +91,8 @@ SIGNATURES = {
                                       C.POINTER(C.c_void_p)]),
     "fg_eltwise_chain_bwd_dt": (i32, [c_ctx, i32, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
                                       C.POINTER(C.c_void_p), i32]),
+    "fg_gemm_lowp": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, c_dev, i32, c_dev]),
+    "fg_gemm_bwd_lowp": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, i32, c_dev, c_dev, c_dev, c_dev]),
     "fg_convert": (i32, [c_ctx, c_dev, i32, c_dev, i32, u64]),
     "fg_graph_create": (i32, [i32, i32, C.POINTER(C.c_void_p)]),
     "fg_graph_destroy": (i32, [C.c_void_p]),

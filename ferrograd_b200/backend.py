@@ -366,6 +366,15 @@ class GpuContext:
         self._check(self.lib.fg_eltwise_chain_bwd_dt(self.handle, DTYPE[dtype], n, prog, len(instrs), inp, len(inputs),
                                                      _ptr(seed), gp, int(accumulate)))
 
+    def gemm_lowp(self, A, B, Cout, M, N, K, dtype, bias=None, act="none", preact_out=None):
+        """GEMM on f16 / bf16 tensors: 16-bit operands straight into the tensor cores, f32 accumulate."""
+        self._check(self.lib.fg_gemm_lowp(self.handle, DTYPE[dtype], M, N, K, _ptr(A), _ptr(B), _ptr(Cout), _ptr(bias),
+                                          ACT[act], _ptr(preact_out)))
+
+    def gemm_bwd_lowp(self, A, B, dY, M, N, K, dtype, act="none", saved=None, dA=None, dB=None, dbias=None):
+        self._check(self.lib.fg_gemm_bwd_lowp(self.handle, DTYPE[dtype], M, N, K, _ptr(A), _ptr(B), _ptr(dY), ACT[act],
+                                              _ptr(saved), _ptr(dA), _ptr(dB), _ptr(dbias)))
+
     def convert(self, src, src_dtype, dst, dst_dtype, n):
         self._check(self.lib.fg_convert(self.handle, _ptr(src), DTYPE[src_dtype], _ptr(dst), DTYPE[dst_dtype], n))
 

@@ -436,6 +436,12 @@ int32_t fg_eltwise_chain_bwd(fg_ctx* ctx, uint64_t n, const fg_ew_instr* prog, i
 
 int32_t fg_convert(fg_ctx* ctx, const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype, uint64_t n) {
     FG_ENTER(ctx);
+    return fg_convert_launch(ctx, src, src_dtype, dst, dst_dtype, n);
+}
+
+}  // extern "C"
+
+int32_t fg_convert_launch(fg_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, uint64_t n) {
     FG_REQUIRE(ctx, src && dst, "fg_convert: NULL pointer");
     FG_REQUIRE(ctx, src_dtype >= FG_DTYPE_F32 && src_dtype <= FG_DTYPE_BF16 && dst_dtype >= FG_DTYPE_F32 &&
                         dst_dtype <= FG_DTYPE_BF16, "fg_convert: unknown dtype");
@@ -449,5 +455,3 @@ int32_t fg_convert(fg_ctx* ctx, const void* src, int32_t src_dtype, void* dst, i
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
-
-}  // extern "C"

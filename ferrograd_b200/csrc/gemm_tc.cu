@@ -48,7 +48,32 @@ struct Epilogue {
     // partial sums over equal shares of the K chunks, written raw to `partial` and folded by a second kernel.
     float* partial;
     uint32_t t_full, split;
+    int out_dtype;       // storage type of C and preact (fg_dtype); bias and partial are always f32
 };
+
+// Element stores in the output's storage type (idx in elements).
+__device__ __forceinline__ void store_out4(void* base, size_t idx, float4 v, int dt) {
+    if (dt == FG_DTYPE_F32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(base) + idx) = v;
+    } else if (dt == FG_DTYPE_F16) {
+        const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&lo);
+        u.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__half*>(base) + idx) = u;
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&lo);
+        u.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + idx) = u;
+    }
+}
+__device__ __forceinline__ void store_out1(void* base, size_t idx, float v, int dt) {
+    if (dt == FG_DTYPE_F32) static_cast<float*>(base)[idx] = v;
+    else if (dt == FG_DTYPE_F16) static_cast<__half*>(base)[idx] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+}
 
 // Origin of pair tile `tile`: tiles are numbered so that eight consecutive pair-rows sweep all columns
 // before the next eight start.  The pairs working at the same time then cover a squarish block of C and
@@ -351,6 +376,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA16, const __grid_constant__ CUtensorMap tmB16, Epilogue ep) {
     static_assert(FMT == 0 || BK == 32, "the bf16 planes use 64-byte rows: 32 values of k per block");
+    // FMT 2 (bf16) and 3 (f16): the operands ARE 16-bit tensors, loaded as they lie (K-major, 64 values of
+    // k = one 128-byte row per k-block) and multiplied by one kind::f16 MMA per 16 values of k.
+    constexpr bool kDirect16 = FMT >= 2;
+    constexpr uint32_t KBE = kDirect16 ? 2 * BK : BK;            // values of k per k-block
+    constexpr uint32_t kChunk = kDirect16 ? 1024 : kChunkK;      // 16-bit results tolerate the longer chain
     using Cfg = PairCfg<BK>;
     constexpr int BN = Cfg::kBN, HB = BN / 2;
     constexpr int S = Cfg::kStages;
@@ -377,8 +407,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         pair_tile_origin(tile, pairs_m, pairs_n, 2 * BM, BN, m0, n0);
         m0 += rank * BM;                                               // this CTA's rows of A and C
     };
-    const uint32_t nkb = (ep.K + BK - 1) / BK;
-    constexpr uint32_t kChunkKB = kChunkK / BK;
+    const uint32_t nkb = (ep.K + KBE - 1) / KBE;
+    constexpr uint32_t kChunkKB = kChunk / KBE;
     const uint32_t nchunks = (nkb + kChunkKB - 1) / kChunkKB;
     // Work units: whole tiles first, then the tail tiles in `split` K-shares each (the host sizes the
     // tail so that it fills one last wave instead of leaving most pairs idle for a whole tile time).
@@ -399,7 +429,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         fence_mbar_init();
         prefetch_tmap(&tmA);
         prefetch_tmap(&tmB);
-        if (FMT == 1) { prefetch_tmap(&tmA16); prefetch_tmap(&tmB16); }
+        if (FMT >= 1) { prefetch_tmap(&tmA16); prefetch_tmap(&tmB16); }
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::kTmemCols);
@@ -430,9 +460,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         ok = false;
                         break;
                     }
-                    if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
                     const uint32_t lf = map_to_cta(full_bar(s), 0);
                     const uint32_t sa = base + s * Cfg::kStageBytes;
+                    if (kDirect16) {
+                        if (leader) mbar_expect_tx(full_bar(s), 2 * (BM + HB) * BK * 4);   // both CTAs' bytes
+                        tma_load_3d_pair(sa, &tmA16, lf, (int)(kb * KBE), (int)m0, 0);
+                        tma_load_3d_pair(sa + Cfg::kABytes, &tmB16, lf, (int)(kb * KBE), (int)nb0, 0);
+                        continue;
+                    }
+                    if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
                     tma_load_3d_pair(sa, &tmA, lf, (int)(kb * BK), (int)m0, 0);
                     tma_load_3d_pair(sa + Cfg::kABytes, &tmB, lf, (int)(kb * BK), (int)nb0, 0);
                     if (FMT == 1) {
@@ -475,7 +511,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const uint64_t a_hi = make_desc_kmajor<BK * 4>(sa);
                         const uint64_t b_hi = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes);
                         const uint32_t first = (kb == c * kChunkKB) ? 0u : 1u;   // a chunk starts from zero
-                        if (FMT == 0) {
+                        if (kDirect16) {
+                            constexpr uint32_t idesc16 = make_idesc(FMT == 2 ? 1u /*bf16*/ : 0u /*f16*/, 2 * BM, BN);
+#pragma unroll
+                            for (int kk = 0; kk < (int)KBE / 16; ++kk) {
+                                const uint64_t adv = (uint64_t)(kk * 16 * 2 >> 4);
+                                mma_f16_pair(d_tmem, a_hi + adv, b_hi + adv, idesc16, first | (uint32_t)kk);
+                            }
+                        } else if (FMT == 0) {
                             const uint64_t a_lo = make_desc_kmajor<BK * 4>(sa + BM * BK * 4);
                             const uint64_t b_lo = make_desc_kmajor<BK * 4>(sa + Cfg::kABytes + HB * BK * 4);
 #pragma unroll
@@ -555,8 +598,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // A K-share of a tail tile goes out raw (no bias, no activation) into its 256x256 slot.
             float* tb = tbuf + (warp - 2) * (32 * 33);
             const uint32_t rsub = lane >> 3, c4 = (lane & 7) * 4;
-            float* const out = part ? ep.partial + (size_t)slot * (2 * BM * BN) : ep.C;
-            float* const pre = part ? nullptr : ep.preact;
+            void* const out = part ? (void*)(ep.partial + (size_t)slot * (2 * BM * BN)) : (void*)ep.C;
+            void* const pre = part ? nullptr : (void*)ep.preact;
+            const int odt = part ? (int)FG_DTYPE_F32 : ep.out_dtype;
             const uint32_t out_ld = part ? BN : ep.N, row_lim = part ? 2 * BM : ep.M, col_lim = part ? BN : ep.N;
             const uint32_t row_base = part ? rank * BM : m0, col_base = part ? 0u : n0;
             const int act = part ? FG_ACT_NONE : ep.act;
@@ -583,19 +627,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                     for (int t = 0; t < 4; ++t) z[t] = tb[lr * 33 + c4 + t] + bz[t];
                     if (row < row_lim && col < col_lim) {
-                        float* crow = out + (size_t)row * out_ld + col;
-                        float* prow = pre ? pre + (size_t)row * out_ld + col : nullptr;
+                        const size_t off = (size_t)row * out_ld + col;
                         if (vec && col + 3 < col_lim) {
                             const float4 o = act == FG_ACT_NONE ? make_float4(z[0], z[1], z[2], z[3])
                                                                 : act_fwd4(act, make_float4(z[0], z[1], z[2], z[3]));
-                            if (prow) *reinterpret_cast<float4*>(prow) = make_float4(z[0], z[1], z[2], z[3]);
-                            *reinterpret_cast<float4*>(crow) = o;
+                            if (pre) store_out4(pre, off, make_float4(z[0], z[1], z[2], z[3]), odt);
+                            store_out4(out, off, o, odt);
                         } else {
 #pragma unroll
                             for (int t = 0; t < 4; ++t)
                                 if (col + t < col_lim) {
-                                    if (prow) prow[t] = z[t];
-                                    crow[t] = fg_act_fwd(act, z[t]);
+                                    if (pre) store_out1(pre, off + t, z[t], odt);
+                                    store_out1(out, off + t, fg_act_fwd(act, z[t]), odt);
                                 }
                         }
                     }
@@ -635,20 +678,19 @@ __global__ void __launch_bounds__(256) gemm_tc_pair_fold_kernel(Epilogue ep) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) if (col + t < ep.N) zz[t] += ep.bias[col + t];
     }
-    float* crow = ep.C + (size_t)row * ep.N + col;
-    float* prow = ep.preact ? ep.preact + (size_t)row * ep.N + col : nullptr;
+    const size_t off = (size_t)row * ep.N + col;
     const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
                         (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
     if (vec_ok && col + 3 < ep.N) {
         const float4 zin = make_float4(zz[0], zz[1], zz[2], zz[3]);
-        if (prow) *reinterpret_cast<float4*>(prow) = zin;
-        *reinterpret_cast<float4*>(crow) = ep.act == FG_ACT_NONE ? zin : act_fwd4(ep.act, zin);
+        if (ep.preact) store_out4(ep.preact, off, zin, ep.out_dtype);
+        store_out4(ep.C, off, ep.act == FG_ACT_NONE ? zin : act_fwd4(ep.act, zin), ep.out_dtype);
     } else {
 #pragma unroll
         for (int t = 0; t < 4; ++t)
             if (col + t < ep.N) {
-                if (prow) prow[t] = zz[t];
-                crow[t] = fg_act_fwd(ep.act, zz[t]);
+                if (ep.preact) store_out1(ep.preact, off + t, zz[t], ep.out_dtype);
+                store_out1(ep.C, off + t, fg_act_fwd(ep.act, zz[t]), ep.out_dtype);
             }
     }
 }
@@ -876,16 +918,18 @@ typedef CUresult (*pfn_encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, vo
 
 // Tensor map over planes [nplanes][rows][ld] with contraction extent `kdim`; box {bk, box_rows, nplanes}.
 // The swizzle span equals the box's inner extent in bytes: 128 or 64.
-int32_t make_tmap(fg_ctx* ctx, CUtensorMap* out, const void* planes, bool bf16, uint32_t nplanes, uint32_t rows,
+// elem: 0 f32, 1 bf16, 2 f16.
+int32_t make_tmap(fg_ctx* ctx, CUtensorMap* out, const void* planes, int elem, uint32_t nplanes, uint32_t rows,
                   uint32_t kdim, uint32_t ld, uint32_t box_rows, uint32_t bk) {
     if (!ctx->tmap_encode) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "cuTensorMapEncodeTiled unavailable");
-    const uint32_t esz = bf16 ? 2 : 4;
+    const uint32_t esz = elem ? 2 : 4;
     cuuint64_t dims[3] = {kdim, rows, nplanes};
     cuuint64_t strides[2] = {(cuuint64_t)ld * esz, (cuuint64_t)rows * ld * esz};
     cuuint32_t box[3] = {bk, box_rows, nplanes};
     cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapSwizzle swz = bk * esz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-    CUresult r = ((pfn_encode)ctx->tmap_encode)(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+    CUresult r = ((pfn_encode)ctx->tmap_encode)(out, elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                                                 3, (void*)planes, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                                 swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -900,11 +944,11 @@ int32_t launch_tc(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilo
     using Cfg = TileCfg<BN, BK>;
     CUtensorMap tmA, tmB, tmA16, tmB16;
     int32_t s;
-    if ((s = make_tmap(ctx, &tmA, a.p32, false, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
-    if ((s = make_tmap(ctx, &tmB, b.p32, false, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, BN, BK)) != FG_OK) return s;
+    if ((s = make_tmap(ctx, &tmA, a.p32, 0, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
+    if ((s = make_tmap(ctx, &tmB, b.p32, 0, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, BN, BK)) != FG_OK) return s;
     if (FMT == 1) {
-        if ((s = make_tmap(ctx, &tmA16, a.p16, true, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
-        if ((s = make_tmap(ctx, &tmB16, b.p16, true, 2, ep.N, ep.K, b.ld16, BN, BK)) != FG_OK) return s;
+        if ((s = make_tmap(ctx, &tmA16, a.p16, 1, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
+        if ((s = make_tmap(ctx, &tmB16, b.p16, 1, 2, ep.N, ep.K, b.ld16, BN, BK)) != FG_OK) return s;
     } else {
         tmA16 = tmA;
         tmB16 = tmB;
@@ -933,14 +977,24 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
     using Cfg = PairCfg<BK>;
     CUtensorMap tmA, tmB, tmA16, tmB16;
     int32_t s;
-    if ((s = make_tmap(ctx, &tmA, a.p32, false, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
-    if ((s = make_tmap(ctx, &tmB, b.p32, false, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, Cfg::kBN / 2, BK)) != FG_OK) return s;
-    if (FMT == 1) {
-        if ((s = make_tmap(ctx, &tmA16, a.p16, true, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
-        if ((s = make_tmap(ctx, &tmB16, b.p16, true, 2, ep.N, ep.K, b.ld16, Cfg::kBN / 2, BK)) != FG_OK) return s;
+    constexpr bool kDirect16 = FMT >= 2;
+    if (kDirect16) {
+        // the operands themselves: one 16-bit "plane", 64 values of k (128 bytes) per row of a k-block
+        const int elem = FMT == 2 ? 1 : 2;
+        if ((s = make_tmap(ctx, &tmA16, a.p16, elem, 1, ep.M, ep.K, a.ld16, BM, 2 * BK)) != FG_OK) return s;
+        if ((s = make_tmap(ctx, &tmB16, b.p16, elem, 1, ep.N, ep.K, b.ld16, Cfg::kBN / 2, 2 * BK)) != FG_OK) return s;
+        tmA = tmA16;
+        tmB = tmB16;
     } else {
-        tmA16 = tmA;
-        tmB16 = tmB;
+        if ((s = make_tmap(ctx, &tmA, a.p32, 0, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
+        if ((s = make_tmap(ctx, &tmB, b.p32, 0, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, Cfg::kBN / 2, BK)) != FG_OK) return s;
+        if (FMT == 1) {
+            if ((s = make_tmap(ctx, &tmA16, a.p16, 1, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
+            if ((s = make_tmap(ctx, &tmB16, b.p16, 1, 2, ep.N, ep.K, b.ld16, Cfg::kBN / 2, BK)) != FG_OK) return s;
+        } else {
+            tmA16 = tmA;
+            tmB16 = tmB;
+        }
     }
     static uint64_t attr_done = 0;   // one bit per device
     if (!(attr_done >> (ctx->device & 63) & 1ull)) {
@@ -979,7 +1033,8 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
     // The last wave: `rem` tiles for `slots` pairs.  When at least two pairs are free per tile, each tail
     // tile is cut into K-shares (whole accumulation chunks, at least two per share) so that the wave
     // lasts a fraction of a tile time; the shares are folded by a second, bandwidth-bound kernel.
-    const uint32_t nchunks = (uint32_t)(((ep.K + BK - 1) / BK + kChunkK / BK - 1) / (kChunkK / BK));
+    const uint32_t chunk_k = kDirect16 ? 1024 : kChunkK;          // as in the kernel
+    const uint32_t nchunks = (ep.K + chunk_k - 1) / chunk_k;
     const uint64_t rem = ntiles % slots;
     uint64_t split = rem ? slots / rem : 1;
     if (split > nchunks / 2) split = nchunks / 2;
@@ -1278,6 +1333,219 @@ int32_t fg_gemm_batched_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint3
                                     dY + t * strideC, act, saved ? saved + t * strideC : nullptr,
                                     dA ? dA + t * strideA : nullptr, dB ? dB + t * strideB : nullptr, nullptr, nullptr);
         if (s != FG_OK) return s;
+    }
+    return FG_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------
+// 16-bit storage (f16 / bf16 tensors, f32 accumulation).  The operands are multiplied as they
+// are: one kind::f16 MMA per 16 values of k, no operand planes.  What the tensor core needs is
+// the contraction index contiguous, rows 16-byte aligned; an operand that already lies that way
+// is loaded in place, the others go through prep16_kernel (copy with padded pitch and/or
+// transpose, optionally fused with dY * act'(saved) and the bias gradient's column sums).
+// ------------------------------------------------------------------------------------
+namespace {
+
+struct Prep16Args {
+    const void* x;        // [R, C] 16-bit
+    const void* saved;    // non-NULL: value = x * act'(saved), rounded to the storage type
+    int act;
+    uint32_t R, C;
+    void* n_out;          // [R][ld_n] or NULL
+    void* t_out;          // [C][ld_t] or NULL
+    uint32_t ld_n, ld_t;
+    float* colsum_part;   // [ceil(R/32)][C] f32 or NULL
+};
+
+template <typename T> __device__ __forceinline__ float lp_to_float(T v);
+template <> __device__ __forceinline__ float lp_to_float<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float lp_to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T lp_from_float(float v);
+template <> __device__ __forceinline__ __half lp_from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 lp_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) prep16_kernel(const Prep16Args a) {
+    __shared__ T tile[32][33];
+    __shared__ float cs[8][33];
+    const uint32_t c = blockIdx.x * 32 + threadIdx.x;
+    const uint32_t r0 = blockIdx.y * 32;
+    float colsum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t lr = threadIdx.y + 8 * k, r = r0 + lr;
+        T v = lp_from_float<T>(0.0f);
+        if (r < a.R && c < a.C) {
+            const size_t i = (size_t)r * a.C + c;
+            v = static_cast<const T*>(a.x)[i];
+            if (a.saved)
+                v = lp_from_float<T>(lp_to_float(v) * fg_act_grad(a.act, lp_to_float(static_cast<const T*>(a.saved)[i])));
+            if (a.n_out) static_cast<T*>(a.n_out)[(size_t)r * a.ld_n + c] = v;
+            colsum += lp_to_float(v);
+        }
+        tile[lr][threadIdx.x] = v;
+    }
+    if (a.colsum_part) cs[threadIdx.y][threadIdx.x] = colsum;
+    __syncthreads();
+    if (a.colsum_part && threadIdx.y == 0 && c < a.C) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += cs[k][threadIdx.x];
+        a.colsum_part[(size_t)blockIdx.y * a.C + c] = t;
+    }
+    if (a.t_out) {
+        const uint32_t tr = r0 + threadIdx.x;          // row of x = column of the transposed copy
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t lc = threadIdx.y + 8 * k, tc = blockIdx.x * 32 + lc;
+            if (tc < a.C && tr < a.R) static_cast<T*>(a.t_out)[(size_t)tc * a.ld_t + tr] = tile[threadIdx.x][lc];
+        }
+    }
+}
+
+int32_t launch_prep16(fg_ctx* ctx, int dtype, const Prep16Args& a, uint32_t* chunks_out = nullptr) {
+    dim3 grid((a.C + 31) / 32, (a.R + 31) / 32), block(32, 8);
+    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "16-bit GEMM operand has too many rows");
+    if (chunks_out) *chunks_out = grid.y;
+    if (dtype == FG_DTYPE_F16) prep16_kernel<__half><<<grid, block, 0, ctx->stream>>>(a);
+    else prep16_kernel<__nv_bfloat16><<<grid, block, 0, ctx->stream>>>(a);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+inline uint32_t pad8(uint32_t x) { return (x + 7u) & ~7u; }
+// An operand [rows, kdim] whose contraction index is contiguous can be loaded in place when every row
+// starts on a 16-byte boundary.
+inline bool in_place16(const void* p, uint32_t kdim) { return fg_aligned16(p) && kdim % 8 == 0; }
+
+int32_t lowp_gemm(fg_ctx* ctx, int dtype, const void* a_rows, uint32_t lda, const void* b_rows, uint32_t ldb, uint32_t M,
+                  uint32_t N, uint32_t K, void* C, const float* bias32, int act, void* preact) {
+    PlaneSet pa{nullptr, (__nv_bfloat16*)a_rows, 0, lda}, pb{nullptr, (__nv_bfloat16*)b_rows, 0, ldb};
+    Epilogue ep{(float*)C, bias32, (float*)preact, M, N, K, act, ctx->dev_status, nullptr, 0, 1, dtype};
+    return dtype == FG_DTYPE_BF16 ? launch_tc_pair<32, 2>(ctx, pa, pb, ep) : launch_tc_pair<32, 3>(ctx, pa, pb, ep);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fg_gemm_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, void* C,
+                     const void* bias, int32_t act, void* preact_out) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, dtype == FG_DTYPE_F16 || dtype == FG_DTYPE_BF16, "fg_gemm_lowp: dtype must be f16 or bf16");
+    FG_REQUIRE(ctx, A && B && C, "fg_gemm_lowp: NULL operand");
+    FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_lowp: dimensions must be >= 1");
+    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_lowp: unknown activation");
+    FG_REQUIRE(ctx, fg_aligned16(C) && (!preact_out || fg_aligned16(preact_out)), "fg_gemm_lowp: outputs must be 16-byte aligned");
+    if (!ctx->tmap_encode) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "fg_gemm_lowp: tensor maps unavailable");
+    const uint32_t ldk = pad8(K);
+    const bool a_direct = in_place16(A, K);
+    const uint64_t need = (uint64_t)N * ldk * 2 + (a_direct ? 0 : (uint64_t)M * ldk * 2) + (uint64_t)N * 4 + kPairPartialBytes + 2048;
+    if (ctx->ws_bytes < need) {
+        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
+        if (s0 != FG_OK) return s0;
+    }
+    int32_t s;
+    void *bt, *ac = nullptr, *bias32 = nullptr;
+    if ((s = fg_ws_alloc(ctx, (uint64_t)N * ldk * 2, &bt)) != FG_OK) return s;
+    Prep16Args pb{};
+    pb.x = B; pb.R = K; pb.C = N; pb.t_out = bt; pb.ld_t = ldk;          // B [K,N] -> [N][K]
+    if ((s = launch_prep16(ctx, dtype, pb)) != FG_OK) return s;
+    const void* a_rows = A;
+    uint32_t lda = K;
+    if (!a_direct) {
+        if ((s = fg_ws_alloc(ctx, (uint64_t)M * ldk * 2, &ac)) != FG_OK) return s;
+        Prep16Args pa{};
+        pa.x = A; pa.R = M; pa.C = K; pa.n_out = ac; pa.ld_n = ldk;
+        if ((s = launch_prep16(ctx, dtype, pa)) != FG_OK) return s;
+        a_rows = ac;
+        lda = ldk;
+    }
+    if (bias) {
+        if ((s = fg_ws_alloc(ctx, (uint64_t)N * 4, &bias32)) != FG_OK) return s;
+        if ((s = fg_convert_launch(ctx, bias, dtype, bias32, FG_DTYPE_F32, N)) != FG_OK) return s;
+    }
+    return lowp_gemm(ctx, dtype, a_rows, lda, bt, ldk, M, N, K, C, (const float*)bias32, act, preact_out);
+}
+
+int32_t fg_gemm_bwd_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B,
+                         const void* dY, int32_t act, const void* saved, void* dA, void* dB, void* dbias) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, dtype == FG_DTYPE_F16 || dtype == FG_DTYPE_BF16, "fg_gemm_bwd_lowp: dtype must be f16 or bf16");
+    FG_REQUIRE(ctx, dY != nullptr, "fg_gemm_bwd_lowp: dY is NULL");
+    FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_bwd_lowp: dimensions must be >= 1");
+    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_bwd_lowp: unknown activation");
+    FG_REQUIRE(ctx, act == FG_ACT_NONE || saved, "fg_gemm_bwd_lowp: the activation backward needs the saved tensor");
+    FG_REQUIRE(ctx, !dA || B, "fg_gemm_bwd_lowp: dA needs B");
+    FG_REQUIRE(ctx, !dB || A, "fg_gemm_bwd_lowp: dB needs A");
+    FG_REQUIRE(ctx, (!dA || fg_aligned16(dA)) && (!dB || fg_aligned16(dB)), "fg_gemm_bwd_lowp: outputs must be 16-byte aligned");
+    if (!ctx->tmap_encode) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "fg_gemm_bwd_lowp: tensor maps unavailable");
+    const bool fuse = act != FG_ACT_NONE;
+    const uint32_t ldn = pad8(N), ldm = pad8(M);
+    const bool dz_direct = !fuse && in_place16(dY, N);       // dZ == dY, usable as the [M rows, N contiguous] operand
+    const bool b_direct = in_place16(B, N);
+    const uint32_t nchunk_rows = (M + 31) / 32;
+    uint64_t need = 4096 + 2 * kPairPartialBytes;
+    if (dA) need += (dz_direct ? 0 : (uint64_t)M * ldn * 2) + (b_direct ? 0 : (uint64_t)K * ldn * 2);
+    if (dB) need += (uint64_t)N * ldm * 2 + (uint64_t)K * ldm * 2;
+    if (dbias) need += (uint64_t)nchunk_rows * N * 4 + (uint64_t)N * 4 + 512;
+    if (ctx->ws_bytes < need) {
+        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
+        if (s0 != FG_OK) return s0;
+    }
+    int32_t s;
+    void *dz_n = nullptr, *dz_t = nullptr, *cs_part = nullptr;
+    Prep16Args pz{};
+    pz.x = dY; pz.saved = fuse ? saved : nullptr; pz.act = act; pz.R = M; pz.C = N;
+    if (dA && !dz_direct) {
+        if ((s = fg_ws_alloc(ctx, (uint64_t)M * ldn * 2, &dz_n)) != FG_OK) return s;
+        pz.n_out = dz_n; pz.ld_n = ldn;
+    }
+    if (dB) {
+        if ((s = fg_ws_alloc(ctx, (uint64_t)N * ldm * 2, &dz_t)) != FG_OK) return s;
+        pz.t_out = dz_t; pz.ld_t = ldm;
+    }
+    if (dbias) {
+        if ((s = fg_ws_alloc(ctx, (uint64_t)nchunk_rows * N * 4, &cs_part)) != FG_OK) return s;
+        pz.colsum_part = (float*)cs_part;
+    }
+    uint32_t cs_chunks = 0;
+    if (pz.n_out || pz.t_out || pz.colsum_part) {
+        if ((s = launch_prep16(ctx, dtype, pz, &cs_chunks)) != FG_OK) return s;
+    }
+    if (dB) {
+        // dB[K,N] = A^T · dZ: contraction over M; operands A^T [K][M] and dZ^T [N][M]
+        void* at;
+        if ((s = fg_ws_alloc(ctx, (uint64_t)K * ldm * 2, &at)) != FG_OK) return s;
+        Prep16Args pa{};
+        pa.x = A; pa.R = M; pa.C = K; pa.t_out = at; pa.ld_t = ldm;
+        if ((s = launch_prep16(ctx, dtype, pa)) != FG_OK) return s;
+        if ((s = lowp_gemm(ctx, dtype, at, ldm, dz_t, ldm, K, N, M, dB, nullptr, FG_ACT_NONE, nullptr)) != FG_OK) return s;
+    }
+    if (dbias) {
+        void* db32;
+        if ((s = fg_ws_alloc(ctx, (uint64_t)N * 4, &db32)) != FG_OK) return s;
+        if ((s = fg_colsum_fold_launch(ctx, N, cs_chunks, (const float*)cs_part, (float*)db32)) != FG_OK) return s;
+        if ((s = fg_convert_launch(ctx, db32, FG_DTYPE_F32, dbias, dtype, N)) != FG_OK) return s;
+    }
+    if (dA) {
+        // dA[M,K] = dZ · B^T: contraction over N; dZ [M][N] and B [K][N] both have it contiguous already
+        const void* b_rows = B;
+        uint32_t ldb = N;
+        if (!b_direct) {
+            void* bc;
+            if ((s = fg_ws_alloc(ctx, (uint64_t)K * ldn * 2, &bc)) != FG_OK) return s;
+            Prep16Args pb{};
+            pb.x = B; pb.R = K; pb.C = N; pb.n_out = bc; pb.ld_n = ldn;
+            if ((s = launch_prep16(ctx, dtype, pb)) != FG_OK) return s;
+            b_rows = bc;
+            ldb = ldn;
+        }
+        const void* z_rows = dz_direct ? dY : dz_n;
+        if ((s = lowp_gemm(ctx, dtype, z_rows, dz_direct ? N : ldn, b_rows, ldb, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr)) != FG_OK)
+            return s;
     }
     return FG_OK;
 }

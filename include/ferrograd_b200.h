@@ -298,6 +298,18 @@ int32_t fg_eltwise_chain_fwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg
 int32_t fg_eltwise_chain_bwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg_ew_instr* prog,
                                 int32_t ninstr, const void* const* inputs, int32_t ninputs,
                                 const void* seed, void* const* grads, int32_t accumulate);
+/* GEMM on f16 or bf16 tensors (all of A [M,K], B [K,N], C [M,N], bias [N], preact_out, and in the
+ * backward form dY, saved, dA, dB, dbias [N] have the storage type `dtype`): the tensor cores
+ * multiply the 16-bit operands directly (kind::f16) and accumulate in f32; bias and activation are
+ * applied in f32 and the result is rounded once to the storage type.  Semantics otherwise as
+ * fg_gemm_f32 / fg_gemm_bwd_f32; dZ = dY * act'(saved) is rounded to the storage type before the two
+ * products.  C, preact_out, dA and dB must be 16-byte aligned. */
+int32_t fg_gemm_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uint32_t K,
+                     const void* A, const void* B, void* C, const void* bias, int32_t act,
+                     void* preact_out);
+int32_t fg_gemm_bwd_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uint32_t K,
+                         const void* A, const void* B, const void* dY, int32_t act,
+                         const void* saved, void* dA, void* dB, void* dbias);
 /* dst[i] = src[i] converted between storage types (round to nearest even when narrowing). */
 int32_t fg_convert(fg_ctx* ctx, const void* src, int32_t src_dtype, void* dst, int32_t dst_dtype,
                    uint64_t n);

@@ -320,6 +320,55 @@ def test_chain_16bit_all_ops(ctx, oracle, dtype):
         check(down16(ctx, g, dtype), gr, 4 * tol, f"{dtype} chain bwd")
 
 
+LOWP_SHAPES = [(256, 256, 64), (512, 384, 1024), (300, 520, 1100),     # ragged: copies with padded pitch
+               (130, 10, 257), (1100, 264, 4100), (600, 712, 2304)]     # narrow N; long K; split-K tail
+
+
+def new16m(ctx, shape, dtype):
+    return ctx.new_tensor(shape, np.float16 if dtype == "f16" else np.uint16)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", LOWP_SHAPES)
+def test_gemm_16bit_storage(ctx, oracle, dtype, M, N, K):
+    # products of 16-bit values are exact in f32, so against a float64 accumulation the only visible error
+    # is the final rounding to the storage type (half a unit in the last place: 2^-11 / 2^-8 relative)
+    tol = 2.0 ** -10 if dtype == "f16" else 2.0 ** -7
+    r = rng(M + 3 * N + 7 * K)
+    A = oracle.round_to(r.standard_normal((M, K), np.float32), dtype)
+    B = oracle.round_to(r.standard_normal((K, N), np.float32) / np.sqrt(K), dtype)
+    bias = oracle.round_to(r.standard_normal(N, np.float32), dtype)
+    Cd, Pd = new16m(ctx, (M, N), dtype), new16m(ctx, (M, N), dtype)
+    ctx.gemm_lowp(up16(ctx, A, dtype), up16(ctx, B, dtype), Cd, M, N, K, dtype, bias=up16(ctx, bias, dtype), act="tanh",
+                  preact_out=Pd)
+    assert ctx.device_status() == 0
+    y, pre = oracle.bias_act_fwd(oracle.gemm(A, B, f64=True), bias, "tanh")
+    check(down16(ctx, Pd, dtype), pre, tol, f"{dtype} pre-activation")
+    check(down16(ctx, Cd, dtype), y, tol, f"{dtype} output")
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K,act", [(256, 384, 512, "none"), (300, 264, 200, "tanh"), (520, 130, 1000, "gelu"),
+                                       (1024, 512, 768, "relu")])
+def test_gemm_16bit_storage_backward(ctx, oracle, dtype, M, N, K, act):
+    tol = 2.0 ** -10 if dtype == "f16" else 2.0 ** -7
+    r = rng(M + N + K)
+    A = oracle.round_to(r.standard_normal((M, K), np.float32), dtype)
+    B = oracle.round_to(r.standard_normal((K, N), np.float32) / np.sqrt(K), dtype)
+    bias = oracle.round_to(r.standard_normal(N, np.float32) * 0.1, dtype)
+    y, pre = oracle.bias_act_fwd(oracle.gemm(A, B, f64=True), bias, act)
+    saved = oracle.round_to(pre if act == "gelu" else y, dtype)
+    dY = oracle.round_to(r.standard_normal((M, N), np.float32), dtype)
+    dA, dB, db = new16m(ctx, (M, K), dtype), new16m(ctx, (K, N), dtype), new16m(ctx, (N,), dtype)
+    ctx.gemm_bwd_lowp(up16(ctx, A, dtype), up16(ctx, B, dtype), up16(ctx, dY, dtype), M, N, K, dtype, act=act,
+                      saved=up16(ctx, saved, dtype) if act != "none" else None, dA=dA, dB=dB, dbias=db)
+    assert ctx.device_status() == 0
+    dz = oracle.round_to(oracle.act_bwd(dY, saved, act), dtype)      # dZ is rounded to the storage type
+    check(down16(ctx, dA, dtype), oracle.gemm(dz, B, transB=True, f64=True), tol, f"{dtype} dA")
+    check(down16(ctx, dB, dtype), oracle.gemm(A, dz, transA=True, f64=True), tol, f"{dtype} dB")
+    check(down16(ctx, db, dtype), dz.astype(np.float64).sum(axis=0), 2 * tol, f"{dtype} dbias")
+
+
 # ---------------------------------------------------------------- GEMM
 GEMM_SHAPES = [(32, 64, 16), (1, 1, 1), (64, 2, 16), (70, 33, 45), (130, 257, 100), (256, 512, 384)]
 
