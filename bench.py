@@ -237,6 +237,22 @@ def _kernel_lines(torch, stream, ctx, peaks):
                                           "frac_of_3xtf32_peak": work / ms / 1e9 / tf32x3_burst,
                                           "call_ms_with_prepass": e_ms,
                                           "call_tflops_with_prepass": 4.0 * N ** 3 / e_ms / 1e9}
+    # the same shape on bf16 tensors: 16-bit operands go to the tensor cores as they are (kind::f16)
+    del dC, dA, dB
+    A16, B16, C16 = A.to(torch.bfloat16), B.to(torch.bfloat16), torch.empty(N, N, device="cuda", dtype=torch.bfloat16)
+    b16 = bias.to(torch.bfloat16)
+    torch.cuda.synchronize()
+    f16 = lambda: ctx.gemm_lowp(A16.data_ptr(), B16.data_ptr(), C16.data_ptr(), N, N, N, "bf16", bias=b16.data_ptr(),
+                                act="relu")
+    f16(); f16()
+    ctx.timing_read("gemm_tc")
+    e_ms = timed(torch, stream, ctx, lambda i: f16(), 5) / 5
+    n, ms, work = ctx.timing_read("gemm_tc")
+    out["gemm_c3_fwd_bf16_storage"] = {"mode": "bf16 tensors, kind::f16 MMA, f32 accumulate", "kernel_ms": ms / n,
+                                       "kernel_tflops": work / ms / 1e9,
+                                       "frac_of_bf16_peak": work / ms / 1e9 / peaks["bf16_tflops"],
+                                       "call_ms_with_transpose": e_ms,
+                                       "call_tflops_with_transpose": 2.0 * N ** 3 / e_ms / 1e9}
     out["peak_note"] = ("tensor peaks derive from the measured bf16 burst: TF32 runs at half the bf16 rate; the 3xTF32 "
                         "peak is that / 3, the default mode's own peak that / 2; bandwidth fractions are of the measured "
                         "copy bandwidth")

@@ -163,8 +163,8 @@ int32_t lower(fg_exec* e) {
     const int N = (int)g.nodes.size();
     e->n.assign(N, ENode());
     e->last = N - 1;
-    // ---- storage type: one per graph.  16-bit graphs run their elementwise regions in that type; ----
-    // ---- matmul, softmax, the losses and the optimizers are f32-only here.                      ----
+    // ---- storage type: one per graph.  16-bit graphs run their elementwise regions and matmuls in ----
+    // ---- that type (f32 accumulation); softmax, the losses and AdamW are f32-only.               ----
     {
         int dt = -1;
         for (const GNode& gn : g.nodes) {
@@ -176,8 +176,8 @@ int32_t lower(fg_exec* e) {
         e->esize = e->dtype == FG_DTYPE_F32 ? 4 : 2;
         if (e->dtype != FG_DTYPE_F32)
             for (const GNode& gn : g.nodes)
-                if (gn.op == OP_MATMUL || gn.op == OP_SOFTMAX)
-                    return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: matmul and softmax need f32 storage");
+                if (gn.op == OP_SOFTMAX)
+                    return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: softmax needs f32 storage");
     }
     // ---- shapes (the reference's validate: backend/mod.rs:854-975) ----
     for (int i = 0; i < N; ++i) {
@@ -449,10 +449,19 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
             const GemmStep& gs = e->gemms[st.idx];
             const size_t sa = (size_t)gs.M * gs.K, sb = (size_t)gs.K * gs.N, sc = (size_t)gs.M * gs.N;
             s = FG_OK;
-            for (uint32_t t = 0; t < gs.batch && s == FG_OK; ++t)
+            for (uint32_t t = 0; t < gs.batch && s == FG_OK; ++t) {
+                if (e->dtype != FG_DTYPE_F32) {
+                    char* const pa = (char*)vptr(e, gs.a) + t * sa * 2;
+                    char* const pb = (char*)vptr(e, gs.b) + t * sb * 2;
+                    s = fg_gemm_lowp(e->ctx, e->dtype, gs.M, gs.N, gs.K, pa, pb, (char*)vptr(e, gs.out) + t * sc * 2,
+                                     gs.bias >= 0 ? vptr(e, gs.bias) : nullptr, gs.act,
+                                     gs.preact ? (char*)gs.preact->ptr + t * sc * 2 : nullptr);
+                    continue;
+                }
                 s = fg_gemm_f32(e->ctx, e->gemm_mode, 0, 0, gs.M, gs.N, gs.K, vptr(e, gs.a) + t * sa, vptr(e, gs.b) + t * sb,
                                 vptr(e, gs.out) + t * sc, gs.bias >= 0 ? vptr(e, gs.bias) : nullptr, gs.act,
                                 gs.preact ? (float*)gs.preact->ptr + t * sc : nullptr);
+            }
         } else if (st.kind == 1) {
             const ChainStep& c = e->chains[st.idx];
             const float* in[FG_EW_MAX_INPUTS];
@@ -492,12 +501,23 @@ int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
                            (float*)e->seed->ptr);
 }
 
+// The backward of one matmul in the graph's storage type.
+static int32_t gemm_bwd_any(fg_exec* e, uint32_t M, uint32_t N, uint32_t K, const void* A, const void* B, const void* dY, int act,
+                            const void* saved, void* dA, void* dB, void* dbias) {
+    if (e->dtype == FG_DTYPE_F32)
+        return fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, N, K, (const float*)A, (const float*)B, (const float*)dY, act,
+                               (const float*)saved, (float*)dA, (float*)dB, (float*)dbias, nullptr);
+    return fg_gemm_bwd_lowp(e->ctx, e->dtype, M, N, K, A, B, dY, act, saved, dA, dB, dbias);
+}
+
 int32_t fg_exec_dispatch_backward(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_backward: bind the input tensors first");
     const int N = (int)e->n.size();
     std::vector<uint8_t> written(N, 0);
     auto grad_of = [&](int node) -> float* { return node == e->last ? (float*)e->seed->ptr : gptr(e, node); };
+    // a tensor's t-th matrix: offsets are in elements of the graph's storage type
+    auto off = [&](const void* p, size_t elems) -> float* { return (float*)((char*)p + elems * e->esize); };
     int32_t s;
     for (int k = (int)e->fwd.size() - 1; k >= 0; --k) {
         const Step& st = e->fwd[k];
@@ -513,10 +533,10 @@ int32_t fg_exec_dispatch_backward(fg_exec* e) {
                 // one product per Z index: every operand, gradient and saved tensor is stepped by one matrix
                 auto run = [&](float* da_dst, float* db_dst) -> int32_t {
                     for (uint32_t t = 0; t < gs.batch; ++t) {
-                        int32_t r = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a) + t * sa, vptr(e, gs.b) + t * sb,
-                                                    grad_of(gs.out) + t * sc, gs.act, saved ? saved + t * sc : nullptr,
-                                                    da_dst ? da_dst + t * sa : nullptr, db_dst ? db_dst + t * sb : nullptr,
-                                                    nullptr, nullptr);
+                        int32_t r = gemm_bwd_any(e, M, Nn, K, off(vptr(e, gs.a), t * sa), off(vptr(e, gs.b), t * sb),
+                                                 off(grad_of(gs.out), t * sc), gs.act, saved ? off(saved, t * sc) : nullptr,
+                                                 da_dst ? off(da_dst, t * sa) : nullptr, db_dst ? off(db_dst, t * sb) : nullptr,
+                                                 nullptr);
                         if (r != FG_OK) return r;
                     }
                     return FG_OK;
@@ -540,23 +560,21 @@ int32_t fg_exec_dispatch_backward(fg_exec* e) {
             if (gs.bias >= 0 && written[gs.bias]) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: a bias used by two layers");
             if (!written[gs.a] && !written[gs.b] && gs.a != gs.b) {
                 // the common case: one call computes dZ once and both products from it
-                s = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act,
-                                    saved, gptr(e, gs.a), gptr(e, gs.b), dbias, nullptr);
+                s = gemm_bwd_any(e, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved, gptr(e, gs.a),
+                                 gptr(e, gs.b), dbias);
                 if (s != FG_OK) return s;
                 written[gs.a] = written[gs.b] = 1;
                 if (gs.bias >= 0) written[gs.bias] = 1;
                 continue;
             }
             // dA first (it may need the scratch tensor), then dB
-            s = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved,
-                                dA, nullptr, dbias, nullptr);
+            s = gemm_bwd_any(e, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved, dA, nullptr, dbias);
             if (s != FG_OK) return s;
             if (written[gs.a] && (s = accumulate_into(e, gs.a, dA)) != FG_OK) return s;
             written[gs.a] = 1;
             if (gs.bias >= 0) written[gs.bias] = 1;
             float* dB = written[gs.b] ? (float*)e->tmp->ptr : gptr(e, gs.b);
-            s = fg_gemm_bwd_f32(e->ctx, e->gemm_mode, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved,
-                                nullptr, dB, nullptr, nullptr);
+            s = gemm_bwd_any(e, M, Nn, K, vptr(e, gs.a), vptr(e, gs.b), grad_of(gs.out), gs.act, saved, nullptr, dB, nullptr);
             if (s != FG_OK) return s;
             if (written[gs.b] && (s = accumulate_into(e, gs.b, dB)) != FG_OK) return s;
             written[gs.b] = 1;

@@ -254,14 +254,60 @@ def test_mul_add_f16(ctx, dtype):
     t.destroy()
 
 
-def test_16bit_graph_rejects_matmul(ctx):
+def test_16bit_graph_rejects_softmax(ctx):
     from ferrograd_b200 import FgError, SimpleDType
 
     def define(g, m):
         a = g.input([m, m], SimpleDType.F16)
-        g.matmul(a, a)
+        g.softmax(a)
     with pytest.raises(FgError):
         build(ctx, define, [32])
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_16bit_dense_layer_graph(ctx, oracle, dtype):
+    """tanh(x @ W + b) with every tensor stored in 16 bits: the fused GEMM runs on the 16-bit operands with f32
+    accumulation; outputs and gradients are rounded once to the storage type."""
+    from ferrograd_b200 import SimpleDType
+    from ferrograd_b200.backend import from_bf16_bits, to_bf16_bits
+    sd = SimpleDType.F16 if dtype == "f16" else SimpleDType.BF16
+    tol = 2.0 ** -10 if dtype == "f16" else 2.0 ** -7
+    Bn, I, O = 64, 40, 72
+    r = np.random.Generator(np.random.Philox(55))
+    x = oracle.round_to(r.standard_normal((Bn, I), np.float32), dtype)
+    W = oracle.round_to(r.standard_normal((I, O), np.float32) * 0.2, dtype)
+    b = oracle.round_to(r.standard_normal(O, np.float32) * 0.1, dtype)
+    seed = oracle.round_to(r.standard_normal((Bn, O), np.float32), dtype)
+
+    def define(g, fb, fi, fo):
+        xi, w, bb = g.input([fb, fi], sd), g.input([fi, fo], sd), g.input([fo], sd)
+        g.tanh(g.add(g.matmul(xi, w), bb))
+    graph, t, kernels, binding = build(ctx, define, [Bn, I, O])
+    assert t.forward_steps() == 1
+    init = ctx.init_tensor_f16 if dtype == "f16" else ctx.init_tensor_bf16
+    enc = (lambda a: a.astype(np.float16)) if dtype == "f16" else to_bf16_bits
+    dec = (lambda a: a.astype(np.float32)) if dtype == "f16" else from_bf16_bits
+    ins = [init(a.shape, a) for a in (x, W, b)]
+    ctx.upload(t.seed, enc(seed))
+    sch = ctx.schedule(kernels, binding, ins, t, [], ())
+    ctx.dispatch_forward(sch)
+    ctx.dispatch_backward(sch)
+    ctx.sync()
+    raw = np.float16 if dtype == "f16" else np.uint16
+    get = lambda buf, shape: dec(ctx.download(buf, np.empty(shape, raw)))
+    y, _ = oracle.bias_act_fwd(oracle.gemm(x, W, f64=True), b, "tanh")
+    y16 = oracle.round_to(y, dtype)
+    ok, worst = rel_err_ok(get(t.forward_out, (Bn, O)), y, tol)
+    assert ok, f"output: {worst:.3g} x {tol}"
+    dz = oracle.round_to(oracle.act_bwd(seed, get(t.forward_out, (Bn, O)), "tanh"), dtype)
+    grads = {n: t.grad_tensors[i] for i, n in enumerate(t.grad_nodes)}
+    for got, ref, what in ((get(grads[0], (Bn, I)), oracle.gemm(dz, W, transB=True, f64=True), "dx"),
+                           (get(grads[1], (I, O)), oracle.gemm(x, dz, transA=True, f64=True), "dW"),
+                           (get(grads[2], (O,)), dz.astype(np.float64).sum(axis=0), "db")):
+        ok, worst = rel_err_ok(got, ref, 2 * tol)
+        assert ok, f"{what}: {worst:.3g} x {2 * tol}"
+    assert y16.shape == (Bn, O)
+    t.destroy()
 
 
 # ---------------------------------------------------------------- beyond the reference's tests
