@@ -404,3 +404,9 @@ class GpuContext:
 
     def comm_join(self):
         self._check(self.lib.fg_comm_join(self.handle))
+
+    def comm_checkpoint(self, slot):
+        self._check(self.lib.fg_comm_checkpoint(self.handle, slot))
+
+    def comm_wait(self, slot):
+        self._check(self.lib.fg_comm_wait(self.handle, slot))

@@ -59,6 +59,12 @@ int32_t fg_ws_alloc(fg_ctx* ctx, uint64_t bytes, void** out) {
     return FG_OK;
 }
 
+static bool create_events(cudaEvent_t* ev, int n) {
+    for (int i = 0; i < n; ++i)
+        if (cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) return false;
+    return true;
+}
+
 extern "C" {
 
 const char* fg_version(void) { return "ferrograd_b200 0.1 (sm_100a)"; }
@@ -94,6 +100,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
         cudaEventCreateWithFlags(&c->ev_main_mark, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        !create_events(c->ev_ckpt, 8) ||
         cudaMalloc((void**)&c->dev_status, 256) != cudaSuccess ||
         cudaMemset(c->dev_status, 0, 256) != cudaSuccess) {
         delete c;
@@ -124,6 +131,7 @@ int32_t fg_ctx_destroy(fg_ctx* ctx) {
     }
     cudaEventDestroy(ctx->ev_fork);
     cudaEventDestroy(ctx->ev_join);
+    for (cudaEvent_t ev : ctx->ev_ckpt) if (ev) cudaEventDestroy(ev);
     cudaStreamDestroy(ctx->comm_stream);
     cudaStreamSynchronize(ctx->copy_stream);
     cudaStreamDestroy(ctx->copy_stream);
@@ -498,6 +506,25 @@ int32_t fg_allreduce_sum_f32(fg_ctx* ctx, float* buf, uint64_t count) {
     }
     ctx->comm_pending = true;
     if (ctx->capturing) ctx->capture_launches++; else ctx->launches++;
+    return FG_OK;
+}
+
+// A checkpoint marks "every exchange started so far"; fg_comm_wait makes the compute stream wait for
+// just those, so work that needs only the early exchanges (the update of the last layers) can run while
+// a later exchange (the first layer's) is still in flight.
+int32_t fg_comm_checkpoint(fg_ctx* ctx, int32_t slot) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, slot >= 0 && slot < 8, "fg_comm_checkpoint: slot outside [0, 8)");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_ckpt[slot], ctx->comm_stream));
+    return FG_OK;
+}
+
+int32_t fg_comm_wait(fg_ctx* ctx, int32_t slot) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, slot >= 0 && slot < 8, "fg_comm_wait: slot outside [0, 8)");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->stream, ctx->ev_ckpt[slot], 0));
     return FG_OK;
 }
 

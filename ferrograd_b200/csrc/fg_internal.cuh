@@ -38,6 +38,7 @@ struct fg_ctx {
     cudaStream_t comm_stream;
     cudaEvent_t ev_fork, ev_join;
     bool comm_pending;
+    cudaEvent_t ev_ckpt[8];             // exchange checkpoints (fg_comm_checkpoint / fg_comm_wait)
     int comm_reserved_sms;              // SMs the persistent GEMM leaves free while an exchange is in flight
     cudaStream_t copy_stream;           // host->device prefetches that overlap compute
     cudaEvent_t ev_copy_done, ev_main_mark;

@@ -179,6 +179,7 @@ class MLPTrainer:
         # A layer's gradients wait for the next layer's when they are small (a 10-class head is not worth a
         # launch, and the GEMMs give up SMs while an exchange is in flight).
         pend_hi = self.n_arena
+        exchanged = []      # (lo, hi, checkpoint slot) of every exchange, in issue order
         for l in range(L - 1, -1, -1):
             a = self.act if l < L - 1 else "none"
             saved = None if a == "none" else (self.pre_buf[l] if a == "gelu" else self.act_buf[l + 1])
@@ -190,21 +191,41 @@ class MLPTrainer:
                 # weight and bias gradients first; their exchange runs beside this layer's dX GEMM and the
                 # backward of the layers below
                 c.gemm_bwd_exchange(*args, self.grads.ptr + 4 * lo, pend_hi - lo, **kw)
+                if len(exchanged) < 7:
+                    c.comm_checkpoint(len(exchanged))
+                    exchanged.append((lo, pend_hi, len(exchanged)))
+                else:                                   # out of checkpoint slots: this range waits for the join
+                    exchanged.append((lo, pend_hi, -1))
                 pend_hi = lo
             else:
                 c.gemm_bwd(*args, **kw)
+        # gradients were computed with the global-mean scale, so the sum over ranks needs no further factor
+        if self.opt[0] == "adamw":
+            c.counter_increment(self.step_counter)
+        if self.world > 1 and self.overlap and len(exchanged) > 1 and all(s >= 0 for _, _, s in exchanged):
+            # update each exchanged range as soon as its own exchange is complete: the last layers' update
+            # runs while the first layer's gradients are still on the wire
+            for lo, hi, slot in exchanged[:-1]:
+                c.comm_wait(slot)
+                self._update(lo, hi)
+            c.comm_join()
+            self._update(*exchanged[-1][:2])
+            return
         if self.world > 1:
             if not self.overlap:
                 c.allreduce_sum(self.grads, self.n_arena)
             c.comm_join()
-        # gradients were computed with the global-mean scale, so the sum over ranks needs no further factor
+        self._update(0, self.n_arena)
+
+    def _update(self, lo, hi):
+        """The optimizer step on arena elements [lo, hi)."""
+        c, off, n = self.ctx, 4 * lo, hi - lo
         if self.opt[0] == "adamw":
             _, lr, b1, b2, eps, wd = self.opt
-            c.counter_increment(self.step_counter)
-            c.adamw_step(self.params, self.grads, self.m, self.v, self.n_arena, lr, b1, b2, eps, wd, step=0,
-                         step_dev=self.step_counter, zero_grad=False)
+            c.adamw_step(self.params.ptr + off, self.grads.ptr + off, self.m.ptr + off, self.v.ptr + off, n, lr, b1, b2,
+                         eps, wd, step=0, step_dev=self.step_counter, zero_grad=False)
         elif self.opt[0] == "sgd":
-            c.sgd_step(self.params, self.grads, self.n_arena, self.opt[1], zero_grad=False)
+            c.sgd_step(self.params.ptr + off, self.grads.ptr + off, n, self.opt[1], zero_grad=False)
 
     def step(self):
         """Eager step (one launch per kernel)."""

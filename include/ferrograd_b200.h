@@ -400,6 +400,11 @@ int32_t fg_comm_init(fg_ctx* ctx, int32_t nranks, int32_t rank, const uint8_t id
  * enqueued afterwards, until fg_comm_join. */
 int32_t fg_allreduce_sum_f32(fg_ctx* ctx, float* buf, uint64_t count);
 int32_t fg_comm_join(fg_ctx* ctx);
+/* fg_comm_checkpoint(slot) marks the exchanges started so far (slot in [0, 8));
+ * fg_comm_wait(slot) makes the compute stream wait for exactly those.  Work that needs only the early
+ * exchanges (the update of the last layers) can then run while a later one is still in flight. */
+int32_t fg_comm_checkpoint(fg_ctx* ctx, int32_t slot);
+int32_t fg_comm_wait(fg_ctx* ctx, int32_t slot);
 int32_t fg_comm_destroy(fg_ctx* ctx);
 
 /* Library / build information. */
