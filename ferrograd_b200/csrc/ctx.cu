@@ -5,6 +5,7 @@
 // crates/fused_gpu/src/dispatch/backend/rocm/mod.rs:58-421): one device, one stream,
 // synchronous upload/download, asynchronous dispatch, schedules as captured graphs.
 #include <dlfcn.h>
+#include <limits.h>
 
 #include <new>
 
@@ -16,6 +17,17 @@ namespace {
 typedef struct { char internal[FG_COMM_ID_BYTES]; } nccl_uid;
 typedef int (*pfn_ncclGetUniqueId)(nccl_uid*);
 typedef int (*pfn_ncclCommInitRank)(void**, int, nccl_uid, int);
+// ncclCommInitRankConfig with the communicator options as they were laid out in NCCL 2.18; newer
+// libraries accept an older, shorter structure (they go by its size and version fields) and default the rest.
+struct nccl_config_2_18 {
+    size_t size;
+    unsigned int magic, version;
+    int blocking, cgaClusterSize, minCTAs, maxCTAs;
+    const char* netName;
+    int splitShare;
+};
+typedef int (*pfn_ncclCommInitRankConfig)(void**, int, nccl_uid, int, nccl_config_2_18*);
+typedef int (*pfn_ncclGetVersion)(int*);
 typedef int (*pfn_ncclAllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*pfn_ncclCommDestroy)(void*);
 typedef const char* (*pfn_ncclGetErrorString)(int);
@@ -467,15 +479,40 @@ int32_t fg_comm_init(fg_ctx* ctx, int32_t nranks, int32_t rank, const uint8_t id
     // An exchange CTA and a GEMM CTA cannot share an SM (registers, shared memory), and the pair GEMM is
     // persistent: if it took every SM the exchange would start only when it ended, and if the exchange
     // took some first the GEMM's last CTAs would start late with a full share of tiles.  So the exchange
-    // is held to 16 CTAs (unless the caller's environment says otherwise) and the GEMM leaves 20 SMs free
-    // while one is in flight.  FG_COMM_SMS overrides the number; 0 turns the reservation off.
-    setenv("NCCL_MAX_CTAS", "16", 0);
-    ctx->comm_reserved_sms = 20;
+    // is held to 12 CTAs (unless the caller's environment says otherwise) and the GEMM leaves 16 SMs free
+    // while one is in flight.  FG_COMM_SMS overrides the number; 0 turns the reservation off.  Measured on
+    // two GPUs (config-4 step, ms): 12 CTAs / 16 SMs 2.04, 8 / 12 2.03-2.07, 16 / 20 2.12, 4 / 8 2.42
+    // (exchange-bound), no reservation 2.15-2.18; one GPU alone 1.96-2.00.
+    // The limit is given in the communicator's own options: NCCL reads its environment once per process,
+    // so a variable set here would be missed whenever another communicator (the host framework's) came first.
+    int max_ctas = 12;
+    if (const char* e = getenv("NCCL_MAX_CTAS")) max_ctas = atoi(e);
+    ctx->comm_reserved_sms = 16;
     if (const char* e = getenv("FG_COMM_SMS")) ctx->comm_reserved_sms = atoi(e);
     if (ctx->comm_reserved_sms < 0 || ctx->comm_reserved_sms > ctx->sm_count / 2) ctx->comm_reserved_sms = 0;
+    auto init_cfg = (pfn_ncclCommInitRankConfig)dlsym(ctx->nccl_lib, "ncclCommInitRankConfig");
+    auto get_ver = (pfn_ncclGetVersion)dlsym(ctx->nccl_lib, "ncclGetVersion");
+    int nccl_ver = 0;
+    if (get_ver) get_ver(&nccl_ver);
     nccl_uid uid;
     memcpy(uid.internal, id, FG_COMM_ID_BYTES);
-    int r = init(&ctx->comm, nranks, uid, rank);
+    int r = -1;
+    if (init_cfg && nccl_ver >= 21800 && max_ctas >= 1) {
+        nccl_config_2_18 cfg;
+        cfg.size = sizeof(cfg);
+        cfg.magic = 0xcafebeef;
+        cfg.version = 21800;
+        cfg.blocking = 1;
+        cfg.cgaClusterSize = INT_MIN;      // INT_MIN / NULL: "not set"
+        cfg.minCTAs = INT_MIN;
+        cfg.maxCTAs = max_ctas;
+        cfg.netName = nullptr;
+        cfg.splitShare = INT_MIN;
+        r = init_cfg(&ctx->comm, nranks, uid, rank, &cfg);
+    } else {
+        r = init(&ctx->comm, nranks, uid, rank);
+        ctx->comm_reserved_sms = 0;        // the exchange's CTA count is not under control: no reservation
+    }
     if (r != 0) {
         auto es = (pfn_ncclGetErrorString)dlsym(ctx->nccl_lib, "ncclGetErrorString");
         snprintf(ctx->err, sizeof(ctx->err), "ncclCommInitRank: %s", es ? es(r) : "error");
