@@ -2,7 +2,7 @@
 than the 126 MB L2 so DRAM counters mean something, but well under a few GB on the device
 and only a handful of launches.
 
-    python -m ferrograd_b200.cases gemm|gemm_bwd|softmax_ce|adamw|sgd|split|mlp [--iters N]
+    python -m ferrograd_b200.cases gemm|gemm_bwd|gemm_bf16|softmax_ce|adamw|sgd|mlp [--iters N]
 """
 import argparse
 import sys
@@ -15,7 +15,7 @@ from .mlp import MLPTrainer
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_bwd", "softmax_ce", "adamw", "sgd", "mlp"])
+    ap.add_argument("case", choices=["gemm", "gemm_bwd", "gemm_bf16", "softmax_ce", "adamw", "sgd", "mlp"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--n", type=int, default=0, help="override the problem size")
     ap.add_argument("--mode", default="auto", choices=["auto", "simt", "3xtf32", "tf32_bf16x2"], help="GEMM mode")
@@ -37,6 +37,14 @@ def main():
             dA, dB = ctx.new_tensor((n, n)), ctx.new_tensor((n, n))
             for _ in range(a.iters):
                 ctx.gemm_bwd(A, B, dY, n, n, n, act="relu", saved=Cm, dA=dA, dB=dB, mode=a.mode)
+    elif a.case == "gemm_bf16":
+        n = a.n or 8192
+        A = ctx.init_tensor_bf16((n, n), r.standard_normal((n, n), np.float32) / np.float32(n ** 0.5))
+        B = ctx.init_tensor_bf16((n, n), r.standard_normal((n, n), np.float32) / np.float32(n ** 0.5))
+        bias = ctx.init_tensor_bf16((n,), r.standard_normal(n, np.float32))
+        Cm = ctx.new_tensor((n, n), np.uint16)
+        for _ in range(a.iters):
+            ctx.gemm_lowp(A, B, Cm, n, n, n, "bf16", bias=bias, act="relu")
     elif a.case == "softmax_ce":
         rows, cols = a.n or 2048, 32000
         x = ctx.init_tensor_f32((rows, cols), 2.0 * r.standard_normal((rows, cols), np.float32))

@@ -353,11 +353,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // ------------------------------------------------------------------------------------
 constexpr long long kPairWaitCycles = 400000000LL;   // about 0.2 s
 
-template <int BK>
+template <int BK, int FMT>
 struct PairCfg {
     static constexpr int kBN = 256;
-    static constexpr int kABytes = 2 * BM * BK * 4;          // this CTA's 128 rows of A: hi + lo (or f32 + bf16 pair)
-    static constexpr int kBBytes = 2 * (kBN / 2) * BK * 4;   // this CTA's half of the B tile
+    static constexpr int kPlanes = FMT >= 2 ? 1 : 2;         // 16-bit operands are loaded as they are: one 128-byte row
+    static constexpr int kABytes = kPlanes * BM * BK * 4;          // this CTA's 128 rows of A: hi + lo (or f32 + bf16 pair)
+    static constexpr int kBBytes = kPlanes * (kBN / 2) * BK * 4;   // this CTA's half of the B tile
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
     static constexpr int kStoreBytes = 8 * 32 * 33 * 4;       // the epilogue warps' transpose buffers
@@ -381,7 +382,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr bool kDirect16 = FMT >= 2;
     constexpr uint32_t KBE = kDirect16 ? 2 * BK : BK;            // values of k per k-block
     constexpr uint32_t kChunk = kDirect16 ? 1024 : kChunkK;      // 16-bit results tolerate the longer chain
-    using Cfg = PairCfg<BK>;
+    using Cfg = PairCfg<BK, FMT>;
     constexpr int BN = Cfg::kBN, HB = BN / 2;
     constexpr int S = Cfg::kStages;
     constexpr int CPT = BN / 2;
@@ -463,7 +464,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const uint32_t lf = map_to_cta(full_bar(s), 0);
                     const uint32_t sa = base + s * Cfg::kStageBytes;
                     if (kDirect16) {
-                        if (leader) mbar_expect_tx(full_bar(s), 2 * (BM + HB) * BK * 4);   // both CTAs' bytes
+                        if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
                         tma_load_3d_pair(sa, &tmA16, lf, (int)(kb * KBE), (int)m0, 0);
                         tma_load_3d_pair(sa + Cfg::kABytes, &tmB16, lf, (int)(kb * KBE), (int)nb0, 0);
                         continue;
@@ -974,7 +975,7 @@ constexpr uint64_t kPairPartialBytes = 80ull * (2 * BM) * 256 * 4 + 256;
 template <int BK, int FMT>
 int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilogue& ep_in) {
     Epilogue ep = ep_in;
-    using Cfg = PairCfg<BK>;
+    using Cfg = PairCfg<BK, FMT>;
     CUtensorMap tmA, tmB, tmA16, tmB16;
     int32_t s;
     constexpr bool kDirect16 = FMT >= 2;
