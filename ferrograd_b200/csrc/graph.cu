@@ -23,7 +23,10 @@
 // loss is not differentiated a second time (the loss kernel's p - onehot already is dL/dlogits;
 // the reference pushes it through the softmax backward again, dispatch/mod.rs:713-718); shapes
 // need not be multiples of 16; `add` accepts a bias of shape [N] or [1,N] after a matmul.
+#include <stdlib.h>
+
 #include <algorithm>
+#include <functional>
 #include <new>
 #include <vector>
 
@@ -106,6 +109,13 @@ struct fg_exec {
     int last;                       // output node
     int dtype = FG_DTYPE_F32;       // storage type of every tensor of the graph
     uint64_t esize = 4;
+    // Each dispatch_* is recorded as a CUDA graph on its second call and replayed from then on (the
+    // reference's Schedule is a captured hipGraph: rocm/mod.rs:324-389).  0 forward, 1 loss, 2 backward, 3 optim.
+    fg_plan* plan[4] = {nullptr, nullptr, nullptr, nullptr};
+    int calls[4] = {0, 0, 0, 0};
+    const void* plan_key[4] = {nullptr, nullptr, nullptr, nullptr};   // loss: the target buffer
+    const void* plan_ws[4] = {nullptr, nullptr, nullptr, nullptr};    // scratch arena the plan was recorded against
+    bool use_plans = true;
     bool ce_softmax_tail = false;   // graph ends in softmax and the loss is cross-entropy
 };
 
@@ -337,6 +347,14 @@ int32_t accumulate_into(fg_exec* e, int node, const float* src) {
                                    nullptr);
 }
 
+void drop_plans(fg_exec* e) {
+    for (int k = 0; k < 4; ++k) {
+        if (e->plan[k]) fg_plan_destroy(e->plan[k]);
+        e->plan[k] = nullptr;
+        e->calls[k] = 0;
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -415,6 +433,7 @@ int32_t fg_exec_destroy(fg_exec* e) {
     for (fg_buf* b : e->m) fg_free(e->ctx, b);
     for (fg_buf* b : e->v) fg_free(e->ctx, b);
     for (fg_buf* b : {e->seed, e->loss_t, e->tmp, e->step_counter}) if (b) fg_free(e->ctx, b);
+    drop_plans(e);
     delete e;
     return FG_OK;
 }
@@ -437,12 +456,11 @@ int32_t fg_exec_bind(fg_exec* e, fg_buf* const* in_tensors, uint32_t count, cons
     e->trainable.assign(count, 1);
     if (trainable) e->trainable.assign(trainable, trainable + count);
     e->bound = true;
+    drop_plans(e);        // recorded against the previous tensors
     return FG_OK;
 }
 
-int32_t fg_exec_dispatch_forward(fg_exec* e) {
-    if (!e) return FG_ERR_NOT_INITIALIZED;
-    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_forward: bind the input tensors first");
+static int32_t forward_eager(fg_exec* e) {
     int32_t s;
     for (const Step& st : e->fwd) {
         if (st.kind == 0) {
@@ -478,11 +496,7 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
     return FG_OK;
 }
 
-int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
-    if (!e) return FG_ERR_NOT_INITIALIZED;
-    if (e->dtype != FG_DTYPE_F32) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "dispatch_loss: the losses need f32 storage");
-    FG_REQUIRE(e->ctx, target != nullptr, "dispatch_loss: target is NULL");
-    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_loss: bind the input tensors first");
+static int32_t loss_eager(fg_exec* e, const fg_buf* target) {
     const ENode& o = e->n[e->last];
     if (e->g.loss == FG_LOSS_MSE) {
         FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
@@ -510,9 +524,7 @@ static int32_t gemm_bwd_any(fg_exec* e, uint32_t M, uint32_t N, uint32_t K, cons
     return fg_gemm_bwd_lowp(e->ctx, e->dtype, M, N, K, A, B, dY, act, saved, dA, dB, dbias);
 }
 
-int32_t fg_exec_dispatch_backward(fg_exec* e) {
-    if (!e) return FG_ERR_NOT_INITIALIZED;
-    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_backward: bind the input tensors first");
+static int32_t backward_eager(fg_exec* e) {
     const int N = (int)e->n.size();
     std::vector<uint8_t> written(N, 0);
     auto grad_of = [&](int node) -> float* { return node == e->last ? (float*)e->seed->ptr : gptr(e, node); };
@@ -643,14 +655,66 @@ static int32_t optim_one(fg_exec* e, uint32_t slot, fg_buf* weight) {
 
 // Updates every bound tensor that is marked trainable (the reference updates all of them:
 // dispatch/mod.rs:735-748) and zeroes its gradient.
-int32_t fg_exec_dispatch_optim(fg_exec* e) {
-    if (!e) return FG_ERR_NOT_INITIALIZED;
-    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_optim: bind the input tensors first");
+static int32_t optim_eager(fg_exec* e) {
     int32_t s;
     if (e->g.optim == FG_OPTIM_ADAMW && (s = fg_counter_increment(e->ctx, (uint32_t*)e->step_counter->ptr)) != FG_OK) return s;
     for (uint32_t k = 0; k < e->inputs.size(); ++k)
         if (e->trainable[k] && (s = optim_one(e, k, e->n[e->inputs[k]].value)) != FG_OK) return s;
     return FG_OK;
+}
+
+// Runs one dispatch: eagerly the first time (which also sizes the scratch arena), recorded as a plan the
+// second time, replayed afterwards.  A plan is recorded again when its key (the loss target) or the
+// scratch arena it was recorded against has changed.  Inside a caller's own recording the work is
+// simply enqueued, so that it becomes part of the caller's plan.
+static int32_t run_planned(fg_exec* e, int which, const void* key, const std::function<int32_t()>& eager) {
+    fg_ctx* ctx = e->ctx;
+    if (e->calls[which] == 0 && getenv("FG_EXEC_NO_PLANS")) e->use_plans = false;
+    if (!e->use_plans || ctx->capturing) return eager();
+    if (e->plan[which] && e->plan_key[which] == key && e->plan_ws[which] == (const void*)ctx->ws)
+        return fg_plan_launch(ctx, e->plan[which]);
+    if (e->calls[which]++ == 0) return eager();
+    if (e->plan[which]) { fg_plan_destroy(e->plan[which]); e->plan[which] = nullptr; }
+    int32_t s = fg_plan_begin(ctx);
+    if (s != FG_OK) return eager();
+    s = eager();
+    fg_plan* p = nullptr;
+    const int32_t s2 = fg_plan_end(ctx, &p);
+    if (s != FG_OK || s2 != FG_OK) {
+        if (p) fg_plan_destroy(p);
+        e->use_plans = false;             // something in this graph cannot be recorded: stay eager
+        return s != FG_OK ? s : eager();
+    }
+    e->plan[which] = p;
+    e->plan_key[which] = key;
+    e->plan_ws[which] = (const void*)ctx->ws;
+    return fg_plan_launch(ctx, p);
+}
+
+int32_t fg_exec_dispatch_forward(fg_exec* e) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_forward: bind the input tensors first");
+    return run_planned(e, 0, nullptr, [&] { return forward_eager(e); });
+}
+
+int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (e->dtype != FG_DTYPE_F32) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "dispatch_loss: the losses need f32 storage");
+    FG_REQUIRE(e->ctx, target != nullptr, "dispatch_loss: target is NULL");
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_loss: bind the input tensors first");
+    return run_planned(e, 1, target->ptr, [&] { return loss_eager(e, target); });
+}
+
+int32_t fg_exec_dispatch_backward(fg_exec* e) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_backward: bind the input tensors first");
+    return run_planned(e, 2, nullptr, [&] { return backward_eager(e); });
+}
+
+int32_t fg_exec_dispatch_optim(fg_exec* e) {
+    if (!e) return FG_ERR_NOT_INITIALIZED;
+    if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_optim: bind the input tensors first");
+    return run_planned(e, 3, nullptr, [&] { return optim_eager(e); });
 }
 
 // dispatch_single_optim (dispatch/mod.rs:790-814): one weight, its gradient chosen by index.

@@ -360,6 +360,49 @@ def test_mlp_graph_matches_oracle(ctx, oracle, act, loss_name):
     t.destroy()
 
 
+def test_replayed_dispatches_equal_eager(ctx, monkeypatch):
+    """From its second call on, every dispatch_* replays a recorded CUDA graph.  Five training steps with new
+    data each step end with bit-identical parameters whether the dispatches are replayed or run eagerly, also
+    after the loss target moves to another buffer."""
+    from ferrograd_b200 import CROSS_ENTROPY, Optim
+    B, I, Hd, O = 128, 48, 136, 10
+    r = np.random.Generator(np.random.Philox(77))
+    W = [r.standard_normal((I, Hd), np.float32) * 0.2, r.standard_normal((Hd, O), np.float32) * 0.2]
+    b = [np.zeros(Hd, np.float32), np.zeros(O, np.float32)]
+    xs = [r.standard_normal((B, I), np.float32) for _ in range(5)]
+    ls = [r.integers(0, O, B).astype(np.uint32) for _ in range(5)]
+
+    def define(g, fb, fi, fh, fo):
+        xi, w0, b0, w1, b1 = g.input([fb, fi]), g.input([fi, fh]), g.input([fh]), g.input([fh, fo]), g.input([fo])
+        g.softmax(g.add(g.matmul(g.gelu(g.add(g.matmul(xi, w0), b0)), w1), b1))
+
+    def train(eager):
+        if eager:
+            monkeypatch.setenv("FG_EXEC_NO_PLANS", "1")
+        else:
+            monkeypatch.delenv("FG_EXEC_NO_PLANS", raising=False)
+        graph, t, kernels, binding = build(ctx, define, [B, I, Hd, O], loss=CROSS_ENTROPY, optim=Optim.adamw(),
+                                           lr=1e-2)
+        ins = [ctx.init_tensor_f32(a.shape, a) for a in (xs[0], W[0], b[0], W[1], b[1])]
+        sch = ctx.schedule(kernels, binding, ins, t, [], Optim.adamw().state, trainable=[0, 1, 1, 1, 1])
+        targets = [ctx.new_onehot_init(ls[0]), ctx.new_onehot_init(ls[0])]
+        for step in range(5):
+            ctx.upload(ins[0], xs[step])
+            tgt = targets[0 if step < 3 else 1]          # the target moves: the loss plan is recorded again
+            ctx.upload(tgt, ls[step])
+            ctx.dispatch_forward(sch)
+            ctx.dispatch_loss(sch, tgt)
+            ctx.dispatch_backward(sch)
+            ctx.dispatch_optim(sch)
+        ctx.sync()
+        out = [ctx.to_numpy(ins[i]).copy() for i in (1, 2, 3, 4)]
+        t.destroy()
+        return out
+    for got, ref in zip(train(eager=False), train(eager=True)):
+        assert np.array_equal(got, ref)
+    assert not np.array_equal(train(eager=False)[0], W[0])       # and training moved the weights
+
+
 def test_binary_cross_entropy_graph(ctx, oracle):
     """p = 1 / (1 + exp(-x)) built from graph ops, BINARY_CROSS_ENTROPY against soft and hard targets:
     loss_t holds the per-element loss, the seed is p - t (loss/basic_loss.rs:81-85), and the backward
