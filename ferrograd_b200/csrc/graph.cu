@@ -102,6 +102,7 @@ struct fg_exec {
     std::vector<int> grads;         // nodes that own a gradient buffer, in node order
     std::vector<uint8_t> trainable;
     fg_buf *seed = nullptr, *loss_t = nullptr, *tmp = nullptr;
+    fg_buf* stage[4] = {nullptr, nullptr, nullptr, nullptr};   // 16-bit graphs: f32 staging for softmax and the losses
     std::vector<fg_buf*> m, v;      // AdamW moments per input
     fg_buf* step_counter = nullptr;
     fg_adamw_hyper hyper{1e-3f, 0.9f, 0.999f, 1e-8f, 0.01f};
@@ -174,7 +175,8 @@ int32_t lower(fg_exec* e) {
     e->n.assign(N, ENode());
     e->last = N - 1;
     // ---- storage type: one per graph.  16-bit graphs run their elementwise regions and matmuls in ----
-    // ---- that type (f32 accumulation); softmax, the losses and AdamW are f32-only.               ----
+    // ---- that type (f32 accumulation); softmax and the losses are computed in f32 on widened      ----
+    // ---- copies and rounded back; AdamW is f32-only.                                              ----
     {
         int dt = -1;
         for (const GNode& gn : g.nodes) {
@@ -184,10 +186,6 @@ int32_t lower(fg_exec* e) {
         }
         e->dtype = dt < 0 ? FG_DTYPE_F32 : dt;
         e->esize = e->dtype == FG_DTYPE_F32 ? 4 : 2;
-        if (e->dtype != FG_DTYPE_F32)
-            for (const GNode& gn : g.nodes)
-                if (gn.op == OP_SOFTMAX)
-                    return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: softmax needs f32 storage");
     }
     // ---- shapes (the reference's validate: backend/mod.rs:854-975) ----
     for (int i = 0; i < N; ++i) {
@@ -304,6 +302,9 @@ int32_t lower(fg_exec* e) {
     uint64_t biggest = 1;
     for (int i = 0; i < N; ++i) biggest = std::max(biggest, e->n[i].numel);
     if ((s = alloc_buf(e, biggest, false, &e->tmp)) != FG_OK) return s;
+    if (e->dtype != FG_DTYPE_F32)
+        for (fg_buf*& st : e->stage)
+            if ((s = fg_alloc(e->ctx, biggest * 4, &st)) != FG_OK) return s;
     for (GemmStep& gs : e->gemms)
         if (gs.act == FG_ACT_GELU && (s = alloc_buf(e, e->n[gs.out].numel, false, &gs.preact)) != FG_OK) return s;
     if (g.optim == FG_OPTIM_ADAMW) {
@@ -433,6 +434,7 @@ int32_t fg_exec_destroy(fg_exec* e) {
     for (fg_buf* b : e->m) fg_free(e->ctx, b);
     for (fg_buf* b : e->v) fg_free(e->ctx, b);
     for (fg_buf* b : {e->seed, e->loss_t, e->tmp, e->step_counter}) if (b) fg_free(e->ctx, b);
+    for (fg_buf* b : e->stage) if (b) fg_free(e->ctx, b);
     drop_plans(e);
     delete e;
     return FG_OK;
@@ -489,7 +491,14 @@ static int32_t forward_eager(fg_exec* e) {
         } else {
             const auto& d = e->n[st.idx].dims;
             const uint32_t cols = d.back();
-            s = fg_softmax_fwd(e->ctx, (uint32_t)(e->n[st.idx].numel / cols), cols, vptr(e, e->g.nodes[st.idx].a), vptr(e, st.idx));
+            const uint64_t numel = e->n[st.idx].numel;
+            if (e->dtype != FG_DTYPE_F32) {
+                float *x32 = (float*)e->stage[0]->ptr, *y32 = (float*)e->stage[1]->ptr;
+                if ((s = fg_convert(e->ctx, vptr(e, e->g.nodes[st.idx].a), e->dtype, x32, FG_DTYPE_F32, numel)) != FG_OK) return s;
+                if ((s = fg_softmax_fwd(e->ctx, (uint32_t)(numel / cols), cols, x32, y32)) != FG_OK) return s;
+                s = fg_convert(e->ctx, y32, FG_DTYPE_F32, vptr(e, st.idx), e->dtype, numel);
+            } else
+            s = fg_softmax_fwd(e->ctx, (uint32_t)(numel / cols), cols, vptr(e, e->g.nodes[st.idx].a), vptr(e, st.idx));
         }
         if (s != FG_OK) return s;
     }
@@ -498,6 +507,26 @@ static int32_t forward_eager(fg_exec* e) {
 
 static int32_t loss_eager(fg_exec* e, const fg_buf* target) {
     const ENode& o = e->n[e->last];
+    if (e->dtype != FG_DTYPE_F32) {
+        // widen the prediction (and a dense target) to f32, run the f32 loss kernel, round loss and seed back
+        float *p32 = (float*)e->stage[0]->ptr, *t32 = (float*)e->stage[1]->ptr, *l32 = (float*)e->stage[2]->ptr,
+              *g32 = (float*)e->stage[3]->ptr;
+        int32_t s;
+        if ((s = fg_convert(e->ctx, vptr(e, e->last), e->dtype, p32, FG_DTYPE_F32, o.numel)) != FG_OK) return s;
+        if (e->g.loss == FG_LOSS_CROSS_ENTROPY) {
+            const uint32_t cols = o.dims.back(), rows = (uint32_t)(o.numel / cols);
+            FG_REQUIRE(e->ctx, target->bytes >= (uint64_t)rows * 4, "dispatch_loss: one u32 label per row is required");
+            s = fg_ce_loss_grad(e->ctx, p32, (const uint32_t*)target->ptr, rows, cols, l32, g32);
+        } else {
+            FG_REQUIRE(e->ctx, target->bytes >= o.numel * e->esize, "dispatch_loss: target smaller than the output");
+            if ((s = fg_convert(e->ctx, target->ptr, e->dtype, t32, FG_DTYPE_F32, o.numel)) != FG_OK) return s;
+            s = e->g.loss == FG_LOSS_MSE ? fg_mse_loss_grad(e->ctx, p32, t32, o.numel, 1.0f, l32, nullptr, g32)
+                                         : fg_bce_loss_grad(e->ctx, p32, t32, o.numel, 1.0f, l32, nullptr, g32);
+        }
+        if (s != FG_OK) return s;
+        if ((s = fg_convert(e->ctx, l32, FG_DTYPE_F32, e->loss_t->ptr, e->dtype, o.numel)) != FG_OK) return s;
+        return fg_convert(e->ctx, g32, FG_DTYPE_F32, e->seed->ptr, e->dtype, o.numel);
+    }
     if (e->g.loss == FG_LOSS_MSE) {
         FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
         return fg_mse_loss_grad(e->ctx, vptr(e, e->last), (const float*)target->ptr, o.numel, 1.0f, (float*)e->loss_t->ptr,
@@ -617,8 +646,20 @@ static int32_t backward_eager(fg_exec* e) {
                 // the loss kernel's p - onehot is already dL/dlogits
                 if (written[src]) s = accumulate_into(e, src, (const float*)e->seed->ptr);
                 else {
-                    cudaError_t ce = cudaMemcpyAsync(gptr(e, src), e->seed->ptr, e->n[src].numel * 4, cudaMemcpyDeviceToDevice, e->ctx->stream);
+                    cudaError_t ce = cudaMemcpyAsync(gptr(e, src), e->seed->ptr, e->n[src].numel * e->esize, cudaMemcpyDeviceToDevice, e->ctx->stream);
                     s = ce == cudaSuccess ? FG_OK : fg_fail_cuda(e->ctx, FG_ERR_FAILED_BUFFER_COPY, "seed copy", ce);
+                }
+            } else if (e->dtype != FG_DTYPE_F32) {
+                const uint64_t numel = e->n[node].numel;
+                float *y32 = (float*)e->stage[0]->ptr, *dy32 = (float*)e->stage[1]->ptr, *dx32 = (float*)e->stage[2]->ptr;
+                if ((s = fg_convert(e->ctx, vptr(e, node), e->dtype, y32, FG_DTYPE_F32, numel)) != FG_OK) return s;
+                if ((s = fg_convert(e->ctx, grad_of(node), e->dtype, dy32, FG_DTYPE_F32, numel)) != FG_OK) return s;
+                if ((s = fg_softmax_bwd(e->ctx, rows, cols, y32, dy32, dx32, 0)) != FG_OK) return s;
+                if (written[src]) {
+                    if ((s = fg_convert(e->ctx, dx32, FG_DTYPE_F32, e->tmp->ptr, e->dtype, numel)) != FG_OK) return s;
+                    s = accumulate_into(e, src, (const float*)e->tmp->ptr);
+                } else {
+                    s = fg_convert(e->ctx, dx32, FG_DTYPE_F32, gptr(e, src), e->dtype, numel);
                 }
             } else {
                 s = fg_softmax_bwd(e->ctx, rows, cols, vptr(e, node), grad_of(node), gptr(e, src), written[src] ? 1 : 0);
@@ -699,7 +740,6 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
 
 int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
-    if (e->dtype != FG_DTYPE_F32) return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "dispatch_loss: the losses need f32 storage");
     FG_REQUIRE(e->ctx, target != nullptr, "dispatch_loss: target is NULL");
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_loss: bind the input tensors first");
     return run_planned(e, 1, target->ptr, [&] { return loss_eager(e, target); });

@@ -331,9 +331,12 @@ int32_t fg_graph_create(int32_t loss, int32_t optim, fg_graph** out);           
 int32_t fg_graph_destroy(fg_graph* g);
 int32_t fg_graph_node_count(const fg_graph* g);
 int32_t fg_graph_input(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t* node); /* DefineOps::input */
-/* An input stored as f16 or bf16 (fg_dtype).  All inputs of a graph share one storage type; 16-bit
- * graphs may hold elementwise operations and use SGD (matmul, softmax, the losses and AdamW are
- * f32-only), and every tensor the engine allocates for them has that type. */
+/* An input stored as f16 or bf16 (fg_dtype).  All inputs of a graph share one storage type, and every
+ * tensor the engine allocates for the graph (results, gradients, seed, loss) has that type.  In a
+ * 16-bit graph elementwise regions and SGD compute in the storage type, matmul multiplies the 16-bit
+ * operands with f32 accumulation, softmax and the losses are computed in f32 on widened copies and
+ * rounded back; a dense loss target has the storage type too (class labels stay u32).  AdamW needs
+ * f32 storage. */
 int32_t fg_graph_input_dt(fg_graph* g, const uint32_t* shape_fields, uint32_t ndim, int32_t dtype, int32_t* node);
 int32_t fg_graph_constant_f32(fg_graph* g, float value, int32_t* node);          /* constant_f32      */
 /* op: FG_EW_ADD..FG_EW_ELU, FG_GRAPH_MATMUL, FG_GRAPH_SOFTMAX; b is ignored for unary ops.          */

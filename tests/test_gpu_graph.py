@@ -254,14 +254,86 @@ def test_mul_add_f16(ctx, dtype):
     t.destroy()
 
 
-def test_16bit_graph_rejects_softmax(ctx):
-    from ferrograd_b200 import FgError, SimpleDType
+def test_16bit_graph_rejects_adamw(ctx):
+    from ferrograd_b200 import FgError, Optim, SimpleDType
 
     def define(g, m):
         a = g.input([m, m], SimpleDType.F16)
-        g.softmax(a)
+        g.tanh(a)
+    graph, t, kernels, binding = build(ctx, define, [32], optim=Optim.adamw())
+    ins = [ctx.init_tensor_f16((32, 32), np.ones((32, 32), np.float32))]
+    sch = ctx.schedule(kernels, binding, ins, t, [], Optim.adamw().state)
+    ctx.dispatch_forward(sch)
+    ctx.dispatch_backward(sch)
     with pytest.raises(FgError):
-        build(ctx, define, [32])
+        ctx.dispatch_optim(sch)
+    t.destroy()
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("loss_name", ["mse", "ce"])
+def test_16bit_classifier_step(ctx, oracle, dtype, loss_name):
+    """softmax(x @ W + b) stored in 16 bits, loss, backward and one SGD step: softmax and the loss are computed
+    in f32 on widened copies and rounded back.  Checked against the same chain in float64 on the rounded inputs;
+    the bar is a few units of the storage type's precision (every stored tensor is rounded once)."""
+    from ferrograd_b200 import CROSS_ENTROPY, MEAN_SQUARED_ERROR, Optim, SimpleDType
+    from ferrograd_b200.backend import from_bf16_bits, to_bf16_bits
+    sd = SimpleDType.F16 if dtype == "f16" else SimpleDType.BF16
+    tol = 4 * (2.0 ** -10 if dtype == "f16" else 2.0 ** -7)
+    Bn, I, O = 64, 40, 16
+    r = np.random.Generator(np.random.Philox(91))
+    x = oracle.round_to(r.standard_normal((Bn, I), np.float32), dtype)
+    W = oracle.round_to(r.standard_normal((I, O), np.float32) * 0.3, dtype)
+    b = oracle.round_to(r.standard_normal(O, np.float32) * 0.1, dtype)
+    ce = loss_name == "ce"
+
+    def define(g, fb, fi, fo):
+        xi, w, bb = g.input([fb, fi], sd), g.input([fi, fo], sd), g.input([fo], sd)
+        g.softmax(g.add(g.matmul(xi, w), bb))
+    graph, t, kernels, binding = build(ctx, define, [Bn, I, O], loss=CROSS_ENTROPY if ce else MEAN_SQUARED_ERROR,
+                                       optim=Optim.sgd(), lr=0.5)
+    init = ctx.init_tensor_f16 if dtype == "f16" else ctx.init_tensor_bf16
+    dec = (lambda a: a.astype(np.float32)) if dtype == "f16" else from_bf16_bits
+    raw = np.float16 if dtype == "f16" else np.uint16
+    get = lambda buf, shape: dec(ctx.download(buf, np.empty(shape, raw)))
+    ins = [init(a.shape, a) for a in (x, W, b)]
+    sch = ctx.schedule(kernels, binding, ins, t, [], (), trainable=[0, 1, 1])
+    if ce:
+        labels = r.integers(0, O, Bn).astype(np.uint32)
+        target = ctx.new_onehot_init(labels)
+        tgt = np.eye(O, dtype=np.float64)[labels]
+    else:
+        tg = oracle.round_to(r.random((Bn, O)).astype(np.float32), dtype)
+        target = init(tg.shape, tg)
+        tgt = tg.astype(np.float64)
+    ctx.dispatch_forward(sch)
+    ctx.dispatch_loss(sch, target)
+    ctx.dispatch_backward(sch)
+    ctx.sync()
+    z = x.astype(np.float64) @ W.astype(np.float64) + b
+    ez = np.exp(z - z.max(axis=1, keepdims=True))
+    p = ez / ez.sum(axis=1, keepdims=True)
+    if ce:
+        loss = np.where(tgt > 0, -np.log(p), 0.0)
+        dz = p - tgt                                     # softmax + CE: p - onehot is dL/dlogits
+    else:
+        loss = (p - tgt) ** 2
+        seed = 2 * (p - tgt)
+        dz = p * (seed - (seed * p).sum(axis=1, keepdims=True))
+    grads = {n: t.grad_tensors[i] for i, n in enumerate(t.grad_nodes)}
+    for got, ref, what in ((get(t.forward_out, (Bn, O)), p, "probabilities"), (get(t.loss_t, (Bn, O)), loss, "loss"),
+                           (get(grads[1], (I, O)), x.astype(np.float64).T @ dz, "dW"),
+                           (get(grads[2], (O,)), dz.sum(axis=0), "db")):
+        ok, worst = rel_err_ok(got, ref, tol)
+        assert ok, f"{what}: {worst:.3g} x {tol}"
+    gW = get(grads[1], (I, O))
+    ctx.dispatch_optim(sch)
+    ctx.sync()
+    lr = oracle.round_to(np.array([0.5], np.float32), dtype)[0]
+    expect = oracle.round_to(W - oracle.round_to(gW * lr, dtype), dtype)      # SGD in the storage type, exactly
+    assert np.array_equal(dec(ctx.to_numpy(ins[1])), expect)
+    assert np.array_equal(dec(ctx.to_numpy(ins[0])), x)
+    t.destroy()
 
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
