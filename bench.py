@@ -126,9 +126,9 @@ def run_reference(args, rank, world):
     probe_b = min(256, w["batch"])
     one(probe_b, 0)
     t_probe = one(probe_b, 1)
-    budget = 120.0 / max(1, args.steps + args.warmup)
+    step_limit_s = 120.0 / max(1, args.steps + args.warmup)
     batch = probe_b
-    while batch * 2 <= w["batch"] and t_probe * (batch * 2 / probe_b) <= budget:
+    while batch * 2 <= w["batch"] and t_probe * (batch * 2 / probe_b) <= step_limit_s:
         batch *= 2
     for s in range(args.warmup):
         one(batch, s)
