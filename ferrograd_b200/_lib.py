@@ -134,6 +134,8 @@ SIGNATURES = {
     "fg_comm_init": (i32, [c_ctx, i32, i32, C.c_void_p]),
     "fg_allreduce_sum_f32": (i32, [c_ctx, c_dev, u64]),
     "fg_comm_join": (i32, [c_ctx]),
+    "fg_comm_sync": (i32, [c_ctx, u32]),
+    "fg_comm_abort": (i32, [c_ctx]),
     "fg_comm_checkpoint": (i32, [c_ctx, i32]),
     "fg_comm_wait": (i32, [c_ctx, i32]),
     "fg_comm_destroy": (i32, [c_ctx]),

@@ -405,6 +405,14 @@ class GpuContext:
     def comm_join(self):
         self._check(self.lib.fg_comm_join(self.handle))
 
+    def comm_sync(self, timeout_ms):
+        """Host wait for the exchanges in flight; raises FgError(FG_ERR_TIMEOUT) and aborts the communicator
+        when they do not complete in time."""
+        self._check(self.lib.fg_comm_sync(self.handle, int(timeout_ms)))
+
+    def comm_abort(self):
+        self._check(self.lib.fg_comm_abort(self.handle))
+
     def comm_checkpoint(self, slot):
         self._check(self.lib.fg_comm_checkpoint(self.handle, slot))
 

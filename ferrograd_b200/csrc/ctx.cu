@@ -5,6 +5,7 @@
 // crates/fused_gpu/src/dispatch/backend/rocm/mod.rs:58-421): one device, one stream,
 // synchronous upload/download, asynchronous dispatch, schedules as captured graphs.
 #include <dlfcn.h>
+#include <time.h>
 #include <limits.h>
 
 #include <new>
@@ -570,6 +571,48 @@ int32_t fg_comm_join(fg_ctx* ctx) {
     if (!ctx->comm_pending) return FG_OK;
     FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
     FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_join, ctx->comm_stream));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    ctx->comm_pending = false;
+    return FG_OK;
+}
+
+// Tears the communicator down without waiting for its peers: a collective that is still waiting for
+// a rank that will never arrive is ended (ncclCommAbort makes its kernel leave).
+int32_t fg_comm_abort(fg_ctx* ctx) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (ctx->comm && ctx->nccl_lib) {
+        auto ab = (pfn_ncclCommDestroy)dlsym(ctx->nccl_lib, "ncclCommAbort");
+        if (ab) ab(ctx->comm);
+    }
+    ctx->comm = nullptr;
+    ctx->comm_pending = false;
+    return FG_OK;
+}
+
+// Host-side wait for every exchange started so far, at most timeout_ms.  On expiry the communicator is
+// aborted, the context stays usable for everything but exchanges, and FG_ERR_TIMEOUT is returned.
+int32_t fg_comm_sync(fg_ctx* ctx, uint32_t timeout_ms) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    if (ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "fg_comm_sync while recording a plan");
+    FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    FG_CUDA(ctx, FG_ERR_SYNC, cudaEventRecord(ctx->ev_join, ctx->comm_stream));
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        cudaError_t q = cudaEventQuery(ctx->ev_join);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) return fg_fail_cuda(ctx, FG_ERR_SYNC, "exchange", q);
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        const double ms = (t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6;
+        if (ms > (double)timeout_ms) {
+            fg_comm_abort(ctx);
+            cudaStreamSynchronize(ctx->comm_stream);      // the aborted collective's kernel leaves promptly
+            return fg_fail(ctx, FG_ERR_TIMEOUT, "fg_comm_sync: the exchange did not complete in time; communicator aborted");
+        }
+        timespec nap = {0, 200000};
+        nanosleep(&nap, nullptr);
+    }
     FG_CUDA(ctx, FG_ERR_SYNC, cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
     ctx->comm_pending = false;
     return FG_OK;

@@ -408,6 +408,13 @@ int32_t fg_comm_join(fg_ctx* ctx);
  * exchanges (the update of the last layers) can then run while a later one is still in flight. */
 int32_t fg_comm_checkpoint(fg_ctx* ctx, int32_t slot);
 int32_t fg_comm_wait(fg_ctx* ctx, int32_t slot);
+/* Failure handling (no counterpart in the single-device reference).  fg_comm_sync blocks the host
+ * until every exchange started so far is complete, for at most timeout_ms; when the time runs out
+ * (a peer died or never joined) the communicator is aborted, FG_ERR_TIMEOUT is returned and the
+ * context remains usable for everything except exchanges.  fg_comm_abort ends the communicator
+ * without waiting for its peers. */
+int32_t fg_comm_sync(fg_ctx* ctx, uint32_t timeout_ms);
+int32_t fg_comm_abort(fg_ctx* ctx);
 int32_t fg_comm_destroy(fg_ctx* ctx);
 
 /* Library / build information. */

@@ -62,3 +62,56 @@ def test_two_gpus_match_one_gpu_on_the_global_batch(tmp_path):
     for got, ref in zip([r0[k] for k in r0.files], W + b):
         # same mathematics, different summation order (per-rank partial sums); Adam steps are at most lr each
         assert np.max(np.abs(got - ref)) <= 2e-5 + 1e-4 * np.max(np.abs(ref)), float(np.max(np.abs(got - ref)))
+
+
+def _rank_peer_absent(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    from ferrograd_b200 import FgError, GpuContext, dp
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)     # host plumbing only
+    ctx = GpuContext(rank)
+    ctx.comm_init(world, rank, dp.exchange_unique_id(ctx, dist, rank))
+    n = 4096
+    buf = ctx.init_tensor_f32((n,), np.full(n, rank + 1.0, np.float32))
+    ctx.allreduce_sum(buf, n)                 # a healthy exchange first: 1 + 2 on both ranks
+    ctx.comm_sync(5000)
+    ctx.sync()
+    ok_first = bool((ctx.to_numpy(buf) == 3.0).all())
+    dist.barrier()
+    result = "none"
+    if rank == 0:
+        # rank 1 has stopped taking part (between steps, nothing of its own in flight): this exchange can
+        # never complete; the bounded wait must report it and leave the context usable
+        ctx.allreduce_sum(buf, n)
+        try:
+            ctx.comm_sync(1000)
+            result = "completed"
+        except FgError as e:
+            result = e.kind
+        w, g = ctx.init_tensor_f32((n,), np.full(n, 3.0, np.float32)), ctx.init_tensor_f32((n,), np.full(n, 2.0, np.float32))
+        ctx.sgd_step(w, g, n, 0.5)
+        ctx.sync()
+        usable = bool((ctx.to_numpy(w) == 2.0).all())
+        with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+            f.write(f"{ok_first} {result} {usable}")
+    dist.barrier()                            # rank 1 waits here, on the host, until rank 0 is done
+    if rank == 1:
+        ctx.comm_abort()                      # its peer's communicator is gone: no collective teardown
+    dist.destroy_process_group()
+    ctx.destroy()
+
+
+def test_absent_peer_ends_the_exchange_with_a_timeout(tmp_path):
+    """Failure detection without a GPU fault: the failure is made on the host (a rank that does not join),
+    the wait on the exchange is bounded, the communicator is aborted and the context stays usable."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_rank_peer_absent, args=(2, 29300 + os.getpid() % 300, str(tmp_path)), nprocs=2, join=True)
+    ok_first, result, usable = open(tmp_path / "rank0.txt").read().split()
+    assert ok_first == "True"
+    assert result == "FG_ERR_TIMEOUT", result
+    assert usable == "True"
