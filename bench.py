@@ -253,6 +253,22 @@ def _kernel_lines(torch, stream, ctx, peaks):
                                        "frac_of_bf16_peak": work / ms / 1e9 / peaks["bf16_tflops"],
                                        "call_ms_with_transpose": e_ms,
                                        "call_tflops_with_transpose": 2.0 * N ** 3 / e_ms / 1e9}
+    # C1: the reference's own CPU-scale case (MLP 2-16-2, batch 64, MSE, SGD), 1000 steps replayed as a plan;
+    # launch-bound, so the figure is steps per second
+    from ferrograd_b200 import dp
+    from ferrograd_b200.mlp import MLPTrainer
+    w1 = dp.WORKLOADS["c1"]
+    tr1 = MLPTrainer(ctx, w1["dims"], w1["batch"], w1["act"], w1["loss"], w1["opt"], gemm_mode="simt")
+    tr1.set_params(*MLPTrainer.init_params(w1["dims"], w1["init"], w1["seed"]))
+    tr1.upload_batch(*dp.synth_batch("c1", 0, 0))
+    tr1.step()
+    tr1.build_plan()
+    for _ in range(10):
+        tr1.step_plan()
+    ms = timed(torch, stream, ctx, lambda i: tr1.step_plan(), w1["steps"])
+    out["mlp_c1"] = {"steps": w1["steps"], "ms_total": ms, "steps_per_s": w1["steps"] / ms * 1e3,
+                     "samples_per_s": w1["steps"] * w1["batch"] / ms * 1e3, "final_loss_sum": tr1.get_loss(),
+                     "note": "exact SIMT GEMM path; one CUDA-graph replay per step"}
     out["peak_note"] = ("tensor peaks derive from the measured bf16 burst: TF32 runs at half the bf16 rate; the 3xTF32 "
                         "peak is that / 3, the default mode's own peak that / 2; bandwidth fractions are of the measured "
                         "copy bandwidth")
