@@ -530,6 +530,23 @@ def test_gemm_skinny_output_layer(ctx, oracle, M, N, K, act):
     assert ctx.device_status() == 0
 
 
+def test_exchange_entry_points_without_a_communicator(ctx):
+    # the data-parallel entry points refuse to run before fg_comm_init instead of launching anything
+    from ferrograd_b200 import FgError
+    M, N, K = 64, 32, 48
+    A, B, dY = ctx.new_tensor((M, K), zeroed=True), ctx.new_tensor((K, N), zeroed=True), ctx.new_tensor((M, N), zeroed=True)
+    dA, dB = ctx.new_tensor((M, K)), ctx.new_tensor((K, N))
+    before = ctx.launch_count()
+    with pytest.raises(FgError) as e:
+        ctx.gemm_bwd_exchange(A, B, dY, M, N, K, dB, K * N, dA=dA, dB=dB)
+    assert e.value.kind == "FG_ERR_NOT_INITIALIZED"
+    with pytest.raises(FgError):
+        ctx.allreduce_sum(dB, K * N)
+    assert ctx.launch_count() == before
+    ctx.comm_join()                      # nothing pending: a no-op
+    ctx.comm_sync(100)                   # likewise
+
+
 @pytest.mark.parametrize("mode", ["simt", "auto"])
 def test_gemm_batched(ctx, oracle, mode):
     # rank-3 matmul: T independent products, every tensor stepped by one matrix per product
