@@ -54,7 +54,8 @@ enum fg_act { FG_ACT_NONE = 0, FG_ACT_RELU = 1, FG_ACT_TANH = 2, FG_ACT_GELU = 3
 
 /* How the f32 GEMM is computed. */
 enum fg_gemm_mode {
-    FG_GEMM_AUTO = 0,   /* tensor cores when the shape is large enough, else SIMT */
+    FG_GEMM_AUTO = 0,   /* FG_GEMM_TF32_BF16X2 when the shape is large enough; plain-FMA streaming
+                           kernels when N <= 16 (a narrow output layer); else SIMT */
     FG_GEMM_SIMT = 1,   /* sequential-k fmaf, bit-identical to the reference kernel body
                            (crates/ferrograd-nn/src/op/matmul/generic.rs:98-319) */
     FG_GEMM_3XTF32 = 2, /* tcgen05 kind::tf32, hi/lo split, three MMAs per k-step */
