@@ -68,6 +68,11 @@ SIGNATURES = {
     "fg_gemm_bwd_f32": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, i32, c_dev, c_dev, c_dev, c_dev, c_dev]),
     "fg_gemm_bwd_exchange_f32": (i32, [c_ctx, i32, u32, u32, u32, c_dev, c_dev, c_dev, i32, c_dev, c_dev, c_dev, c_dev, c_dev,
                                        u64]),
+    "fg_pairs_from_f32": (i32, [c_ctx, c_dev, u64, c_dev, u64]),
+    "fg_gemm_paired_f32": (i32, [c_ctx, u32, u32, u32, c_dev, c_dev, u64, c_dev, c_dev, u64, c_dev, c_dev, i32, c_dev,
+                                 c_dev, u64]),
+    "fg_gemm_bwd_paired_f32": (i32, [c_ctx, u32, u32, u32, c_dev, c_dev, u64, c_dev, c_dev, u64, c_dev, c_dev, u64,
+                                     c_dev, c_dev, c_dev, i32, c_dev, c_dev, u64, c_dev, c_dev, u64]),
     "fg_gemm_batched_f32": (i32, [c_ctx, i32, u32, u32, u32, u32, c_dev, u64, c_dev, u64, c_dev, u64, c_dev, i32, c_dev]),
     "fg_gemm_batched_bwd_f32": (i32, [c_ctx, i32, u32, u32, u32, u32, c_dev, u64, c_dev, u64, c_dev, u64, i32, c_dev,
                                       c_dev, c_dev]),
@@ -82,6 +87,9 @@ SIGNATURES = {
     "fg_mse_loss_grad_noalloc": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
     "fg_sgd_step": (i32, [c_ctx, c_dev, c_dev, u64, f32, f32, i32]),
     "fg_adamw_step": (i32, [c_ctx, c_dev, c_dev, c_dev, c_dev, u64, C.POINTER(AdamWHyper), u32, c_dev, f32, i32]),
+    "fg_sgd_step_paired": (i32, [c_ctx, c_dev, c_dev, u64, f32, f32, i32, c_dev, u64]),
+    "fg_adamw_step_paired": (i32, [c_ctx, c_dev, c_dev, c_dev, c_dev, u64, C.POINTER(AdamWHyper), u32, c_dev, f32, i32,
+                                   c_dev, u64]),
     "fg_counter_increment": (i32, [c_ctx, c_dev]),
     "fg_eltwise_chain_fwd": (i32, [c_ctx, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
                                    C.POINTER(C.c_void_p)]),

@@ -282,6 +282,24 @@ class GpuContext:
                                                       ACT[act], _ptr(saved), _ptr(dA), _ptr(dB), _ptr(dbias),
                                                       _ptr(exch_buf), exch_count))
 
+    # ---- f32 tensors with bf16 pairs: no operand pre-pass (see include/ferrograd_b200.h) ----
+    def pairs_from_f32(self, x, n, pairs, plane_stride=None):
+        self._check(self.lib.fg_pairs_from_f32(self.handle, _ptr(x), n, _ptr(pairs), plane_stride or n))
+
+    def gemm_paired(self, A, B, Cout, M, N, K, A_pairs=None, B_pairs=None, bias=None, act="none", preact_out=None,
+                    C_pairs=None, A_stride=None, B_stride=None, C_stride=None):
+        self._check(self.lib.fg_gemm_paired_f32(self.handle, M, N, K, _ptr(A), _ptr(A_pairs), A_stride or M * K, _ptr(B),
+                                                _ptr(B_pairs), B_stride or K * N, _ptr(Cout), _ptr(bias), ACT[act],
+                                                _ptr(preact_out), _ptr(C_pairs), C_stride or M * N))
+
+    def gemm_bwd_paired(self, A, B, dZ, M, N, K, A_pairs=None, B_pairs=None, dZ_pairs=None, dB=None, dbias=None, dA=None,
+                        below_act="none", below_saved=None, dA_pairs=None, below_dbias=None, exch_buf=None,
+                        exch_count=0, A_stride=None, B_stride=None, dZ_stride=None, dA_stride=None):
+        self._check(self.lib.fg_gemm_bwd_paired_f32(
+            self.handle, M, N, K, _ptr(A), _ptr(A_pairs), A_stride or M * K, _ptr(B), _ptr(B_pairs), B_stride or K * N,
+            _ptr(dZ), _ptr(dZ_pairs), dZ_stride or M * N, _ptr(dB), _ptr(dbias), _ptr(dA), ACT[below_act], _ptr(below_saved),
+            _ptr(dA_pairs), dA_stride or M * K, _ptr(below_dbias), _ptr(exch_buf), exch_count))
+
     def gemm_batched(self, A, B, Cout, batch, M, N, K, bias=None, act="none", preact_out=None, mode="auto",
                      strides=None):
         sa, sb, sc = strides or (M * K, K * N, M * N)
@@ -339,6 +357,17 @@ class GpuContext:
         h = _lib.AdamWHyper(lr, beta1, beta2, eps, weight_decay)
         self._check(self.lib.fg_adamw_step(self.handle, _ptr(w), _ptr(g), _ptr(m), _ptr(v), n, C.byref(h),
                                            int(step), _ptr(step_dev), grad_scale, int(zero_grad)))
+
+    def sgd_step_paired(self, w, g, n, lr, w_pairs, pairs_stride, grad_scale=1.0, zero_grad=True):
+        self._check(self.lib.fg_sgd_step_paired(self.handle, _ptr(w), _ptr(g), n, lr, grad_scale, int(zero_grad),
+                                                _ptr(w_pairs), pairs_stride))
+
+    def adamw_step_paired(self, w, g, m, v, n, lr, beta1, beta2, eps, weight_decay, w_pairs, pairs_stride, step=1,
+                          step_dev=None, grad_scale=1.0, zero_grad=True):
+        h = _lib.AdamWHyper(lr, beta1, beta2, eps, weight_decay)
+        self._check(self.lib.fg_adamw_step_paired(self.handle, _ptr(w), _ptr(g), _ptr(m), _ptr(v), n, C.byref(h),
+                                                  int(step), _ptr(step_dev), grad_scale, int(zero_grad), _ptr(w_pairs),
+                                                  pairs_stride))
 
     def counter_increment(self, counter):
         self._check(self.lib.fg_counter_increment(self.handle, _ptr(counter)))

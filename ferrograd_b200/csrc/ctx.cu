@@ -72,6 +72,18 @@ int32_t fg_ws_alloc(fg_ctx* ctx, uint64_t bytes, void** out) {
     return FG_OK;
 }
 
+// Makes sure `bytes` more can be carved from the arena.  Growing is only possible before anything has been
+// carved for the current operation, so entry points ask for their whole need up front.
+int32_t fg_ws_ensure(fg_ctx* ctx, uint64_t bytes) {
+    const uint64_t off = (ctx->ws_used + 255u) & ~uint64_t(255);
+    if (off + bytes <= ctx->ws_bytes) return FG_OK;
+    if (ctx->ws_used != 0) return fg_fail(ctx, FG_ERR_INTERNAL, "scratch arena grown in the middle of an operation");
+    void* p;
+    const int32_t s = fg_ws_alloc(ctx, bytes, &p);
+    ctx->ws_used = 0;
+    return s;
+}
+
 static bool create_events(cudaEvent_t* ev, int n) {
     for (int i = 0; i < n; ++i)
         if (cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) return false;
@@ -243,10 +255,7 @@ int32_t fg_ctx_timing_read(fg_ctx* ctx, int32_t kind, uint64_t* launches, double
 int32_t fg_ctx_reserve_workspace(fg_ctx* ctx, uint64_t bytes) {
     FG_ENTER(ctx);
     if (bytes <= ctx->ws_bytes) return FG_OK;
-    void* p;
-    int32_t s = fg_ws_alloc(ctx, bytes - 256, &p);
-    ctx->ws_used = 0;
-    return s;
+    return fg_ws_ensure(ctx, bytes);
 }
 
 // ---- memory ----

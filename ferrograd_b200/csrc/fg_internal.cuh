@@ -1,5 +1,6 @@
 // Internal definitions shared by the translation units of libferrograd_b200.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -118,6 +119,8 @@ inline bool fg_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p)
 
 // Returns a 256-byte aligned slice of the scratch arena, growing it when allowed.
 int32_t fg_ws_alloc(fg_ctx* ctx, uint64_t bytes, void** out);
+// Room for `bytes` more in the arena (grows it when nothing has been carved yet for this operation).
+int32_t fg_ws_ensure(fg_ctx* ctx, uint64_t bytes);
 
 // Grid for a bandwidth-bound grid-stride kernel: a multiple of the SM count.
 inline int fg_stream_grid(const fg_ctx* ctx, uint64_t work_items, int threads, int per_sm) {
@@ -164,6 +167,26 @@ __device__ __forceinline__ float fg_act_grad(int act, float saved) {
     }
 }
 
+// ---- bf16 pairs of an f32 tensor (operands of the default GEMM mode) ----
+// A kind::tf32 MMA that reads an f32 word from shared memory uses sign, exponent and the top 10 mantissa
+// bits: it sees trunc(x).  The pairs carry what the split product needs beside that: plane 0 = bf16(x),
+// plane 1 = bf16(x - trunc(x)).  Whoever writes a tensor writes its pairs in the same pass.
+__device__ __forceinline__ float fg_trunc_tf32(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+__device__ __forceinline__ void fg_store_pairs4(__nv_bfloat16* pairs, uint64_t plane_stride, size_t idx, float4 v) {
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+    const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - fg_trunc_tf32(v.x), v.y - fg_trunc_tf32(v.y));
+    const __nv_bfloat162 l1 = __floats2bfloat162_rn(v.z - fg_trunc_tf32(v.z), v.w - fg_trunc_tf32(v.w));
+    uint2 h, l;
+    h.x = *reinterpret_cast<const uint32_t*>(&h0); h.y = *reinterpret_cast<const uint32_t*>(&h1);
+    l.x = *reinterpret_cast<const uint32_t*>(&l0); l.y = *reinterpret_cast<const uint32_t*>(&l1);
+    *reinterpret_cast<uint2*>(pairs + idx) = h;
+    *reinterpret_cast<uint2*>(pairs + plane_stride + idx) = l;
+}
+__device__ __forceinline__ void fg_store_pairs1(__nv_bfloat16* pairs, uint64_t plane_stride, size_t idx, float v) {
+    pairs[idx] = __float2bfloat16_rn(v);
+    pairs[plane_stride + idx] = __float2bfloat16_rn(v - fg_trunc_tf32(v));
+}
+
 // ---- internal launchers used across translation units ----
 int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uint32_t N, uint32_t K,
                             const float* A, const float* B, float* C, const float* bias, int act,
@@ -171,8 +194,17 @@ int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uin
 uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K);   // enough for any one skinny launch
 int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
                                 const float* bias, int act, float* preact_out);
+// Optional extras of the dA kernel: dA = (dZ·Bᵀ) * act'(mul_saved), its bf16 pairs, and the column sums of each
+// 32-row block ([ceil(M/32)][K], the partials of the bias gradient of the layer below).
+struct fg_skinny_extras {
+    const float* mul_saved;
+    int mul_act;
+    __nv_bfloat16* pairs;
+    uint64_t pairs_stride;
+    float* colsum_part;
+};
 int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N, const float* dZ, const float* B,
-                                 float* dA);
+                                 float* dA, const fg_skinny_extras* extras = nullptr);
 int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t N, const float* A, const float* dZ,
                                  float* dB);
 int32_t fg_convert_launch(fg_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, uint64_t n);

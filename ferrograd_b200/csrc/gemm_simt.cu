@@ -236,10 +236,12 @@ __global__ void __launch_bounds__(128) gemm_skinny_tn_partial_kernel(uint32_t M,
 
 // dA[m][k] = sum_n dZ[m][n] * B[k][n]   (dZ is [M, N], B is [K, N]): bound by writing dA once.
 // A thread owns four consecutive k and keeps their rows of B in registers while it walks 32 rows of dZ.
+// With extras: the product is multiplied by act'(mul_saved) (the layer below's backward factor), its bf16
+// pairs are written beside it, and the thread's own column sums over the 32 rows go to colsum_part.
 template <int NT>
 __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_t K, uint32_t N,
                                                              const float* __restrict__ dZ, const float* __restrict__ B,
-                                                             float* __restrict__ dA) {
+                                                             float* __restrict__ dA, fg_skinny_extras ex) {
     __shared__ float zs[32][NT];
     const uint32_t m0 = blockIdx.y * 32, rows = min(32u, M - m0);
     for (uint32_t e = threadIdx.x; e < 32 * NT; e += 128) {
@@ -254,7 +256,10 @@ __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_
     for (int q = 0; q < 4; ++q)
 #pragma unroll
         for (int n = 0; n < NT; ++n) b[q][n] = (n < (int)N && k0 + q < K) ? B[(size_t)(k0 + q) * N + n] : 0.0f;
-    const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15u) == 0);
+    const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15u) == 0) &&
+                     (!ex.mul_saved || (reinterpret_cast<uintptr_t>(ex.mul_saved) & 15u) == 0) &&
+                     (!ex.pairs || ((reinterpret_cast<uintptr_t>(ex.pairs) & 15u) == 0 && ex.pairs_stride % 4 == 0));
+    float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
     for (uint32_t r = 0; r < rows; ++r) {
         float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -264,13 +269,32 @@ __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_
 #pragma unroll
             for (int q = 0; q < 4; ++q) o[q] = fmaf(z, b[q][n], o[q]);
         }
-        float* dst = dA + (size_t)(m0 + r) * K + k0;
+        const size_t off = (size_t)(m0 + r) * K + k0;
         if (vec) {
-            *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+            if (ex.mul_saved) {
+                const float4 sv = __ldcs(reinterpret_cast<const float4*>(ex.mul_saved + off));
+                o[0] *= fg_act_grad(ex.mul_act, sv.x); o[1] *= fg_act_grad(ex.mul_act, sv.y);
+                o[2] *= fg_act_grad(ex.mul_act, sv.z); o[3] *= fg_act_grad(ex.mul_act, sv.w);
+            }
+            const float4 v = make_float4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<float4*>(dA + off) = v;
+            if (ex.pairs) fg_store_pairs4(ex.pairs, ex.pairs_stride, off, v);
         } else {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) if (k0 + q < K) dst[q] = o[q];
+            for (int q = 0; q < 4; ++q)
+                if (k0 + q < K) {
+                    if (ex.mul_saved) o[q] *= fg_act_grad(ex.mul_act, ex.mul_saved[off + q]);
+                    dA[off + q] = o[q];
+                    if (ex.pairs) fg_store_pairs1(ex.pairs, ex.pairs_stride, off + q, o[q]);
+                } else o[q] = 0.0f;
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cs[q] += o[q];
+    }
+    if (ex.colsum_part) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            if (k0 + q < K) ex.colsum_part[(size_t)blockIdx.y * K + k0 + q] = cs[q];
     }
 }
 
@@ -323,11 +347,12 @@ int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K,
 
 // dA[M, K] = dZ · B^T with dZ [M, N], B [K, N], N <= 16.
 int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N, const float* dZ, const float* B,
-                                 float* dA) {
+                                 float* dA, const fg_skinny_extras* extras) {
     if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
     dim3 grid((K + 511) / 512, (M + 31) / 32);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
-    FG_SKINNY_DISPATCH(N, (gemm_skinny_nt_kernel<NT><<<grid, 128, 0, ctx->stream>>>(M, K, N, dZ, B, dA)));
+    const fg_skinny_extras ex = extras ? *extras : fg_skinny_extras{nullptr, 0, nullptr, 0, nullptr};
+    FG_SKINNY_DISPATCH(N, (gemm_skinny_nt_kernel<NT><<<grid, 128, 0, ctx->stream>>>(M, K, N, dZ, B, dA, ex)));
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

@@ -49,6 +49,13 @@ struct Epilogue {
     float* partial;
     uint32_t t_full, split;
     int out_dtype;       // storage type of C and preact (fg_dtype); bias and partial are always f32
+    // ---- pair kernel on f32 tensors with bf16 pairs (FMT 1) ----
+    uint32_t a_mn, b_mn;              // the operand's storage has the non-contraction index contiguous
+    __nv_bfloat16* c_pairs;           // optional: bf16 pairs of the stored C (see pairs_kernel)
+    uint64_t c_pairs_stride;          // elements between the two planes of c_pairs
+    const float* mul_saved;           // optional [M,N]: C = (acc + bias) * act'(mul_saved), act = mul_act
+    int mul_act;
+    float* colsum_part;               // optional [ceil(M/32)][N]: column sums of the stored C per 32-row block
 };
 
 // Element stores in the output's storage type (idx in elements).
@@ -95,6 +102,11 @@ __host__ __device__ __forceinline__ void pair_tile_origin(uint32_t tile, uint32_
 // of instruction cache (measured on the pair kernel: 45,000 cycles for ~1,000 useful instructions).
 __device__ __noinline__ float4 act_fwd4(int act, float4 z) {
     return make_float4(fg_act_fwd(act, z.x), fg_act_fwd(act, z.y), fg_act_fwd(act, z.z), fg_act_fwd(act, z.w));
+}
+// z * act'(saved): the backward factor of the layer below, applied while a dA tile is stored.
+__device__ __noinline__ float4 act_mul4(int act, float4 z, float4 sv) {
+    return make_float4(z.x * fg_act_grad(act, sv.x), z.y * fg_act_grad(act, sv.y), z.z * fg_act_grad(act, sv.z),
+                       z.w * fg_act_grad(act, sv.w));
 }
 
 template <int BN, int BK>
@@ -470,11 +482,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         continue;
                     }
                     if (leader) mbar_expect_tx(full_bar(s), 2 * Cfg::kStageBytes);   // both CTAs' bytes
-                    tma_load_3d_pair(sa, &tmA, lf, (int)(kb * BK), (int)m0, 0);
-                    tma_load_3d_pair(sa + Cfg::kABytes, &tmB, lf, (int)(kb * BK), (int)nb0, 0);
                     if (FMT == 1) {
-                        tma_load_3d_pair(sa + BM * BK * 4, &tmA16, lf, (int)(kb * BK), (int)m0, 0);
-                        tma_load_3d_pair(sa + Cfg::kABytes + HB * BK * 4, &tmB16, lf, (int)(kb * BK), (int)nb0, 0);
+                        // One operand tile = 128 rows x 32 values of k as f32 (16 KiB) followed by its two
+                        // bf16 planes (2 x 8 KiB).  K-major storage: one box each.  MN-major storage
+                        // ([k][rows]): the f32 tile arrives as four boxes of 32 rows x 32 k (each [k][32 rows],
+                        // 4 KiB), the bf16 planes as two boxes of 64 rows x 32 k x 2 planes ([plane][k][64 rows]).
+                        auto load_tile = [&](uint32_t dst, const CUtensorMap* t32, const CUtensorMap* t16, bool mn, uint32_t r0) {
+                            if (!mn) {
+                                tma_load_3d_pair(dst, t32, lf, (int)(kb * BK), (int)r0, 0);
+                                tma_load_3d_pair(dst + BM * BK * 4, t16, lf, (int)(kb * BK), (int)r0, 0);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    tma_load_3d_pair(dst + i * 4096, t32, lf, (int)(r0 + 32 * i), (int)(kb * BK), 0);
+#pragma unroll
+                                for (int i = 0; i < 2; ++i)
+                                    tma_load_3d_pair(dst + BM * BK * 4 + i * 8192, t16, lf, (int)(r0 + 64 * i), (int)(kb * BK), 0);
+                            }
+                        };
+                        load_tile(sa, &tmA, &tmA16, ep.a_mn != 0, m0);
+                        load_tile(sa + Cfg::kABytes, &tmB, &tmB16, ep.b_mn != 0, nb0);
+                    } else {
+                        tma_load_3d_pair(sa, &tmA, lf, (int)(kb * BK), (int)m0, 0);
+                        tma_load_3d_pair(sa + Cfg::kABytes, &tmB, lf, (int)(kb * BK), (int)nb0, 0);
                     }
                 }
             }
@@ -530,21 +560,45 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                 mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
                             }
                         } else {
-                            constexpr uint32_t idesc16 = make_idesc(1u /*bf16*/, 2 * BM, BN);
-                            const uint32_t a16 = sa + BM * BK * 4, b16 = sa + Cfg::kABytes + HB * BK * 4;
-                            const uint64_t a_h16 = make_desc_kmajor<64>(a16), a_l16 = make_desc_kmajor<64>(a16 + BM * BK * 2);
-                            const uint64_t b_h16 = make_desc_kmajor<64>(b16), b_l16 = make_desc_kmajor<64>(b16 + HB * BK * 2);
+                            // Per operand: descriptors of the f32 tile and of its two bf16 planes, and how far
+                            // one MMA's worth of k advances them (address field, 16-byte units).  K-major: 32 bytes
+                            // inside the swizzled row.  MN-major: eight k-rows = 1024 bytes per tf32 MMA (two 512-byte
+                            // atoms of the 32-byte-atomicity swizzle), sixteen k-rows = two 1024-byte atoms per bf16
+                            // MMA; column blocks are 4 KiB (f32) / 8 KiB (bf16) apart.
+                            const uint32_t idesc_t = idesc | (ep.a_mn ? kIdescAMnMajor : 0u) | (ep.b_mn ? kIdescBMnMajor : 0u);
+                            const uint32_t idesc16 = make_idesc(1u /*bf16*/, 2 * BM, BN) | (ep.a_mn ? kIdescAMnMajor : 0u) |
+                                                     (ep.b_mn ? kIdescBMnMajor : 0u);
+                            const uint32_t a32 = sa, a16 = sa + BM * BK * 4;
+                            const uint32_t b32 = sa + Cfg::kABytes, b16 = b32 + HB * BK * 4;
+                            uint64_t a_f, a_h16, a_l16, b_f, b_h16, b_l16;
+                            uint32_t a_adv32, a_adv16, b_adv32, b_adv16;
+                            if (!ep.a_mn) {
+                                a_f = make_desc_kmajor<128>(a32);
+                                a_h16 = make_desc_kmajor<64>(a16); a_l16 = make_desc_kmajor<64>(a16 + BM * BK * 2);
+                                a_adv32 = 2; a_adv16 = 2;
+                            } else {
+                                a_f = make_desc_mnmajor(a32, 4096, 512, 1);
+                                a_h16 = make_desc_mnmajor(a16, 8192, 1024, 2); a_l16 = make_desc_mnmajor(a16 + 4096, 8192, 1024, 2);
+                                a_adv32 = 64; a_adv16 = 128;
+                            }
+                            if (!ep.b_mn) {
+                                b_f = make_desc_kmajor<128>(b32);
+                                b_h16 = make_desc_kmajor<64>(b16); b_l16 = make_desc_kmajor<64>(b16 + HB * BK * 2);
+                                b_adv32 = 2; b_adv16 = 2;
+                            } else {
+                                b_f = make_desc_mnmajor(b32, 4096, 512, 1);
+                                b_h16 = make_desc_mnmajor(b16, 8192, 1024, 2); b_l16 = make_desc_mnmajor(b16 + 4096, 8192, 1024, 2);
+                                b_adv32 = 64; b_adv16 = 128;
+                            }
 #pragma unroll
                             for (int kk = 0; kk < BK / 16; ++kk) {
-                                const uint64_t adv = (uint64_t)(kk * 16 * 2 >> 4);
-                                mma_f16_pair(d_tmem, a_l16 + adv, b_h16 + adv, idesc16, first | (uint32_t)kk);
-                                mma_f16_pair(d_tmem, a_h16 + adv, b_l16 + adv, idesc16, 1u);
+                                mma_f16_pair(d_tmem, a_l16 + (uint64_t)(kk * a_adv16), b_h16 + (uint64_t)(kk * b_adv16), idesc16,
+                                             first | (uint32_t)kk);
+                                mma_f16_pair(d_tmem, a_h16 + (uint64_t)(kk * a_adv16), b_l16 + (uint64_t)(kk * b_adv16), idesc16, 1u);
                             }
 #pragma unroll
-                            for (int kk = 0; kk < BK / UK; ++kk) {
-                                const uint64_t adv = (uint64_t)(kk * UK * 4 >> 4);
-                                mma_tf32_pair(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
-                            }
+                            for (int kk = 0; kk < BK / UK; ++kk)
+                                mma_tf32_pair(d_tmem, a_f + (uint64_t)(kk * a_adv32), b_f + (uint64_t)(kk * b_adv32), idesc_t, 1u);
                         }
                         mma_commit_pair(empty_bar(s), 3);        // frees this stage in both CTAs
                     }
@@ -606,6 +660,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t row_base = part ? rank * BM : m0, col_base = part ? 0u : n0;
             const int act = part ? FG_ACT_NONE : ep.act;
             const bool vec = part || vec_ok;
+            // extras of the f32 + pairs path; a K-share of a tail tile leaves them to the fold kernel
+            const float* const mul = part ? nullptr : ep.mul_saved;
+            __nv_bfloat16* const pairs = part ? nullptr : ep.c_pairs;
+            float* const csp = part ? nullptr : ep.colsum_part;
 #pragma unroll
             for (int g4 = 0; g4 < CPT / 32; ++g4) {
                 const uint32_t col = col_base + half * CPT + g4 * 32 + c4;     // this lane's 4 columns on the way out
@@ -617,6 +675,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                     for (int t = 0; t < 4; ++t) if (col + t < col_lim) bz[t] = ep.bias[col + t];
                 }
+                float cs[4] = {0.f, 0.f, 0.f, 0.f};     // column sums of what this lane stores (rows r*4 + rsub)
                 // rolled on purpose: the activation code (tanhf, GELU) is inlined at every call site, and
                 // 128 copies of it per thread made this section miss the instruction cache on every line
                 // (measured: 45,000 cycles per tile for ~1,000 useful instructions)
@@ -630,18 +689,39 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (row < row_lim && col < col_lim) {
                         const size_t off = (size_t)row * out_ld + col;
                         if (vec && col + 3 < col_lim) {
-                            const float4 o = act == FG_ACT_NONE ? make_float4(z[0], z[1], z[2], z[3])
-                                                                : act_fwd4(act, make_float4(z[0], z[1], z[2], z[3]));
-                            if (pre) store_out4(pre, off, make_float4(z[0], z[1], z[2], z[3]), odt);
+                            const float4 zin = make_float4(z[0], z[1], z[2], z[3]);
+                            float4 o;
+                            if (mul) o = act_mul4(ep.mul_act, zin, __ldg(reinterpret_cast<const float4*>(mul + off)));
+                            else o = act == FG_ACT_NONE ? zin : act_fwd4(act, zin);
+                            if (pre) store_out4(pre, off, zin, odt);
                             store_out4(out, off, o, odt);
+                            if (pairs) fg_store_pairs4(pairs, ep.c_pairs_stride, off, o);
+                            cs[0] += o.x; cs[1] += o.y; cs[2] += o.z; cs[3] += o.w;
                         } else {
 #pragma unroll
                             for (int t = 0; t < 4; ++t)
                                 if (col + t < col_lim) {
+                                    const float o = mul ? z[t] * fg_act_grad(ep.mul_act, mul[off + t]) : fg_act_fwd(act, z[t]);
                                     if (pre) store_out1(pre, off + t, z[t], odt);
-                                    store_out1(out, off + t, fg_act_fwd(act, z[t]), odt);
+                                    store_out1(out, off + t, o, odt);
+                                    if (pairs) fg_store_pairs1(pairs, ep.c_pairs_stride, off + t, o);
+                                    cs[t] += o;
                                 }
                         }
+                    }
+                }
+                if (csp) {
+                    // the four lanes that share these columns hold rows 0,4,.. / 1,5,.. / 2,6,.. / 3,7,..: add them in a fixed order
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        cs[t] += __shfl_xor_sync(0xffffffffu, cs[t], 8);
+                        cs[t] += __shfl_xor_sync(0xffffffffu, cs[t], 16);
+                    }
+                    const uint32_t row0 = row_base + q * 32;
+                    if (lane < 8 && row0 < row_lim) {
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            if (col + t < col_lim) csp[(size_t)(row0 >> 5) * ep.N + col + t] = cs[t];
                     }
                 }
                 __syncwarp();
@@ -657,42 +737,76 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
-// Folds the K-shares of the pair kernel's tail tiles in a fixed order, then bias, activation and store.
-// 64 blocks of 256 threads per tile; a thread owns four consecutive columns of one row.
+// Folds the K-shares of the pair kernel's tail tiles in a fixed order, then does what the pair kernel's own
+// epilogue does for a whole tile: bias, activation (or the act' factor), store, bf16 pairs, column sums.
+// 64 blocks of 256 threads per tile, one 32 x 32 sub-block each (so that a block owns whole 32-row column
+// sums); thread t handles four consecutive columns of row t / 8.
 __global__ void __launch_bounds__(256) gemm_tc_pair_fold_kernel(Epilogue ep) {
     constexpr uint32_t TM = 2 * BM, TN = 256;
+    __shared__ float cs_sm[8][32];
     const uint32_t pairs_m = (ep.M + TM - 1) / TM, pairs_n = (ep.N + TN - 1) / TN;
-    const uint32_t tail = blockIdx.x >> 6;
+    const uint32_t tail = blockIdx.x >> 6, sub = blockIdx.x & 63u;
     uint32_t m0, n0;
     pair_tile_origin(ep.t_full + tail, pairs_m, pairs_n, TM, TN, m0, n0);
-    const uint32_t e = ((blockIdx.x & 63u) * 256 + threadIdx.x) * 4;        // element of the 256x256 tile
-    const uint32_t row = m0 + e / TN, col = n0 + e % TN;
-    if (row >= ep.M || col >= ep.N) return;
-    const float* p = ep.partial + (size_t)tail * ep.split * (TM * TN) + e;
-    float4 z = *reinterpret_cast<const float4*>(p);
-    for (uint32_t k = 1; k < ep.split; ++k) {
-        const float4 t = *reinterpret_cast<const float4*>(p + (size_t)k * (TM * TN));
-        z.x += t.x; z.y += t.y; z.z += t.z; z.w += t.w;
-    }
-    float zz[4] = {z.x, z.y, z.z, z.w};
-    if (ep.bias) {
+    const uint32_t lrow = (sub >> 3) * 32 + (threadIdx.x >> 3), lcol = (sub & 7u) * 32 + (threadIdx.x & 7u) * 4;
+    const uint32_t row = m0 + lrow, col = n0 + lcol;
+    const bool live = row < ep.M && col < ep.N;
+    float ov[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        const float* p = ep.partial + (size_t)tail * ep.split * (TM * TN) + (size_t)lrow * TN + lcol;
+        float4 z = *reinterpret_cast<const float4*>(p);
+        for (uint32_t k = 1; k < ep.split; ++k) {
+            const float4 t = *reinterpret_cast<const float4*>(p + (size_t)k * (TM * TN));
+            z.x += t.x; z.y += t.y; z.z += t.z; z.w += t.w;
+        }
+        float zz[4] = {z.x, z.y, z.z, z.w};
+        if (ep.bias) {
 #pragma unroll
-        for (int t = 0; t < 4; ++t) if (col + t < ep.N) zz[t] += ep.bias[col + t];
-    }
-    const size_t off = (size_t)row * ep.N + col;
-    const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
-                        (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
-    if (vec_ok && col + 3 < ep.N) {
-        const float4 zin = make_float4(zz[0], zz[1], zz[2], zz[3]);
-        if (ep.preact) store_out4(ep.preact, off, zin, ep.out_dtype);
-        store_out4(ep.C, off, ep.act == FG_ACT_NONE ? zin : act_fwd4(ep.act, zin), ep.out_dtype);
-    } else {
+            for (int t = 0; t < 4; ++t) if (col + t < ep.N) zz[t] += ep.bias[col + t];
+        }
+        const size_t off = (size_t)row * ep.N + col;
+        const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
+                            (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
+        if (vec_ok && col + 3 < ep.N) {
+            const float4 zin = make_float4(zz[0], zz[1], zz[2], zz[3]);
+            float4 o;
+            if (ep.mul_saved) o = act_mul4(ep.mul_act, zin, __ldg(reinterpret_cast<const float4*>(ep.mul_saved + off)));
+            else o = ep.act == FG_ACT_NONE ? zin : act_fwd4(ep.act, zin);
+            if (ep.preact) store_out4(ep.preact, off, zin, ep.out_dtype);
+            store_out4(ep.C, off, o, ep.out_dtype);
+            if (ep.c_pairs) fg_store_pairs4(ep.c_pairs, ep.c_pairs_stride, off, o);
+            ov[0] = o.x; ov[1] = o.y; ov[2] = o.z; ov[3] = o.w;
+        } else {
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
-            if (col + t < ep.N) {
-                if (ep.preact) store_out1(ep.preact, off + t, zz[t], ep.out_dtype);
-                store_out1(ep.C, off + t, fg_act_fwd(ep.act, zz[t]), ep.out_dtype);
-            }
+            for (int t = 0; t < 4; ++t)
+                if (col + t < ep.N) {
+                    const float o = ep.mul_saved ? zz[t] * fg_act_grad(ep.mul_act, ep.mul_saved[off + t]) : fg_act_fwd(ep.act, zz[t]);
+                    if (ep.preact) store_out1(ep.preact, off + t, zz[t], ep.out_dtype);
+                    store_out1(ep.C, off + t, o, ep.out_dtype);
+                    if (ep.c_pairs) fg_store_pairs1(ep.c_pairs, ep.c_pairs_stride, off + t, o);
+                    ov[t] = o;
+                }
+        }
+    }
+    if (!ep.colsum_part) return;
+    // column sums over this block's 32 rows: four rows inside each warp, then the eight warps in order
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        ov[t] += __shfl_xor_sync(0xffffffffu, ov[t], 8);
+        ov[t] += __shfl_xor_sync(0xffffffffu, ov[t], 16);
+    }
+    if (lane < 8) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) cs_sm[warp][lane * 4 + t] = ov[t];
+    }
+    __syncthreads();
+    const uint32_t row0 = m0 + (sub >> 3) * 32, c = n0 + (sub & 7u) * 32 + threadIdx.x;
+    if (threadIdx.x < 32 && row0 < ep.M && c < ep.N) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += cs_sm[w][threadIdx.x];
+        ep.colsum_part[(size_t)(row0 >> 5) * ep.N + c] = t;
     }
 }
 
@@ -708,6 +822,8 @@ struct PlaneSet {
     float* p32;
     __nv_bfloat16* p16;
     uint32_t ld32, ld16;
+    uint64_t plane16;      // elements between the two bf16 planes (0: rows * ld16, planes back to back)
+    bool mn;               // storage is [contraction][rows] (rows contiguous): the f32 tensor itself with its pairs
 };
 
 struct SplitArgs {
@@ -886,6 +1002,8 @@ int32_t alloc_planes(fg_ctx* ctx, int fmt, uint32_t rows, uint32_t k, PlaneSet* 
     out->ld16 = round8(k);
     out->p16 = fmt == 0 ? nullptr
                         : (__nv_bfloat16*)((char*)p + align256((uint64_t)rows * round4(k) * 4ull));
+    out->plane16 = 0;
+    out->mn = false;
     return FG_OK;
 }
 
@@ -940,6 +1058,44 @@ int32_t make_tmap(fg_ctx* ctx, CUtensorMap* out, const void* planes, int elem, u
     return FG_OK;
 }
 
+// General 3-D tiled map with the 128- or 64-byte swizzle (by the box's inner extent in bytes).
+int32_t make_tmap3(fg_ctx* ctx, CUtensorMap* out, const void* base, int elem, uint64_t d0, uint64_t d1, uint64_t d2,
+                   uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool atom32 = false) {
+    if (!ctx->tmap_encode) return fg_fail(ctx, FG_ERR_UNSUPPORTED_FEATURE, "cuTensorMapEncodeTiled unavailable");
+    const uint32_t esz = elem ? 2 : 4;
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {b0, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    // atom32: 32-byte chunks permuted within the 128-byte span (what an MN-major tf32 operand needs)
+    const CUtensorMapSwizzle swz = atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                   : b0 * esz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    CUresult r = ((pfn_encode)ctx->tmap_encode)(out, elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : elem == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                                3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(ctx->err, sizeof(ctx->err), "cuTensorMapEncodeTiled failed with code %d", (int)r);
+        return FG_ERR_INTERNAL;
+    }
+    return FG_OK;
+}
+
+// The two maps of one operand of the pair kernel in format 1: `rows` x `kdim` values as an f32 tensor
+// (hi plane or the tensor itself) plus two bf16 planes, tile_rows rows per tile.
+int32_t make_operand_maps(fg_ctx* ctx, const PlaneSet& o, uint32_t rows, uint32_t kdim, uint32_t tile_rows, CUtensorMap* t32,
+                          CUtensorMap* t16) {
+    const uint64_t plane16 = o.plane16 ? o.plane16 : (uint64_t)rows * o.ld16;
+    int32_t s;
+    if (!o.mn) {
+        if ((s = make_tmap3(ctx, t32, o.p32, 0, kdim, rows, 1, (uint64_t)o.ld32 * 4, (uint64_t)rows * o.ld32 * 4, 32, tile_rows, 1)) != FG_OK) return s;
+        return make_tmap3(ctx, t16, o.p16, 1, kdim, rows, 2, (uint64_t)o.ld16 * 2, plane16 * 2, 32, tile_rows, 2);
+    }
+    // [kdim][rows]: boxes of 128 bytes along rows x 32 values of k
+    if ((s = make_tmap3(ctx, t32, o.p32, 0, rows, kdim, 1, (uint64_t)o.ld32 * 4, (uint64_t)kdim * o.ld32 * 4, 32, 32, 1, true)) != FG_OK) return s;
+    return make_tmap3(ctx, t16, o.p16, 1, rows, kdim, 2, (uint64_t)o.ld16 * 2, plane16 * 2, 64, 32, 2);
+}
+
 template <int BN, int BK, int FMT>
 int32_t launch_tc(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilogue& ep) {
     using Cfg = TileCfg<BN, BK>;
@@ -987,12 +1143,14 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
         tmA = tmA16;
         tmB = tmB16;
     } else {
-        if ((s = make_tmap(ctx, &tmA, a.p32, 0, FMT == 0 ? 2 : 1, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
-        if ((s = make_tmap(ctx, &tmB, b.p32, 0, FMT == 0 ? 2 : 1, ep.N, ep.K, b.ld32, Cfg::kBN / 2, BK)) != FG_OK) return s;
         if (FMT == 1) {
-            if ((s = make_tmap(ctx, &tmA16, a.p16, 1, 2, ep.M, ep.K, a.ld16, BM, BK)) != FG_OK) return s;
-            if ((s = make_tmap(ctx, &tmB16, b.p16, 1, 2, ep.N, ep.K, b.ld16, Cfg::kBN / 2, BK)) != FG_OK) return s;
+            if ((s = make_operand_maps(ctx, a, ep.M, ep.K, BM, &tmA, &tmA16)) != FG_OK) return s;
+            if ((s = make_operand_maps(ctx, b, ep.N, ep.K, Cfg::kBN / 2, &tmB, &tmB16)) != FG_OK) return s;
+            ep.a_mn = a.mn ? 1u : 0u;
+            ep.b_mn = b.mn ? 1u : 0u;
         } else {
+            if ((s = make_tmap(ctx, &tmA, a.p32, 0, 2, ep.M, ep.K, a.ld32, BM, BK)) != FG_OK) return s;
+            if ((s = make_tmap(ctx, &tmB, b.p32, 0, 2, ep.N, ep.K, b.ld32, Cfg::kBN / 2, BK)) != FG_OK) return s;
             tmA16 = tmA;
             tmB16 = tmB;
         }
@@ -1104,6 +1262,103 @@ int32_t tc_gemm(fg_ctx* ctx, int fmt, const PlaneSet& a, const PlaneSet& b, uint
     return launch_tc<32, 32, 0>(ctx, a, b, ep);
 }
 
+// ------------------------------------------------------------------------------------
+// f32 tensors with bf16 pairs: the pair kernel multiplies the tensors as they lie in HBM.
+// The kind::tf32 MMA reads the f32 words themselves (it uses sign, exponent and the top 10
+// mantissa bits: hi = trunc(x)); the two cross terms of the split product come from two
+// bf16 planes of the same shape and layout, pairs[0] = bf16(x), pairs[1] = bf16(x - trunc(x)).
+// An operand whose contraction index is not the contiguous one is read through MN-major
+// descriptors, so nothing is ever transposed, and whoever produces a tensor (a GEMM
+// epilogue, the optimizer, the kernels below) writes its pairs in the same pass.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pairs_kernel(const float* __restrict__ x, uint64_t n, __nv_bfloat16* __restrict__ pairs,
+                                                    uint64_t plane_stride) {
+    const uint64_t nv = n >> 2, stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride)
+        fg_store_pairs4(pairs, plane_stride, i * 4, __ldcs(reinterpret_cast<const float4*>(x) + i));
+    for (uint64_t i = (nv << 2) + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        fg_store_pairs1(pairs, plane_stride, i, x[i]);
+}
+
+// dz = dy * act'(saved) over [R, C] with its pairs and the column sums of each 32-row block (the bias
+// gradient's partials), in one pass.  A block covers 32 rows x 512 columns; a thread owns four columns.
+// dz may alias dy.  Needs C % 4 == 0 and 16-byte aligned pointers.
+__global__ void __launch_bounds__(128) dz_pairs_kernel(uint32_t R, uint32_t C, const float* dy, const float* __restrict__ saved,
+                                                       int act, float* dz, __nv_bfloat16* __restrict__ pairs,
+                                                       uint64_t plane_stride, float* __restrict__ colsum_part) {
+    const uint32_t c = (blockIdx.x * 128 + threadIdx.x) * 4;
+    if (c >= C) return;
+    const uint32_t r0 = blockIdx.y * 32, r1 = min(R, r0 + 32);
+    float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (uint32_t r = r0; r < r1; ++r) {
+        const size_t off = (size_t)r * C + c;
+        float4 v = __ldcs(reinterpret_cast<const float4*>(dy + off));
+        if (saved) v = act_mul4(act, v, __ldcs(reinterpret_cast<const float4*>(saved + off)));
+        if (dz) *reinterpret_cast<float4*>(dz + off) = v;
+        if (pairs) fg_store_pairs4(pairs, plane_stride, off, v);
+        cs.x += v.x; cs.y += v.y; cs.z += v.z; cs.w += v.w;
+    }
+    if (colsum_part) *reinterpret_cast<float4*>(colsum_part + (size_t)blockIdx.y * C + c) = cs;
+}
+
+int32_t launch_pairs(fg_ctx* ctx, const float* x, uint64_t n, __nv_bfloat16* pairs, uint64_t plane_stride) {
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SPLIT, 8.0 * (double)n);
+    pairs_kernel<<<fg_stream_grid(ctx, (n + 3) / 4, 256, 8), 256, 0, ctx->stream>>>(x, n, pairs, plane_stride);
+    fg_time_end(ctx, tr);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+int32_t launch_dz_pairs(fg_ctx* ctx, uint32_t R, uint32_t C, const float* dy, const float* saved, int act, float* dz,
+                        __nv_bfloat16* pairs, uint64_t plane_stride, float* colsum_part) {
+    dim3 grid((C + 511) / 512, (R + 31) / 32);
+    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM operand has too many rows");
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SPLIT, 4.0 * R * C * (1.0 + (saved ? 1.0 : 0.0) + (dz ? 1.0 : 0.0) + (pairs ? 1.0 : 0.0)));
+    dz_pairs_kernel<<<grid, 128, 0, ctx->stream>>>(R, C, dy, saved, act, dz, pairs, plane_stride, colsum_part);
+    fg_time_end(ctx, tr);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+// A dense row-major f32 tensor [R, C] and its pairs as an operand of the pair kernel.  `contract_cols`:
+// the contraction runs over the columns (K-major), otherwise over the rows (MN-major).
+PlaneSet paired_operand(const float* x, const void* pairs, uint64_t plane_stride, uint32_t C, bool contract_cols) {
+    PlaneSet o{};
+    o.p32 = const_cast<float*>(x);
+    o.p16 = (__nv_bfloat16*)pairs;
+    o.ld32 = o.ld16 = C;
+    o.plane16 = plane_stride;
+    o.mn = !contract_cols;
+    return o;
+}
+
+// Can [M,N] = [M,K] x [K,N] run on the pair kernel straight from f32 tensors and their pairs?  Every
+// tensor's row pitch must be a multiple of 16 bytes in both element sizes (columns % 8), and the tile
+// shape must suit the pair kernel.
+bool paired_shape_ok(const fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, uint32_t pitch_a, uint32_t pitch_b) {
+    return ctx->tmap_encode && M > (uint32_t)BM && N > 128 && K >= 32 && pitch_a % 8 == 0 && pitch_b % 8 == 0;
+}
+
+struct PairedOut {
+    __nv_bfloat16* pairs;     // optional pairs of the result
+    uint64_t stride;
+    const float* mul_saved;   // optional: result = (acc + bias) * act'(mul_saved)
+    int mul_act;
+    float* colsum_part;       // optional [ceil(M/32)][N]
+};
+
+int32_t paired_gemm(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, uint32_t M, uint32_t N, uint32_t K, float* C,
+                    const float* bias, int act, float* preact, const PairedOut& o) {
+    Epilogue ep{C, bias, preact, M, N, K, act, ctx->dev_status};
+    ep.c_pairs = o.pairs;
+    ep.c_pairs_stride = o.stride;
+    ep.mul_saved = o.mul_saved;
+    ep.mul_act = o.mul_act;
+    ep.colsum_part = o.colsum_part;
+    return launch_tc_pair<32, 1>(ctx, a, b, ep);
+}
+
 // Which path a request takes: 0 = SIMT, otherwise the plane format + 1.
 int pick_path(const fg_ctx* ctx, int mode, uint32_t M, uint32_t N, uint32_t K) {
     if (mode == FG_GEMM_SIMT) return 0;
@@ -1112,6 +1367,85 @@ int pick_path(const fg_ctx* ctx, int mode, uint32_t M, uint32_t N, uint32_t K) {
     if (!ctx->tmap_encode) return 0;
     if (!(M >= 64 && (uint64_t)M * N * K >= (1ull << 22))) return 0;
     return 2;   // AUTO: tf32 main term + bf16 cross terms (same accuracy class, two thirds of the tensor work)
+}
+
+}  // namespace
+
+namespace {
+
+struct PairedArg {
+    const float* x;
+    const void* pairs;      // NULL: made on the fly in the scratch arena
+    uint64_t stride;
+};
+
+// Forward product with every way of running it.  c_pairs (optional) receives the pairs of C.
+int32_t gemm_fwd_core(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB, uint32_t M, uint32_t N, uint32_t K,
+                      PairedArg A, PairedArg B, float* C, const float* bias, int32_t act, float* preact_out,
+                      __nv_bfloat16* c_pairs, uint64_t c_stride) {
+    const uint64_t mn = (uint64_t)M * N;
+    const int path = pick_path(ctx, mode, M, N, K);
+    // The result's pairs, when no GEMM epilogue wrote them.
+    auto pairs_after = [&]() -> int32_t { return c_pairs ? launch_pairs(ctx, C, mn, c_pairs, c_stride) : FG_OK; };
+    if (path == 0) {
+        int32_t s = fg_gemm_simt_launch(ctx, transA, transB, M, N, K, A.x, B.x, C, bias, act, preact_out);
+        return s != FG_OK ? s : pairs_after();
+    }
+    // A skinny output (say 10 classes) is bandwidth-bound on reading A once: no pre-pass, no tensor cores.
+    if (mode == FG_GEMM_AUTO && N <= 16 && !transA && !transB) {
+        const uint64_t need = fg_gemm_skinny_scratch_bytes(M, N, K) + 1024;
+        { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
+        int32_t s = fg_gemm_skinny_n_launch(ctx, M, N, K, A.x, B.x, C, bias, act, preact_out);
+        return s != FG_OK ? s : pairs_after();
+    }
+    const int fmt = path - 1;
+    const uint32_t pitch_a = transA ? M : K, pitch_b = transB ? K : N;
+    const bool aligned = fg_aligned16(A.x) && fg_aligned16(B.x) && fg_aligned16(C) && (!preact_out || fg_aligned16(preact_out));
+    if (fmt == 1 && aligned && paired_shape_ok(ctx, M, N, K, pitch_a, pitch_b) && N % 4 == 0) {
+        // The tensors themselves are the operands; pairs the caller does not keep are made here (8 bytes
+        // of traffic per element, no transposition).
+        const uint64_t mk = (uint64_t)M * K, kn = (uint64_t)K * N;
+        const uint64_t need = (A.pairs ? 0 : mk * 4 + 256) + (B.pairs ? 0 : kn * 4 + 256) + kPairPartialBytes + 1024;
+        { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
+        int32_t s;
+        void* p;
+        if (!A.pairs) {
+            if ((s = fg_ws_alloc(ctx, mk * 4, &p)) != FG_OK) return s;
+            if ((s = launch_pairs(ctx, A.x, mk, (__nv_bfloat16*)p, mk)) != FG_OK) return s;
+            A.pairs = p; A.stride = mk;
+        }
+        if (!B.pairs) {
+            if ((s = fg_ws_alloc(ctx, kn * 4, &p)) != FG_OK) return s;
+            if ((s = launch_pairs(ctx, B.x, kn, (__nv_bfloat16*)p, kn)) != FG_OK) return s;
+            B.pairs = p; B.stride = kn;
+        }
+        // A operand: rows = M; stored [M,K] (contraction along columns) or, transposed, [K,M].
+        const PlaneSet pa = paired_operand(A.x, A.pairs, A.stride, pitch_a, !transA);
+        // B operand: rows = N; stored [K,N] (contraction along rows) or, transposed, [N,K].
+        const PlaneSet pb = paired_operand(B.x, B.pairs, B.stride, pitch_b, transB != 0);
+        return paired_gemm(ctx, pa, pb, M, N, K, C, bias, act, preact_out, PairedOut{c_pairs, c_stride, nullptr, 0, nullptr});
+    }
+    // Operand planes written by a pre-pass (any shape and alignment; the strict 3xTF32 mode).
+    const uint64_t need = planes_bytes(fmt, M, K) + planes_bytes(fmt, N, K) + kPairPartialBytes + 1024;
+    { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
+    PlaneSet pa{}, pb{};
+    int32_t s;
+    if ((s = alloc_planes(ctx, fmt, M, K, &pa)) != FG_OK) return s;
+    if ((s = alloc_planes(ctx, fmt, N, K, &pb)) != FG_OK) return s;
+    // A operand: [M, K] with K contiguous.
+    SplitArgs sa{};
+    sa.x = A.x;
+    if (!transA) { sa.R = M; sa.C = K; sa.n = pa; }
+    else         { sa.R = K; sa.C = M; sa.t = pa; }
+    if ((s = launch_split(ctx, fmt, sa)) != FG_OK) return s;
+    // B operand: [N, K] with K contiguous.
+    SplitArgs sb{};
+    sb.x = B.x;
+    if (!transB) { sb.R = K; sb.C = N; sb.t = pb; }
+    else         { sb.R = N; sb.C = K; sb.n = pb; }
+    if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
+    if ((s = tc_gemm(ctx, fmt, pa, pb, M, N, K, C, bias, act, preact_out)) != FG_OK) return s;
+    return pairs_after();
 }
 
 }  // namespace
@@ -1127,60 +1461,46 @@ int32_t fg_gemm_f32(fg_ctx* ctx, int32_t mode, int32_t transA, int32_t transB, u
     FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_f32: unknown activation");
     FG_REQUIRE(ctx, (uint64_t)M * N < (1ull << 40) && (uint64_t)M * K < (1ull << 40) && (uint64_t)N * K < (1ull << 40),
                "fg_gemm_f32: operand too large");
-    const int path = pick_path(ctx, mode, M, N, K);
-    if (path == 0) return fg_gemm_simt_launch(ctx, transA, transB, M, N, K, A, B, C, bias, act, preact_out);
-    // A skinny output (say 10 classes) is bandwidth-bound on reading A once: no pre-pass, no tensor cores.
-    if (mode == FG_GEMM_AUTO && N <= 16 && !transA && !transB) {
-        const uint64_t need = fg_gemm_skinny_scratch_bytes(M, N, K) + 1024;
-        if (ctx->ws_bytes < need) {
-            int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
-            if (s0 != FG_OK) return s0;
-        }
-        return fg_gemm_skinny_n_launch(ctx, M, N, K, A, B, C, bias, act, preact_out);
-    }
-    const int fmt = path - 1;
-    // Size the arena for both operands before carving it.
-    const uint64_t need = planes_bytes(fmt, M, K) + planes_bytes(fmt, N, K) + kPairPartialBytes + 1024;
-    if (ctx->ws_bytes < need) {
-        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
-        if (s0 != FG_OK) return s0;
-    }
-    PlaneSet pa{}, pb{};
-    int32_t s;
-    if ((s = alloc_planes(ctx, fmt, M, K, &pa)) != FG_OK) return s;
-    if ((s = alloc_planes(ctx, fmt, N, K, &pb)) != FG_OK) return s;
-    // A operand: [M, K] with K contiguous.
-    SplitArgs sa{};
-    sa.x = A;
-    if (!transA) { sa.R = M; sa.C = K; sa.n = pa; }
-    else         { sa.R = K; sa.C = M; sa.t = pa; }
-    if ((s = launch_split(ctx, fmt, sa)) != FG_OK) return s;
-    // B operand: [N, K] with K contiguous.
-    SplitArgs sb{};
-    sb.x = B;
-    if (!transB) { sb.R = K; sb.C = N; sb.t = pb; }
-    else         { sb.R = N; sb.C = K; sb.n = pb; }
-    if ((s = launch_split(ctx, fmt, sb)) != FG_OK) return s;
-    return tc_gemm(ctx, fmt, pa, pb, M, N, K, C, bias, act, preact_out);
+    return gemm_fwd_core(ctx, mode, transA, transB, M, N, K, PairedArg{A, nullptr, 0}, PairedArg{B, nullptr, 0}, C, bias, act,
+                         preact_out, nullptr, 0);
+}
+
+int32_t fg_pairs_from_f32(fg_ctx* ctx, const float* x, uint64_t n, void* pairs, uint64_t plane_stride) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, x && pairs, "fg_pairs_from_f32: NULL pointer");
+    FG_REQUIRE(ctx, fg_aligned16(x) && fg_aligned16(pairs) && plane_stride % 8 == 0 && plane_stride >= n,
+               "fg_pairs_from_f32: pointers must be 16-byte aligned, the plane stride a multiple of 8 and at least n");
+    if (n == 0) return FG_OK;
+    return launch_pairs(ctx, x, n, (__nv_bfloat16*)pairs, plane_stride);
+}
+
+int32_t fg_gemm_paired_f32(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const void* A_pairs,
+                           uint64_t A_stride, const float* B, const void* B_pairs, uint64_t B_stride, float* C,
+                           const float* bias, int32_t act, float* preact_out, void* C_pairs_out, uint64_t C_stride) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, A && B && C, "fg_gemm_paired_f32: NULL operand");
+    FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_paired_f32: dimensions must be >= 1");
+    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_paired_f32: unknown activation");
+    FG_REQUIRE(ctx, (uint64_t)M * N < (1ull << 40) && (uint64_t)M * K < (1ull << 40) && (uint64_t)N * K < (1ull << 40),
+               "fg_gemm_paired_f32: operand too large");
+    FG_REQUIRE(ctx, (!A_pairs || (fg_aligned16(A_pairs) && A_stride % 8 == 0 && A_stride >= (uint64_t)M * K)) &&
+                        (!B_pairs || (fg_aligned16(B_pairs) && B_stride % 8 == 0 && B_stride >= (uint64_t)K * N)) &&
+                        (!C_pairs_out || (fg_aligned16(C_pairs_out) && C_stride % 8 == 0 && C_stride >= (uint64_t)M * N)),
+               "fg_gemm_paired_f32: pairs must be 16-byte aligned with a plane stride that is a multiple of 8 and covers the tensor");
+    return gemm_fwd_core(ctx, FG_GEMM_AUTO, 0, 0, M, N, K, PairedArg{A, A_pairs, A_stride}, PairedArg{B, B_pairs, B_stride}, C,
+                         bias, act, preact_out, (__nv_bfloat16*)C_pairs_out, C_stride);
 }
 
 }  // extern "C"
 
 namespace {
 
-// Backward of one layer.  With exch_buf set, dB and dbias are finished first, the sum of exch_buf over the
-// ranks is started on the exchange stream, and dA is computed while it runs.
-int32_t gemm_bwd_impl(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
-                      const float* dY, int32_t act, const float* saved, float* dA, float* dB, float* dbias,
-                      float* dZ_out, float* exch_buf, uint64_t exch_count) {
-    FG_ENTER(ctx);
-    FG_REQUIRE(ctx, dY != nullptr, "fg_gemm_bwd_f32: dY is NULL");
-    FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_bwd_f32: dimensions must be >= 1");
-    FG_REQUIRE(ctx, mode >= FG_GEMM_AUTO && mode <= FG_GEMM_TF32_BF16X2, "fg_gemm_bwd_f32: unknown mode");
-    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_bwd_f32: unknown activation");
-    FG_REQUIRE(ctx, act == FG_ACT_NONE || saved, "fg_gemm_bwd_f32: the activation backward needs the saved tensor");
-    FG_REQUIRE(ctx, !dA || B, "fg_gemm_bwd_f32: dA needs B");
-    FG_REQUIRE(ctx, !dB || A, "fg_gemm_bwd_f32: dB needs A");
+// Backward of one layer through the SIMT kernels, the narrow-layer kernels or operand planes written by a
+// pre-pass: any shape and alignment.  With exch_buf set, dB and dbias are finished first, the sum of exch_buf
+// over the ranks is started on the exchange stream, and dA is computed while it runs.
+int32_t gemm_bwd_planes(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
+                        const float* dY, int32_t act, const float* saved, float* dA, float* dB, float* dbias,
+                        float* dZ_out, float* exch_buf, uint64_t exch_count) {
     const bool fuse = act != FG_ACT_NONE;
     const int path = pick_path(ctx, mode, M, N, K);
     const uint64_t mn = (uint64_t)M * N;
@@ -1190,10 +1510,7 @@ int32_t gemm_bwd_impl(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_
         const float* dz = dY;
         {
             uint64_t need = mn * 4 + (uint64_t)((M + 255) / 256) * N * 4 + 1024;
-            if (ctx->ws_bytes < need) {
-                int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
-                if (s0 != FG_OK) return s0;
-            }
+            { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
         }
         if (fuse || dZ_out) {
             float* buf = dZ_out;
@@ -1232,10 +1549,7 @@ int32_t gemm_bwd_impl(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_
     if (tc_db) need += planes_bytes(fmt, N, M) + planes_bytes(fmt, K, M) + kPairPartialBytes;
     if (skinny) need += mn * 4 + 256 + fg_gemm_skinny_scratch_bytes(M, N, K);
     if (dbias) need += (uint64_t)((M + 31) / 32) * N * 4 + 256;   // per-tile column sums from the pre-pass
-    if (ctx->ws_bytes < need) {
-        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
-        if (s0 != FG_OK) return s0;
-    }
+    { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
     PlaneSet dz_n{}, dz_t{}, b_n{}, a_t{};
     void* dz_val = dZ_out;
     int32_t s;
@@ -1287,6 +1601,149 @@ int32_t gemm_bwd_impl(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_
     return FG_OK;
 }
 
+// Scratch gemm_bwd_planes may carve (an upper bound over its three routes).
+uint64_t bwd_planes_need(uint32_t M, uint32_t N, uint32_t K) {
+    const uint64_t mn = (uint64_t)M * N;
+    uint64_t need = 4096 + mn * 4 + (uint64_t)((M + 31) / 32) * N * 4;
+    need += planes_bytes(1, M, N) + planes_bytes(1, K, N) + planes_bytes(1, N, M) + planes_bytes(1, K, M) + 2 * kPairPartialBytes;
+    need += fg_gemm_skinny_scratch_bytes(M, N, K);
+    return need;
+}
+
+// Both products of a backward step straight from the f32 tensors and their pairs?
+bool bwd_paired_ok(const fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, bool want_dA, bool want_dB) {
+    if (N % 8 != 0 || K % 8 != 0) return false;
+    if (want_dB && !paired_shape_ok(ctx, K, N, M, K, N)) return false;     // dB [K,N], contraction over M
+    if (want_dA && !paired_shape_ok(ctx, M, K, N, N, N)) return false;     // dA [M,K], contraction over N
+    return want_dA || want_dB;
+}
+
+// Backward of Y = A·B given dZ = dL/dY (already multiplied by this layer's act'), on f32 tensors with pairs:
+//   dB [K,N] = Aᵀ·dZ, then the exchange (if asked for), then
+//   dA [M,K] = (dZ·Bᵀ) * act'(o.mul_saved) with its pairs (o.pairs) and its column sums (dbias_prev [K]) --
+//   i.e. the dZ of the layer below and that layer's bias gradient come out of the dA epilogue.
+// Pairs that are not supplied are made in the scratch arena.  The caller has reserved bwd_paired_need().
+uint64_t bwd_paired_need(uint32_t M, uint32_t N, uint32_t K) {
+    return 4ull * ((uint64_t)M * K + (uint64_t)K * N + (uint64_t)M * N) + (uint64_t)((M + 31) / 32) * K * 4 +
+           2 * kPairPartialBytes + 4096 + fg_gemm_skinny_scratch_bytes(M, N, K) + bwd_planes_need(M, N, K);
+}
+
+int32_t gemm_bwd_paired_core(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, PairedArg A, PairedArg B, PairedArg dZ, float* dB,
+                             float* dA, PairedOut o, float* dbias_prev, float* exch_buf, uint64_t exch_count) {
+    int32_t s;
+    void* p;
+    const uint32_t cs_chunks = (M + 31) / 32;
+    float* cs_part = nullptr;
+    if (dA && dbias_prev) {
+        if ((s = fg_ws_alloc(ctx, (uint64_t)cs_chunks * K * 4, &p)) != FG_OK) return s;
+        cs_part = (float*)p;
+    }
+    if (N <= 16) {
+        // narrow layer: plain-FMA streaming kernels on the tensors themselves
+        if (dB && (s = fg_gemm_skinny_tn_launch(ctx, M, K, N, A.x, dZ.x, dB)) != FG_OK) return s;
+        if (exch_buf && (s = fg_allreduce_sum_f32(ctx, exch_buf, exch_count)) != FG_OK) return s;
+        if (dA) {
+            const fg_skinny_extras ex{o.mul_saved, o.mul_act, o.pairs, o.stride, cs_part};
+            if ((s = fg_gemm_skinny_nt_launch(ctx, M, K, N, dZ.x, B.x, dA, &ex)) != FG_OK) return s;
+            if (cs_part && (s = fg_colsum_fold_launch(ctx, K, cs_chunks, cs_part, dbias_prev)) != FG_OK) return s;
+        }
+        return FG_OK;
+    }
+    const bool aligned = (!dB || (fg_aligned16(A.x) && fg_aligned16(dB))) && (!dA || (fg_aligned16(B.x) && fg_aligned16(dA))) &&
+                         fg_aligned16(dZ.x) && (!o.mul_saved || fg_aligned16(o.mul_saved));
+    if (aligned && bwd_paired_ok(ctx, M, N, K, dA != nullptr, dB != nullptr)) {
+        const uint64_t mk = (uint64_t)M * K, kn = (uint64_t)K * N, mn = (uint64_t)M * N;
+        if (!dZ.pairs) {
+            if ((s = fg_ws_alloc(ctx, mn * 4, &p)) != FG_OK) return s;
+            if ((s = launch_pairs(ctx, dZ.x, mn, (__nv_bfloat16*)p, mn)) != FG_OK) return s;
+            dZ.pairs = p; dZ.stride = mn;
+        }
+        if (dB) {
+            if (!A.pairs) {
+                if ((s = fg_ws_alloc(ctx, mk * 4, &p)) != FG_OK) return s;
+                if ((s = launch_pairs(ctx, A.x, mk, (__nv_bfloat16*)p, mk)) != FG_OK) return s;
+                A.pairs = p; A.stride = mk;
+            }
+            // operands Aᵀ (rows = K) and dZᵀ (rows = N), both read from [M, .] storage: contraction over the rows
+            const PlaneSet pa = paired_operand(A.x, A.pairs, A.stride, K, false);
+            const PlaneSet pz = paired_operand(dZ.x, dZ.pairs, dZ.stride, N, false);
+            if ((s = paired_gemm(ctx, pa, pz, K, N, M, dB, nullptr, FG_ACT_NONE, nullptr, PairedOut{nullptr, 0, nullptr, 0, nullptr})) != FG_OK)
+                return s;
+        }
+        if (exch_buf && (s = fg_allreduce_sum_f32(ctx, exch_buf, exch_count)) != FG_OK) return s;
+        if (dA) {
+            if (!B.pairs) {
+                if ((s = fg_ws_alloc(ctx, kn * 4, &p)) != FG_OK) return s;
+                if ((s = launch_pairs(ctx, B.x, kn, (__nv_bfloat16*)p, kn)) != FG_OK) return s;
+                B.pairs = p; B.stride = kn;
+            }
+            // operands dZ (rows = M) and B (rows = K), both with the contraction index N contiguous
+            const PlaneSet pz = paired_operand(dZ.x, dZ.pairs, dZ.stride, N, true);
+            const PlaneSet pb = paired_operand(B.x, B.pairs, B.stride, N, true);
+            PairedOut po = o;
+            po.colsum_part = cs_part;
+            if ((s = paired_gemm(ctx, pz, pb, M, K, N, dA, nullptr, FG_ACT_NONE, nullptr, po)) != FG_OK) return s;
+            if (cs_part && (s = fg_colsum_fold_launch(ctx, K, cs_chunks, cs_part, dbias_prev)) != FG_OK) return s;
+        }
+        return FG_OK;
+    }
+    // Any other shape: operand planes, then what the dA epilogue would have done as passes of their own.
+    if ((s = gemm_bwd_planes(ctx, FG_GEMM_AUTO, M, N, K, A.x, B.x, dZ.x, FG_ACT_NONE, nullptr, dA, dB, nullptr, nullptr, exch_buf,
+                             exch_count)) != FG_OK)
+        return s;
+    if (!dA) return FG_OK;
+    const uint64_t mk = (uint64_t)M * K;
+    if (K % 4 == 0 && fg_aligned16(dA) && (!o.mul_saved || fg_aligned16(o.mul_saved))) {
+        if (o.mul_saved || o.pairs || cs_part) {
+            if ((s = launch_dz_pairs(ctx, M, K, dA, o.mul_saved, o.mul_act, o.mul_saved ? dA : nullptr, o.pairs, o.stride, cs_part)) != FG_OK)
+                return s;
+            if (cs_part && (s = fg_colsum_fold_launch(ctx, K, cs_chunks, cs_part, dbias_prev)) != FG_OK) return s;
+        }
+        return FG_OK;
+    }
+    if (o.mul_saved && (s = fg_act_bwd_launch(ctx, mk, o.mul_act, dA, o.mul_saved, dA)) != FG_OK) return s;
+    if (o.pairs && (s = launch_pairs(ctx, dA, mk, o.pairs, o.stride)) != FG_OK) return s;
+    if (dbias_prev && (s = fg_colsum_launch(ctx, M, K, dA, dbias_prev)) != FG_OK) return s;
+    return FG_OK;
+}
+
+// Backward of Y = act(A·B + bias) from dY: forms dZ = dY * act'(saved) first.
+int32_t gemm_bwd_impl(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B,
+                      const float* dY, int32_t act, const float* saved, float* dA, float* dB, float* dbias,
+                      float* dZ_out, float* exch_buf, uint64_t exch_count) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, dY != nullptr, "fg_gemm_bwd_f32: dY is NULL");
+    FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_bwd_f32: dimensions must be >= 1");
+    FG_REQUIRE(ctx, mode >= FG_GEMM_AUTO && mode <= FG_GEMM_TF32_BF16X2, "fg_gemm_bwd_f32: unknown mode");
+    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_bwd_f32: unknown activation");
+    FG_REQUIRE(ctx, act == FG_ACT_NONE || saved, "fg_gemm_bwd_f32: the activation backward needs the saved tensor");
+    FG_REQUIRE(ctx, !dA || B, "fg_gemm_bwd_f32: dA needs B");
+    FG_REQUIRE(ctx, !dB || A, "fg_gemm_bwd_f32: dB needs A");
+    const bool fuse = act != FG_ACT_NONE;
+    const int path = pick_path(ctx, mode, M, N, K);
+    const bool aligned = fg_aligned16(dY) && (!saved || fg_aligned16(saved)) && (!dZ_out || fg_aligned16(dZ_out)) &&
+                         (!dA || (fg_aligned16(B) && fg_aligned16(dA))) && (!dB || (fg_aligned16(A) && fg_aligned16(dB)));
+    if (path == 2 && N > 16 && aligned && bwd_paired_ok(ctx, M, N, K, dA != nullptr, dB != nullptr)) {
+        // dZ with its pairs and the bias gradient's partials in one pass, then both products from the tensors themselves
+        const uint64_t mn = (uint64_t)M * N;
+        const uint32_t cs_chunks = (M + 31) / 32;
+        const uint64_t need = bwd_paired_need(M, N, K) + mn * 4 + (uint64_t)cs_chunks * N * 4 + 1024;
+        { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
+        int32_t s;
+        void *pz = nullptr, *dzb = dZ_out, *csp = nullptr;
+        if ((s = fg_ws_alloc(ctx, mn * 4, &pz)) != FG_OK) return s;
+        if (fuse && !dzb && (s = fg_ws_alloc(ctx, mn * 4, &dzb)) != FG_OK) return s;
+        if (dbias && (s = fg_ws_alloc(ctx, (uint64_t)cs_chunks * N * 4, &csp)) != FG_OK) return s;
+        if ((s = launch_dz_pairs(ctx, M, N, dY, fuse ? saved : nullptr, act, (float*)dzb, (__nv_bfloat16*)pz, mn, (float*)csp)) != FG_OK)
+            return s;
+        if (dbias && (s = fg_colsum_fold_launch(ctx, N, cs_chunks, (const float*)csp, dbias)) != FG_OK) return s;
+        const float* dz_src = dzb ? (const float*)dzb : dY;
+        return gemm_bwd_paired_core(ctx, M, N, K, PairedArg{A, nullptr, 0}, PairedArg{B, nullptr, 0}, PairedArg{dz_src, pz, mn}, dB, dA,
+                                    PairedOut{nullptr, 0, nullptr, 0, nullptr}, nullptr, exch_buf, exch_count);
+    }
+    return gemm_bwd_planes(ctx, mode, M, N, K, A, B, dY, act, saved, dA, dB, dbias, dZ_out, exch_buf, exch_count);
+}
+
 }  // namespace
 
 extern "C" {
@@ -1304,6 +1761,37 @@ int32_t fg_gemm_bwd_exchange_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t
     FG_REQUIRE(ctx, exch_buf != nullptr && exch_count > 0, "fg_gemm_bwd_exchange_f32: nothing to exchange");
     if (!ctx->comm) return fg_fail(ctx, FG_ERR_NOT_INITIALIZED, "fg_gemm_bwd_exchange_f32: call fg_comm_init first");
     return gemm_bwd_impl(ctx, mode, M, N, K, A, B, dY, act, saved, dA, dB, dbias, nullptr, exch_buf, exch_count);
+}
+
+int32_t fg_gemm_bwd_paired_f32(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const void* A_pairs,
+                               uint64_t A_stride, const float* B, const void* B_pairs, uint64_t B_stride, const float* dZ,
+                               const void* dZ_pairs, uint64_t dZ_stride, float* dB, float* dbias, float* dA,
+                               int32_t below_act, const float* below_saved, void* dA_pairs_out, uint64_t dA_stride,
+                               float* below_dbias, float* exch_buf, uint64_t exch_count) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, dZ != nullptr, "fg_gemm_bwd_paired_f32: dZ is NULL");
+    FG_REQUIRE(ctx, M >= 1 && N >= 1 && K >= 1, "fg_gemm_bwd_paired_f32: dimensions must be >= 1");
+    FG_REQUIRE(ctx, below_act >= FG_ACT_NONE && below_act <= FG_ACT_GELU, "fg_gemm_bwd_paired_f32: unknown activation");
+    FG_REQUIRE(ctx, below_act == FG_ACT_NONE || below_saved, "fg_gemm_bwd_paired_f32: the activation backward needs the saved tensor");
+    FG_REQUIRE(ctx, !dA || B, "fg_gemm_bwd_paired_f32: dA needs B");
+    FG_REQUIRE(ctx, !dB || A, "fg_gemm_bwd_paired_f32: dB needs A");
+    FG_REQUIRE(ctx, dA || (!dA_pairs_out && !below_dbias), "fg_gemm_bwd_paired_f32: pairs and bias gradient of dA need dA");
+    auto pairs_ok = [](const void* p, uint64_t stride, uint64_t n) { return !p || (fg_aligned16(p) && stride % 8 == 0 && stride >= n); };
+    FG_REQUIRE(ctx, pairs_ok(A_pairs, A_stride, (uint64_t)M * K) && pairs_ok(B_pairs, B_stride, (uint64_t)K * N) &&
+                        pairs_ok(dZ_pairs, dZ_stride, (uint64_t)M * N) && pairs_ok(dA_pairs_out, dA_stride, (uint64_t)M * K),
+               "fg_gemm_bwd_paired_f32: pairs must be 16-byte aligned with a plane stride that is a multiple of 8 and covers the tensor");
+    if (exch_buf && !ctx->comm) return fg_fail(ctx, FG_ERR_NOT_INITIALIZED, "fg_gemm_bwd_paired_f32: call fg_comm_init first");
+    FG_REQUIRE(ctx, !exch_buf || exch_count > 0, "fg_gemm_bwd_paired_f32: nothing to exchange");
+    { int32_t s0 = fg_ws_ensure(ctx, bwd_paired_need(M, N, K)); if (s0 != FG_OK) return s0; }
+    if (dbias) {
+        const int32_t s0 = fg_colsum_launch(ctx, M, N, dZ, dbias);
+        if (s0 != FG_OK) return s0;
+    }
+    const bool mul = below_act != FG_ACT_NONE;
+    return gemm_bwd_paired_core(ctx, M, N, K, PairedArg{A, A_pairs, A_stride}, PairedArg{B, B_pairs, B_stride},
+                                PairedArg{dZ, dZ_pairs, dZ_stride}, dB, dA,
+                                PairedOut{(__nv_bfloat16*)dA_pairs_out, dA_stride, mul ? below_saved : nullptr, below_act, nullptr},
+                                below_dbias, exch_buf, exch_count);
 }
 
 // Batched forms: `batch` independent products, operand t at base + t*stride (strides in elements).
@@ -1444,10 +1932,7 @@ int32_t fg_gemm_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uint32_
     const uint32_t ldk = pad8(K);
     const bool a_direct = in_place16(A, K);
     const uint64_t need = (uint64_t)N * ldk * 2 + (a_direct ? 0 : (uint64_t)M * ldk * 2) + (uint64_t)N * 4 + kPairPartialBytes + 2048;
-    if (ctx->ws_bytes < need) {
-        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
-        if (s0 != FG_OK) return s0;
-    }
+    { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
     int32_t s;
     void *bt, *ac = nullptr, *bias32 = nullptr;
     if ((s = fg_ws_alloc(ctx, (uint64_t)N * ldk * 2, &bt)) != FG_OK) return s;
@@ -1492,10 +1977,7 @@ int32_t fg_gemm_bwd_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uin
     if (dA) need += (dz_direct ? 0 : (uint64_t)M * ldn * 2) + (b_direct ? 0 : (uint64_t)K * ldn * 2);
     if (dB) need += (uint64_t)N * ldm * 2 + (uint64_t)K * ldm * 2;
     if (dbias) need += (uint64_t)nchunk_rows * N * 4 + (uint64_t)N * 4 + 512;
-    if (ctx->ws_bytes < need) {
-        int32_t s0 = fg_ctx_reserve_workspace(ctx, need);
-        if (s0 != FG_OK) return s0;
-    }
+    { int32_t s0 = fg_ws_ensure(ctx, need); if (s0 != FG_OK) return s0; }
     int32_t s;
     void *dz_n = nullptr, *dz_t = nullptr, *cs_part = nullptr;
     Prep16Args pz{};

@@ -19,9 +19,11 @@ __device__ __forceinline__ float sgd_one(float w, float g, float lr, float gs) {
     return w - __fmul_rn(gi, lr);   // keep the product rounded, as the reference's two statements do
 }
 
+// pairs (optional): the bf16 pairs of the updated weights, written in the same pass, so the next GEMM that reads
+// them needs no pre-pass (fg_store_pairs4).
 template <bool ZERO>
 __global__ void __launch_bounds__(256) sgd_kernel(float* __restrict__ w, float* __restrict__ g, uint64_t n,
-                                                  float lr, float gs) {
+                                                  float lr, float gs, __nv_bfloat16* __restrict__ pairs, uint64_t pairs_stride) {
     const uint64_t nv = n >> 2;
     float4* w4 = reinterpret_cast<float4*>(w);
     float4* g4 = reinterpret_cast<float4*>(g);
@@ -33,11 +35,13 @@ __global__ void __launch_bounds__(256) sgd_kernel(float* __restrict__ w, float* 
         a.z = sgd_one(a.z, b.z, lr, gs);
         a.w = sgd_one(a.w, b.w, lr, gs);
         st_stream(w4 + i, a);
+        if (pairs) fg_store_pairs4(pairs, pairs_stride, i * 4, a);
         if (ZERO) st_stream(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
     }
     // tail (n not a multiple of 4)
     for (uint64_t i = (nv << 2) + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         w[i] = sgd_one(w[i], g[i], lr, gs);
+        if (pairs) fg_store_pairs1(pairs, pairs_stride, i, w[i]);
         if (ZERO) g[i] = 0.0f;
     }
 }
@@ -62,7 +66,8 @@ __device__ __forceinline__ void adam_one(float& w, float g, float& m, float& v, 
 template <bool ZERO>
 __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ w, float* __restrict__ g,
                                                     float* __restrict__ m, float* __restrict__ v, uint64_t n,
-                                                    AdamConsts c, uint32_t step, const uint32_t* __restrict__ step_dev) {
+                                                    AdamConsts c, uint32_t step, const uint32_t* __restrict__ step_dev,
+                                                    __nv_bfloat16* __restrict__ pairs, uint64_t pairs_stride) {
     const uint32_t t = step_dev ? *step_dev : step;
     const float inv_bc1 = 1.0f / (1.0f - powf(c.b1, (float)t));
     const float inv_bc2 = 1.0f / (1.0f - powf(c.b2, (float)t));
@@ -79,6 +84,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ w, float
         adam_one(a.z, b.z, mm.z, vv.z, c, inv_bc1, inv_bc2);
         adam_one(a.w, b.w, mm.w, vv.w, c, inv_bc1, inv_bc2);
         st_stream(w4 + i, a);
+        if (pairs) fg_store_pairs4(pairs, pairs_stride, i * 4, a);
         st_stream(m4 + i, mm);
         st_stream(v4 + i, vv);
         if (ZERO) st_stream(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -87,6 +93,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ w, float
         float a = w[i], mm = m[i], vv = v[i];
         adam_one(a, g[i], mm, vv, c, inv_bc1, inv_bc2);
         w[i] = a; m[i] = mm; v[i] = vv;
+        if (pairs) fg_store_pairs1(pairs, pairs_stride, i, a);
         if (ZERO) g[i] = 0.0f;
     }
 }
@@ -95,15 +102,45 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ w, float
 
 extern "C" {
 
-int32_t fg_sgd_step(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr, float grad_scale, int32_t zero_grad) {
+int32_t fg_sgd_step_paired(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr, float grad_scale, int32_t zero_grad,
+                           void* w_pairs, uint64_t pairs_stride) {
     FG_ENTER(ctx);
     FG_REQUIRE(ctx, w && g, "fg_sgd_step: NULL pointer");
     FG_REQUIRE(ctx, fg_aligned16(w) && fg_aligned16(g), "fg_sgd_step: pointers must be 16-byte aligned");
+    FG_REQUIRE(ctx, !w_pairs || (fg_aligned16(w_pairs) && pairs_stride % 8 == 0 && pairs_stride >= n),
+               "fg_sgd_step_paired: pairs must be 16-byte aligned with a plane stride that is a multiple of 8 and at least n");
     if (n == 0) return FG_OK;
     int grid = fg_stream_grid(ctx, (n + 3) / 4, 256, 8);
-    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SGD, (zero_grad ? 16.0 : 12.0) * n);
-    if (zero_grad) sgd_kernel<true><<<grid, 256, 0, ctx->stream>>>(w, g, n, lr, grad_scale);
-    else sgd_kernel<false><<<grid, 256, 0, ctx->stream>>>(w, g, n, lr, grad_scale);
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SGD, ((zero_grad ? 16.0 : 12.0) + (w_pairs ? 4.0 : 0.0)) * n);
+    if (zero_grad) sgd_kernel<true><<<grid, 256, 0, ctx->stream>>>(w, g, n, lr, grad_scale, (__nv_bfloat16*)w_pairs, pairs_stride);
+    else sgd_kernel<false><<<grid, 256, 0, ctx->stream>>>(w, g, n, lr, grad_scale, (__nv_bfloat16*)w_pairs, pairs_stride);
+    fg_time_end(ctx, tr);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+int32_t fg_sgd_step(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr, float grad_scale, int32_t zero_grad) {
+    return fg_sgd_step_paired(ctx, w, g, n, lr, grad_scale, zero_grad, nullptr, 0);
+}
+
+int32_t fg_adamw_step_paired(fg_ctx* ctx, float* w, float* g, float* m, float* v, uint64_t n,
+                             const fg_adamw_hyper* h, uint32_t step, const uint32_t* step_dev, float grad_scale,
+                             int32_t zero_grad, void* w_pairs, uint64_t pairs_stride) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, w && g && m && v && h, "fg_adamw_step: NULL pointer");
+    FG_REQUIRE(ctx, fg_aligned16(w) && fg_aligned16(g) && fg_aligned16(m) && fg_aligned16(v),
+               "fg_adamw_step: pointers must be 16-byte aligned");
+    FG_REQUIRE(ctx, step_dev != nullptr || step >= 1, "fg_adamw_step: step is 1-based");
+    FG_REQUIRE(ctx, h->beta1 >= 0.f && h->beta1 < 1.f && h->beta2 >= 0.f && h->beta2 < 1.f,
+               "fg_adamw_step: betas must lie in [0,1)");
+    FG_REQUIRE(ctx, !w_pairs || (fg_aligned16(w_pairs) && pairs_stride % 8 == 0 && pairs_stride >= n),
+               "fg_adamw_step_paired: pairs must be 16-byte aligned with a plane stride that is a multiple of 8 and at least n");
+    if (n == 0) return FG_OK;
+    AdamConsts c{h->lr, h->beta1, h->beta2, h->eps, h->weight_decay, grad_scale};
+    int grid = fg_stream_grid(ctx, (n + 3) / 4, 256, 8);
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_ADAMW, ((zero_grad ? 32.0 : 28.0) + (w_pairs ? 4.0 : 0.0)) * n);
+    if (zero_grad) adamw_kernel<true><<<grid, 256, 0, ctx->stream>>>(w, g, m, v, n, c, step, step_dev, (__nv_bfloat16*)w_pairs, pairs_stride);
+    else adamw_kernel<false><<<grid, 256, 0, ctx->stream>>>(w, g, m, v, n, c, step, step_dev, (__nv_bfloat16*)w_pairs, pairs_stride);
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
@@ -112,22 +149,7 @@ int32_t fg_sgd_step(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr, float
 int32_t fg_adamw_step(fg_ctx* ctx, float* w, float* g, float* m, float* v, uint64_t n,
                       const fg_adamw_hyper* h, uint32_t step, const uint32_t* step_dev, float grad_scale,
                       int32_t zero_grad) {
-    FG_ENTER(ctx);
-    FG_REQUIRE(ctx, w && g && m && v && h, "fg_adamw_step: NULL pointer");
-    FG_REQUIRE(ctx, fg_aligned16(w) && fg_aligned16(g) && fg_aligned16(m) && fg_aligned16(v),
-               "fg_adamw_step: pointers must be 16-byte aligned");
-    FG_REQUIRE(ctx, step_dev != nullptr || step >= 1, "fg_adamw_step: step is 1-based");
-    FG_REQUIRE(ctx, h->beta1 >= 0.f && h->beta1 < 1.f && h->beta2 >= 0.f && h->beta2 < 1.f,
-               "fg_adamw_step: betas must lie in [0,1)");
-    if (n == 0) return FG_OK;
-    AdamConsts c{h->lr, h->beta1, h->beta2, h->eps, h->weight_decay, grad_scale};
-    int grid = fg_stream_grid(ctx, (n + 3) / 4, 256, 8);
-    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_ADAMW, (zero_grad ? 32.0 : 28.0) * n);
-    if (zero_grad) adamw_kernel<true><<<grid, 256, 0, ctx->stream>>>(w, g, m, v, n, c, step, step_dev);
-    else adamw_kernel<false><<<grid, 256, 0, ctx->stream>>>(w, g, m, v, n, c, step, step_dev);
-    fg_time_end(ctx, tr);
-    FG_LAUNCHED(ctx);
-    return FG_OK;
+    return fg_adamw_step_paired(ctx, w, g, m, v, n, h, step, step_dev, grad_scale, zero_grad, nullptr, 0);
 }
 
 }  // extern "C"

@@ -146,10 +146,32 @@ __device__ __forceinline__ uint64_t make_desc_kmajor(uint32_t smem_addr) {
     return d;
 }
 
+// An MN-major operand tile (the storage has the NON-contraction index contiguous, e.g. A given as
+// [K][M]): rows of 128 bytes along M (32 f32 / 64 bf16) stacked along k, written by a TMA load.
+// 16-bit operands use the ordinary 128-byte swizzle (layout type 2): eight k-rows form one 1024-byte
+// atom.  32-bit (tf32) operands have one MN-major layout only, the 128-byte swizzle with 32-byte
+// atomicity (layout type 1; TMA mode SWIZZLE_128B_ATOM_32B): 32-byte chunks are permuted over FOUR
+// k-rows, so an atom is 512 bytes.  `k_group_bytes` (stride byte offset) is the distance between
+// consecutive atoms along k, `mn_block_bytes` (leading byte offset) the distance between consecutive
+// 128-byte-wide column blocks of the tile.
+__device__ __forceinline__ uint64_t make_desc_mnmajor(uint32_t smem_addr, uint32_t mn_block_bytes, uint32_t k_group_bytes,
+                                                      uint32_t layout_type) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((k_group_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout_type << 61;
+    return d;
+}
+
 // Instruction descriptor: D = f32, A and B of format `fmt` (0 f16, 1 bf16, 2 tf32), both K-major.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
+// Bits that mark an operand as MN-major (allowed for f16, bf16 and tf32 operands).
+constexpr uint32_t kIdescAMnMajor = 1u << 15;
+constexpr uint32_t kIdescBMnMajor = 1u << 16;
 
 // ---- CTA pairs (cta_group::2): one MMA spans the tensor cores and tensor memory of two SMs ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -11,6 +11,13 @@ grad_tensors, `dact` the seed (dL/dout) and the intermediate gradients, `loss_ro
 (W0, b0, W1, b1, ...), with gradients and optimizer moments in arenas of the same layout,
 so the update is a single fused pass and each layer's gradient is one contiguous range
 for the allreduce.
+
+In the default GEMM mode every tensor a tensor-core GEMM reads (weights, activations, the
+gradients dZ) keeps its bf16 pairs beside it, written by whoever writes the tensor: the
+forward epilogue, the dA epilogue (which also applies the activation derivative of the
+layer below and sums the columns for its bias gradient), the narrow layer's dA kernel and
+the optimizer.  No operand pre-pass and no transposition is left in the step; only the
+input batch, which arrives from outside, gets its pairs from a kernel of its own.
 """
 import numpy as np
 
@@ -76,6 +83,13 @@ class MLPTrainer:
         self.loss_out = ctx.alloc_zeroed(256)     # one float: mean CE loss, or summed squared error
         self.plan = None
         self.steps_done = 0
+        # ---- bf16 pairs (default GEMM mode): weights [2][n_arena], activations and dZ [2][B*d] each ----
+        self.paired = gemm_mode == "auto"
+        if self.paired:
+            self.w_pairs = ctx.alloc_zeroed(2 * self.n_arena * 2)
+            self.act_pairs = [ctx.alloc(2 * B * self.dims[l] * 2) for l in range(self.L)]
+            # dz[l] = dL/d(pre-activation of layer l) lives in dact[l + 1]; the top layer's comes from the loss kernel
+            self.dz_pairs = [ctx.alloc(2 * B * self.dims[l + 1] * 2) if l < self.L - 1 else None for l in range(self.L)]
 
     # ---- parameter access ----
     def W(self, l):
@@ -96,6 +110,8 @@ class MLPTrainer:
             arena[self.w_off[l]:self.w_off[l] + W[l].size] = np.asarray(W[l], np.float32).ravel()
             arena[self.b_off[l]:self.b_off[l] + b[l].size] = np.asarray(b[l], np.float32).ravel()
         self.ctx.upload(self.params, arena)
+        if self.paired:
+            self.ctx.pairs_from_f32(self.params, self.n_arena, self.w_pairs, self.n_arena)
 
     def _split(self, arena):
         W = [arena[self.w_off[l]:self.w_off[l] + self.dims[l] * self.dims[l + 1]]
@@ -162,8 +178,56 @@ class MLPTrainer:
         self.ctx.prefetch_mark()
 
     # ---- one training step, enqueued on the context's stream ----
+    def Wp(self, l):
+        return self.w_pairs.ptr + 2 * self.w_off[l]
+
+    def _enqueue_step_paired(self):
+        """The step on f32 tensors with bf16 pairs: no operand pre-pass between the GEMMs."""
+        c, B, L, d = self.ctx, self.batch, self.L, self.dims
+        c.pairs_from_f32(self.x, B * d[0], self.act_pairs[0])
+        for l in range(L):
+            a = self.act if l < L - 1 else "none"
+            c.gemm_paired(self.act_buf[l], self.W(l), self.act_buf[l + 1], B, d[l + 1], d[l],
+                          A_pairs=self.act_pairs[l], B_pairs=self.Wp(l), B_stride=self.n_arena, bias=self.b(l), act=a,
+                          preact_out=self.pre_buf[l], C_pairs=self.act_pairs[l + 1] if l + 1 < L else None)
+        od = d[-1]
+        if self.loss_kind == "ce":
+            c.softmax_ce(self.act_buf[L], self.target, B, od, grad_scale=self.grad_scale, loss_row=self.loss_row,
+                         loss_mean=self.loss_out, dlogits=self.dact[L])
+        else:
+            c.mse_loss_grad(self.act_buf[L], self.target, B * od, grad_scale=self.grad_scale,
+                            loss_sum=self.loss_out, grad=self.dact[L])
+        pend_hi = self.n_arena
+        exchanged = []
+        for l in range(L - 1, -1, -1):
+            # the layer below (l - 1) has the hidden activation; its saved tensor is its pre-activation (GELU)
+            # or its output, which is this layer's input
+            below = self.act if l > 0 else "none"
+            below_saved = None if l == 0 else (self.pre_buf[l - 1] if self.act == "gelu" else self.act_buf[l])
+            lo = self.layer_range[l][0]
+            exch = self.world > 1 and self.overlap and (l == 0 or pend_hi - lo >= self.min_exchange)
+            c.gemm_bwd_paired(self.act_buf[l], self.W(l), self.dact[l + 1], B, d[l + 1], d[l],
+                              A_pairs=self.act_pairs[l], B_pairs=self.Wp(l), B_stride=self.n_arena,
+                              dZ_pairs=self.dz_pairs[l], dB=self.gW(l), dbias=self.gb(l) if l == L - 1 else None,
+                              dA=self.dact[l] if l > 0 else None, below_act=below, below_saved=below_saved,
+                              dA_pairs=self.dz_pairs[l - 1] if l > 0 else None,
+                              below_dbias=self.gb(l - 1) if l > 0 else None,
+                              exch_buf=self.grads.ptr + 4 * lo if exch else None, exch_count=pend_hi - lo if exch else 0)
+            if exch:
+                # NOTE: the bias gradient of layer l - 1 is written by this call's dA epilogue, after the
+                # exchange of [lo, pend_hi) has started; it belongs to the range below lo, exchanged later.
+                if len(exchanged) < 7:
+                    c.comm_checkpoint(len(exchanged))
+                    exchanged.append((lo, pend_hi, len(exchanged)))
+                else:
+                    exchanged.append((lo, pend_hi, -1))
+                pend_hi = lo
+        return exchanged
+
     def enqueue_step(self):
         c, B, L = self.ctx, self.batch, self.L
+        if self.paired:
+            return self._finish_step(self._enqueue_step_paired())
         for l in range(L):
             a = self.act if l < L - 1 else "none"
             c.gemm(self.act_buf[l], self.W(l), self.act_buf[l + 1], B, self.dims[l + 1], self.dims[l],
@@ -199,6 +263,10 @@ class MLPTrainer:
                 pend_hi = lo
             else:
                 c.gemm_bwd(*args, **kw)
+        self._finish_step(exchanged)
+
+    def _finish_step(self, exchanged):
+        c = self.ctx
         # gradients were computed with the global-mean scale, so the sum over ranks needs no further factor
         if self.opt[0] == "adamw":
             c.counter_increment(self.step_counter)
@@ -220,12 +288,14 @@ class MLPTrainer:
     def _update(self, lo, hi):
         """The optimizer step on arena elements [lo, hi)."""
         c, off, n = self.ctx, 4 * lo, hi - lo
+        wp = self.w_pairs.ptr + 2 * lo if self.paired else None      # the updated weights' pairs, same pass
         if self.opt[0] == "adamw":
             _, lr, b1, b2, eps, wd = self.opt
-            c.adamw_step(self.params.ptr + off, self.grads.ptr + off, self.m.ptr + off, self.v.ptr + off, n, lr, b1, b2,
-                         eps, wd, step=0, step_dev=self.step_counter, zero_grad=False)
+            c.adamw_step_paired(self.params.ptr + off, self.grads.ptr + off, self.m.ptr + off, self.v.ptr + off, n, lr,
+                                b1, b2, eps, wd, wp, self.n_arena, step=0, step_dev=self.step_counter, zero_grad=False)
         elif self.opt[0] == "sgd":
-            c.sgd_step(self.params.ptr + off, self.grads.ptr + off, n, self.opt[1], zero_grad=False)
+            c.sgd_step_paired(self.params.ptr + off, self.grads.ptr + off, n, self.opt[1], wp, self.n_arena,
+                              zero_grad=False)
 
     def step(self):
         """Eager step (one launch per kernel)."""

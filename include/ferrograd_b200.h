@@ -60,8 +60,11 @@ enum fg_gemm_mode {
                            (crates/ferrograd-nn/src/op/matmul/generic.rs:98-319) */
     FG_GEMM_3XTF32 = 2, /* tcgen05 kind::tf32, hi/lo split, three MMAs per k-step */
     FG_GEMM_TF32_BF16X2 = 3 /* the dominant hi*hi term as kind::tf32, the two cross terms
-                               (lo*hi, hi*lo: 2^-12 of the product) as bf16 MMAs: two
-                               tf32-units of tensor work per product instead of three */
+                               (lo*hi, hi*lo: 2^-11 of the product) as bf16 MMAs: two
+                               tf32-units of tensor work per product instead of three.
+                               Shapes whose dimensions are multiples of 8 are multiplied
+                               straight from the f32 tensors (see "f32 tensors with bf16
+                               pairs" below); others go through operand planes */
 };
 
 typedef struct fg_ctx fg_ctx;   /* one device + one stream (rocm/mod.rs:58-78)   */
@@ -166,6 +169,49 @@ int32_t fg_gemm_bwd_exchange_f32(fg_ctx* ctx, int32_t mode, uint32_t M, uint32_t
                                  float* dA, float* dB, float* dbias,
                                  float* exch_buf, uint64_t exch_count);
 
+/* ---- f32 tensors with bf16 pairs: the default GEMM mode without any operand pre-pass ----
+ * (No counterpart in the reference; it serves the same rule as its prologue fusion, kernel/forward.rs:373-457:
+ * nothing elementwise runs as a pass of its own between two matmuls.)
+ * In the default mode a product a*b is computed as trunc(a)*trunc(b) on kind::tf32 -- the tensor core reads
+ * the f32 words themselves and ignores their low 13 mantissa bits -- plus two bf16 cross terms.  The cross
+ * terms come from the tensor's PAIRS: two bf16 planes with the tensor's own shape and layout,
+ *   pairs[i] = bf16(x[i]),   pairs[plane_stride + i] = bf16(x[i] - trunc(x[i])),
+ * `plane_stride` (elements, a multiple of 8, at least the tensor's size) apart; pairs are 16-byte aligned.
+ * fg_gemm_f32 / fg_gemm_bwd_f32 make the pairs of their operands on every call (8 bytes of traffic per
+ * element).  A caller that keeps each tensor's pairs beside it pays nothing: every entry point that writes
+ * a tensor can write its pairs in the same pass (the GEMM epilogues below, fg_adamw_step_paired,
+ * fg_sgd_step_paired), and fg_pairs_from_f32 makes them for tensors that arrive from outside.  Operands are
+ * never transposed: the product that contracts over a tensor's rows reads it through MN-major descriptors.
+ * Shapes the pair kernel cannot take (a dimension that is not a multiple of 8, tiny matrices, N <= 16)
+ * are computed as fg_gemm_f32 would, with the same results and outputs. */
+int32_t fg_pairs_from_f32(fg_ctx* ctx, const float* x, uint64_t n, void* pairs, uint64_t plane_stride);
+/* C[M,N] = act(A[M,K]·B[K,N] + bias), as fg_gemm_f32 in FG_GEMM_AUTO mode.  A_pairs / B_pairs may be NULL
+ * (made on the fly).  C_pairs_out (may be NULL) receives the pairs of C. */
+int32_t fg_gemm_paired_f32(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K,
+                           const float* A, const void* A_pairs, uint64_t A_stride,
+                           const float* B, const void* B_pairs, uint64_t B_stride,
+                           float* C, const float* bias, int32_t act, float* preact_out,
+                           void* C_pairs_out, uint64_t C_stride);
+/* Backward of Y = A[M,K]·B[K,N] given dZ = dL/dY with this layer's own activation factor already applied
+ * (matmul backward edges: op/matmul/mod.rs:75-101):
+ *   dB [K,N] = Aᵀ·dZ                                   (skipped when dB == NULL)
+ *   dbias [N] = column sums of dZ                      (skipped when NULL; meant for the top layer, whose dZ
+ *                                                       comes from the loss and not from a dA epilogue)
+ *   then, when exch_buf != NULL, the sum of exch_buf[0..exch_count) over the ranks is started as by
+ *   fg_allreduce_sum_f32 (see fg_gemm_bwd_exchange_f32), and beside it
+ *   dA [M,K] = (dZ·Bᵀ) ⊙ act'(below_saved)             (skipped when dA == NULL)
+ * where below_act / below_saved describe the layer BELOW (the one whose output A is; FG_ACT_NONE: no
+ * factor), so dA is that layer's dZ, ready to be passed to its own backward call.  dA_pairs_out (may be
+ * NULL) receives dA's pairs and below_dbias (may be NULL, [K]) its column sums, the bias gradient of the
+ * layer below -- all from the dA epilogue.  Any of the input pairs may be NULL. */
+int32_t fg_gemm_bwd_paired_f32(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K,
+                               const float* A, const void* A_pairs, uint64_t A_stride,
+                               const float* B, const void* B_pairs, uint64_t B_stride,
+                               const float* dZ, const void* dZ_pairs, uint64_t dZ_stride,
+                               float* dB, float* dbias, float* dA, int32_t below_act, const float* below_saved,
+                               void* dA_pairs_out, uint64_t dA_stride, float* below_dbias,
+                               float* exch_buf, uint64_t exch_count);
+
 /* Rank-3 matmul: `batch` independent products; product t uses A + t*strideA, B + t*strideB and
  * C (or dY, saved, preact_out) + t*strideC, strides in elements.  The reference steps every operand
  * by one matrix per Z index (kernel/forward.rs:159-190, op/matmul/generic.rs:131,194).  Each stride
@@ -257,6 +303,13 @@ typedef struct fg_adamw_hyper {
 int32_t fg_adamw_step(fg_ctx* ctx, float* w, float* g, float* m, float* v, uint64_t n,
                       const fg_adamw_hyper* hyper, uint32_t step, const uint32_t* step_dev,
                       float grad_scale, int32_t zero_grad);
+/* The same updates, also writing the bf16 pairs of the updated weights (see fg_gemm_paired_f32) in the same
+ * pass: +4 bytes per parameter.  w_pairs == NULL: exactly fg_sgd_step / fg_adamw_step. */
+int32_t fg_sgd_step_paired(fg_ctx* ctx, float* w, float* g, uint64_t n, float lr, float grad_scale,
+                           int32_t zero_grad, void* w_pairs, uint64_t pairs_stride);
+int32_t fg_adamw_step_paired(fg_ctx* ctx, float* w, float* g, float* m, float* v, uint64_t n,
+                             const fg_adamw_hyper* hyper, uint32_t step, const uint32_t* step_dev,
+                             float grad_scale, int32_t zero_grad, void* w_pairs, uint64_t pairs_stride);
 int32_t fg_counter_increment(fg_ctx* ctx, uint32_t* counter_dev);
 
 /* ---- fused elementwise chains (op/binary.rs add :74, mul :236, sub :449, div :644;
