@@ -204,6 +204,10 @@ class GpuContext:
         return self.download(t, out)
 
     # ---- misc ----
+    def set_option(self, name, value):
+        """fg_ctx_set_option: "gemm_tile", "gemm_split_k", "gemm_pairs", "exec_plans", "comm_max_ctas", "comm_sms"."""
+        self._check(self.lib.fg_ctx_set_option(self.handle, name.encode(), str(value).encode()))
+
     def stream(self):
         return self.lib.fg_ctx_stream(self.handle)
 

@@ -5,6 +5,7 @@
 // crates/fused_gpu/src/dispatch/backend/rocm/mod.rs:58-421): one device, one stream,
 // synchronous upload/download, asynchronous dispatch, schedules as captured graphs.
 #include <dlfcn.h>
+#include <stdlib.h>
 #include <time.h>
 #include <limits.h>
 
@@ -62,6 +63,7 @@ int32_t fg_ws_alloc(fg_ctx* ctx, uint64_t bytes, void** out) {
         if (ctx->ws) cudaFree(ctx->ws);
         ctx->ws = nullptr;
         ctx->ws_bytes = 0;
+        ctx->ws_generation++;      // plans recorded against the old arena must not be replayed (fg_plan_launch checks)
         uint64_t want = need + need / 4;
         cudaError_t e = cudaMalloc((void**)&ctx->ws, want);
         if (e != cudaSuccess) return fg_fail_cuda(ctx, FG_ERR_OUT_OF_MEMORY, "scratch arena", e);
@@ -94,6 +96,38 @@ extern "C" {
 
 const char* fg_version(void) { return "ferrograd_b200 0.1 (sm_100a)"; }
 
+int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value) {
+    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_REQUIRE(ctx, name && value, "fg_ctx_set_option: NULL argument");
+    auto truth = [&](bool* dst) -> int32_t {
+        if (!strcmp(value, "1") || !strcmp(value, "on")) { *dst = true; return FG_OK; }
+        if (!strcmp(value, "0") || !strcmp(value, "off")) { *dst = false; return FG_OK; }
+        return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_ctx_set_option: the value must be 0, 1, on or off");
+    };
+    if (!strcmp(name, "gemm_tile")) {
+        int x = 0, y = 0;
+        if (!strcmp(value, "auto")) { ctx->opt_tile_pair = -1; return FG_OK; }
+        if (!strcmp(value, "pair")) { ctx->opt_tile_pair = 1; return FG_OK; }
+        if (sscanf(value, "%dx%d", &x, &y) == 2 && (x == 256 || x == 128) && (y == 32 || y == 16)) {
+            ctx->opt_tile_pair = 0; ctx->opt_tile_bn = x; ctx->opt_tile_bk = y;
+            return FG_OK;
+        }
+        return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_ctx_set_option: gemm_tile is auto, pair, 256x32, 256x16, 128x32 or 128x16");
+    }
+    if (!strcmp(name, "gemm_split_k")) return truth(&ctx->opt_split_k);
+    if (!strcmp(name, "gemm_pairs")) return truth(&ctx->opt_pairs);
+    if (!strcmp(name, "exec_plans")) return truth(&ctx->opt_exec_plans);
+    if (!strcmp(name, "comm_max_ctas") || !strcmp(name, "comm_sms")) {
+        char* end = nullptr;
+        const long v = strtol(value, &end, 10);
+        if (end == value || *end || v < 0 || v > 1024) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_ctx_set_option: not a count");
+        if (!strcmp(name, "comm_max_ctas")) ctx->opt_comm_max_ctas = (int)v;
+        else ctx->comm_reserved_sms = (v > ctx->sm_count / 2) ? 0 : (int)v;
+        return FG_OK;
+    }
+    return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_ctx_set_option: unknown option");
+}
+
 int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out) {
     if (!out) return FG_ERR_INVALID_ARGUMENT;
     *out = nullptr;
@@ -109,6 +143,19 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     memset(c, 0, sizeof(*c));
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
+    c->opt_tile_pair = -1;
+    c->opt_split_k = true;
+    c->opt_pairs = true;
+    c->opt_exec_plans = true;
+    c->opt_comm_max_ctas = 12;
+    c->comm_reserved_sms = 16;
+    // the environment gives initial values, once
+    if (const char* e = getenv("FG_GEMM_TILE")) fg_ctx_set_option(c, "gemm_tile", e);
+    if (getenv("FG_GEMM_NO_SPLITK")) c->opt_split_k = false;
+    if (getenv("FG_GEMM_NO_PAIRS")) c->opt_pairs = false;
+    if (getenv("FG_EXEC_NO_PLANS")) c->opt_exec_plans = false;
+    if (const char* e = getenv("NCCL_MAX_CTAS")) fg_ctx_set_option(c, "comm_max_ctas", e);
+    if (const char* e = getenv("FG_COMM_SMS")) fg_ctx_set_option(c, "comm_sms", e);
     if (cuda_stream) {
         c->stream = (cudaStream_t)cuda_stream;
         c->own_stream = false;
@@ -439,6 +486,7 @@ int32_t fg_plan_end(fg_ctx* ctx, fg_plan** out) {
     if (!p) { cudaGraphDestroy(graph); return fg_fail(ctx, FG_ERR_OUT_OF_MEMORY, "fg_plan_end"); }
     p->graph = graph;
     p->launches = ctx->capture_launches;
+    p->ws_generation = ctx->ws_generation;
     e = cudaGraphInstantiate(&p->exec, graph, 0);
     if (e != cudaSuccess) { cudaGraphDestroy(graph); delete p; return fg_fail_cuda(ctx, FG_ERR_INTERNAL, "cudaGraphInstantiate", e); }
     *out = p;
@@ -449,6 +497,12 @@ int32_t fg_plan_launch(fg_ctx* ctx, fg_plan* plan) {
     if (!ctx) return FG_ERR_NOT_INITIALIZED;
     FG_REQUIRE(ctx, plan != nullptr, "fg_plan_launch: plan is NULL");
     if (ctx->capturing) return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE, "fg_plan_launch while recording");
+    // The recorded kernels carry addresses inside the scratch arena as it was at recording time.  If an eager
+    // call has grown (reallocated) the arena since, replaying would read and write freed memory: refuse.
+    if (plan->ws_generation != ctx->ws_generation)
+        return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE,
+                       "fg_plan_launch: the scratch arena was reallocated after this plan was recorded; record it again "
+                       "(fg_ctx_reserve_workspace before recording avoids this)");
     FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
     FG_CUDA(ctx, FG_ERR_LAUNCH_FAILURE, cudaGraphLaunch(plan->exec, ctx->stream));
     ctx->launches += plan->launches;
@@ -490,16 +544,12 @@ int32_t fg_comm_init(fg_ctx* ctx, int32_t nranks, int32_t rank, const uint8_t id
     // persistent: if it took every SM the exchange would start only when it ended, and if the exchange
     // took some first the GEMM's last CTAs would start late with a full share of tiles.  So the exchange
     // is held to 12 CTAs (unless the caller's environment says otherwise) and the GEMM leaves 16 SMs free
-    // while one is in flight.  FG_COMM_SMS overrides the number; 0 turns the reservation off.  Measured on
+    // while one is in flight (options comm_max_ctas and comm_sms; comm_sms 0 turns the reservation off).  Measured on
     // two GPUs (config-4 step, ms): 12 CTAs / 16 SMs 2.04, 8 / 12 2.03-2.07, 16 / 20 2.12, 4 / 8 2.42
     // (exchange-bound), no reservation 2.15-2.18; one GPU alone 1.96-2.00.
     // The limit is given in the communicator's own options: NCCL reads its environment once per process,
     // so a variable set here would be missed whenever another communicator (the host framework's) came first.
-    int max_ctas = 12;
-    if (const char* e = getenv("NCCL_MAX_CTAS")) max_ctas = atoi(e);
-    ctx->comm_reserved_sms = 16;
-    if (const char* e = getenv("FG_COMM_SMS")) ctx->comm_reserved_sms = atoi(e);
-    if (ctx->comm_reserved_sms < 0 || ctx->comm_reserved_sms > ctx->sm_count / 2) ctx->comm_reserved_sms = 0;
+    const int max_ctas = ctx->opt_comm_max_ctas;
     auto init_cfg = (pfn_ncclCommInitRankConfig)dlsym(ctx->nccl_lib, "ncclCommInitRankConfig");
     auto get_ver = (pfn_ncclGetVersion)dlsym(ctx->nccl_lib, "ncclGetVersion");
     int nccl_ver = 0;

@@ -22,6 +22,7 @@ struct fg_plan {
     cudaGraph_t graph;
     cudaGraphExec_t exec;
     uint64_t launches;  // kernels recorded in the graph
+    uint64_t ws_generation;   // the scratch arena whose addresses the recorded kernels carry
 };
 
 // One timed launch: events on the launching stream around a single kernel.
@@ -64,6 +65,14 @@ struct fg_ctx {
     void* nccl_lib;
     void* comm;
     int nranks, rank;
+    // Options (fg_ctx_set_option); the FG_* environment variables give their initial values once, at creation.
+    int opt_tile_pair;          // -1: chosen per shape; 1: CTA pairs whenever the shape allows; 0: opt_tile_bn x opt_tile_bk
+    int opt_tile_bn, opt_tile_bk;
+    bool opt_split_k;           // split-K tail of the pair kernel
+    bool opt_pairs;             // multiply f32 tensors as they lie (bf16 pairs) where the shape allows
+    bool opt_exec_plans;        // the graph engine records each dispatch as a CUDA graph
+    int opt_comm_max_ctas;      // CTAs the communicator may use (fg_comm_init)
+    uint64_t ws_generation;     // bumped whenever the scratch arena is reallocated
 };
 
 inline int32_t fg_fail(fg_ctx* ctx, int32_t code, const char* msg) {
@@ -162,6 +171,37 @@ __device__ __forceinline__ float fg_act_grad(int act, float saved) {
             fg_gelu_fwd(saved, &t);
             float du = FG_GELU_B * (1.0f + (FG_GELU_A * 3.0f) * (saved * saved));
             return 0.5f * ((1.0f + t) + (1.0f - t * t) * (saved * du));
+        }
+        default: return 1.0f;
+    }
+}
+
+// ---- the same activations for GEMM epilogues ----
+// An epilogue runs while the tensor core is already on the next tile and must be done before the two
+// accumulators it can run ahead by are full, so its arithmetic is kept short: tanh through one fast
+// exponential and one reciprocal, 0.5*(1 + tanh(u)) = 1 / (1 + exp(-2u)).  For GELU this form has no
+// cancellation at all; results agree with the libm forms above to a few 1e-7 of the output's scale.
+__device__ __forceinline__ float fg_sigmoid_fast(float a) { return __frcp_rn(1.0f + __expf(-a)); }
+
+__device__ __forceinline__ float fg_act_fwd_fast(int act, float z) {
+    switch (act) {
+        case FG_ACT_RELU: return z > 0.0f ? z : 0.0f;
+        case FG_ACT_TANH: return 2.0f * fg_sigmoid_fast(2.0f * z) - 1.0f;
+        case FG_ACT_GELU: return z * fg_sigmoid_fast((2.0f * FG_GELU_B) * (z + (z * z * z) * FG_GELU_A));
+        default: return z;
+    }
+}
+
+__device__ __forceinline__ float fg_act_grad_fast(int act, float saved) {
+    switch (act) {
+        case FG_ACT_RELU: return saved > 0.0f ? 1.0f : 0.0f;
+        case FG_ACT_TANH: return 1.0f - saved * saved;
+        case FG_ACT_GELU: {
+            // s = 0.5*(1 + tanh(u)); 1 - tanh(u)^2 = 4*s*(1 - s); gelu' = s + 0.5*x*(1 - tanh^2)*du/dx
+            const float xx = saved * saved;
+            const float s = fg_sigmoid_fast((2.0f * FG_GELU_B) * (saved + (xx * saved) * FG_GELU_A));
+            const float du = FG_GELU_B * (1.0f + (FG_GELU_A * 3.0f) * xx);
+            return s + (2.0f * saved) * (s * (1.0f - s)) * du;
         }
         default: return 1.0f;
     }

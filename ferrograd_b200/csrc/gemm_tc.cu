@@ -24,6 +24,7 @@
 // multiples).  One 3-D tensor map per operand: dims {contraction, rows, 2},
 // box {32, tile rows, 2}, so one load brings the hi and the lo tile of a k-block.
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "fg_internal.cuh"
 #include "ptx_sm100.cuh"
@@ -56,6 +57,9 @@ struct Epilogue {
     const float* mul_saved;           // optional [M,N]: C = (acc + bias) * act'(mul_saved), act = mul_act
     int mul_act;
     float* colsum_part;               // optional [ceil(M/32)][N]: column sums of the stored C per 32-row block
+#ifdef FG_GEMM_PROFILE
+    uint32_t dbg;                     // diagnostic build: bit 0 = leave out the global stores of the epilogue
+#endif
 };
 
 // Element stores in the output's storage type (idx in elements).
@@ -101,12 +105,12 @@ __host__ __device__ __forceinline__ void pair_tile_origin(uint32_t tile, uint32_
 // site; an epilogue that is unrolled over a thread's 128 accumulators would carry 128 copies and run out
 // of instruction cache (measured on the pair kernel: 45,000 cycles for ~1,000 useful instructions).
 __device__ __noinline__ float4 act_fwd4(int act, float4 z) {
-    return make_float4(fg_act_fwd(act, z.x), fg_act_fwd(act, z.y), fg_act_fwd(act, z.z), fg_act_fwd(act, z.w));
+    return make_float4(fg_act_fwd_fast(act, z.x), fg_act_fwd_fast(act, z.y), fg_act_fwd_fast(act, z.z), fg_act_fwd_fast(act, z.w));
 }
 // z * act'(saved): the backward factor of the layer below, applied while a dA tile is stored.
 __device__ __noinline__ float4 act_mul4(int act, float4 z, float4 sv) {
-    return make_float4(z.x * fg_act_grad(act, sv.x), z.y * fg_act_grad(act, sv.y), z.z * fg_act_grad(act, sv.z),
-                       z.w * fg_act_grad(act, sv.w));
+    return make_float4(z.x * fg_act_grad_fast(act, sv.x), z.y * fg_act_grad_fast(act, sv.y), z.z * fg_act_grad_fast(act, sv.z),
+                       z.w * fg_act_grad_fast(act, sv.w));
 }
 
 template <int BN, int BK>
@@ -119,6 +123,18 @@ struct TileCfg {
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators (ping-pong)
     static constexpr int kColsPerThread = BN / 2;                 // each lane quarter is shared by two warps
 };
+
+#ifdef FG_GEMM_PROFILE
+// Diagnostic build only (-DFG_GEMM_PROFILE): cycle counters of the pair kernel's roles, summed over CTAs.
+// 0 MMA wait for a drained accumulator, 1 MMA wait for loads, 2 MMA loop total, 3 epilogue (warp 2) wait for a
+// finished chunk, 4 epilogue store phase, 5 units, 6 producer wait for a free stage, 7 reporting CTAs.
+__device__ unsigned long long g_prof[8];
+#define PROF_T0() const long long _pt0 = clock64()
+#define PROF_ADD(var) var += clock64() - _pt0
+#else
+#define PROF_T0()
+#define PROF_ADD(var)
+#endif
 
 constexpr int kThreads = 320;      // warp 0: loads, warp 1: MMA issue, warps 2..9: accumulate + epilogue
 constexpr int kChunkK = 256;       // values of k per accumulation chunk
@@ -459,6 +475,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // ---- producer (both CTAs): own rows of A, own half of B; completion counted on the leader ----
             uint32_t g = 0;      // k-blocks issued so far, across tiles: ring position and phase
             bool ok = true;
+            long long prof_a = 0;
+            (void)prof_a;
             for (uint32_t u = pair; u < nunits && ok; u += npairs) {
                 uint32_t tile, c0, c1, slot, m0, n0;
                 unit_at(u, tile, c0, c1, slot);
@@ -468,10 +486,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 for (uint32_t kb = c0 * kChunkKB; kb < kb_last; ++kb, ++g) {
                     const int s = g % S;
                     const uint32_t ph = (g / S) & 1u;
-                    if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, kPairWaitCycles)) {
-                        atomicOr(ep.dev_status, FG_DEVERR_TMA_WAIT);
-                        ok = false;
-                        break;
+                    {
+                        PROF_T0();
+                        const bool got = mbar_wait_bounded(empty_bar(s), ph ^ 1u, kPairWaitCycles);
+                        PROF_ADD(prof_a);
+                        if (!got) {
+                            atomicOr(ep.dev_status, FG_DEVERR_TMA_WAIT);
+                            ok = false;
+                            break;
+                        }
                     }
                     const uint32_t lf = map_to_cta(full_bar(s), 0);
                     const uint32_t sa = base + s * Cfg::kStageBytes;
@@ -508,6 +531,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                 }
             }
+#ifdef FG_GEMM_PROFILE
+            atomicAdd(&g_prof[6], (unsigned long long)prof_a);
+#endif
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
@@ -515,16 +541,26 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             constexpr uint32_t idesc = make_idesc(2u /*tf32*/, 2 * BM, BN);
             bool ok = true;
             uint32_t g = 0, gc = 0;     // k-blocks and chunks consumed so far, across tiles
+            long long prof_e = 0, prof_f = 0;
+            (void)prof_e; (void)prof_f;
+#ifdef FG_GEMM_PROFILE
+            const long long prof_start = clock64();
+#endif
             for (uint32_t u = pair; u < nunits && ok; u += npairs) {
                 uint32_t tile, c0, c1, slot;
                 unit_at(u, tile, c0, c1, slot);
                 for (uint32_t c = c0; c < c1 && ok; ++c, ++gc) {
                     const uint32_t buf = gc & 1u;
                     // the accumulator must have been drained by both CTAs' epilogue warps (two chunks ago)
-                    if (!mbar_wait_bounded(acc_empty_bar(buf), ((gc >> 1) & 1u) ^ 1u, kPairWaitCycles)) {
-                        atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
-                        ok = false;
-                        break;
+                    {
+                        PROF_T0();
+                        const bool got = mbar_wait_bounded(acc_empty_bar(buf), ((gc >> 1) & 1u) ^ 1u, kPairWaitCycles);
+                        PROF_ADD(prof_e);
+                        if (!got) {
+                            atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
+                            ok = false;
+                            break;
+                        }
                     }
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * BN;
@@ -532,10 +568,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (uint32_t kb = c * kChunkKB; kb < kb_end; ++kb, ++g) {
                         const int s = g % S;
                         const uint32_t ph = (g / S) & 1u;
-                        if (!mbar_wait_bounded(full_bar(s), ph, kPairWaitCycles)) {
-                            atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
-                            ok = false;
-                            break;
+                        {
+                            PROF_T0();
+                            const bool got = mbar_wait_bounded(full_bar(s), ph, kPairWaitCycles);
+                            PROF_ADD(prof_f);
+                            if (!got) {
+                                atomicOr(ep.dev_status, FG_DEVERR_MMA_WAIT);
+                                ok = false;
+                                break;
+                            }
                         }
                         tc_fence_after();
                         const uint32_t sa = base + s * Cfg::kStageBytes;
@@ -605,6 +646,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (ok) mma_commit_pair(acc_full_bar(buf), 3);   // both CTAs may drain their half
                 }
             }
+#ifdef FG_GEMM_PROFILE
+            atomicAdd(&g_prof[0], (unsigned long long)prof_e);
+            atomicAdd(&g_prof[1], (unsigned long long)prof_f);
+            atomicAdd(&g_prof[2], (unsigned long long)(clock64() - prof_start));
+            atomicAdd(&g_prof[7], 1ull);
+#endif
         }
     } else {
         // ---- accumulate + epilogue (both CTAs, own 128 rows); see gemm_tc_kernel ----
@@ -617,6 +664,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float sum[CPT];
         bool ok = true;
         uint32_t gc = 0;
+        long long prof_w = 0, prof_s = 0, prof_n = 0;
+        (void)prof_w; (void)prof_s; (void)prof_n;
         for (uint32_t u = pair; u < nunits && ok; u += npairs) {
             uint32_t tile, c0, c1, slot, m0, n0;
             const bool part = unit_at(u, tile, c0, c1, slot);
@@ -625,7 +674,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
             for (uint32_t c = c0; c < c1; ++c, ++gc) {
                 const uint32_t buf = gc & 1u;
+                PROF_T0();
                 bool got = mbar_wait_bounded(acc_full_bar(buf), (gc >> 1) & 1u, kPairWaitCycles + kPairWaitCycles / 2);
+                PROF_ADD(prof_w);
                 got = __all_sync(0xffffffffu, got);
                 if (!got) {
                     if (lane == 0) atomicOr(ep.dev_status, FG_DEVERR_EPI_WAIT);
@@ -646,6 +697,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8u * buf);   // 16 warps report to the leader
             }
             if (!ok) break;
+#ifdef FG_GEMM_PROFILE
+            const long long prof_st = clock64();
+#endif
             // Store this tile from registers; the tensor core is already working on the next one.  A thread
             // owns one row, so storing directly would touch 32 different lines per instruction; instead each
             // warp passes 32x32 blocks through a padded shared-memory buffer and writes 4 rows x 128 bytes
@@ -676,37 +730,58 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int t = 0; t < 4; ++t) if (col + t < col_lim) bz[t] = ep.bias[col + t];
                 }
                 float cs[4] = {0.f, 0.f, 0.f, 0.f};     // column sums of what this lane stores (rows r*4 + rsub)
-                // rolled on purpose: the activation code (tanhf, GELU) is inlined at every call site, and
-                // 128 copies of it per thread made this section miss the instruction cache on every line
-                // (measured: 45,000 cycles per tile for ~1,000 useful instructions)
+                // Two rounds of four rows.  The four loads of the saved tensor of a round are issued together, before
+                // anything waits for one of them: one load per row in a rolled loop put eight DRAM latencies per
+                // 32 x 32 block end to end, and this store phase has to finish before the tensor core has filled
+                // the two accumulators it can run ahead by (measured: +70 us on a 4096^3 product).  The activation
+                // code exists once (act_fwd4 / act_mul4 are not inlined): inlined at every call site it had made
+                // this section miss the instruction cache on every line.
 #pragma unroll 1
-                for (int r = 0; r < 8; ++r) {
-                    const uint32_t lr = r * 4 + rsub;
-                    const uint32_t row = row_base + q * 32 + lr;
-                    float z[4];
+                for (int rh = 0; rh < 2; ++rh) {
+                    float4 sv[4];
+                    if (mul) {
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) z[t] = tb[lr * 33 + c4 + t] + bz[t];
-                    if (row < row_lim && col < col_lim) {
-                        const size_t off = (size_t)row * out_ld + col;
-                        if (vec && col + 3 < col_lim) {
-                            const float4 zin = make_float4(z[0], z[1], z[2], z[3]);
-                            float4 o;
-                            if (mul) o = act_mul4(ep.mul_act, zin, __ldg(reinterpret_cast<const float4*>(mul + off)));
-                            else o = act == FG_ACT_NONE ? zin : act_fwd4(act, zin);
-                            if (pre) store_out4(pre, off, zin, odt);
-                            store_out4(out, off, o, odt);
-                            if (pairs) fg_store_pairs4(pairs, ep.c_pairs_stride, off, o);
-                            cs[0] += o.x; cs[1] += o.y; cs[2] += o.z; cs[3] += o.w;
-                        } else {
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t row = row_base + q * 32 + (rh * 4 + i) * 4 + rsub;
+                            sv[i] = (vec && row < row_lim && col + 3 < col_lim)
+                                        ? __ldg(reinterpret_cast<const float4*>(mul + (size_t)row * out_ld + col))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
 #pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (col + t < col_lim) {
-                                    const float o = mul ? z[t] * fg_act_grad(ep.mul_act, mul[off + t]) : fg_act_fwd(act, z[t]);
-                                    if (pre) store_out1(pre, off + t, z[t], odt);
-                                    store_out1(out, off + t, o, odt);
-                                    if (pairs) fg_store_pairs1(pairs, ep.c_pairs_stride, off + t, o);
-                                    cs[t] += o;
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t lr = (rh * 4 + i) * 4 + rsub;
+                        const uint32_t row = row_base + q * 32 + lr;
+                        float z[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) z[t] = tb[lr * 33 + c4 + t] + bz[t];
+                        if (row < row_lim && col < col_lim) {
+                            const size_t off = (size_t)row * out_ld + col;
+                            if (vec && col + 3 < col_lim) {
+                                const float4 zin = make_float4(z[0], z[1], z[2], z[3]);
+                                float4 o;
+                                if (mul) o = act_mul4(ep.mul_act, zin, sv[i]);
+                                else o = act == FG_ACT_NONE ? zin : act_fwd4(act, zin);
+#ifdef FG_GEMM_PROFILE
+                                if (!(ep.dbg & 1u) || o.x == 12345.678f)
+#endif
+                                {
+                                if (pre) store_out4(pre, off, zin, odt);
+                                store_out4(out, off, o, odt);
+                                if (pairs) fg_store_pairs4(pairs, ep.c_pairs_stride, off, o);
                                 }
+                                cs[0] += o.x; cs[1] += o.y; cs[2] += o.z; cs[3] += o.w;
+                            } else {
+#pragma unroll
+                                for (int t = 0; t < 4; ++t)
+                                    if (col + t < col_lim) {
+                                        const float o = mul ? z[t] * fg_act_grad_fast(ep.mul_act, mul[off + t]) : fg_act_fwd_fast(act, z[t]);
+                                        if (pre) store_out1(pre, off + t, z[t], odt);
+                                        store_out1(out, off + t, o, odt);
+                                        if (pairs) fg_store_pairs1(pairs, ep.c_pairs_stride, off + t, o);
+                                        cs[t] += o;
+                                    }
+                            }
                         }
                     }
                 }
@@ -726,7 +801,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 __syncwarp();
             }
+#ifdef FG_GEMM_PROFILE
+            prof_s += clock64() - prof_st;
+            prof_n += 1;
+#endif
         }
+#ifdef FG_GEMM_PROFILE
+        if (warp == 2 && lane == 0 && leader) {
+            atomicAdd(&g_prof[3], (unsigned long long)prof_w);
+            atomicAdd(&g_prof[4], (unsigned long long)prof_s);
+            atomicAdd(&g_prof[5], (unsigned long long)prof_n);
+        }
+#endif
     }
     tc_fence_before();
     __syncthreads();
@@ -780,7 +866,7 @@ __global__ void __launch_bounds__(256) gemm_tc_pair_fold_kernel(Epilogue ep) {
 #pragma unroll
             for (int t = 0; t < 4; ++t)
                 if (col + t < ep.N) {
-                    const float o = ep.mul_saved ? zz[t] * fg_act_grad(ep.mul_act, ep.mul_saved[off + t]) : fg_act_fwd(ep.act, zz[t]);
+                    const float o = ep.mul_saved ? zz[t] * fg_act_grad_fast(ep.mul_act, ep.mul_saved[off + t]) : fg_act_fwd_fast(ep.act, zz[t]);
                     if (ep.preact) store_out1(ep.preact, off + t, zz[t], ep.out_dtype);
                     store_out1(ep.C, off + t, o, ep.out_dtype);
                     if (ep.c_pairs) fg_store_pairs1(ep.c_pairs, ep.c_pairs_stride, off + t, o);
@@ -1198,7 +1284,7 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
     uint64_t split = rem ? slots / rem : 1;
     if (split > nchunks / 2) split = nchunks / 2;
     if (split > 4) split = 4;
-    if (getenv("FG_GEMM_NO_SPLITK")) split = 1;
+    if (!ctx->opt_split_k) split = 1;
     ep.partial = nullptr;
     ep.t_full = (uint32_t)ntiles;
     ep.split = 1;
@@ -1239,13 +1325,10 @@ int32_t tc_gemm(fg_ctx* ctx, int fmt, const PlaneSet& a, const PlaneSet& b, uint
     int bn = N > 128 ? (s_256 >= s_128 ? 256 : 128) : N > 64 ? 128 : N > 32 ? 64 : 32;
     int bk = (fmt == 0 && bn == 256) ? 16 : 32;
     bool pair = s_pair > 0.0 && s_pair >= s_256 && s_pair >= s_128;
-    // Tuning override for experiments: FG_GEMM_TILE="pair" or "<BN>x<BK>", e.g. "256x16".
-    if (const char* e = getenv("FG_GEMM_TILE")) {
-        int x = 0, y = 0;
-        if (strcmp(e, "pair") == 0) pair = N > 128;
-        else if (sscanf(e, "%dx%d", &x, &y) == 2 && (x == 256 || x == 128) && (y == 32 || (y == 16 && fmt == 0))) {
-            bn = x; bk = y; pair = false;
-        }
+    // Option gemm_tile: "pair" or "<BN>x<BK>" instead of the choice above.
+    if (ctx->opt_tile_pair == 1) pair = N > 128;
+    else if (ctx->opt_tile_pair == 0 && (ctx->opt_tile_bk == 32 || fmt == 0)) {
+        bn = ctx->opt_tile_bn; bk = ctx->opt_tile_bk; pair = false;
     }
     if (pair) return fmt == 1 ? launch_tc_pair<32, 1>(ctx, a, b, ep) : launch_tc_pair<32, 0>(ctx, a, b, ep);
     if (fmt == 1) {
@@ -1337,7 +1420,8 @@ PlaneSet paired_operand(const float* x, const void* pairs, uint64_t plane_stride
 // tensor's row pitch must be a multiple of 16 bytes in both element sizes (columns % 8), and the tile
 // shape must suit the pair kernel.
 bool paired_shape_ok(const fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, uint32_t pitch_a, uint32_t pitch_b) {
-    return ctx->tmap_encode && M > (uint32_t)BM && N > 128 && K >= 32 && pitch_a % 8 == 0 && pitch_b % 8 == 0;
+    return ctx->opt_pairs && ctx->opt_tile_pair != 0 && ctx->tmap_encode && M > (uint32_t)BM && N > 128 && K >= 32 &&
+           pitch_a % 8 == 0 && pitch_b % 8 == 0;
 }
 
 struct PairedOut {
@@ -1351,6 +1435,9 @@ struct PairedOut {
 int32_t paired_gemm(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, uint32_t M, uint32_t N, uint32_t K, float* C,
                     const float* bias, int act, float* preact, const PairedOut& o) {
     Epilogue ep{C, bias, preact, M, N, K, act, ctx->dev_status};
+#ifdef FG_GEMM_PROFILE
+    if (const char* e = getenv("FG_GEMM_DBG")) ep.dbg = (uint32_t)atoi(e);
+#endif
     ep.c_pairs = o.pairs;
     ep.c_pairs_stride = o.stride;
     ep.mul_saved = o.mul_saved;
@@ -2034,3 +2121,13 @@ int32_t fg_gemm_bwd_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uin
 }
 
 }  // extern "C"
+
+#ifdef FG_GEMM_PROFILE
+extern "C" int32_t fg_gemm_profile_read(unsigned long long out[8]) {
+    unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return FG_ERR_SYNC;
+    if (cudaMemcpyFromSymbol(out, g_prof, sizeof(zero)) != cudaSuccess) return FG_ERR_INTERNAL;
+    if (cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)) != cudaSuccess) return FG_ERR_INTERNAL;
+    return FG_OK;
+}
+#endif

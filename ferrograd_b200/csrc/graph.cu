@@ -710,8 +710,7 @@ static int32_t optim_eager(fg_exec* e) {
 // simply enqueued, so that it becomes part of the caller's plan.
 static int32_t run_planned(fg_exec* e, int which, const void* key, const std::function<int32_t()>& eager) {
     fg_ctx* ctx = e->ctx;
-    if (e->calls[which] == 0 && getenv("FG_EXEC_NO_PLANS")) e->use_plans = false;
-    if (!e->use_plans || ctx->capturing) return eager();
+    if (!e->use_plans || !ctx->opt_exec_plans || ctx->capturing) return eager();
     if (e->plan[which] && e->plan_key[which] == key && e->plan_ws[which] == (const void*)ctx->ws)
         return fg_plan_launch(ctx, e->plan[which]);
     if (e->calls[which]++ == 0) return eager();

@@ -88,6 +88,18 @@ uint64_t fg_ctx_launch_count(fg_ctx* ctx);
  * planes, so that no allocation happens later (required before fg_plan_begin). */
 int32_t fg_ctx_reserve_workspace(fg_ctx* ctx, uint64_t bytes);
 uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
+/* Tuning and debugging switches of one context (no counterpart in the reference, whose only switch is
+ * CompilationOptions: dispatch/mod.rs:369-455).  Values are strings.
+ *   "gemm_tile"     "auto" (default) | "pair" | "256x32" | "256x16" | "128x32" | "128x16": the tensor-core tile
+ *   "gemm_split_k"  "1" (default) | "0": cut the tiles of an under-filled last wave into K-shares
+ *   "gemm_pairs"    "1" (default) | "0": multiply f32 tensors as they lie, with bf16 pairs, where the shape
+ *                   allows; "0" sends every shape through operand planes written by a pre-pass
+ *   "exec_plans"    "1" (default) | "0": the graph engine records each dispatch as a CUDA graph
+ *   "comm_max_ctas" CTAs the communicator may use (default 12; read by fg_comm_init)
+ *   "comm_sms"      SMs the persistent GEMM leaves free while an exchange is in flight (default 16; 0 = none)
+ * The environment variables FG_GEMM_TILE, FG_GEMM_NO_SPLITK, FG_GEMM_NO_PAIRS, FG_EXEC_NO_PLANS,
+ * NCCL_MAX_CTAS and FG_COMM_SMS give the initial values; they are read once, when the context is created. */
+int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value);
 /* Reads and clears the device-side error word (bounded waits that expired). */
 int32_t fg_ctx_device_status(fg_ctx* ctx, int32_t* status_word);
 
@@ -441,7 +453,11 @@ int32_t fg_bpat_load_tensor(fg_ctx* ctx, const fg_bpat_file* f, uint32_t index, 
  *      hipGraph the same way) ----
  * Between fg_plan_begin and fg_plan_end every compute entry point on this context is
  * recorded instead of executed.  No allocation may happen in between: reserve the
- * workspace first. */
+ * workspace first (or run the same calls once eagerly).  A plan carries addresses inside the
+ * scratch arena as it was when the plan was recorded: if a later eager call needs a larger
+ * arena, the arena is reallocated and every older plan becomes stale -- fg_plan_launch then
+ * returns FG_ERR_INCONSISTENT_CAPTURE instead of running it, and the plan must be recorded
+ * again.  fg_ctx_reserve_workspace with the largest need, before recording, avoids this. */
 int32_t fg_plan_begin(fg_ctx* ctx);
 int32_t fg_plan_end(fg_ctx* ctx, fg_plan** out);
 int32_t fg_plan_launch(fg_ctx* ctx, fg_plan* plan);

@@ -117,7 +117,10 @@ def ce_loss_grad(probs, labels):
     return loss, grad
 
 
-def softmax_ce(logits, labels, grad_scale=1.0, want_probs=False, want_dlogits=True):
+QUIRK_RELU_MASK_GE0, QUIRK_GELU_BWD_T, QUIRK_SOFTMAX_BWD_COL0, QUIRK_CE_THROUGH_SOFTMAX = 1, 2, 4, 8
+
+
+def softmax_ce(logits, labels, grad_scale=1.0, want_probs=False, want_dlogits=True, quirks=0):
     logits = _f(logits)
     labels = np.ascontiguousarray(labels, dtype=np.uint32)
     rows, cols = logits.shape
@@ -126,9 +129,9 @@ def softmax_ce(logits, labels, grad_scale=1.0, want_probs=False, want_dlogits=Tr
     dl = np.empty_like(logits) if want_dlogits else None
     pr = np.empty_like(logits) if want_probs else None
     am = np.empty(rows, np.uint32)
-    lib().ref_softmax_ce_fwd_bwd(C.c_uint32(rows), C.c_uint32(cols), _p(logits), _p(labels),
-                                 C.c_float(grad_scale), _p(loss_row), _p(mean), _p(dl), _p(pr),
-                                 _p(am))
+    lib().ref_softmax_ce_fwd_bwd_q(C.c_uint32(rows), C.c_uint32(cols), _p(logits), _p(labels),
+                                   C.c_float(grad_scale), _p(loss_row), _p(mean), _p(dl), _p(pr),
+                                   _p(am), int(quirks))
     return {"loss_row": loss_row, "loss_mean": float(mean[0]), "dlogits": dl, "probs": pr,
             "argmax": am}
 

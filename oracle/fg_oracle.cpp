@@ -330,6 +330,23 @@ void ref_softmax_ce_fwd_bwd(uint32_t rows, uint32_t cols, const float* logits,
     if (loss_mean) *loss_mean = (float)(s / rows);
 }
 
+void ref_softmax_ce_fwd_bwd_q(uint32_t rows, uint32_t cols, const float* logits, const uint32_t* labels,
+                              float grad_scale, float* loss_row, float* loss_mean, float* dlogits, float* probs,
+                              uint32_t* argmax, int quirks) {
+    if (!(quirks & REF_QUIRK_CE_THROUGH_SOFTMAX) || !dlogits) {
+        ref_softmax_ce_fwd_bwd(rows, cols, logits, labels, grad_scale, loss_row, loss_mean, dlogits, probs, argmax);
+        return;
+    }
+    // The reference's order: softmax forward, CROSS_ENTROPY on the probabilities (seed = p - onehot, unscaled:
+    // loss/basic_loss.rs:91-133), then the softmax node's backward with that seed as dy (dispatch/mod.rs:713-718).
+    std::vector<float> p((size_t)rows * cols), seed((size_t)rows * cols), unused((size_t)rows * cols);
+    ref_softmax_ce_fwd_bwd(rows, cols, logits, labels, 1.0f, loss_row, loss_mean, nullptr, p.data(), argmax);
+    ref_ce_loss_grad(rows, cols, p.data(), labels, unused.data(), seed.data());
+    for (size_t i = 0; i < seed.size(); ++i) { seed[i] *= grad_scale; dlogits[i] = 0.0f; }
+    ref_softmax_bwd(rows, cols, p.data(), seed.data(), dlogits, 0, quirks & REF_QUIRK_SOFTMAX_BWD_COL0);
+    if (probs) std::memcpy(probs, p.data(), p.size() * sizeof(float));
+}
+
 void ref_mse_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,
                        float* loss_elem, float* loss_sum, float* grad) {
     // loss/basic_loss.rs:3-27: diff = p - t; loss = diff*diff; grad = 2*diff (unreduced).

@@ -30,7 +30,11 @@ enum { REF_ACT_NONE = 0, REF_ACT_RELU = 1, REF_ACT_TANH = 2, REF_ACT_GELU = 3 };
 enum {
     REF_QUIRK_RELU_MASK_GE0 = 1,  /* relu backward mask is saved_output >= 0 (op/unary.rs:453-472) */
     REF_QUIRK_GELU_BWD_T = 2,     /* gelu backward uses t = tanh(u) where x is meant (op/unary.rs:588-714) */
-    REF_QUIRK_SOFTMAX_BWD_COL0 = 4/* softmax backward updates only columns = 0 mod 256 (op/softmax.rs:601) */
+    REF_QUIRK_SOFTMAX_BWD_COL0 = 4,/* softmax backward updates only columns = 0 mod 256 (op/softmax.rs:601) */
+    REF_QUIRK_CE_THROUGH_SOFTMAX = 8 /* the loss kernel's p - onehot is used as dL/dprobs and pushed through the
+                                        softmax backward once more: the seed written by dispatch_loss
+                                        (crates/fused_gpu/src/dispatch/mod.rs:713-718) is the upstream gradient of
+                                        the graph's last node, the softmax (op/softmax.rs:448-688) */
 };
 
 int ref_num_threads(void);
@@ -53,6 +57,10 @@ void ref_ce_loss_grad(uint32_t rows, uint32_t cols, const float* probs, const ui
 void ref_softmax_ce_fwd_bwd(uint32_t rows, uint32_t cols, const float* logits,
                             const uint32_t* labels, float grad_scale, float* loss_row,
                             float* loss_mean, float* dlogits, float* probs, uint32_t* argmax);
+/* The same with quirk switches (REF_QUIRK_CE_THROUGH_SOFTMAX, REF_QUIRK_SOFTMAX_BWD_COL0). */
+void ref_softmax_ce_fwd_bwd_q(uint32_t rows, uint32_t cols, const float* logits,
+                              const uint32_t* labels, float grad_scale, float* loss_row,
+                              float* loss_mean, float* dlogits, float* probs, uint32_t* argmax, int quirks);
 void ref_mse_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,
                        float* loss_elem, float* loss_sum, float* grad);
 void ref_bce_loss_grad(uint64_t n, const float* pred, const float* target, float grad_scale,

@@ -432,7 +432,7 @@ def test_mlp_graph_matches_oracle(ctx, oracle, act, loss_name):
     t.destroy()
 
 
-def test_replayed_dispatches_equal_eager(ctx, monkeypatch):
+def test_replayed_dispatches_equal_eager(ctx):
     """From its second call on, every dispatch_* replays a recorded CUDA graph.  Five training steps with new
     data each step end with bit-identical parameters whether the dispatches are replayed or run eagerly, also
     after the loss target moves to another buffer."""
@@ -449,10 +449,7 @@ def test_replayed_dispatches_equal_eager(ctx, monkeypatch):
         g.softmax(g.add(g.matmul(g.gelu(g.add(g.matmul(xi, w0), b0)), w1), b1))
 
     def train(eager):
-        if eager:
-            monkeypatch.setenv("FG_EXEC_NO_PLANS", "1")
-        else:
-            monkeypatch.delenv("FG_EXEC_NO_PLANS", raising=False)
+        ctx.set_option("exec_plans", "0" if eager else "1")
         graph, t, kernels, binding = build(ctx, define, [B, I, Hd, O], loss=CROSS_ENTROPY, optim=Optim.adamw(),
                                            lr=1e-2)
         ins = [ctx.init_tensor_f32(a.shape, a) for a in (xs[0], W[0], b[0], W[1], b[1])]
@@ -470,9 +467,12 @@ def test_replayed_dispatches_equal_eager(ctx, monkeypatch):
         out = [ctx.to_numpy(ins[i]).copy() for i in (1, 2, 3, 4)]
         t.destroy()
         return out
-    for got, ref in zip(train(eager=False), train(eager=True)):
-        assert np.array_equal(got, ref)
-    assert not np.array_equal(train(eager=False)[0], W[0])       # and training moved the weights
+    try:
+        for got, ref in zip(train(eager=False), train(eager=True)):
+            assert np.array_equal(got, ref)
+        assert not np.array_equal(train(eager=False)[0], W[0])       # and training moved the weights
+    finally:
+        ctx.set_option("exec_plans", "1")
 
 
 def test_binary_cross_entropy_graph(ctx, oracle):

@@ -406,15 +406,16 @@ def test_gemm_tensor_core_vs_oracle(ctx, oracle, M, N, K, mode):
 
 @pytest.mark.parametrize("mode", ["3xtf32", "tf32_bf16x2"])
 @pytest.mark.parametrize("tile", ["128x32", "256x32", "pair"])
-def test_gemm_every_tile_kernel(ctx, oracle, monkeypatch, mode, tile):
+def test_gemm_every_tile_kernel(ctx, oracle, mode, tile):
     # The tile heuristic picks one kernel per shape; force each of them on the same ragged problem.
-    monkeypatch.setenv("FG_GEMM_TILE", tile)
+    ctx.set_option("gemm_tile", tile)
     M, N, K = 400, 600, 700
     r = rng(4242)
     A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
     bias = r.standard_normal(N, np.float32)
     Cd, Pd = ctx.new_tensor((M, N)), ctx.new_tensor((M, N))
     ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, bias=up(ctx, bias), act="tanh", preact_out=Pd, mode=mode)
+    ctx.set_option("gemm_tile", "auto")
     yref, pre = oracle.bias_act_fwd(oracle.gemm(A, B), bias, "tanh")
     assert ctx.device_status() == 0
     check(ctx.to_numpy(Pd), pre, TOL_GEMM, f"{mode}/{tile} pre-activation")
@@ -425,14 +426,14 @@ def test_gemm_every_tile_kernel(ctx, oracle, monkeypatch, mode, tile):
 @pytest.mark.parametrize("M,N,K", [(600, 700, 2304),      # 9 tiles, no full wave: every tile in 4 K-shares
                                    (2500, 2304, 1024),    # 90 tiles: one full wave, then 16 tiles in 2 K-shares
                                    (300, 520, 1100)])     # 5 chunks in 2 uneven shares
-def test_gemm_pair_split_k_tail(ctx, oracle, monkeypatch, mode, M, N, K):
+def test_gemm_pair_split_k_tail(ctx, oracle, mode, M, N, K):
     # The pair kernel cuts the tiles of an under-filled last wave into K-shares that a second kernel folds.
     r = rng(M + N + K)
     A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32) * 0.1
     bias = r.standard_normal(N, np.float32)
     Ad, Bd, bd = up(ctx, A), up(ctx, B), up(ctx, bias)
     Cd, Pd = ctx.new_tensor((M, N)), ctx.new_tensor((M, N))
-    monkeypatch.setenv("FG_GEMM_TILE", "pair")
+    ctx.set_option("gemm_tile", "pair")
     ctx.gemm(Ad, Bd, Cd, M, N, K, bias=bd, act="gelu", preact_out=Pd, mode=mode)
     got, got_pre = ctx.to_numpy(Cd), ctx.to_numpy(Pd)
     assert ctx.device_status() == 0
@@ -442,8 +443,10 @@ def test_gemm_pair_split_k_tail(ctx, oracle, monkeypatch, mode, M, N, K):
     # the same product without the split agrees to rounding, and the split is deterministic
     ctx.gemm(Ad, Bd, Cd, M, N, K, bias=bd, act="gelu", preact_out=Pd, mode=mode)
     assert np.array_equal(ctx.to_numpy(Cd), got)
-    monkeypatch.setenv("FG_GEMM_NO_SPLITK", "1")
+    ctx.set_option("gemm_split_k", "0")
     ctx.gemm(Ad, Bd, Cd, M, N, K, bias=bd, act="gelu", preact_out=Pd, mode=mode)
+    ctx.set_option("gemm_split_k", "1")
+    ctx.set_option("gemm_tile", "auto")
     check(ctx.to_numpy(Pd), got_pre, TOL_EW, "split vs unsplit")
 
 
