@@ -20,9 +20,41 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes (read + write) per tensor-core GEMM (a pair launch and its fold), averaged over the five of
-# one training step, from an ncu capture of one step (dram__bytes_read.sum + dram__bytes_write.sum).
-GEMM_TRAFFIC_PER_LAUNCH = {"c4": 505.0e6}
+# Datasheet figures, reported beside the measured ones: HBM3e 8 TB/s, dense TF32 1.1 PFLOP/s.
+NOMINAL = {"hbm_gbs": 8000.0, "tf32_tflops": 1100.0}
+# DRAM bytes (read + write) per tensor-core GEMM launch of one training step come from the committed ncu
+# summary of that step (a line `dram_bytes_per_gemm_launch = <bytes>`).
+TRAFFIC_PROFILE = {"c4": "mlp_c4_gemm_dram_traffic.md", "c5": "mlp_c5_gemm_dram_traffic.md"}
+
+
+def gemm_traffic_per_launch(workload):
+    import re
+    path = os.path.join(ROOT, "profiles", TRAFFIC_PROFILE.get(workload, ""))
+    try:
+        m = re.search(r"dram_bytes_per_gemm_launch\s*=\s*([0-9.eE+]+)", open(path).read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
+
+
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def host_threads():
+    """Every host core, whatever OMP_NUM_THREADS says (torchrun exports 1 to its children)."""
+    n = int(os.environ.get("FG_REF_THREADS", "0")) or (os.cpu_count() or 1)
+    try:
+        n = min(n, len(os.sched_getaffinity(0))) if not os.environ.get("FG_REF_THREADS") else n
+    except AttributeError:
+        pass
+    return max(1, n)
 
 
 def load_peaks():
@@ -109,6 +141,7 @@ def run_reference(args, rank, world):
     from ferrograd_b200 import dp
     from ferrograd_b200.mlp import MLPTrainer
     w = dp.WORKLOADS[args.workload]
+    oracle.set_num_threads(host_threads())
     threads = oracle.num_threads()
     dims = w["dims"]
     W, b = MLPTrainer.init_params(dims, w["init"], w["seed"])
@@ -141,7 +174,8 @@ def run_reference(args, rank, world):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": w["name"], "note": "CPU oracle port; the reference has no CPU path and needs "
                        "Rust + HIP or wgpu (unavailable on this box)"},
-            "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port", "sample": sample,
+                             "cpu": cpu_model()},
             "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -181,7 +215,7 @@ def _kernel_lines(torch, stream, ctx, peaks):
         fn()
     n, ms, work = per_launch("softmax_ce", fn, 10)
     out["softmax_ce_c2"] = {"ms": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm,
-                            "bytes": work, "shape": [rows, cols]}
+                            "frac_of_nominal_hbm": work / ms / 1e6 / NOMINAL["hbm_gbs"], "bytes": work, "shape": [rows, cols]}
     del x, dl
     # AdamW / SGD on the C5 parameter count
     n_par = 8 * (8192 * 8192 + 8192)
@@ -192,13 +226,14 @@ def _kernel_lines(torch, stream, ctx, peaks):
     for _ in range(3):
         fn()
     n, ms, work = per_launch("adamw", fn, 5)
-    out["adamw_c5"] = {"ms": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm, "params": n_par,
-                       "bytes_per_param": 28}
+    out["adamw_c5"] = {"ms": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm,
+                       "frac_of_nominal_hbm": work / ms / 1e6 / NOMINAL["hbm_gbs"], "params": n_par, "bytes_per_param": 28}
     fn = lambda: ctx.sgd_step(bufs[0].data_ptr(), bufs[1].data_ptr(), n_par, 1e-3)
     for _ in range(3):
         fn()
     n, ms, work = per_launch("sgd", fn, 5)
-    out["sgd_c5"] = {"ms": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm, "bytes_per_param": 16}
+    out["sgd_c5"] = {"ms": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm,
+                     "frac_of_nominal_hbm": work / ms / 1e6 / NOMINAL["hbm_gbs"], "bytes_per_param": 16}
     del bufs
     # C3
     N = 8192
@@ -227,6 +262,7 @@ def _kernel_lines(torch, stream, ctx, peaks):
                                     "kernel_tflops": work / ms / 1e9, "tensor_units_per_product": units,
                                     "frac_of_own_tensor_peak": work / ms / 1e9 / peak,
                                     "frac_of_3xtf32_peak": work / ms / 1e9 / tf32x3_burst,
+                                    "frac_of_nominal_3xtf32": work / ms / 1e9 / (NOMINAL["tf32_tflops"] / 3.0),
                                     "call_ms_with_prepass": e_ms, "call_tflops_with_prepass": 2.0 * N ** 3 / e_ms / 1e9}
         ctx.timing_read("split")
         e_ms = timed(torch, stream, ctx, lambda i: bwd(), 5) / 5
@@ -270,8 +306,8 @@ def _kernel_lines(torch, stream, ctx, peaks):
                      "samples_per_s": w1["steps"] * w1["batch"] / ms * 1e3, "final_loss_sum": tr1.get_loss(),
                      "note": "exact SIMT GEMM path; one CUDA-graph replay per step"}
     out["peak_note"] = ("tensor peaks derive from the measured bf16 burst: TF32 runs at half the bf16 rate; the 3xTF32 "
-                        "peak is that / 3, the default mode's own peak that / 2; bandwidth fractions are of the measured "
-                        "copy bandwidth")
+                        "peak is that / 3, the default mode's own peak that / 2; frac_of_hbm is of the measured copy "
+                        "bandwidth; frac_of_nominal_* are of the datasheet figures (HBM 8 TB/s, dense TF32 1.1 PFLOP/s / 3)")
     return out
 
 
@@ -323,6 +359,49 @@ def graph_api_line(torch, stream, ctx, workload, steps):
     tensors.destroy()
     for t in ins:
         t.data.free()
+    return out
+
+
+def dp_parity_check(torch, dist, ctx, tr, w, workload, rank, world, W0, b0):
+    """One training step on `world` ranks against the same step on ONE GPU over the concatenated batch.
+    Returns (on every rank) the largest parameter difference between replicas -- it must be 0: every rank
+    applies the same update to the same summed gradient -- and, measured on rank 0, how far the N-rank loss
+    and parameters are from the single-GPU ones (summation order is the only difference)."""
+    from ferrograd_b200 import dp
+    from ferrograd_b200.mlp import MLPTrainer
+    tr.upload_batch(*dp.synth_batch(workload, rank, 0))
+    tr.step()
+    ctx.sync()
+    n = tr.n_arena
+    mine = torch.empty(n, device="cuda", dtype=torch.float32)
+    ctx.copy_dev_async(mine.data_ptr(), tr.params.ptr, n * 4)
+    ctx.sync()
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    diff = (mine - ref).abs().max().to(torch.float64).reshape(1)
+    dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    loss = torch.tensor([tr.get_loss()], device="cuda", dtype=torch.float64)
+    dist.all_reduce(loss, op=dist.ReduceOp.SUM)
+    # cross-entropy reports the mean over the local rows, MSE the local sum of squares
+    loss_dp = float(loss.item()) / (world if w["loss"] == "ce" else 1)
+    out = {"replica_max_abs_diff": float(diff.item()), "loss_n_ranks": loss_dp}
+    if rank == 0:
+        single = MLPTrainer(ctx, w["dims"], w["batch"] * world, w["act"], w["loss"], w["opt"], world=1, rank=0)
+        single.set_params(W0, b0)
+        single.upload_batch(*dp.global_batch(workload, world, 0))
+        single.step()
+        ctx.sync()
+        one = torch.empty(n, device="cuda", dtype=torch.float32)
+        ctx.copy_dev_async(one.data_ptr(), single.params.ptr, n * 4)
+        ctx.sync()
+        rms = float(one.double().pow(2).mean().sqrt().item())
+        out["loss_one_gpu_on_concatenated_batch"] = single.get_loss()
+        out["params_vs_one_gpu_max_abs_diff"] = float((mine - one).abs().max().item())
+        out["params_rms"] = rms
+        out["note"] = ("the first AdamW step moves every weight by about lr, sign(g) deciding the direction, so where "
+                       "|g| is at rounding level the two summation orders may differ by up to 2*lr")
+        single.destroy()
+    dist.barrier()
     return out
 
 
@@ -379,6 +458,13 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    # ---- data-parallel parity, outside every timed region: one step from the initial parameters ----
+    dp_check = None
+    if world > 1:
+        dp_check = dp_parity_check(torch, dist, ctx, tr, w, args.workload, rank, world, W0, b0)
+        tr.set_params(W0, b0)
+        tr.reset_state()
 
     # ---- warm-up (also sizes the scratch arena) ----
     tr.upload_batch_async(xs[0], ts[0])
@@ -445,10 +531,14 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         gb = w["batch"] * world
         value = gb * args.steps / (ms / 1e3)
-        tf32x3_sust = peaks["bf16_tflops_sustained"] / 6.0
-        # the default GEMM mode spends two TF32-MMA units of tensor work per f32 product (one tf32 MMA + two
-        # bf16 MMAs at half cost), so its own ceiling is the TF32 rate / 2 = bf16 / 4
-        own_peak = peaks["bf16_tflops_sustained"] / 4.0
+        # The default GEMM mode spends two TF32-MMA units of tensor work per f32 product (one tf32 MMA + two
+        # bf16 MMAs at half cost), so its own ceiling is the TF32 rate / 2 = bf16 / 4.  Which measured bf16
+        # figure applies depends on how long the GPU has been under load: the burst figure for a timed region
+        # of under a second (the clocks stay near their maximum), the sustained one for a long region.
+        region_s = eager_ms / 1e3
+        basis = "burst" if region_s < 1.0 else "sustained"
+        bf16_peak = peaks["bf16_tflops"] if basis == "burst" else peaks["bf16_tflops_sustained"]
+        own_peak = bf16_peak / 4.0
         ach = gemm_flop / gemm_ms / 1e9 if gemm_ms > 0 else 0.0
         line = {
             "metric": "mlp_train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
@@ -466,11 +556,15 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel / gemm_tc_kernel", "achieved": ach,
                          "peak": own_peak, "unit": "TFLOP/s", "frac": ach / own_peak if own_peak else None,
-                         "traffic": GEMM_TRAFFIC_PER_LAUNCH.get(args.workload),
+                         "traffic": gemm_traffic_per_launch(args.workload),
                          "launches": int(gemm_n), "avg_launch_ms": gemm_ms / max(gemm_n, 1),
-                         "peak_basis": f"{peak_src} bf16 sustained {peaks['bf16_tflops_sustained']} TF/s / 2 (tf32 rate) / 2 "
-                                       "(tensor work per f32 product: one tf32 MMA + two half-cost bf16 MMAs)",
-                         "frac_of_3xtf32_peak": ach / tf32x3_sust if tf32x3_sust else None,
+                         "peak_basis": f"{peak_src} bf16 {basis} {bf16_peak} TF/s / 2 (tf32 rate) / 2 (tensor work per f32 "
+                                       f"product: one tf32 MMA + two half-cost bf16 MMAs); {basis} because the timed region "
+                                       f"lasted {region_s:.3f} s",
+                         "frac_of_burst": ach / (peaks["bf16_tflops"] / 4.0),
+                         "frac_of_sustained": ach / (peaks["bf16_tflops_sustained"] / 4.0),
+                         "frac_of_3xtf32_peak": ach / (bf16_peak / 6.0),
+                         "frac_of_nominal_3xtf32": ach / (NOMINAL["tf32_tflops"] / 3.0),
                          "flop_per_launch": gemm_flop / max(gemm_n, 1),
                          "share_of_step": gemm_ms / eager_ms if eager_ms else None},
             "eager_ms_per_step": eager_ms / args.steps,
@@ -478,8 +572,9 @@ def run_ours(args, rank, world, local_rank):
                                                 "share_of_step": split_ms / eager_ms if eager_ms else None},
                               "adamw": {"launches": int(adam_n), "gbs": adam_bytes / adam_ms / 1e6 if adam_ms else None,
                                         "frac_of_hbm": adam_bytes / adam_ms / 1e6 / peaks["hbm_gbs"] if adam_ms else None,
+                                        "frac_of_nominal_hbm": adam_bytes / adam_ms / 1e6 / NOMINAL["hbm_gbs"] if adam_ms else None,
                                         "share_of_step": adam_ms / eager_ms if eager_ms else None}},
-            "final_loss": final_loss, "peaks": peak_src,
+            "final_loss": final_loss, "peaks": peak_src, "dp_check": dp_check,
             "model_tflops": tr.flops_per_step() * world * args.steps / (ms / 1e3) / 1e12,
         }
         if world == 1 and not args.no_kernels:
@@ -490,6 +585,8 @@ def run_ours(args, rank, world, local_rank):
             ctx.timing_enable(True)
             line["kernels"] = kernel_lines(torch, stream, ctx, peaks)
             ctx.timing_enable(False)
+            if not args.no_cpu:
+                line["kernels"]["cpu"] = cpu_kernel_baselines()
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(args.workload)
         emit(line)
@@ -505,6 +602,7 @@ def cpu_baseline(workload):
     from ferrograd_b200.mlp import MLPTrainer
     w = dp.WORKLOADS[workload]
     dims, batch = w["dims"], w["batch"]
+    oracle.set_num_threads(host_threads())
     W, b = MLPTrainer.init_params(dims, w["init"], w["seed"])
     state = {k: [np.zeros_like(t) for t in (W if k[1] == "W" else b)] for k in ("mW", "vW", "mb", "vb")}
     od = dims[-1]
@@ -520,7 +618,63 @@ def cpu_baseline(workload):
             break
     use = times[1:] if len(times) > 1 else times
     return {"value": batch * len(use) / sum(use), "unit": "samples/s", "cores": oracle.num_threads(), "kind": "port",
-            "sample": f"{len(use)} full training steps of {batch} samples after one warm-up step"}
+            "sample": f"{len(use)} full training steps of {batch} samples after one warm-up step", "cpu": cpu_model()}
+
+
+def cpu_kernel_baselines():
+    """The CPU oracle on this host's cores for the single-kernel figures, each on a bounded sample."""
+    import oracle
+    from ferrograd_b200 import dp
+    from ferrograd_b200.mlp import MLPTrainer
+    oracle.set_num_threads(host_threads())
+    cores = oracle.num_threads()
+    r = np.random.Generator(np.random.Philox(99))
+    out = {"cores": cores, "cpu": cpu_model(), "kind": "port"}
+
+    def best(fn, reps=3):
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return min(ts)
+
+    # softmax-CE: 1024 of the 8192 rows of 32000 logits
+    rows, cols = 1024, 32000
+    x = (2.0 * r.standard_normal((rows, cols), np.float32)).astype(np.float32)
+    lab = r.integers(0, cols, rows).astype(np.uint32)
+    t = best(lambda: oracle.softmax_ce(x, lab, grad_scale=1.0 / rows))
+    out["softmax_ce_c2"] = {"gbs": 2.0 * rows * cols * 4 / t / 1e9, "sample": f"{rows} of 8192 rows x {cols}",
+                            "full_size_ms_estimate": t * 8192 / rows * 1e3}
+    del x
+    # AdamW / SGD: 32 Mi of the 537 M parameters
+    n = 32 << 20
+    w, g, m, v = (np.zeros(n, np.float32) for _ in range(4))
+    t = best(lambda: oracle.adamw(w, g, m, v, 1e-3, 0.9, 0.999, 1e-8, 0.01, 2, zero_grad=False))
+    out["adamw_c5"] = {"gbs": 28.0 * n / t / 1e9, "sample": f"{n} of 536936448 parameters",
+                       "full_size_ms_estimate": t * 536936448 / n * 1e3}
+    t = best(lambda: oracle.sgd(w, g, 1e-3))
+    out["sgd_c5"] = {"gbs": 16.0 * n / t / 1e9, "sample": f"{n} of 536936448 parameters",
+                     "full_size_ms_estimate": t * 536936448 / n * 1e3}
+    del w, g, m, v
+    # GEMM: a 2048^3 slice of the 8192^3 product (1/64 of the flop; same k-sequential f32 fma arithmetic)
+    N = 2048
+    A, B = r.standard_normal((N, N), np.float32), r.standard_normal((N, N), np.float32)
+    t = best(lambda: oracle.gemm(A, B), reps=2)
+    out["gemm_c3"] = {"tflops": 2.0 * N ** 3 / t / 1e12, "sample": "2048^3 slice of 8192^3 (1/64 of the work)",
+                      "full_size_ms_estimate": t * 64 * 1e3}
+    # the tiny MLP: 200 of its 1000 steps
+    w1 = dp.WORKLOADS["c1"]
+    W, b = MLPTrainer.init_params(w1["dims"], w1["init"], w1["seed"])
+    xs, ts = dp.synth_batch("c1", 0, 0)
+    steps = 200
+    t0 = time.perf_counter()
+    for s_ in range(steps):
+        oracle.mlp_step(w1["dims"], w1["batch"], w1["act"], W, b, xs, ts, w1["loss"], 1.0 / (w1["batch"] * 2), w1["opt"],
+                        step=s_ + 1)
+    t = time.perf_counter() - t0
+    out["mlp_c1"] = {"steps_per_s": steps / t, "sample": f"{steps} of 1000 steps (one ctypes call per step)"}
+    return out
 
 
 def main():

@@ -56,6 +56,7 @@ SIGNATURES = {
     "fg_upload": (i32, [c_ctx, c_buf, C.c_void_p, u64, u64]),
     "fg_download": (i32, [c_ctx, c_buf, C.c_void_p, u64, u64]),
     "fg_copy": (i32, [c_ctx, c_buf, c_buf]),
+    "fg_buf_touch": (i32, [c_buf]),
     "fg_upload_async": (i32, [c_ctx, c_dev, C.c_void_p, u64]),
     "fg_download_async": (i32, [c_ctx, C.c_void_p, c_dev, u64]),
     "fg_upload_prefetch": (i32, [c_ctx, c_dev, C.c_void_p, u64]),
@@ -83,6 +84,7 @@ SIGNATURES = {
     "fg_softmax_bwd": (i32, [c_ctx, u32, u32, c_dev, c_dev, c_dev, i32]),
     "fg_softmax_ce_fwd_bwd": (i32, [c_ctx, c_dev, c_dev, u32, u32, f32, c_dev, c_dev, c_dev, c_dev, c_dev]),
     "fg_ce_loss_grad": (i32, [c_ctx, c_dev, c_dev, u32, u32, c_dev, c_dev]),
+    "fg_sum_f32": (i32, [c_ctx, c_dev, u64, c_dev]),
     "fg_mse_loss_grad": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
     "fg_bce_loss_grad": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
     "fg_mse_loss_grad_noalloc": (i32, [c_ctx, c_dev, c_dev, u64, f32, c_dev, c_dev, c_dev]),
@@ -122,6 +124,7 @@ SIGNATURES = {
     "fg_exec_forward_out": (c_buf, [C.c_void_p]),
     "fg_exec_seed": (c_buf, [C.c_void_p]),
     "fg_exec_loss_t": (c_buf, [C.c_void_p]),
+    "fg_exec_loss_sum": (c_buf, [C.c_void_p]),
     "fg_exec_num_saved": (u32, [C.c_void_p]),
     "fg_exec_saved": (c_buf, [C.c_void_p, u32, C.POINTER(i32)]),
     "fg_exec_num_grads": (u32, [C.c_void_p]),

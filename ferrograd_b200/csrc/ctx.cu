@@ -117,6 +117,13 @@ int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value) {
     if (!strcmp(name, "gemm_split_k")) return truth(&ctx->opt_split_k);
     if (!strcmp(name, "gemm_pairs")) return truth(&ctx->opt_pairs);
     if (!strcmp(name, "exec_plans")) return truth(&ctx->opt_exec_plans);
+    if (!strcmp(name, "comm_min_exchange")) {
+        char* end = nullptr;
+        const unsigned long long v = strtoull(value, &end, 10);
+        if (end == value || *end) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_ctx_set_option: not a count");
+        ctx->opt_min_exchange = v;
+        return FG_OK;
+    }
     if (!strcmp(name, "comm_max_ctas") || !strcmp(name, "comm_sms")) {
         char* end = nullptr;
         const long v = strtol(value, &end, 10);
@@ -148,6 +155,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     c->opt_pairs = true;
     c->opt_exec_plans = true;
     c->opt_comm_max_ctas = 12;
+    c->opt_min_exchange = 1ull << 20;
     c->comm_reserved_sms = 16;
     // the environment gives initial values, once
     if (const char* e = getenv("FG_GEMM_TILE")) fg_ctx_set_option(c, "gemm_tile", e);
@@ -314,6 +322,8 @@ int32_t fg_alloc(fg_ctx* ctx, uint64_t bytes, fg_buf** out) {
     if (!b) return fg_fail(ctx, FG_ERR_OUT_OF_MEMORY, "fg_alloc: host allocation failed");
     b->ptr = nullptr;
     b->bytes = bytes;
+    b->version = 0;
+    b->view = false;
     cudaError_t e = cudaMalloc(&b->ptr, bytes ? bytes : 1);
     if (e != cudaSuccess) { delete b; return fg_fail_cuda(ctx, FG_ERR_OUT_OF_MEMORY, "cudaMalloc", e); }
     *out = b;
@@ -339,8 +349,10 @@ int32_t fg_free(fg_ctx* ctx, fg_buf* buf) {
     if (!ctx) return FG_ERR_NOT_INITIALIZED;
     if (!buf) return FG_OK;
     cudaSetDevice(ctx->device);
-    cudaStreamSynchronize(ctx->stream);
-    cudaFree(buf->ptr);
+    if (!buf->view) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(buf->ptr);
+    }
     delete buf;
     return FG_OK;
 }
@@ -354,6 +366,7 @@ int32_t fg_upload(fg_ctx* ctx, fg_buf* dst, const void* src, uint64_t bytes, uin
     FG_REQUIRE(ctx, dst_off <= dst->bytes && bytes <= dst->bytes - dst_off, "fg_upload: range exceeds the buffer");
     FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
     if (bytes == 0) return FG_OK;
+    dst->version++;
     FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
             cudaMemcpyAsync((char*)dst->ptr + dst_off, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaStreamSynchronize(ctx->stream));
@@ -377,8 +390,15 @@ int32_t fg_copy(fg_ctx* ctx, const fg_buf* src, fg_buf* dst) {
     FG_REQUIRE(ctx, src && dst, "fg_copy: NULL argument");
     FG_REQUIRE(ctx, src->bytes <= dst->bytes, "fg_copy: destination smaller than source");
     FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice(ctx->device));
+    dst->version++;
     FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY,
             cudaMemcpyAsync(dst->ptr, src->ptr, src->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return FG_OK;
+}
+
+int32_t fg_buf_touch(fg_buf* buf) {
+    if (!buf) return FG_ERR_INVALID_ARGUMENT;
+    buf->version++;
     return FG_OK;
 }
 

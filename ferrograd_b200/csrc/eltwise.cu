@@ -107,6 +107,26 @@ __global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restr
     }
 }
 
+// Sum of n values, stage 1: one partial per CTA (grid-stride over float4, fixed order inside a CTA).
+__global__ void __launch_bounds__(256) sum_partial_kernel(const float* __restrict__ x, uint64_t n, float* __restrict__ partials) {
+    __shared__ float red[8];
+    float s = 0.0f;
+    const uint64_t nv = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) ? n >> 2 : 0, stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(x) + i);
+        s += (v.x + v.y) + (v.z + v.w);
+    }
+    for (uint64_t i = (nv << 2) + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) s += x[i];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        partials[blockIdx.x] = t;
+    }
+}
+
 // Column sums, stage 1: block (32 x 8) covers 32 columns and `chunk` rows.
 __global__ void __launch_bounds__(256) colsum_partial_kernel(uint32_t rows, uint32_t cols, uint32_t chunk,
                                                              const float* __restrict__ x, float* __restrict__ part) {
@@ -317,6 +337,24 @@ int32_t fg_act_bwd(fg_ctx* ctx, uint64_t n, int32_t act, const float* dy, const 
     FG_REQUIRE(ctx, act == FG_ACT_NONE || saved, "fg_act_bwd: saved tensor required");
     if (n == 0) return FG_OK;
     return fg_act_bwd_launch(ctx, n, act, dy, saved, dz);
+}
+
+int32_t fg_sum_f32(fg_ctx* ctx, const float* x, uint64_t n, float* out) {
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, x && out, "fg_sum_f32: NULL pointer");
+    if (n == 0) {
+        FG_CUDA(ctx, FG_ERR_FAILED_BUFFER_COPY, cudaMemsetAsync(out, 0, 4, ctx->stream));
+        return FG_OK;
+    }
+    const int grid = fg_stream_grid(ctx, (n + 3) / 4, 256, 4);
+    void* p;
+    int32_t s = fg_ws_alloc(ctx, (uint64_t)grid * sizeof(float), &p);
+    if (s != FG_OK) return s;
+    sum_partial_kernel<<<grid, 256, 0, ctx->stream>>>(x, n, (float*)p);
+    FG_LAUNCHED(ctx);
+    fold_partials_kernel<<<1, 256, 0, ctx->stream>>>((const float*)p, grid, out);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
 }
 
 int32_t fg_mse_loss_grad(fg_ctx* ctx, const float* pred, const float* target, uint64_t n, float grad_scale,

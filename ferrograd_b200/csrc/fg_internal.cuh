@@ -16,6 +16,8 @@
 struct fg_buf {
     void* ptr;
     uint64_t bytes;
+    uint64_t version;   // bumped by every entry point that writes the buffer through its handle (fg_upload, fg_copy, ...)
+    bool view;          // a window into a larger allocation owned by someone else: fg_free releases the handle only
 };
 
 struct fg_plan {
@@ -72,6 +74,7 @@ struct fg_ctx {
     bool opt_pairs;             // multiply f32 tensors as they lie (bf16 pairs) where the shape allows
     bool opt_exec_plans;        // the graph engine records each dispatch as a CUDA graph
     int opt_comm_max_ctas;      // CTAs the communicator may use (fg_comm_init)
+    uint64_t opt_min_exchange;  // elements: the graph engine starts an exchange once this much is complete
     uint64_t ws_generation;     // bumped whenever the scratch arena is reallocated
 };
 

@@ -19,10 +19,27 @@
 // output, has more than one consumer, or feeds a matmul/softmax; everything else lives in registers
 // inside a chain kernel.
 //
+// The default GEMM mode multiplies f32 tensors as they lie with their bf16 pairs beside them
+// (fg_gemm_paired_f32): the engine keeps pairs for every tensor a matmul reads, written by whoever
+// writes the tensor -- the producing GEMM's epilogue, the optimizer (weights), or one elementwise
+// kernel for tensors that arrive from outside.  In the backward pass a matmul whose first operand is
+// the fused result of another matmul (x·W + b, activation) applies that layer's activation derivative
+// in its own dA epilogue, which also writes the pairs of the result and sums its columns into the
+// layer's bias gradient; the gradient tensor of such a node therefore holds dL/d(pre-activation).
+//
+// Data parallelism (no counterpart in the reference, which is single device): when the context has a
+// communicator (fg_comm_init), dispatch_backward sums the gradients of the trainable inputs over the
+// ranks.  Those gradients live in one arena in the order in which the backward pass completes them, so
+// what is complete is always a contiguous range: each matmul's backward starts the exchange of the
+// range completed so far between its dB and its dA product, and dispatch_optim starts the exchange of
+// the last range, updates the tensors of the earlier ranges beside it, and updates the last range when
+// it has arrived.
+//
 // Deviations from the reference, by design: a softmax that ends the graph under the CROSS_ENTROPY
 // loss is not differentiated a second time (the loss kernel's p - onehot already is dL/dlogits;
 // the reference pushes it through the softmax backward again, dispatch/mod.rs:713-718); shapes
 // need not be multiples of 16; `add` accepts a bias of shape [N] or [1,N] after a matmul.
+#include <limits.h>
 #include <stdlib.h>
 
 #include <algorithm>
@@ -64,8 +81,10 @@ struct ENode {
     bool bias_bcast = false;     // ADD whose second operand is a [N] bias (legal only after a matmul)
     fg_buf* value = nullptr;     // owned, or the bound input tensor
     bool own_value = false;
-    fg_buf* grad = nullptr;      // owned
+    fg_buf* grad = nullptr;      // owned (a view into the gradient arena for inputs)
     int input_slot = -1;         // index among the graph's inputs
+    fg_buf* pairs = nullptr;     // bf16 pairs of the value, for tensors a matmul reads (f32 graphs)
+    int produced_by_gemm = -1;   // index of the GemmStep whose fused result this node is
 };
 
 struct GemmStep {
@@ -75,6 +94,9 @@ struct GemmStep {
     // and the result by one matrix per Z index: kernel/forward.rs:159-190); [T,M,K] x [K,N] is one product
     // with T*M rows.
     uint32_t batch, M, K, N;
+    fg_buf* dz_pairs = nullptr;     // pairs of dL/d(pre-activation), written by the consumer's dA epilogue
+    bool dz_ready = false;          // this backward pass: grad(out) already holds dL/d(pre-activation)
+    bool dbias_done = false;        // this backward pass: the bias gradient came out of the consumer's dA epilogue
 };
 struct ChainStep {
     int root;
@@ -101,7 +123,7 @@ struct fg_exec {
     std::vector<int> saved;         // materialised non-input nodes except the output, in node order
     std::vector<int> grads;         // nodes that own a gradient buffer, in node order
     std::vector<uint8_t> trainable;
-    fg_buf *seed = nullptr, *loss_t = nullptr, *tmp = nullptr;
+    fg_buf *seed = nullptr, *loss_t = nullptr, *tmp = nullptr, *loss_sum = nullptr;
     fg_buf* stage[4] = {nullptr, nullptr, nullptr, nullptr};   // 16-bit graphs: f32 staging for softmax and the losses
     std::vector<fg_buf*> m, v;      // AdamW moments per input
     fg_buf* step_counter = nullptr;
@@ -118,6 +140,22 @@ struct fg_exec {
     const void* plan_ws[4] = {nullptr, nullptr, nullptr, nullptr};    // scratch arena the plan was recorded against
     bool use_plans = true;
     bool ce_softmax_tail = false;   // graph ends in softmax and the loss is cross-entropy
+    // Gradients (and AdamW moments) of the inputs: one arena each, tensors in the order in which the backward
+    // pass completes them.  ready_key[slot] = 2 * (backward step that completes it) + (0: by the time the step's
+    // dB is done, 1: at the end of the step).
+    fg_buf *grad_arena = nullptr, *m_arena = nullptr, *v_arena = nullptr;
+    uint64_t arena_elems = 0;
+    std::vector<int> arena_order;          // input slots in arena order
+    std::vector<uint64_t> arena_off;       // per input slot: element offset in the arenas
+    std::vector<int> ready_key;            // per input slot
+    std::vector<uint64_t> pairs_version;   // per input slot: version of the bound tensor its pairs were made from
+    std::vector<uint8_t> pairs_fresh;      // per input slot
+    bool paired = false;                   // f32 graph in the default GEMM mode: keep pairs, fuse the backward epilogues
+    // data-parallel state of one step
+    uint64_t exchanged_end = 0;            // arena elements whose exchange has been started by dispatch_backward
+    uint64_t final_lo = 0;                 // [final_lo, arena_elems): exchanged by dispatch_optim (set by the backward pass)
+    uint64_t optim_lo = 0;                 // the value dispatch_optim works with: final_lo after a backward pass, else 0
+    bool backward_done = false;            // a backward pass has run since the last dispatch_optim
 };
 
 namespace {
@@ -125,6 +163,8 @@ namespace {
 int32_t fail(fg_exec* e, int32_t code, const char* msg) { return fg_fail(e->ctx, code, msg); }
 
 float* vptr(fg_exec* e, int node) { return (float*)e->n[node].value->ptr; }
+// Elements between the two planes of a tensor's bf16 pairs: its size rounded up to a multiple of 8.
+uint64_t pstride(const fg_exec* e, int node) { return (e->n[node].numel + 7) / 8 * 8; }
 float* gptr(fg_exec* e, int node) { return (float*)e->n[node].grad->ptr; }
 
 // Emits the straight-line program that computes `node` from materialised values.
@@ -265,8 +305,10 @@ int32_t lower(fg_exec* e) {
             s.out = c;
         }
         gemm_of_out[s.out] = (int)e->gemms.size();
+        e->n[s.out].produced_by_gemm = (int)e->gemms.size();
         e->gemms.push_back(s);
     }
+    e->paired = e->dtype == FG_DTYPE_F32 && e->gemm_mode == FG_GEMM_AUTO;
     for (int i = 0; i < N; ++i)
         if (e->n[i].bias_bcast && !(i > 0 && e->n[g.nodes[i].a].absorbed))
             return fail(e, FG_ERR_UNSUPPORTED_FEATURE, "graph: a broadcast bias is only supported directly after a matmul");
@@ -292,13 +334,15 @@ int32_t lower(fg_exec* e) {
             if (i != e->last) e->saved.push_back(i);
         }
         if ((is_input || en.materialized) && i != e->last) {
-            if ((s = alloc_buf(e, en.numel, true, &en.grad)) != FG_OK) return s;   // zeroed like the reference
+            // inputs: a view into the gradient arena, made below once the order of the backward pass is known
+            if (!is_input && (s = alloc_buf(e, en.numel, true, &en.grad)) != FG_OK) return s;   // zeroed like the reference
             e->grads.push_back(i);
         }
     }
     const uint64_t on = e->n[e->last].numel;
     if ((s = alloc_buf(e, on, true, &e->seed)) != FG_OK) return s;
     if ((s = alloc_buf(e, on, true, &e->loss_t)) != FG_OK) return s;
+    if ((s = fg_alloc_zeroed(e->ctx, 256, &e->loss_sum)) != FG_OK) return s;
     uint64_t biggest = 1;
     for (int i = 0; i < N; ++i) biggest = std::max(biggest, e->n[i].numel);
     if ((s = alloc_buf(e, biggest, false, &e->tmp)) != FG_OK) return s;
@@ -307,16 +351,7 @@ int32_t lower(fg_exec* e) {
             if ((s = fg_alloc(e->ctx, biggest * 4, &st)) != FG_OK) return s;
     for (GemmStep& gs : e->gemms)
         if (gs.act == FG_ACT_GELU && (s = alloc_buf(e, e->n[gs.out].numel, false, &gs.preact)) != FG_OK) return s;
-    if (g.optim == FG_OPTIM_ADAMW) {
-        for (int id : e->inputs) {
-            fg_buf *m = nullptr, *v = nullptr;
-            if ((s = alloc_buf(e, e->n[id].numel, true, &m)) != FG_OK) return s;
-            if ((s = alloc_buf(e, e->n[id].numel, true, &v)) != FG_OK) return s;
-            e->m.push_back(m);
-            e->v.push_back(v);
-        }
-        if ((s = fg_alloc_zeroed(e->ctx, 256, &e->step_counter)) != FG_OK) return s;
-    }
+    if (g.optim == FG_OPTIM_ADAMW && (s = fg_alloc_zeroed(e->ctx, 256, &e->step_counter)) != FG_OK) return s;
     // ---- forward step list ----
     for (int i = 0; i < N; ++i) {
         const GNode& gn = g.nodes[i];
@@ -337,6 +372,88 @@ int32_t lower(fg_exec* e) {
     for (const GemmStep& gs : e->gemms)
         if (!(e->n[gs.a].materialized || g.nodes[gs.a].op == FG_EW_INPUT) || !(e->n[gs.b].materialized || g.nodes[gs.b].op == FG_EW_INPUT))
             return fail(e, FG_ERR_INTERNAL, "graph: matmul operand without a buffer");
+
+    // ---- gradient arena: the inputs' gradients in the order in which the backward pass completes them ----
+    const int nin = (int)e->inputs.size();
+    e->ready_key.assign(nin, INT_MAX);
+    auto completes = [&](int node, int key) {
+        const int slot = e->n[node].input_slot;
+        if (slot < 0) return;
+        if (e->ready_key[slot] == INT_MAX || key > e->ready_key[slot]) e->ready_key[slot] = key;
+    };
+    {
+        int bstep = 0;   // index of the step in the backward pass
+        for (int k = (int)e->fwd.size() - 1; k >= 0; --k, ++bstep) {
+            const Step& st = e->fwd[k];
+            if (st.kind == 0) {
+                const GemmStep& gs = e->gemms[st.idx];
+                completes(gs.b, 2 * bstep);                       // weight gradient: before the exchange point
+                if (gs.bias >= 0) completes(gs.bias, 2 * bstep);
+                completes(gs.a, 2 * bstep + 1);
+            } else if (st.kind == 1) {
+                for (int in : e->chains[st.idx].inputs) completes(in, 2 * bstep + 1);
+            } else {
+                completes(g.nodes[st.idx].a, 2 * bstep + 1);
+            }
+        }
+    }
+    e->arena_order.resize(nin);
+    for (int k = 0; k < nin; ++k) e->arena_order[k] = k;
+    std::stable_sort(e->arena_order.begin(), e->arena_order.end(),
+                     [&](int x, int y) { return e->ready_key[x] < e->ready_key[y]; });
+    e->arena_off.assign(nin, 0);
+    uint64_t off = 0;
+    for (int slot : e->arena_order) {
+        e->arena_off[slot] = off;
+        off += (e->n[e->inputs[slot]].numel + 63) / 64 * 64;       // every tensor 256-byte aligned (f32)
+    }
+    e->arena_elems = off;
+    if ((s = alloc_buf(e, off ? off : 1, true, &e->grad_arena)) != FG_OK) return s;
+    const bool adam = g.optim == FG_OPTIM_ADAMW;
+    if (adam) {
+        if ((s = alloc_buf(e, off ? off : 1, true, &e->m_arena)) != FG_OK) return s;
+        if ((s = alloc_buf(e, off ? off : 1, true, &e->v_arena)) != FG_OK) return s;
+    }
+    auto view = [&](fg_buf* arena, int slot) -> fg_buf* {
+        fg_buf* b = new (std::nothrow) fg_buf();
+        if (!b) return nullptr;
+        b->ptr = (char*)arena->ptr + e->arena_off[slot] * e->esize;
+        b->bytes = e->n[e->inputs[slot]].numel * e->esize;
+        b->version = 0;
+        b->view = true;
+        return b;
+    };
+    for (int slot = 0; slot < nin; ++slot) {
+        ENode& en = e->n[e->inputs[slot]];
+        if (!(en.grad = view(e->grad_arena, slot))) return fail(e, FG_ERR_OUT_OF_MEMORY, "graph: gradient views");
+        if (adam) {
+            fg_buf *m = view(e->m_arena, slot), *v = view(e->v_arena, slot);
+            if (!m || !v) return fail(e, FG_ERR_OUT_OF_MEMORY, "graph: moment views");
+            e->m.push_back(m);
+            e->v.push_back(v);
+        }
+    }
+    e->pairs_version.assign(nin, 0);
+    e->pairs_fresh.assign(nin, 0);
+
+    // ---- bf16 pairs of everything a matmul reads, and of the dZ a fused backward epilogue hands down ----
+    if (e->paired) {
+        auto want_pairs = [&](int node) -> int32_t {
+            ENode& en = e->n[node];
+            return en.pairs ? FG_OK : fg_alloc(e->ctx, pstride(e, node) * 4, &en.pairs);
+        };
+        for (GemmStep& gs : e->gemms) {
+            if (gs.batch != 1) continue;
+            if ((s = want_pairs(gs.a)) != FG_OK || (s = want_pairs(gs.b)) != FG_OK) return s;
+        }
+        for (GemmStep& gs : e->gemms) {
+            if (gs.batch != 1) continue;
+            const int h = e->n[gs.a].produced_by_gemm;
+            if (h >= 0 && e->n[gs.a].consumers == 1 && e->gemms[h].batch == 1 && !e->gemms[h].dz_pairs &&
+                (s = fg_alloc(e->ctx, pstride(e, gs.a) * 4, &e->gemms[h].dz_pairs)) != FG_OK)
+                return s;
+        }
+    }
     return FG_OK;
 }
 
@@ -430,10 +547,15 @@ int32_t fg_exec_destroy(fg_exec* e) {
         if (en.own_value && en.value) fg_free(e->ctx, en.value);
         if (en.grad) fg_free(e->ctx, en.grad);
     }
-    for (GemmStep& gs : e->gemms) if (gs.preact) fg_free(e->ctx, gs.preact);
-    for (fg_buf* b : e->m) fg_free(e->ctx, b);
+    for (ENode& en : e->n) if (en.pairs) fg_free(e->ctx, en.pairs);
+    for (GemmStep& gs : e->gemms) {
+        if (gs.preact) fg_free(e->ctx, gs.preact);
+        if (gs.dz_pairs) fg_free(e->ctx, gs.dz_pairs);
+    }
+    for (fg_buf* b : e->m) fg_free(e->ctx, b);       // views
     for (fg_buf* b : e->v) fg_free(e->ctx, b);
-    for (fg_buf* b : {e->seed, e->loss_t, e->tmp, e->step_counter}) if (b) fg_free(e->ctx, b);
+    for (fg_buf* b : {e->seed, e->loss_t, e->tmp, e->loss_sum, e->step_counter, e->grad_arena, e->m_arena, e->v_arena})
+        if (b) fg_free(e->ctx, b);
     for (fg_buf* b : e->stage) if (b) fg_free(e->ctx, b);
     drop_plans(e);
     delete e;
@@ -458,17 +580,45 @@ int32_t fg_exec_bind(fg_exec* e, fg_buf* const* in_tensors, uint32_t count, cons
     e->trainable.assign(count, 1);
     if (trainable) e->trainable.assign(trainable, trainable + count);
     e->bound = true;
+    std::fill(e->pairs_fresh.begin(), e->pairs_fresh.end(), 0);
     drop_plans(e);        // recorded against the previous tensors
     return FG_OK;
 }
 
+// Brings the pairs of the bound input tensors up to date.  A trainable tensor changes only through the optimizer
+// (which writes its pairs in the same pass) or through an entry point that bumps the buffer's version; a tensor that is
+// only read (the data batch) may be rewritten through its raw pointer at any time, so its pairs are made every pass.
+static int32_t refresh_input_pairs(fg_exec* e) {
+    for (size_t k = 0; k < e->inputs.size(); ++k) {
+        ENode& en = e->n[e->inputs[k]];
+        if (!en.pairs) continue;
+        if (e->trainable[k] && e->pairs_fresh[k] && e->pairs_version[k] == en.value->version) continue;
+        const int32_t s = fg_pairs_from_f32(e->ctx, (const float*)en.value->ptr, en.numel, en.pairs->ptr, pstride(e, e->inputs[k]));
+        if (s != FG_OK) return s;
+        e->pairs_fresh[k] = 1;
+        e->pairs_version[k] = en.value->version;
+    }
+    return FG_OK;
+}
+
+static void* pairs_of(fg_exec* e, int node) { return e->n[node].pairs ? e->n[node].pairs->ptr : nullptr; }
+
 static int32_t forward_eager(fg_exec* e) {
     int32_t s;
+    if (e->paired && (s = refresh_input_pairs(e)) != FG_OK) return s;
     for (const Step& st : e->fwd) {
         if (st.kind == 0) {
             const GemmStep& gs = e->gemms[st.idx];
             const size_t sa = (size_t)gs.M * gs.K, sb = (size_t)gs.K * gs.N, sc = (size_t)gs.M * gs.N;
             s = FG_OK;
+            if (e->paired && gs.batch == 1) {
+                // the tensors themselves are the operands; the epilogue writes the result's pairs for the matmul that reads it
+                s = fg_gemm_paired_f32(e->ctx, gs.M, gs.N, gs.K, vptr(e, gs.a), pairs_of(e, gs.a), pstride(e, gs.a), vptr(e, gs.b),
+                                       pairs_of(e, gs.b), pstride(e, gs.b), vptr(e, gs.out), gs.bias >= 0 ? vptr(e, gs.bias) : nullptr,
+                                       gs.act, gs.preact ? (float*)gs.preact->ptr : nullptr, pairs_of(e, gs.out), pstride(e, gs.out));
+                if (s != FG_OK) return s;
+                continue;
+            }
             for (uint32_t t = 0; t < gs.batch && s == FG_OK; ++t) {
                 if (e->dtype != FG_DTYPE_F32) {
                     char* const pa = (char*)vptr(e, gs.a) + t * sa * 2;
@@ -501,6 +651,12 @@ static int32_t forward_eager(fg_exec* e) {
             s = fg_softmax_fwd(e->ctx, (uint32_t)(numel / cols), cols, vptr(e, e->g.nodes[st.idx].a), vptr(e, st.idx));
         }
         if (s != FG_OK) return s;
+        if (e->paired && st.kind != 0) {
+            const int node = st.kind == 1 ? e->chains[st.idx].root : st.idx;
+            if (e->n[node].pairs &&
+                (s = fg_pairs_from_f32(e->ctx, vptr(e, node), e->n[node].numel, e->n[node].pairs->ptr, pstride(e, node))) != FG_OK)
+                return s;
+        }
     }
     return FG_OK;
 }
@@ -527,21 +683,23 @@ static int32_t loss_eager(fg_exec* e, const fg_buf* target) {
         if ((s = fg_convert(e->ctx, l32, FG_DTYPE_F32, e->loss_t->ptr, e->dtype, o.numel)) != FG_OK) return s;
         return fg_convert(e->ctx, g32, FG_DTYPE_F32, e->seed->ptr, e->dtype, o.numel);
     }
+    float* const lsum = (float*)e->loss_sum->ptr;
     if (e->g.loss == FG_LOSS_MSE) {
         FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
         return fg_mse_loss_grad(e->ctx, vptr(e, e->last), (const float*)target->ptr, o.numel, 1.0f, (float*)e->loss_t->ptr,
-                                nullptr, (float*)e->seed->ptr);
+                                lsum, (float*)e->seed->ptr);
     }
     if (e->g.loss == FG_LOSS_BINARY_CROSS_ENTROPY) {
         FG_REQUIRE(e->ctx, target->bytes >= o.numel * 4, "dispatch_loss: target smaller than the output");
         return fg_bce_loss_grad(e->ctx, vptr(e, e->last), (const float*)target->ptr, o.numel, 1.0f, (float*)e->loss_t->ptr,
-                                nullptr, (float*)e->seed->ptr);
+                                lsum, (float*)e->seed->ptr);
     }
     const uint32_t cols = o.dims.back();
     const uint32_t rows = (uint32_t)(o.numel / cols);
     FG_REQUIRE(e->ctx, target->bytes >= (uint64_t)rows * 4, "dispatch_loss: one u32 label per row is required");
-    return fg_ce_loss_grad(e->ctx, vptr(e, e->last), (const uint32_t*)target->ptr, rows, cols, (float*)e->loss_t->ptr,
-                           (float*)e->seed->ptr);
+    const int32_t s = fg_ce_loss_grad(e->ctx, vptr(e, e->last), (const uint32_t*)target->ptr, rows, cols, (float*)e->loss_t->ptr,
+                                      (float*)e->seed->ptr);
+    return s != FG_OK ? s : fg_sum_f32(e->ctx, (const float*)e->loss_t->ptr, o.numel, lsum);
 }
 
 // The backward of one matmul in the graph's storage type.
@@ -553,20 +711,95 @@ static int32_t gemm_bwd_any(fg_exec* e, uint32_t M, uint32_t N, uint32_t K, cons
     return fg_gemm_bwd_lowp(e->ctx, e->dtype, M, N, K, A, B, dY, act, saved, dA, dB, dbias);
 }
 
+// Data-parallel helpers.  Only trainable tensors are exchanged; the arena is ordered by completion, so the
+// tensors whose gradients are complete form a prefix.
+static bool dp_active(const fg_exec* e) { return e->ctx->comm != nullptr && e->ctx->nranks > 1; }
+
+// End (arena elements) of the trainable tensors whose gradient is complete once the backward step with this key is.
+static uint64_t ready_end(const fg_exec* e, int key) {
+    uint64_t end = 0;
+    for (size_t k = 0; k < e->inputs.size(); ++k)
+        if (e->trainable[k] && e->ready_key[k] <= key) end = std::max(end, e->arena_off[k] + e->n[e->inputs[k]].numel);
+    return end;
+}
+
 static int32_t backward_eager(fg_exec* e) {
     const int N = (int)e->n.size();
     std::vector<uint8_t> written(N, 0);
+    for (GemmStep& gs : e->gemms) gs.dz_ready = gs.dbias_done = false;
+    e->exchanged_end = 0;
+    // an input's gradient is wanted when the input is trainable (every input is, unless fg_exec_bind said otherwise)
+    auto wanted = [&](int node) -> bool {
+        const int slot = e->n[node].input_slot;
+        return slot < 0 || e->trainable[slot] != 0;
+    };
+    int bstep = -1;
     auto grad_of = [&](int node) -> float* { return node == e->last ? (float*)e->seed->ptr : gptr(e, node); };
     // a tensor's t-th matrix: offsets are in elements of the graph's storage type
     auto off = [&](const void* p, size_t elems) -> float* { return (float*)((char*)p + elems * e->esize); };
     int32_t s;
     for (int k = (int)e->fwd.size() - 1; k >= 0; --k) {
         const Step& st = e->fwd[k];
+        ++bstep;
         if (st.kind == 0) {
-            const GemmStep& gs = e->gemms[st.idx];
+            GemmStep& gs = e->gemms[st.idx];
             if (gs.out != e->last && !written[gs.out]) continue;   // does not reach the output
             const uint32_t M = gs.M, K = gs.K, Nn = gs.N;
             const size_t sa = (size_t)M * K, sb = (size_t)K * Nn, sc = (size_t)M * Nn;
+            // The range of the arena whose gradients are complete once this step's weight (and bias) gradient is:
+            // exchanged beside this step's dA product when it is large enough.
+            float* exch_buf = nullptr;
+            uint64_t exch_count = 0;
+            if (dp_active(e)) {
+                const uint64_t end0 = ready_end(e, 2 * bstep);
+                // a smaller range waits for the next one (launch cost; the GEMMs give up SMs while an exchange runs)
+                if (end0 > e->exchanged_end && end0 - e->exchanged_end >= e->ctx->opt_min_exchange) {
+                    exch_buf = (float*)e->grad_arena->ptr + e->exchanged_end;
+                    exch_count = end0 - e->exchanged_end;
+                }
+            }
+            if (e->paired && gs.batch == 1 && !written[gs.a] && !written[gs.b] && gs.a != gs.b &&
+                (gs.act == FG_ACT_NONE || gs.dz_ready) && (gs.bias < 0 || !written[gs.bias] || gs.dbias_done)) {
+                // grad(out) is dL/d(pre-activation) already.  When the first operand is the fused result of another
+                // matmul that nothing else reads, this call's dA epilogue applies that layer's activation derivative,
+                // writes the pairs of the result and sums its columns into that layer's bias gradient.
+                const int h = e->n[gs.a].produced_by_gemm;
+                GemmStep* below = (h >= 0 && e->n[gs.a].consumers == 1 && e->gemms[h].batch == 1) ? &e->gemms[h] : nullptr;
+                const bool want_da = wanted(gs.a), want_db = wanted(gs.b);
+                int below_act = FG_ACT_NONE;
+                const float* below_saved = nullptr;
+                float* below_dbias = nullptr;
+                void* da_pairs = nullptr;
+                if (below && want_da) {
+                    below_act = below->act;
+                    if (below_act != FG_ACT_NONE) below_saved = below_act == FG_ACT_GELU ? (const float*)below->preact->ptr : vptr(e, below->out);
+                    da_pairs = below->dz_pairs ? below->dz_pairs->ptr : nullptr;
+                    if (below->bias >= 0 && !written[below->bias] && wanted(below->bias)) below_dbias = gptr(e, below->bias);
+                }
+                float* dbias = (gs.bias >= 0 && !gs.dbias_done && wanted(gs.bias)) ? gptr(e, gs.bias) : nullptr;
+                s = fg_gemm_bwd_paired_f32(e->ctx, M, Nn, K, vptr(e, gs.a), pairs_of(e, gs.a), pstride(e, gs.a), vptr(e, gs.b),
+                                           pairs_of(e, gs.b), pstride(e, gs.b), grad_of(gs.out),
+                                           gs.dz_ready && gs.dz_pairs ? gs.dz_pairs->ptr : nullptr, pstride(e, gs.out),
+                                           want_db ? gptr(e, gs.b) : nullptr, dbias, want_da ? gptr(e, gs.a) : nullptr, below_act,
+                                           below_saved, da_pairs, pstride(e, gs.a), below_dbias, exch_buf, exch_count);
+                if (s != FG_OK) return s;
+                if (exch_buf) e->exchanged_end += exch_count;
+                written[gs.a] = written[gs.b] = 1;
+                if (gs.bias >= 0) written[gs.bias] = 1;
+                if (below && want_da) {
+                    below->dz_ready = true;
+                    if (below_dbias) { below->dbias_done = true; written[below->bias] = 1; }
+                }
+                continue;
+            }
+            // every other route computes this step's gradients first and exchanges afterwards
+            struct ExchangeAfter {
+                fg_exec* e; float* buf; uint64_t count;
+                ~ExchangeAfter() {
+                    if (buf && fg_allreduce_sum_f32(e->ctx, buf, count) == FG_OK) e->exchanged_end += count;
+                }
+            } exchange_after{e, exch_buf, exch_count};
+            if (gs.act != FG_ACT_NONE && gs.dz_ready) return fail(e, FG_ERR_INTERNAL, "graph: fused gradient reached an unfused matmul backward");
             // destinations: the gradient buffer itself for a first contribution, the scratch tensor otherwise
             float* dA = written[gs.a] ? (float*)e->tmp->ptr : gptr(e, gs.a);
             const float* saved = gs.act == FG_ACT_NONE ? nullptr : gs.act == FG_ACT_GELU ? (float*)gs.preact->ptr : vptr(e, gs.out);
@@ -668,6 +901,9 @@ static int32_t backward_eager(fg_exec* e) {
             written[src] = 1;
         }
     }
+    // what has been exchanged so far is complete before dispatch_optim reads it; the rest is exchanged there
+    e->final_lo = e->exchanged_end;
+    if (e->ctx->comm_pending && !e->ctx->capturing) return fg_comm_join(e->ctx);
     return FG_OK;
 }
 
@@ -686,12 +922,22 @@ static int32_t optim_one(fg_exec* e, uint32_t slot, fg_buf* weight) {
         if (s != FG_OK) return s;
         return fg_memset_zero(e->ctx, gptr(e, node), e->n[node].numel * e->esize);
     }
-    if (e->g.optim == FG_OPTIM_SGD)
-        return fg_sgd_step(e->ctx, (float*)weight->ptr, gptr(e, node), e->n[node].numel, lr, 1.0f, 1);
-    fg_adamw_hyper h = e->hyper;
-    h.lr = lr;
-    return fg_adamw_step(e->ctx, (float*)weight->ptr, gptr(e, node), (float*)e->m[slot]->ptr, (float*)e->v[slot]->ptr,
-                         e->n[node].numel, &h, 0, (const uint32_t*)e->step_counter->ptr, 1.0f, 1);
+    // the updated weights' pairs are written in the same pass when a matmul reads this tensor
+    void* wp = (e->n[node].pairs && weight == e->n[node].value) ? e->n[node].pairs->ptr : nullptr;
+    int32_t s;
+    if (e->g.optim == FG_OPTIM_SGD) {
+        s = fg_sgd_step_paired(e->ctx, (float*)weight->ptr, gptr(e, node), e->n[node].numel, lr, 1.0f, 1, wp, pstride(e, node));
+    } else {
+        fg_adamw_hyper h = e->hyper;
+        h.lr = lr;
+        s = fg_adamw_step_paired(e->ctx, (float*)weight->ptr, gptr(e, node), (float*)e->m[slot]->ptr, (float*)e->v[slot]->ptr,
+                                 e->n[node].numel, &h, 0, (const uint32_t*)e->step_counter->ptr, 1.0f, 1, wp, pstride(e, node));
+    }
+    if (s == FG_OK && wp) {
+        e->pairs_fresh[slot] = 1;
+        e->pairs_version[slot] = weight->version;
+    }
+    return s;
 }
 
 // Updates every bound tensor that is marked trainable (the reference updates all of them:
@@ -699,6 +945,23 @@ static int32_t optim_one(fg_exec* e, uint32_t slot, fg_buf* weight) {
 static int32_t optim_eager(fg_exec* e) {
     int32_t s;
     if (e->g.optim == FG_OPTIM_ADAMW && (s = fg_counter_increment(e->ctx, (uint32_t*)e->step_counter->ptr)) != FG_OK) return s;
+    if (dp_active(e)) {
+        // Gradients in [0, final_lo) were summed over the ranks during dispatch_backward.  The sum of the rest
+        // (the gradients the backward pass finished last) starts now; the tensors of the first range are updated
+        // beside it, the others when it has arrived.
+        const uint64_t lo = e->optim_lo, hi = ready_end(e, INT_MAX - 1);
+        if (hi > lo && (s = fg_allreduce_sum_f32(e->ctx, (float*)e->grad_arena->ptr + lo, hi - lo)) != FG_OK) return s;
+        for (int slot : e->arena_order)
+            if (e->trainable[slot] && e->arena_off[slot] + e->n[e->inputs[slot]].numel <= lo &&
+                (s = optim_one(e, (uint32_t)slot, e->n[e->inputs[slot]].value)) != FG_OK)
+                return s;
+        if ((s = fg_comm_join(e->ctx)) != FG_OK) return s;
+        for (int slot : e->arena_order)
+            if (e->trainable[slot] && e->arena_off[slot] + e->n[e->inputs[slot]].numel > lo &&
+                (s = optim_one(e, (uint32_t)slot, e->n[e->inputs[slot]].value)) != FG_OK)
+                return s;
+        return FG_OK;
+    }
     for (uint32_t k = 0; k < e->inputs.size(); ++k)
         if (e->trainable[k] && (s = optim_one(e, k, e->n[e->inputs[k]].value)) != FG_OK) return s;
     return FG_OK;
@@ -734,6 +997,18 @@ static int32_t run_planned(fg_exec* e, int which, const void* key, const std::fu
 int32_t fg_exec_dispatch_forward(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_forward: bind the input tensors first");
+    if (e->paired) {
+        // A recorded forward pass does not contain the pairs of the weights (the optimizer keeps them current).
+        // If a weight tensor was rewritten from outside since, its pairs are made now, before the replay.
+        for (size_t k = 0; k < e->inputs.size(); ++k) {
+            ENode& en = e->n[e->inputs[k]];
+            if (!en.pairs || !e->trainable[k] || (e->pairs_fresh[k] && e->pairs_version[k] == en.value->version)) continue;
+            const int32_t s = fg_pairs_from_f32(e->ctx, (const float*)en.value->ptr, en.numel, en.pairs->ptr, pstride(e, e->inputs[k]));
+            if (s != FG_OK) return s;
+            e->pairs_fresh[k] = 1;
+            e->pairs_version[k] = en.value->version;
+        }
+    }
     return run_planned(e, 0, nullptr, [&] { return forward_eager(e); });
 }
 
@@ -747,13 +1022,22 @@ int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
 int32_t fg_exec_dispatch_backward(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_backward: bind the input tensors first");
-    return run_planned(e, 2, nullptr, [&] { return backward_eager(e); });
+    const int32_t s = run_planned(e, 2, nullptr, [&] { return backward_eager(e); });
+    if (s == FG_OK) e->backward_done = true;
+    return s;
 }
 
 int32_t fg_exec_dispatch_optim(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_optim: bind the input tensors first");
-    return run_planned(e, 3, nullptr, [&] { return optim_eager(e); });
+    // With a communicator, the range of the gradient arena that is still to be summed over the ranks depends on
+    // whether a backward pass came before (it has exchanged everything below final_lo already); a recorded
+    // dispatch is replayed only for the same range.
+    e->optim_lo = e->backward_done ? e->final_lo : 0;
+    const void* key = dp_active(e) ? (const void*)(uintptr_t)(e->optim_lo + 1) : nullptr;
+    const int32_t s = run_planned(e, 3, key, [&] { return optim_eager(e); });
+    if (s == FG_OK) e->backward_done = false;
+    return s;
 }
 
 // dispatch_single_optim (dispatch/mod.rs:790-814): one weight, its gradient chosen by index.
@@ -770,6 +1054,7 @@ int32_t fg_exec_dispatch_single_optim(fg_exec* e, fg_buf* weight, uint32_t grad_
 fg_buf* fg_exec_forward_out(fg_exec* e) { return e ? e->n[e->last].value : nullptr; }
 fg_buf* fg_exec_seed(fg_exec* e) { return e ? e->seed : nullptr; }
 fg_buf* fg_exec_loss_t(fg_exec* e) { return e ? e->loss_t : nullptr; }
+fg_buf* fg_exec_loss_sum(fg_exec* e) { return e ? e->loss_sum : nullptr; }
 uint32_t fg_exec_num_saved(fg_exec* e) { return e ? (uint32_t)e->saved.size() : 0; }
 fg_buf* fg_exec_saved(fg_exec* e, uint32_t i, int32_t* node) {
     if (!e || i >= e->saved.size()) return nullptr;

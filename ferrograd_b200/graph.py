@@ -183,6 +183,7 @@ class AllocTensors:
             self.grad_nodes.append(node.value)
         lt = wrap(lib.fg_exec_loss_t(handle))
         self.loss_t = Tensor((lt.size_bytes() // 4,), lt)
+        self.loss_sum = wrap(lib.fg_exec_loss_sum(handle))      # one f32: sum over loss_t (this backend's addition)
         self.state = []
 
     def forward_steps(self):

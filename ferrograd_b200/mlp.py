@@ -113,6 +113,27 @@ class MLPTrainer:
         if self.paired:
             self.ctx.pairs_from_f32(self.params, self.n_arena, self.w_pairs, self.n_arena)
 
+    def destroy(self):
+        """Frees every device buffer of the trainer."""
+        from .backend import Buffer
+        if self.plan is not None:
+            self.plan.destroy()
+            self.plan = None
+        for v in list(vars(self).values()):
+            for b in (v if isinstance(v, (list, tuple)) else [v]):
+                if isinstance(b, Buffer):
+                    b.free()
+
+    def reset_state(self):
+        """Zeroes gradients, optimizer moments and the step counter (a fresh start from the current parameters)."""
+        nb = self.n_arena * 4
+        self.ctx.memset_zero(self.grads, nb)
+        if self.m is not None:
+            self.ctx.memset_zero(self.m, nb)
+            self.ctx.memset_zero(self.v, nb)
+        self.ctx.memset_zero(self.step_counter, 256)
+        self.steps_done = 0
+
     def _split(self, arena):
         W = [arena[self.w_off[l]:self.w_off[l] + self.dims[l] * self.dims[l + 1]]
              .reshape(self.dims[l], self.dims[l + 1]).copy() for l in range(self.L)]
@@ -323,3 +344,89 @@ class MLPTrainer:
             g = 2 * self.batch * self.dims[l] * self.dims[l + 1]
             f += g * (3 if l > 0 else 2)
         return f
+
+
+class GraphMLP:
+    """The same training step written against the mirrored graph API, the way a ferrograd program is
+    (crates/ferrograd/examples/save_load_model.rs:148-156): Graph / define_ops / alloc_tensors / schedule, then
+    dispatch_forward, dispatch_loss, dispatch_backward, dispatch_optim per step.  Reference semantics: the loss is
+    unreduced (gradients are sums over the batch, not means), every weight and bias is its own tensor.  With a
+    communicator on the context (ctx.comm_init) the engine sums the gradients over the ranks."""
+
+    def __init__(self, ctx: GpuContext, dims, batch, hidden_act="gelu", loss="ce",
+                 optimizer=("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01), gemm_mode="auto"):
+        from .graph import CROSS_ENTROPY, MEAN_SQUARED_ERROR, Graph, Metadata, Optim, f32_bits
+        self.ctx, self.dims, self.batch, self.loss_kind = ctx, [int(d) for d in dims], int(batch), loss
+        self.L = L = len(self.dims) - 1
+        meta = Metadata.new()
+        fb = meta.new_field()
+        fd = [meta.new_field() for _ in self.dims]
+        self.opt = Optim.adamw(*optimizer[2:]) if optimizer[0] == "adamw" else Optim.sgd()
+        self.graph = Graph.new(CROSS_ENTROPY if loss == "ce" else MEAN_SQUARED_ERROR, self.opt.lower)
+        g = self.graph.define_ops()
+        h = g.input([fb, fd[0]])
+        for l in range(L):
+            h = g.add(g.matmul(h, g.input([fd[l], fd[l + 1]])), g.input([fd[l + 1]]))
+            if l < L - 1:
+                h = getattr(g, hidden_act)(h)
+        if loss == "ce":
+            g.softmax(h)
+        binding = [f32_bits(optimizer[1]), self.batch] + self.dims
+        self.tensors = ctx.alloc_tensors(self.graph, self.graph.compute_saved_nodes(), ctx.alloc_meta(binding), self.opt.state,
+                                         gemm_mode=gemm_mode)
+        kernels = ctx.compile(self.graph.lower(meta, None, None), None)
+        self.x = ctx.new_tensor((self.batch, self.dims[0]))
+        self.W = [ctx.new_tensor((self.dims[l], self.dims[l + 1]), zeroed=True) for l in range(L)]
+        self.b = [ctx.new_tensor((self.dims[l + 1],), zeroed=True) for l in range(L)]
+        od = self.dims[-1]
+        self.target = ctx.new_tensor((self.batch,), np.uint32) if loss == "ce" else ctx.new_tensor((self.batch, od))
+        ins = [self.x]
+        for l in range(L):
+            ins += [self.W[l], self.b[l]]
+        self.schedule = ctx.schedule(kernels, binding, ins, self.tensors, [], self.opt.state, trainable=[0] + [1] * (2 * L))
+        self.loss_out = self.tensors.loss_sum
+        self.n_params = sum(self.dims[l] * self.dims[l + 1] + self.dims[l + 1] for l in range(L))
+
+    def set_params(self, W, b):
+        for l in range(self.L):
+            self.ctx.upload(self.W[l], np.asarray(W[l], np.float32))
+            self.ctx.upload(self.b[l], np.asarray(b[l], np.float32))
+
+    def get_params(self):
+        return [self.ctx.to_numpy(w) for w in self.W], [self.ctx.to_numpy(v) for v in self.b]
+
+    def upload_batch(self, x, target):
+        self.ctx.upload(self.x, np.ascontiguousarray(x, np.float32))
+        self.ctx.upload(self.target, np.ascontiguousarray(target, np.uint32 if self.loss_kind == "ce" else np.float32))
+
+    def upload_batch_async(self, x_pinned, target_pinned):
+        self.ctx.upload_async(self.x, x_pinned.ctypes.data, x_pinned.nbytes)
+        self.ctx.upload_async(self.target, target_pinned.ctypes.data, target_pinned.nbytes)
+
+    prefetch_batch = MLPTrainer.prefetch_batch
+    take_prefetched = MLPTrainer.take_prefetched
+
+    def step(self):
+        c, s = self.ctx, self.schedule
+        c.dispatch_forward(s)
+        c.dispatch_loss(s, self.target)
+        c.dispatch_backward(s)
+        c.dispatch_optim(s)
+
+    def get_loss(self):
+        """Sum of the unreduced loss tensor (cross-entropy: over the rows; MSE: over all elements)."""
+        return float(self.ctx.download(self.loss_out, np.empty(1, np.float32))[0])
+
+    def get_output(self):
+        return self.ctx.download(self.tensors.forward_out, np.empty((self.batch, self.dims[-1]), np.float32))
+
+    def flops_per_step(self):
+        return sum(2 * self.batch * self.dims[l] * self.dims[l + 1] * (3 if l > 0 else 2) for l in range(self.L))
+
+    def destroy(self):
+        self.tensors.destroy()
+        for t in [self.x, self.target] + self.W + self.b:
+            t.data.free()
+        for name in ("stage_x", "stage_t"):
+            if hasattr(self, name):
+                getattr(self, name).free()

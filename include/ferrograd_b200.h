@@ -97,6 +97,8 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  *   "exec_plans"    "1" (default) | "0": the graph engine records each dispatch as a CUDA graph
  *   "comm_max_ctas" CTAs the communicator may use (default 12; read by fg_comm_init)
  *   "comm_sms"      SMs the persistent GEMM leaves free while an exchange is in flight (default 16; 0 = none)
+ *   "comm_min_exchange"  the graph engine starts a gradient exchange during the backward pass once this many
+ *                   elements are complete (default 1048576); smaller ranges wait for the next one
  * The environment variables FG_GEMM_TILE, FG_GEMM_NO_SPLITK, FG_GEMM_NO_PAIRS, FG_EXEC_NO_PLANS,
  * NCCL_MAX_CTAS and FG_COMM_SMS give the initial values; they are read once, when the context is created. */
 int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value);
@@ -129,6 +131,11 @@ void* fg_buf_device_ptr(const fg_buf* buf);
 int32_t fg_upload(fg_ctx* ctx, fg_buf* dst, const void* src, uint64_t bytes, uint64_t dst_off);
 int32_t fg_download(fg_ctx* ctx, const fg_buf* src, void* dst, uint64_t bytes, uint64_t src_off);
 int32_t fg_copy(fg_ctx* ctx, const fg_buf* src, fg_buf* dst);
+/* Tells the library that the buffer's contents were changed through its raw device pointer (by a kernel of
+ * the host framework, fg_upload_async, ...).  The graph engine keeps derived data (the bf16 pairs of bound
+ * weight tensors) and refreshes it only when a tensor has changed: writes through fg_upload / fg_copy and
+ * the engine's own optimizer are seen, writes through the raw pointer need this call. */
+int32_t fg_buf_touch(fg_buf* buf);
 /* Asynchronous copies from/to PINNED host memory on the context stream. */
 int32_t fg_upload_async(fg_ctx* ctx, void* dst_dev, const void* src_pinned, uint64_t bytes);
 int32_t fg_download_async(fg_ctx* ctx, void* dst_pinned, const void* src_dev, uint64_t bytes);
@@ -263,6 +270,10 @@ int32_t fg_softmax_ce_fwd_bwd(fg_ctx* ctx, const float* logits, const uint32_t* 
  * loss[r,c] = −log p at c == label[r] else 0; grad[r,c] = p − 1 at the label else p. */
 int32_t fg_ce_loss_grad(fg_ctx* ctx, const float* probs, const uint32_t* labels,
                         uint32_t rows, uint32_t cols, float* loss_out, float* grad_out);
+
+/* out[0] = sum of x[0..n), reduced in a fixed order (no counterpart in the reference, whose losses stay
+ * unreduced: loss/basic_loss.rs:3-133; used to hand a caller one number per step instead of the loss tensor). */
+int32_t fg_sum_f32(fg_ctx* ctx, const float* x, uint64_t n, float* out);
 
 /* ---- MSE (MEAN_SQUARED_ERROR: loss/basic_loss.rs:3-27) ----
  * loss[i] = (p−t)², grad[i] = 2(p−t)·grad_scale.  loss_elem_out and loss_sum_out
@@ -427,6 +438,9 @@ int32_t fg_exec_dispatch_single_optim(fg_exec* e, fg_buf* weight, uint32_t grad_
 fg_buf* fg_exec_forward_out(fg_exec* e);
 fg_buf* fg_exec_seed(fg_exec* e);
 fg_buf* fg_exec_loss_t(fg_exec* e);
+/* One f32: the sum over loss_t, written by dispatch_loss (f32 graphs; no counterpart in the reference, which
+ * leaves the reduction of its unreduced loss tensor to the caller). */
+fg_buf* fg_exec_loss_sum(fg_exec* e);
 uint32_t fg_exec_num_saved(fg_exec* e);
 fg_buf* fg_exec_saved(fg_exec* e, uint32_t i, int32_t* node);
 uint32_t fg_exec_num_grads(fg_exec* e);

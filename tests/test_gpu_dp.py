@@ -64,6 +64,62 @@ def test_two_gpus_match_one_gpu_on_the_global_batch(tmp_path):
         assert np.max(np.abs(got - ref)) <= 2e-5 + 1e-4 * np.max(np.abs(ref)), float(np.max(np.abs(got - ref)))
 
 
+def _rank_graph_api(rank, world, port, out_dir):
+    """The reference's training loop (dispatch_forward / loss / backward / optim) on two ranks: the graph engine
+    itself sums the gradients over the ranks.  A small exchange threshold makes the backward pass start exchanges
+    of its own, as it does for large layers; four steps cover the eager, the recorded and the replayed dispatch."""
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    from ferrograd_b200 import GpuContext, dp
+    from ferrograd_b200.mlp import GraphMLP, MLPTrainer
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)     # host plumbing only
+    ctx = GpuContext(rank)
+    ctx.comm_init(world, rank, dp.exchange_unique_id(ctx, dist, rank))
+    ctx.set_option("comm_min_exchange", 20000)
+    net = GraphMLP(ctx, GDIMS, BATCH, "gelu", "ce", OPT)
+    net.set_params(*MLPTrainer.init_params(GDIMS, "he_normal", 21))
+    for s in range(GSTEPS):
+        net.upload_batch(*dp.synth_batch(dict(dims=GDIMS, batch=BATCH, loss="ce"), rank, s))
+        net.step()
+    ctx.sync()
+    assert ctx.device_status() == 0
+    W, b = net.get_params()
+    np.savez(os.path.join(out_dir, f"graph_rank{rank}.npz"), *W, *b)
+    dist.barrier()
+    dist.destroy_process_group()
+    ctx.destroy()
+
+
+GDIMS, GSTEPS = [64, 256, 192, 10], 4
+
+
+def test_graph_api_two_gpus_match_one_gpu_on_the_global_batch(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from ferrograd_b200 import GpuContext, dp
+    from ferrograd_b200.mlp import GraphMLP, MLPTrainer
+    mp.spawn(_rank_graph_api, args=(2, 29900 + os.getpid() % 300, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "graph_rank0.npz"), np.load(tmp_path / "graph_rank1.npz")
+    for k in r0.files:
+        assert np.array_equal(r0[k], r1[k])           # replicas stay bit-identical
+    # one GPU, the concatenated batch, the same API: the loss is unreduced, so the summed gradient is the same sum
+    ctx = GpuContext(0)
+    net = GraphMLP(ctx, GDIMS, 2 * BATCH, "gelu", "ce", OPT)
+    net.set_params(*MLPTrainer.init_params(GDIMS, "he_normal", 21))
+    for s in range(GSTEPS):
+        net.upload_batch(*dp.global_batch(dict(dims=GDIMS, batch=BATCH, loss="ce"), 2, s))
+        net.step()
+    ctx.sync()
+    W, b = net.get_params()
+    ctx.destroy()
+    for got, ref in zip([r0[k] for k in r0.files], W + b):
+        assert np.max(np.abs(got - ref)) <= 2e-5 + 1e-4 * np.max(np.abs(ref)), float(np.max(np.abs(got - ref)))
+
+
 def _rank_peer_absent(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
