@@ -311,96 +311,72 @@ def _kernel_lines(torch, stream, ctx, peaks):
     return out
 
 
-def graph_api_line(torch, stream, ctx, workload, steps):
-    """The same training step written against the mirrored graph API (Graph / alloc_tensors / schedule /
-    dispatch_forward / dispatch_loss / dispatch_backward / dispatch_optim): what a ferrograd user would run."""
-    from ferrograd_b200 import CROSS_ENTROPY, MEAN_SQUARED_ERROR, Graph, Metadata, Optim, dp, f32_bits
+def fused_step_line(torch, stream, ctx, workload, steps):
+    """The same workload through MLPTrainer: one flat parameter arena, one update launch, the whole step one
+    CUDA graph, mean-reduced loss.  A side line: how much the four separate dispatches of the reference's loop cost."""
+    from ferrograd_b200 import dp
     from ferrograd_b200.mlp import MLPTrainer
     w = dp.WORKLOADS[workload]
-    dims, B = w["dims"], w["batch"]
-    L = len(dims) - 1
-    meta = Metadata.new()
-    fb = meta.new_field()
-    fd = [meta.new_field() for _ in dims]
-    opt = Optim.adamw(*w["opt"][2:]) if w["opt"][0] == "adamw" else Optim.sgd()
-    graph = Graph.new(CROSS_ENTROPY if w["loss"] == "ce" else MEAN_SQUARED_ERROR, opt.lower)
-    g = graph.define_ops()
-    x = g.input([fb, fd[0]])
-    params = [(g.input([fd[l], fd[l + 1]]), g.input([fd[l + 1]])) for l in range(L)]
-    h = x
-    for l, (wn, bn) in enumerate(params):
-        h = g.add(g.matmul(h, wn), bn)
-        if l < L - 1:
-            h = getattr(g, w["act"])(h)
-    if w["loss"] == "ce":
-        g.softmax(h)
-    binding = [f32_bits(w["opt"][1]), B] + dims
-    tensors = ctx.alloc_tensors(graph, graph.compute_saved_nodes(), ctx.alloc_meta(binding), opt.state)
-    kernels = ctx.compile(graph.lower(meta, None, None), None)
-    W0, b0 = MLPTrainer.init_params(dims, w["init"], w["seed"])
-    xs, ts = dp.synth_batch(workload, 0, 0)
-    ins = [ctx.init_tensor_f32(xs.shape, xs)]
-    for l in range(L):
-        ins += [ctx.init_tensor_f32(W0[l].shape, W0[l]), ctx.init_tensor_f32(b0[l].shape, b0[l])]
-    target = ctx.new_onehot_init(ts) if w["loss"] == "ce" else ctx.init_tensor_f32(ts.shape, ts)
-    sch = ctx.schedule(kernels, binding, ins, tensors, [], opt.state, trainable=[0] + [1] * (2 * L))
-
-    def step(i):
-        ctx.dispatch_forward(sch)
-        ctx.dispatch_loss(sch, target)
-        ctx.dispatch_backward(sch)
-        ctx.dispatch_optim(sch)
-
-    for i in range(3):
-        step(i)
-    ms = timed(torch, stream, ctx, step, steps)
-    out = {"samples_per_s": B * steps / (ms / 1e3), "ms_per_step": ms / steps, "forward_kernel_steps": tensors.forward_steps(),
-           "note": "reference semantics: unreduced loss, one update launch per tensor"}
-    tensors.destroy()
-    for t in ins:
-        t.data.free()
+    tr = MLPTrainer(ctx, w["dims"], w["batch"], w["act"], w["loss"], w["opt"])
+    tr.set_params(*MLPTrainer.init_params(w["dims"], w["init"], w["seed"]))
+    tr.upload_batch(*dp.synth_batch(workload, 0, 0))
+    for _ in range(3):
+        tr.step()
+    tr.build_plan()
+    for _ in range(3):
+        tr.step_plan()
+    ms = timed(torch, stream, ctx, lambda i: tr.step_plan(), steps)
+    out = {"samples_per_s": w["batch"] * steps / (ms / 1e3), "ms_per_step": ms / steps,
+           "note": "MLPTrainer: flat arena, one update launch, one CUDA-graph replay per step, mean-reduced loss"}
+    tr.destroy()
     return out
 
 
-def dp_parity_check(torch, dist, ctx, tr, w, workload, rank, world, W0, b0):
-    """One training step on `world` ranks against the same step on ONE GPU over the concatenated batch.
-    Returns (on every rank) the largest parameter difference between replicas -- it must be 0: every rank
-    applies the same update to the same summed gradient -- and, measured on rank 0, how far the N-rank loss
-    and parameters are from the single-GPU ones (summation order is the only difference)."""
+def get_arena(torch, ctx, net):
+    """All parameters of a GraphMLP as one device vector (W0, b0, W1, b1, ...)."""
+    parts = []
+    for l in range(net.L):
+        for t in (net.W[l], net.b[l]):
+            v = torch.empty(t.size, device="cuda", dtype=torch.float32)
+            ctx.copy_dev_async(v.data_ptr(), t.ptr, t.size * 4)
+            parts.append(v)
+    ctx.sync()
+    return torch.cat(parts)
+
+
+def dp_parity_check(torch, dist, ctx, net, make_net, w, workload, rank, world, W0, b0):
+    """One training step on `world` ranks against the same step on ONE GPU over the concatenated batch, both
+    through the graph API.  Returns (on every rank) the largest parameter difference between replicas -- it must be
+    0: every rank applies the same update to the same summed gradient -- and, measured on rank 0, how far the
+    N-rank loss and parameters are from the single-GPU ones (summation order is the only difference)."""
     from ferrograd_b200 import dp
-    from ferrograd_b200.mlp import MLPTrainer
-    tr.upload_batch(*dp.synth_batch(workload, rank, 0))
-    tr.step()
+    net.upload_batch(*dp.synth_batch(workload, rank, 0))
+    net.step()
     ctx.sync()
-    n = tr.n_arena
-    mine = torch.empty(n, device="cuda", dtype=torch.float32)
-    ctx.copy_dev_async(mine.data_ptr(), tr.params.ptr, n * 4)
-    ctx.sync()
+    mine = get_arena(torch, ctx, net)
     ref = mine.clone()
     dist.broadcast(ref, src=0)
     diff = (mine - ref).abs().max().to(torch.float64).reshape(1)
     dist.all_reduce(diff, op=dist.ReduceOp.MAX)
-    loss = torch.tensor([tr.get_loss()], device="cuda", dtype=torch.float64)
-    dist.all_reduce(loss, op=dist.ReduceOp.SUM)
-    # cross-entropy reports the mean over the local rows, MSE the local sum of squares
-    loss_dp = float(loss.item()) / (world if w["loss"] == "ce" else 1)
-    out = {"replica_max_abs_diff": float(diff.item()), "loss_n_ranks": loss_dp}
+    loss = torch.tensor([net.get_loss()], device="cuda", dtype=torch.float64)
+    dist.all_reduce(loss, op=dist.ReduceOp.SUM)         # the loss is an unreduced sum: the global loss is the sum over ranks
+    out = {"replica_max_abs_diff": float(diff.item()), "loss_sum_n_ranks": float(loss.item())}
     if rank == 0:
-        single = MLPTrainer(ctx, w["dims"], w["batch"] * world, w["act"], w["loss"], w["opt"], world=1, rank=0)
+        from ferrograd_b200 import GpuContext
+        solo = GpuContext(ctx.device)                      # a context of its own: no communicator, nothing is exchanged
+        single = make_net(w["batch"] * world, on=solo)
         single.set_params(W0, b0)
         single.upload_batch(*dp.global_batch(workload, world, 0))
         single.step()
-        ctx.sync()
-        one = torch.empty(n, device="cuda", dtype=torch.float32)
-        ctx.copy_dev_async(one.data_ptr(), single.params.ptr, n * 4)
-        ctx.sync()
-        rms = float(one.double().pow(2).mean().sqrt().item())
-        out["loss_one_gpu_on_concatenated_batch"] = single.get_loss()
+        solo.sync()
+        one = get_arena(torch, solo, single)
+        out["loss_sum_one_gpu_on_concatenated_batch"] = single.get_loss()
         out["params_vs_one_gpu_max_abs_diff"] = float((mine - one).abs().max().item())
-        out["params_rms"] = rms
+        out["params_rms"] = float(one.double().pow(2).mean().sqrt().item())
         out["note"] = ("the first AdamW step moves every weight by about lr, sign(g) deciding the direction, so where "
                        "|g| is at rounding level the two summation orders may differ by up to 2*lr")
         single.destroy()
+        solo.destroy()
     dist.barrier()
     return out
 
@@ -409,7 +385,7 @@ def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     from ferrograd_b200 import GpuContext, dp
-    from ferrograd_b200.mlp import MLPTrainer
+    from ferrograd_b200.mlp import GraphMLP, MLPTrainer
 
     # Libraries (NCCL's version banner, for one) may write to stdout; the contract is ONE JSON line there.
     # Keep the real stdout aside and point fd 1 at stderr until the line is printed.
@@ -431,9 +407,15 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         uid = dp.exchange_unique_id(ctx, dist, rank)
         ctx.comm_init(world, rank, uid)
-    tr = MLPTrainer(ctx, w["dims"], w["batch"], w["act"], w["loss"], w["opt"], world=world, rank=rank)
+
+    # The training loop is the reference's: a Graph, alloc_tensors, schedule, then dispatch_forward / dispatch_loss /
+    # dispatch_backward / dispatch_optim per step.  With a communicator the engine sums the gradients over the ranks.
+    def make_net(batch, on=None):
+        return GraphMLP(on or ctx, w["dims"], batch, w["act"], w["loss"], w["opt"])
+
+    net = make_net(w["batch"])
     W0, b0 = MLPTrainer.init_params(w["dims"], w["init"], w["seed"])
-    tr.set_params(W0, b0)
+    net.set_params(W0, b0)
 
     # synthetic batches in pinned host memory (rotated); shapes and distributions per the workload
     NB = 4
@@ -462,14 +444,16 @@ def run_ours(args, rank, world, local_rank):
     # ---- data-parallel parity, outside every timed region: one step from the initial parameters ----
     dp_check = None
     if world > 1:
-        dp_check = dp_parity_check(torch, dist, ctx, tr, w, args.workload, rank, world, W0, b0)
-        tr.set_params(W0, b0)
-        tr.reset_state()
+        dp_check = dp_parity_check(torch, dist, ctx, net, make_net, w, args.workload, rank, world, W0, b0)
+        net.destroy()
+        net = make_net(w["batch"])          # a fresh start: initial parameters, zero optimizer state
+        net.set_params(W0, b0)
 
-    # ---- warm-up (also sizes the scratch arena) ----
-    tr.upload_batch_async(xs[0], ts[0])
+    # ---- warm-up, eager (also sizes the scratch arena) ----
+    ctx.set_option("exec_plans", "0")
+    net.upload_batch_async(xs[0], ts[0])
     for _ in range(max(3, args.warmup)):
-        tr.step()
+        net.step()
     barrier()
 
     # ---- timed region 1: eager launches, device-resident inputs; every GEMM / pre-pass / AdamW launch is
@@ -481,7 +465,7 @@ def run_ours(args, rank, world, local_rank):
     if sampler:
         sampler.start()
     barrier()
-    eager_ms = timed(torch, stream, ctx, lambda i: tr.step(), args.steps)
+    eager_ms = timed(torch, stream, ctx, lambda i: net.step(), args.steps)
     barrier()
     eager_ms = max_over_ranks(eager_ms)
     gemm_n, gemm_ms, gemm_flop = ctx.timing_read("gemm_tc")
@@ -489,21 +473,20 @@ def run_ours(args, rank, world, local_rank):
     adam_n, adam_ms, adam_bytes = ctx.timing_read("adamw")
     ctx.timing_enable(False)
 
-    # ---- the step as a replayed CUDA graph (the reference's Schedule is a captured graph too) ----
-    step_fn, mode = (lambda: tr.step()), "eager launches"
-    try:
-        tr.build_plan()
-        for _ in range(3):
-            tr.step_plan()
-        barrier()
-        step_fn, mode = (lambda: tr.step_plan()), "one CUDA-graph replay per step"
-    except Exception as e:   # reported, never hidden
-        mode = f"eager launches (plan unavailable: {e})"
+    # ---- every dispatch recorded as a CUDA graph on its second call and replayed from then on (the
+    #      reference's Schedule is a captured graph too: rocm/mod.rs:324-389) ----
+    ctx.set_option("exec_plans", "1")
+    for _ in range(4):
+        net.step()
+    barrier()
+    mode = ("dispatch_forward + dispatch_loss + dispatch_backward + dispatch_optim through the graph API, each "
+            "replayed as a recorded CUDA graph" + ("; gradients summed over the ranks inside dispatch_backward / "
+                                                   "dispatch_optim (NCCL)" if world > 1 else ""))
 
     # ---- timed region 2 (headline): K steps, inputs resident in HBM ----
     launches0 = ctx.launch_count()
     barrier()
-    ms = timed(torch, stream, ctx, lambda i: step_fn(), args.steps)
+    ms = timed(torch, stream, ctx, lambda i: net.step(), args.steps)
     barrier()
     launches = ctx.launch_count() - launches0
     ms = max_over_ranks(ms)
@@ -511,13 +494,13 @@ def run_ours(args, rank, world, local_rank):
     # ---- timed region 3: end to end through the public API with host buffers ----
     # Every step's inputs travel from pinned host memory inside the timed region; the copy of batch i+1 runs
     # on the context's copy stream while step i computes, and a device-to-device move puts it in place.
-    tr.prefetch_batch(xs[0], ts[0])
+    net.prefetch_batch(xs[0], ts[0])
 
     def e2e_step(i):
-        tr.take_prefetched()                                   # batch i is on the device
-        tr.prefetch_batch(xs[(i + 1) % NB], ts[(i + 1) % NB])  # start moving batch i+1
-        step_fn()
-        ctx.download_async(loss_host.ctypes.data, tr.loss_out, 4)
+        net.take_prefetched()                                   # batch i is on the device
+        net.prefetch_batch(xs[(i + 1) % NB], ts[(i + 1) % NB])  # start moving batch i+1
+        net.step()
+        ctx.download_async(loss_host.ctypes.data, net.loss_out, 4)
 
     for i in range(3):
         e2e_step(i)
@@ -526,7 +509,8 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     e2e_ms = max_over_ranks(e2e_ms)
     clocks = sampler.stop() if sampler else None
-    final_loss = float(loss_host[0])
+    od = w["dims"][-1]
+    final_loss = float(loss_host[0]) / (w["batch"] * (od if w["loss"] == "mse" else 1))     # per-sample mean of this rank
 
     if rank == 0:
         gb = w["batch"] * world
@@ -545,16 +529,17 @@ def run_ours(args, rank, world, local_rank):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": w["name"], "global_batch": gb, "parallelism": f"dp{world}",
-                       "gemm": "tcgen05: hi*hi as kind::tf32, the lo*hi and hi*lo cross terms as bf16 MMAs, f32 accumulate "
-                               "(a 3xTF32 split in which the two 2^-12-sized terms run at bf16 precision)",
-                       "l2": "per-step working set (parameters, moments, activations, operand planes: >1 GB) exceeds the 126 MB L2",
+                       "gemm": "tcgen05 on the f32 tensors as they lie: trunc(a)*trunc(b) as kind::tf32 plus the two cross "
+                               "terms as bf16 MMAs from bf16 pairs kept beside every tensor, f32 accumulate (a 3xTF32 split "
+                               "in which the two 2^-11-sized terms run at bf16 precision); no operand pre-pass",
+                       "l2": "per-step working set (parameters, moments, activations, pairs: >1 GB) exceeds the 126 MB L2",
                        "timed_region": mode,
                        "roofline_region": "the same K steps launched eagerly with per-kernel CUDA events"},
             "clocks": clocks,
             "e2e": {"value": gb * args.steps / (e2e_ms / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel / gemm_tc_kernel", "achieved": ach,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel (+ gemm_tc_pair_fold_kernel)", "achieved": ach,
                          "peak": own_peak, "unit": "TFLOP/s", "frac": ach / own_peak if own_peak else None,
                          "traffic": gemm_traffic_per_launch(args.workload),
                          "launches": int(gemm_n), "avg_launch_ms": gemm_ms / max(gemm_n, 1),
@@ -568,20 +553,20 @@ def run_ours(args, rank, world, local_rank):
                          "flop_per_launch": gemm_flop / max(gemm_n, 1),
                          "share_of_step": gemm_ms / eager_ms if eager_ms else None},
             "eager_ms_per_step": eager_ms / args.steps,
-            "other_kernels": {"split_prepass": {"launches": int(split_n), "gbs": split_bytes / split_ms / 1e6 if split_ms else None,
-                                                "share_of_step": split_ms / eager_ms if eager_ms else None},
+            "other_kernels": {"pairs_of_inputs": {"launches": int(split_n), "gbs": split_bytes / split_ms / 1e6 if split_ms else None,
+                                                  "share_of_step": split_ms / eager_ms if eager_ms else None},
                               "adamw": {"launches": int(adam_n), "gbs": adam_bytes / adam_ms / 1e6 if adam_ms else None,
                                         "frac_of_hbm": adam_bytes / adam_ms / 1e6 / peaks["hbm_gbs"] if adam_ms else None,
                                         "frac_of_nominal_hbm": adam_bytes / adam_ms / 1e6 / NOMINAL["hbm_gbs"] if adam_ms else None,
                                         "share_of_step": adam_ms / eager_ms if eager_ms else None}},
             "final_loss": final_loss, "peaks": peak_src, "dp_check": dp_check,
-            "model_tflops": tr.flops_per_step() * world * args.steps / (ms / 1e3) / 1e12,
+            "model_tflops": net.flops_per_step() * world * args.steps / (ms / 1e3) / 1e12,
         }
         if world == 1 and not args.no_kernels:
             try:
-                line["graph_api"] = graph_api_line(torch, stream, ctx, args.workload, args.steps)
+                line["fused_step_api"] = fused_step_line(torch, stream, ctx, args.workload, args.steps)
             except Exception as e:   # reported, never hidden
-                line["graph_api"] = f"unavailable: {e}"
+                line["fused_step_api"] = f"unavailable: {e}"
             ctx.timing_enable(True)
             line["kernels"] = kernel_lines(torch, stream, ctx, peaks)
             ctx.timing_enable(False)

@@ -135,6 +135,7 @@ SIGNATURES = {
     "fg_bpat_open": (i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "fg_bpat_close": (i32, [C.c_void_p]),
     "fg_bpat_format": (i32, [C.c_void_p]),
+    "fg_bpat_dtype": (i32, [C.c_void_p]),
     "fg_bpat_count": (u32, [C.c_void_p]),
     "fg_bpat_shape": (i32, [C.c_void_p, u32, C.POINTER(u32), C.POINTER(u32)]),
     "fg_bpat_load_tensor": (i32, [c_ctx, C.c_void_p, u32, C.POINTER(c_buf)]),

@@ -9,7 +9,9 @@ from . import _lib
 from .backend import Buffer, FgError, GpuContext, Tensor
 
 # BpatHeader of the reference (crates/fused_gpu/src/io/mod.rs): the formats this backend can write / read
-V0, V1, V1_MICRO, V2_F32 = 0, 1, 2, 3
+V0, V1, V1_MICRO, V2_F32, V2_F16, V2_BF16 = 0, 1, 2, 3, 4, 5
+# numpy view of what fg_bpat_load_tensor returns, by fg_dtype: bf16 tensors are exposed as their uint16 bit patterns
+_NP_DTYPE = {0: np.float32, 1: np.float16, 2: np.uint16}
 
 
 def inspect(path):
@@ -47,12 +49,13 @@ def load_tensors(ctx, path):
         raise FgError(code, f"cannot read {path}: missing, truncated, or a checksum does not match")
     try:
         out = []
+        dtype = _NP_DTYPE[lib.fg_bpat_dtype(h)]
         for i in range(lib.fg_bpat_count(h)):
             nd, dims = C.c_uint32(), (C.c_uint32 * 8)()
             lib.fg_bpat_shape(h, i, C.byref(nd), dims)
             b = C.c_void_p()
             ctx._check(lib.fg_bpat_load_tensor(ctx.handle, h, i, C.byref(b)))
-            out.append(Tensor(tuple(dims[d] for d in range(nd.value)), Buffer(ctx, b), np.float32))
+            out.append(Tensor(tuple(dims[d] for d in range(nd.value)), Buffer(ctx, b), dtype))
         return out
     finally:
         lib.fg_bpat_close(h)

@@ -6,8 +6,10 @@
 //                      of every byte before it
 //   v1m  "BPATv1m\0"   as v1 with u32 ndim, u32 shape, f32 data
 //   v2   "BPAT\0f32"   u8 count | per tensor: u32 ndim, u32 shape[ndim], f32 data (no checksums)
-// All little endian.  Reading accepts all four (f64 data is narrowed to f32, the only storage type on
-// this backend); writing produces v2-f32 or v1m.  The reference's v1m WRITER emits 8-byte shape entries
+//        "BPAT\0f16", "BPATbf16": the same with f16 / bf16 data (headers.rs:60-98; io/mod.rs:170-183)
+// All little endian.  Reading accepts all six (f64 data is narrowed to f32; 16-bit files load into 16-bit
+// tensors, as the reference's init_tensor_f16 / init_tensor_bf16 do); writing produces v2-f32, v2-f16, v2-bf16
+// or v1m.  The reference's v1m WRITER emits 8-byte shape entries
 // after a 4-byte ndim (v1.rs:83-96) although its reader and the documented layout use 4-byte entries
 // (v1.rs:281-288, headers.rs:41-58); this implementation follows the documented layout.
 #include <stdio.h>
@@ -47,8 +49,12 @@ struct Entry {
     uint64_t offset;     // of the data in the file
 };
 
-const char* kMagic[4] = {"bpat", "BPATv1\0\0", "BPATv1m\0", "BPAT\0f32"};
-const size_t kMagicLen[4] = {4, 8, 8, 8};
+const char* kMagic[6] = {"bpat", "BPATv1\0\0", "BPATv1m\0", "BPAT\0f32", "BPAT\0f16", "BPATbf16"};
+const size_t kMagicLen[6] = {4, 8, 8, 8, 8, 8};
+// bytes per stored element
+inline size_t elem_bytes(int format) {
+    return (format == FG_BPAT_V0 || format == FG_BPAT_V1) ? 8 : (format == FG_BPAT_V2_F16 || format == FG_BPAT_V2_BF16) ? 2 : 4;
+}
 
 }  // namespace
 
@@ -64,12 +70,15 @@ int32_t fg_bpat_save(fg_ctx* ctx, const char* path, int32_t format, uint32_t cou
                      const uint32_t* ndims, const uint32_t* const* shapes) {
     if (!ctx) return FG_ERR_NOT_INITIALIZED;
     FG_REQUIRE(ctx, path && (count == 0 || (tensors && ndims && shapes)), "fg_bpat_save: NULL argument");
-    FG_REQUIRE(ctx, format == FG_BPAT_V2_F32 || format == FG_BPAT_V1_MICRO, "fg_bpat_save: only v2-f32 and v1m can be written");
+    FG_REQUIRE(ctx, format == FG_BPAT_V2_F32 || format == FG_BPAT_V1_MICRO || format == FG_BPAT_V2_F16 || format == FG_BPAT_V2_BF16,
+               "fg_bpat_save: only v2-f32, v2-f16, v2-bf16 and v1m can be written");
     FG_REQUIRE(ctx, count <= 255, "fg_bpat_save: exceeds max tensors of 255");
+    const size_t esz_out = elem_bytes(format);
     for (uint32_t t = 0; t < count; ++t) {
         uint64_t n = 1;
         for (uint32_t d = 0; d < ndims[t]; ++d) n *= shapes[t][d];
-        FG_REQUIRE(ctx, tensors[t] && tensors[t]->bytes == n * 4, "fg_bpat_save: tensor prod(shape)/data.size mismatch");
+        // the tensors must already have the file's storage type (the reference writes the buffer's bytes as they are)
+        FG_REQUIRE(ctx, tensors[t] && tensors[t]->bytes == n * esz_out, "fg_bpat_save: tensor prod(shape)/data.size mismatch");
     }
     FILE* f = fopen(path, "wb");
     if (!f) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_bpat_save: cannot open the file for writing");
@@ -115,7 +124,7 @@ int32_t fg_bpat_open(const char* path, fg_bpat_file** out) {
     int format = -1;
     if (fread(magic, 1, 4, f) == 4 && memcmp(magic, "bpat", 4) == 0) format = FG_BPAT_V0;
     else if (fread(magic + 4, 1, 4, f) == 4) {
-        for (int k = 1; k < 4; ++k) if (memcmp(magic, kMagic[k], 8) == 0) format = k;
+        for (int k = 1; k < 6; ++k) if (memcmp(magic, kMagic[k], 8) == 0) format = k;
     }
     if (format < 0) { fclose(f); return FG_ERR_INVALID_ARGUMENT; }
     fg_bpat_file* bf = new (std::nothrow) fg_bpat_file();
@@ -124,7 +133,7 @@ int32_t fg_bpat_open(const char* path, fg_bpat_file** out) {
     bf->format = format;
     const bool wide = format == FG_BPAT_V0 || format == FG_BPAT_V1;     // u64 ndim/shape, f64 data
     const bool crc = format == FG_BPAT_V1 || format == FG_BPAT_V1_MICRO;
-    const size_t isz = wide ? 8 : 4, esz = wide ? 8 : 4;
+    const size_t isz = wide ? 8 : 4, esz = elem_bytes(format);
     uint32_t file_crc = crc_update(0, magic, kMagicLen[format]);
     bool ok = true;
     auto get = [&](void* p, size_t n, uint32_t* tcrc) {
@@ -177,6 +186,11 @@ int32_t fg_bpat_open(const char* path, fg_bpat_file** out) {
 
 int32_t fg_bpat_close(fg_bpat_file* f) { delete f; return FG_OK; }
 int32_t fg_bpat_format(const fg_bpat_file* f) { return f ? f->format : -1; }
+// Storage type of the tensors fg_bpat_load_tensor returns for this file.
+int32_t fg_bpat_dtype(const fg_bpat_file* f) {
+    if (!f) return -1;
+    return f->format == FG_BPAT_V2_F16 ? FG_DTYPE_F16 : f->format == FG_BPAT_V2_BF16 ? FG_DTYPE_BF16 : FG_DTYPE_F32;
+}
 uint32_t fg_bpat_count(const fg_bpat_file* f) { return f ? (uint32_t)f->entries.size() : 0; }
 
 int32_t fg_bpat_shape(const fg_bpat_file* f, uint32_t index, uint32_t* ndim, uint32_t dims_out[8]) {
@@ -186,7 +200,8 @@ int32_t fg_bpat_shape(const fg_bpat_file* f, uint32_t index, uint32_t* ndim, uin
     return FG_OK;
 }
 
-// Allocates a device buffer and fills it with tensor `index` as f32 (init_tensor_*, dispatch/mod.rs:577-655).
+// Allocates a device buffer and fills it with tensor `index`: f32, or the file's 16-bit type (init_tensor_*,
+// dispatch/mod.rs:577-655).
 int32_t fg_bpat_load_tensor(fg_ctx* ctx, const fg_bpat_file* f, uint32_t index, fg_buf** out) {
     if (!ctx) return FG_ERR_NOT_INITIALIZED;
     FG_REQUIRE(ctx, f && out && index < f->entries.size(), "fg_bpat_load_tensor: bad argument");
@@ -194,6 +209,14 @@ int32_t fg_bpat_load_tensor(fg_ctx* ctx, const fg_bpat_file* f, uint32_t index, 
     const bool wide = f->format == FG_BPAT_V0 || f->format == FG_BPAT_V1;
     FILE* fp = fopen(f->path.c_str(), "rb");
     if (!fp) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_bpat_load_tensor: file not found");
+    if (elem_bytes(f->format) == 2) {
+        // a 16-bit file loads into a 16-bit tensor, bytes unchanged (init_tensor_f16 / init_tensor_bf16)
+        std::vector<uint16_t> half(e.numel);
+        const bool ok16 = fseek(fp, (long)e.offset, SEEK_SET) == 0 && fread(half.data(), 2, e.numel, fp) == e.numel;
+        fclose(fp);
+        if (!ok16) return fg_fail(ctx, FG_ERR_FAILED_BUFFER_COPY, "fg_bpat_load_tensor: failed to read the tensor data");
+        return fg_alloc_init(ctx, half.data(), e.numel * 2, out);
+    }
     std::vector<float> host(e.numel);
     bool ok = fseek(fp, (long)e.offset, SEEK_SET) == 0;
     if (ok && !wide) ok = fread(host.data(), 4, e.numel, fp) == e.numel;

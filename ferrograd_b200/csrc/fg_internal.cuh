@@ -181,16 +181,25 @@ __device__ __forceinline__ float fg_act_grad(int act, float saved) {
 
 // ---- the same activations for GEMM epilogues ----
 // An epilogue runs while the tensor core is already on the next tile and must be done before the two
-// accumulators it can run ahead by are full, so its arithmetic is kept short: tanh through one fast
-// exponential and one reciprocal, 0.5*(1 + tanh(u)) = 1 / (1 + exp(-2u)).  For GELU this form has no
-// cancellation at all; results agree with the libm forms above to a few 1e-7 of the output's scale.
-__device__ __forceinline__ float fg_sigmoid_fast(float a) { return __frcp_rn(1.0f + __expf(-a)); }
+// accumulators it can run ahead by are full; eight warps do it, so it is bound by instruction issue and its
+// arithmetic is kept short: tanh through one exponential and one reciprocal (both the hardware approximations,
+// 1-2 ulp), 0.5*(1 + tanh(u)) = 1 / (1 + exp(-2u)), polynomials as explicit fused multiply-adds.  For GELU this
+// form has no cancellation; results agree with the libm forms above to a few 1e-7 of the output's scale.
+__device__ __forceinline__ float fg_ex2_fast(float a) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+__device__ __forceinline__ float fg_rcp_fast(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+// 1 / (1 + exp(-a)) with a given pre-multiplied by -log2(e): sigmoid(a) = 1 / (1 + 2^(a * -log2 e)).
+__device__ __forceinline__ float fg_sigmoid_l2(float a_neg_l2) { return fg_rcp_fast(1.0f + fg_ex2_fast(a_neg_l2)); }
+#define FG_NEG_LOG2E (-1.4426950408889634f)
+__device__ __forceinline__ float fg_sigmoid_fast(float a) { return fg_sigmoid_l2(a * FG_NEG_LOG2E); }
+// -log2(e) * 2 * FG_GELU_B * (x + FG_GELU_A x^3) = x * (c1 + c3 x^2)
+#define FG_GELU_C1 (FG_NEG_LOG2E * 2.0f * FG_GELU_B)
+#define FG_GELU_C3 (FG_NEG_LOG2E * 2.0f * FG_GELU_B * FG_GELU_A)
 
 __device__ __forceinline__ float fg_act_fwd_fast(int act, float z) {
     switch (act) {
         case FG_ACT_RELU: return z > 0.0f ? z : 0.0f;
-        case FG_ACT_TANH: return 2.0f * fg_sigmoid_fast(2.0f * z) - 1.0f;
-        case FG_ACT_GELU: return z * fg_sigmoid_fast((2.0f * FG_GELU_B) * (z + (z * z * z) * FG_GELU_A));
+        case FG_ACT_TANH: return __fmaf_rn(2.0f, fg_sigmoid_l2(z * (2.0f * FG_NEG_LOG2E)), -1.0f);
+        case FG_ACT_GELU: return z * fg_sigmoid_l2(z * __fmaf_rn(z * z, FG_GELU_C3, FG_GELU_C1));
         default: return z;
     }
 }
@@ -198,16 +207,38 @@ __device__ __forceinline__ float fg_act_fwd_fast(int act, float z) {
 __device__ __forceinline__ float fg_act_grad_fast(int act, float saved) {
     switch (act) {
         case FG_ACT_RELU: return saved > 0.0f ? 1.0f : 0.0f;
-        case FG_ACT_TANH: return 1.0f - saved * saved;
+        case FG_ACT_TANH: return __fmaf_rn(-saved, saved, 1.0f);
         case FG_ACT_GELU: {
             // s = 0.5*(1 + tanh(u)); 1 - tanh(u)^2 = 4*s*(1 - s); gelu' = s + 0.5*x*(1 - tanh^2)*du/dx
             const float xx = saved * saved;
-            const float s = fg_sigmoid_fast((2.0f * FG_GELU_B) * (saved + (xx * saved) * FG_GELU_A));
-            const float du = FG_GELU_B * (1.0f + (FG_GELU_A * 3.0f) * xx);
-            return s + (2.0f * saved) * (s * (1.0f - s)) * du;
+            const float s = fg_sigmoid_l2(saved * __fmaf_rn(xx, FG_GELU_C3, FG_GELU_C1));
+            const float du = __fmaf_rn(xx, FG_GELU_B * FG_GELU_A * 3.0f, FG_GELU_B);
+            return __fmaf_rn((saved + saved) * (s * (1.0f - s)), du, s);
         }
         default: return 1.0f;
     }
+}
+
+// Compact forms of the two functions above for code that is unrolled or must stay small: one uniform branch
+// separates the activations that need an exponential from those that do not, and selects do the rest (instead
+// of a switch whose every case is expanded at every call site).
+__device__ __forceinline__ float fg_act_fwd_sel(int act, float z) {
+    if (act >= FG_ACT_TANH) {
+        const float arg = act == FG_ACT_TANH ? z * (2.0f * FG_NEG_LOG2E) : z * __fmaf_rn(z * z, FG_GELU_C3, FG_GELU_C1);
+        const float s = fg_sigmoid_l2(arg);
+        return act == FG_ACT_TANH ? __fmaf_rn(2.0f, s, -1.0f) : z * s;
+    }
+    return act == FG_ACT_RELU ? fmaxf(z, 0.0f) : z;
+}
+__device__ __forceinline__ float fg_act_grad_sel(int act, float saved) {
+    const float xx = saved * saved;
+    if (act == FG_ACT_GELU) {
+        const float s = fg_sigmoid_l2(saved * __fmaf_rn(xx, FG_GELU_C3, FG_GELU_C1));
+        const float du = __fmaf_rn(xx, FG_GELU_B * FG_GELU_A * 3.0f, FG_GELU_B);
+        return __fmaf_rn((saved + saved) * (s * (1.0f - s)), du, s);
+    }
+    const float relu = saved > 0.0f ? 1.0f : 0.0f;
+    return act == FG_ACT_TANH ? 1.0f - xx : act == FG_ACT_RELU ? relu : 1.0f;
 }
 
 // ---- bf16 pairs of an f32 tensor (operands of the default GEMM mode) ----

@@ -113,6 +113,24 @@ __device__ __noinline__ float4 act_mul4(int act, float4 z, float4 sv) {
                        z.w * fg_act_grad_fast(act, sv.w));
 }
 
+// Four columns of one row, element by element: the ragged right edge of a matrix whose width is not a multiple
+// of four, or unaligned pointers.  A cold path, kept out of line so that it does not sit in the unrolled epilogue.
+__device__ __noinline__ float4 epi_store_edge(float4 zin, size_t off, uint32_t col, uint32_t col_lim, char* out, char* pre,
+                                               __nv_bfloat16* pairs, uint64_t pairs_stride, const float* mul, int mul_act, int act,
+                                               int odt) {
+    const float z[4] = {zin.x, zin.y, zin.z, zin.w};
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t = 0; t < 4; ++t)
+        if (col + t < col_lim) {
+            const float o = mul ? z[t] * fg_act_grad_fast(mul_act, mul[off + t]) : fg_act_fwd_fast(act, z[t]);
+            if (pre) store_out1(pre, off + t, z[t], odt);
+            store_out1(out, off + t, o, odt);
+            if (pairs) fg_store_pairs1(pairs, pairs_stride, off + t, o);
+            o4[t] = o;
+        }
+    return make_float4(o4[0], o4[1], o4[2], o4[3]);
+}
+
 template <int BN, int BK>
 struct TileCfg {
     static constexpr int kABytes = 2 * BM * BK * 4;   // hi + lo tiles of A
@@ -137,6 +155,14 @@ __device__ unsigned long long g_prof[8];
 #endif
 
 constexpr int kThreads = 320;      // warp 0: loads, warp 1: MMA issue, warps 2..9: accumulate + epilogue
+// The pair kernel runs three warpgroups: warps 0..3 (loads, MMA issue, two idle warps) keep kPairRegsLow registers
+// per thread, the eight accumulate + epilogue warps 4..11 take kPairRegsHigh.  A thread of those owns 128 running
+// sums; with the 168 registers a 384-thread CTA gets by default, the store phase spilled, and with 227 KB of the
+// SM's memory configured as shared memory there is next to no L1 behind local memory: every spill access cost an
+// L2 round trip (measured: ~50 cycles per instruction in the store phase, 20,000 cycles per tile).
+constexpr int kPairThreads = 384;
+constexpr int kPairRegsLow = 72, kPairRegsHigh = 216;     // 128 * 72 + 256 * 216 = 64,512 <= 65,536
+constexpr int kPairEpiWarp0 = 4;
 constexpr int kChunkK = 256;       // values of k per accumulation chunk
 
 // The tensor core adds into its f32 accumulator with truncation, so a long chain of
@@ -389,7 +415,7 @@ struct PairCfg {
     static constexpr int kBBytes = kPlanes * (kBN / 2) * BK * 4;   // this CTA's half of the B tile
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
-    static constexpr int kStoreBytes = 8 * 32 * 33 * 4;       // the epilogue warps' transpose buffers
+    static constexpr int kStoreBytes = 8 * 32 * 32 * 4;       // the epilogue warps' staging blocks (32 x 32 f32 each)
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kStoreBytes;
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
     static constexpr int kTmemCols = 512;                     // two 256-column accumulators
@@ -401,7 +427,7 @@ struct PairCfg {
 // MMAs of tile t+1 are already under way (per-tile set-up, fill and store cost 20-55 us per wave when
 // every tile was its own CTA pair: 17 % of a 4096^3 GEMM, more than half of a K = 784 one).
 template <int BK, int FMT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA16, const __grid_constant__ CUtensorMap tmB16, Epilogue ep) {
     static_assert(FMT == 0 || BK == 32, "the bf16 planes use 64-byte rows: 32 values of k per block");
@@ -470,6 +496,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (warp < kPairEpiWarp0) {
+    reg_release<kPairRegsLow>();
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer (both CTAs): own rows of A, own half of B; completion counted on the leader ----
@@ -653,14 +681,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             atomicAdd(&g_prof[7], 1ull);
 #endif
         }
+    }
     } else {
+        reg_acquire<kPairRegsHigh>();
         // ---- accumulate + epilogue (both CTAs, own 128 rows); see gemm_tc_kernel ----
         const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - kPairEpiWarp0) >> 2;
         const bool vec_ok = (ep.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(ep.C) & 15u) == 0) &&
                             (!ep.preact || (reinterpret_cast<uintptr_t>(ep.preact) & 15u) == 0);
         const uint32_t leader_acc_empty0 = map_to_cta(acc_empty_bar(0), 0);
-        float* tbuf = reinterpret_cast<float*>(base_ptr + S * Cfg::kStageBytes + 256);   // 8 warps x 32x33 floats
+        float4* tbuf = reinterpret_cast<float4*>(base_ptr + S * Cfg::kStageBytes + 256);   // 8 warps x 32 rows x 8 chunks
         float sum[CPT];
         bool ok = true;
         uint32_t gc = 0;
@@ -672,8 +702,30 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tile_origin(tile, m0, n0);
 #pragma unroll
             for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
+            // Where this warp's part of the tile goes (a K-share of a tail tile goes out raw into its 256 x 256 slot).
+            const uint32_t rsub = lane >> 3, cc = lane & 7;
+            const uint32_t out_ld = part ? BN : ep.N, row_lim = part ? 2 * BM : ep.M, col_lim = part ? BN : ep.N;
+            const uint32_t row0 = (part ? rank * BM : m0) + q * 32;            // first row of this warp's blocks
+            const uint32_t col_base = (part ? 0u : n0) + half * CPT + cc * 4;  // this lane's 4 columns in block 0
+            const bool vec = part || vec_ok;
+            const float* const mul = part ? nullptr : ep.mul_saved;
+            // The saved tensor of the layer below (dA epilogue), rows i*4 + rsub of block `blk`, read a whole block
+            // ahead of its use through a rotating set of eight registers per lane: block 0 while the tile's last
+            // accumulation chunk is still being computed, block b + 1 while block b is stored.  Read when needed,
+            // or only a few rows ahead, each block waited for DRAM two to three times.
+            const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            auto saved_at = [&](int blk, int i) -> float4 {
+                const uint32_t row = row0 + i * 4 + rsub, colb = col_base + blk * 32;
+                return (mul && vec && blk < CPT / 32 && row < row_lim && colb + 3 < col_lim)
+                           ? __ldg(reinterpret_cast<const float4*>(mul + (size_t)row * out_ld + colb)) : zero4;
+            };
+            float4 s0 = zero4, s1 = zero4, s2 = zero4, s3 = zero4, s4 = zero4, s5 = zero4, s6 = zero4, s7 = zero4;
             for (uint32_t c = c0; c < c1; ++c, ++gc) {
                 const uint32_t buf = gc & 1u;
+                if (c + 1 == c1 && mul) {
+                    s0 = saved_at(0, 0); s1 = saved_at(0, 1); s2 = saved_at(0, 2); s3 = saved_at(0, 3);
+                    s4 = saved_at(0, 4); s5 = saved_at(0, 5); s6 = saved_at(0, 6); s7 = saved_at(0, 7);
+                }
                 PROF_T0();
                 bool got = mbar_wait_bounded(acc_full_bar(buf), (gc >> 1) & 1u, kPairWaitCycles + kPairWaitCycles / 2);
                 PROF_ADD(prof_w);
@@ -705,98 +757,97 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // warp passes 32x32 blocks through a padded shared-memory buffer and writes 4 rows x 128 bytes
             // per instruction (bias and activation are applied on the way out).
             // A K-share of a tail tile goes out raw (no bias, no activation) into its 256x256 slot.
-            float* tb = tbuf + (warp - 2) * (32 * 33);
-            const uint32_t rsub = lane >> 3, c4 = (lane & 7) * 4;
-            void* const out = part ? (void*)(ep.partial + (size_t)slot * (2 * BM * BN)) : (void*)ep.C;
-            void* const pre = part ? nullptr : (void*)ep.preact;
-            const int odt = part ? (int)FG_DTYPE_F32 : ep.out_dtype;
-            const uint32_t out_ld = part ? BN : ep.N, row_lim = part ? 2 * BM : ep.M, col_lim = part ? BN : ep.N;
-            const uint32_t row_base = part ? rank * BM : m0, col_base = part ? 0u : n0;
+            // The 32 x 32 staging block of this warp: rows of eight 16-byte chunks, chunk c of row r at position
+            // c ^ (r & 7), so that both the row-wise writes (a lane owns a row) and the reads (eight lanes sweep a
+            // row) are 128-bit accesses without bank conflicts.  A K-share of a tail tile goes out raw (no bias, no
+            // activation, no extras: the fold kernel does those) into its 256 x 256 slot.
+            // Nothing below may touch local memory: no calls, no dynamically indexed arrays, no spills.
+            float4* tb4 = tbuf + (warp - kPairEpiWarp0) * (32 * 8);
+            char* const out = part ? (char*)(ep.partial + (size_t)slot * (2 * BM * BN)) : (char*)ep.C;
+            char* const pre = part ? nullptr : (char*)ep.preact;
+            const int odt = (part || !kDirect16) ? (int)FG_DTYPE_F32 : ep.out_dtype;   // the f32 kernels store f32 only
             const int act = part ? FG_ACT_NONE : ep.act;
-            const bool vec = part || vec_ok;
-            // extras of the f32 + pairs path; a K-share of a tail tile leaves them to the fold kernel
-            const float* const mul = part ? nullptr : ep.mul_saved;
             __nv_bfloat16* const pairs = part ? nullptr : ep.c_pairs;
             float* const csp = part ? nullptr : ep.colsum_part;
+#ifdef FG_GEMM_PROFILE
+            const bool no_store = (ep.dbg & 1u) != 0;
+#else
+            constexpr bool no_store = false;
+#endif
 #pragma unroll
             for (int g4 = 0; g4 < CPT / 32; ++g4) {
-                const uint32_t col = col_base + half * CPT + g4 * 32 + c4;     // this lane's 4 columns on the way out
 #pragma unroll
-                for (int j = 0; j < 32; ++j) tb[lane * 33 + j] = sum[g4 * 32 + j];
+                for (int c = 0; c < 8; ++c)
+                    tb4[lane * 8 + (c ^ (lane & 7))] = make_float4(sum[g4 * 32 + 4 * c], sum[g4 * 32 + 4 * c + 1],
+                                                                   sum[g4 * 32 + 4 * c + 2], sum[g4 * 32 + 4 * c + 3]);
                 __syncwarp();
-                float bz[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t col = col_base + g4 * 32;
+                const bool fast = vec && col + 3 < col_lim;                    // the whole float4 is inside the matrix
+                float4 bz = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (ep.bias && !part) {
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) if (col + t < col_lim) bz[t] = ep.bias[col + t];
-                }
-                float cs[4] = {0.f, 0.f, 0.f, 0.f};     // column sums of what this lane stores (rows r*4 + rsub)
-                // Two rounds of four rows.  The four loads of the saved tensor of a round are issued together, before
-                // anything waits for one of them: one load per row in a rolled loop put eight DRAM latencies per
-                // 32 x 32 block end to end, and this store phase has to finish before the tensor core has filled
-                // the two accumulators it can run ahead by (measured: +70 us on a 4096^3 product).  The activation
-                // code exists once (act_fwd4 / act_mul4 are not inlined): inlined at every call site it had made
-                // this section miss the instruction cache on every line.
-#pragma unroll 1
-                for (int rh = 0; rh < 2; ++rh) {
-                    float4 sv[4];
-                    if (mul) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t row = row_base + q * 32 + (rh * 4 + i) * 4 + rsub;
-                            sv[i] = (vec && row < row_lim && col + 3 < col_lim)
-                                        ? __ldg(reinterpret_cast<const float4*>(mul + (size_t)row * out_ld + col))
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
+                    if (col + 3 < col_lim) bz = __ldg(reinterpret_cast<const float4*>(ep.bias + col));
+                    else {
+                        if (col < col_lim) bz.x = ep.bias[col];
+                        if (col + 1 < col_lim) bz.y = ep.bias[col + 1];
+                        if (col + 2 < col_lim) bz.z = ep.bias[col + 2];
                     }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t lr = (rh * 4 + i) * 4 + rsub;
-                        const uint32_t row = row_base + q * 32 + lr;
-                        float z[4];
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) z[t] = tb[lr * 33 + c4 + t] + bz[t];
-                        if (row < row_lim && col < col_lim) {
-                            const size_t off = (size_t)row * out_ld + col;
-                            if (vec && col + 3 < col_lim) {
-                                const float4 zin = make_float4(z[0], z[1], z[2], z[3]);
-                                float4 o;
-                                if (mul) o = act_mul4(ep.mul_act, zin, sv[i]);
-                                else o = act == FG_ACT_NONE ? zin : act_fwd4(act, zin);
-#ifdef FG_GEMM_PROFILE
-                                if (!(ep.dbg & 1u) || o.x == 12345.678f)
-#endif
-                                {
+                }
+                float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);     // column sums of what this lane stores (rows i*4 + rsub)
+                // Rows i*4 + rsub, i = 0..7, one per iteration of a rolled loop (one copy of the activation code per
+                // block).  Each iteration takes its row of the saved tensor from the front of the rotating set and
+                // refills the back with the same row of the NEXT block.  The staged values come through a rotating
+                // set too: the tensor core reads its operands from shared memory at most of the memory's bandwidth,
+                // and a shared-memory load issued when its value is needed waits behind that traffic.
+                auto staged_row = [&](int i) -> float4 {
+                    const uint32_t lr = (uint32_t)(i & 7) * 4 + rsub;
+                    return tb4[lr * 8 + (cc ^ (lr & 7))];
+                };
+                float4 z0 = staged_row(0), z1 = staged_row(1), z2 = staged_row(2), z3 = staged_row(3);
+#pragma unroll 1
+                for (int i = 0; i < 8; ++i) {
+                    const float4 sv = s0;
+                    s0 = s1; s1 = s2; s2 = s3; s3 = s4; s4 = s5; s5 = s6; s6 = s7;
+                    s7 = saved_at(g4 + 1, i);
+                    float4 zin = z0;
+                    z0 = z1; z1 = z2; z2 = z3; z3 = staged_row(i + 4);
+                    const uint32_t lr = i * 4 + rsub;
+                    const uint32_t row = row0 + lr;
+                    zin.x += bz.x; zin.y += bz.y; zin.z += bz.z; zin.w += bz.w;
+                    if (row < row_lim && col < col_lim) {
+                        const size_t off = (size_t)row * out_ld + col;
+                        if (fast) {
+                            float4 o;
+                            if (mul) {
+                                o = make_float4(zin.x * fg_act_grad_sel(ep.mul_act, sv.x), zin.y * fg_act_grad_sel(ep.mul_act, sv.y),
+                                                zin.z * fg_act_grad_sel(ep.mul_act, sv.z), zin.w * fg_act_grad_sel(ep.mul_act, sv.w));
+                            } else if (act != FG_ACT_NONE) {
+                                o = make_float4(fg_act_fwd_sel(act, zin.x), fg_act_fwd_sel(act, zin.y), fg_act_fwd_sel(act, zin.z),
+                                                fg_act_fwd_sel(act, zin.w));
+                            } else o = zin;
+                            if (!no_store) {
                                 if (pre) store_out4(pre, off, zin, odt);
                                 store_out4(out, off, o, odt);
                                 if (pairs) fg_store_pairs4(pairs, ep.c_pairs_stride, off, o);
-                                }
-                                cs[0] += o.x; cs[1] += o.y; cs[2] += o.z; cs[3] += o.w;
-                            } else {
-#pragma unroll
-                                for (int t = 0; t < 4; ++t)
-                                    if (col + t < col_lim) {
-                                        const float o = mul ? z[t] * fg_act_grad_fast(ep.mul_act, mul[off + t]) : fg_act_fwd_fast(act, z[t]);
-                                        if (pre) store_out1(pre, off + t, z[t], odt);
-                                        store_out1(out, off + t, o, odt);
-                                        if (pairs) fg_store_pairs1(pairs, ep.c_pairs_stride, off + t, o);
-                                        cs[t] += o;
-                                    }
                             }
+                            cs.x += o.x; cs.y += o.y; cs.z += o.z; cs.w += o.w;
+                        } else {
+                            const float4 o = epi_store_edge(zin, off, col, col_lim, out, pre, pairs, ep.c_pairs_stride, mul, ep.mul_act, act, odt);
+                            cs.x += o.x; cs.y += o.y; cs.z += o.z; cs.w += o.w;
                         }
                     }
                 }
                 if (csp) {
                     // the four lanes that share these columns hold rows 0,4,.. / 1,5,.. / 2,6,.. / 3,7,..: add them in a fixed order
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        cs[t] += __shfl_xor_sync(0xffffffffu, cs[t], 8);
-                        cs[t] += __shfl_xor_sync(0xffffffffu, cs[t], 16);
-                    }
-                    const uint32_t row0 = row_base + q * 32;
+                    cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 8); cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 16);
+                    cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 8); cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 16);
+                    cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 8); cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 16);
+                    cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 8); cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 16);
                     if (lane < 8 && row0 < row_lim) {
-#pragma unroll
-                        for (int t = 0; t < 4; ++t)
-                            if (col + t < col_lim) csp[(size_t)(row0 >> 5) * ep.N + col + t] = cs[t];
+                        float* d = csp + (size_t)(row0 >> 5) * ep.N + col;
+                        if (col < col_lim) d[0] = cs.x;
+                        if (col + 1 < col_lim) d[1] = cs.y;
+                        if (col + 2 < col_lim) d[2] = cs.z;
+                        if (col + 3 < col_lim) d[3] = cs.w;
                     }
                 }
                 __syncwarp();
@@ -807,7 +858,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #endif
         }
 #ifdef FG_GEMM_PROFILE
-        if (warp == 2 && lane == 0 && leader) {
+        if (warp == kPairEpiWarp0 && lane == 0 && leader) {
             atomicAdd(&g_prof[3], (unsigned long long)prof_w);
             atomicAdd(&g_prof[4], (unsigned long long)prof_s);
             atomicAdd(&g_prof[5], (unsigned long long)prof_n);
@@ -1255,7 +1306,7 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
     if (max_clusters[ctx->device & 63] == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)ctx->sm_count & ~1u);
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(kPairThreads);
         cfg.dynamicSmemBytes = Cfg::kSmemBytes;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -1298,7 +1349,7 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
     const uint64_t nunits = ep.t_full + (ntiles - ep.t_full) * ep.split;
     dim3 grid((unsigned)(2 * (nunits < slots ? nunits : slots)));
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_GEMM_TC, 2.0 * ep.M * ep.N * ep.K);
-    gemm_tc_pair_kernel<BK, FMT><<<grid, kThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
+    gemm_tc_pair_kernel<BK, FMT><<<grid, kPairThreads, Cfg::kSmemBytes, ctx->stream>>>(tmA, tmB, tmA16, tmB16, ep);
     FG_LAUNCHED(ctx);
     if (ep.split > 1) {
         gemm_tc_pair_fold_kernel<<<(unsigned)((ntiles - ep.t_full) * 64), 256, 0, ctx->stream>>>(ep);

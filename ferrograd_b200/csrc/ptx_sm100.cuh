@@ -233,6 +233,11 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask)
                  ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
+// Register re-balancing between the warpgroups (4 consecutive warps) of a CTA: a group that needs few registers
+// gives them up, a group that needs many takes them.  Every warp of the group must execute the instruction.
+template <int N> __device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 __device__ __forceinline__ uint32_t cvt_tf32(float x) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));

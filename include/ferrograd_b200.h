@@ -449,15 +449,18 @@ uint32_t fg_exec_forward_steps(fg_exec* e);   /* kernels-level steps of one forw
 
 /* ---- .bpat tensor files (crates/fused_gpu/src/io/headers.rs:16-117; save_tensors / load_tensors:
  *      crates/fused_gpu/src/io/mod.rs:98-159) ----
- * Reading accepts v0, v1, v1m and v2-f32 and verifies the CRC-32s of v1/v1m; writing produces
- * v2-f32 or v1m.  Tensors are f32 on the device; f64 files are narrowed on load. */
-enum fg_bpat_format { FG_BPAT_V0 = 0, FG_BPAT_V1 = 1, FG_BPAT_V1_MICRO = 2, FG_BPAT_V2_F32 = 3 };
+ * Reading accepts v0, v1, v1m, v2-f32, v2-f16 and v2-bf16 and verifies the CRC-32s of v1/v1m; writing
+ * produces v2-f32, v2-f16, v2-bf16 or v1m.  f64 files are narrowed to f32 on load; a 16-bit file loads into
+ * 16-bit tensors and is written from 16-bit tensors (fg_bpat_dtype tells which type a file's tensors have). */
+enum fg_bpat_format { FG_BPAT_V0 = 0, FG_BPAT_V1 = 1, FG_BPAT_V1_MICRO = 2, FG_BPAT_V2_F32 = 3,
+                      FG_BPAT_V2_F16 = 4, FG_BPAT_V2_BF16 = 5 };   /* io/headers.rs:79, :98 */
 typedef struct fg_bpat_file fg_bpat_file;
 int32_t fg_bpat_save(fg_ctx* ctx, const char* path, int32_t format, uint32_t count, fg_buf* const* tensors,
                      const uint32_t* ndims, const uint32_t* const* shapes);
 int32_t fg_bpat_open(const char* path, fg_bpat_file** out);   /* no device needed */
 int32_t fg_bpat_close(fg_bpat_file* f);
 int32_t fg_bpat_format(const fg_bpat_file* f);
+int32_t fg_bpat_dtype(const fg_bpat_file* f);    /* fg_dtype of the tensors fg_bpat_load_tensor returns */
 uint32_t fg_bpat_count(const fg_bpat_file* f);
 int32_t fg_bpat_shape(const fg_bpat_file* f, uint32_t index, uint32_t* ndim, uint32_t dims_out[8]);
 int32_t fg_bpat_load_tensor(fg_ctx* ctx, const fg_bpat_file* f, uint32_t index, fg_buf** out);

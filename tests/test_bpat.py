@@ -14,7 +14,7 @@ sys.path.insert(0, os.path.join(HERE, "golden"))
 import make_bpat_fixtures as fx  # noqa: E402
 
 GOLD = os.path.join(HERE, "golden")
-FORMATS = {"v0": 0, "v1": 1, "v1m": 2, "v2": 3}
+FORMATS = {"v0": 0, "v1": 1, "v1m": 2, "v2": 3, "v2f16": 4, "v2bf16": 5}
 
 
 @pytest.mark.parametrize("fmt", list(FORMATS))
@@ -56,8 +56,8 @@ def test_reference_example_checkpoint_summary():
     s = json.load(open(os.path.join(GOLD, "bpat_reference_readme_summary.json")))
     assert s["shapes"] == [[768, 512], [512, 384], [256, 768], [384, 256], [256, 256]]
     assert s["bytes"] == 9 + sum(4 + 8 + 4 * a * b for a, b in s["shapes"])
-    ref = "/root/reference/data/v2f32_readme.bpat"
-    if os.path.exists(ref):                                  # only in the development container
+    ref = os.path.join(os.environ.get("FERROGRAD_REFERENCE", ""), "data", "v2f32_readme.bpat")
+    if os.environ.get("FERROGRAD_REFERENCE") and os.path.exists(ref):      # only where the reference tree is at hand
         shapes, code = bpat.inspect(ref)
         assert code == 3 and [list(x) for x in shapes] == s["shapes"]
 
@@ -71,7 +71,12 @@ def test_load_fixture_to_device(fmt):
         got = ctx.load_tensors(os.path.join(GOLD, f"fixture_{fmt}.bpat"))
         for t, ref in zip(got, fx.tensors()):
             assert t.shape == ref.shape
-            assert np.array_equal(ctx.to_numpy(t), ref)      # f64 files hold f32-representable values
+            if fmt == "v2f16":
+                assert t.dtype == np.float16 and np.array_equal(ctx.to_numpy(t), ref.astype(np.float16))
+            elif fmt == "v2bf16":
+                assert np.array_equal(ctx.to_numpy(t), fx.bf16_bits(ref))          # bf16 bit patterns
+            else:
+                assert np.array_equal(ctx.to_numpy(t), ref)      # f64 files hold f32-representable values
     finally:
         ctx.destroy()
 
@@ -91,5 +96,29 @@ def test_save_is_byte_identical_and_round_trips(tmp_path, fmt, header):
             assert np.array_equal(ctx.to_numpy(t), ref)
         with pytest.raises(FgError):
             ctx.save_tensors(tmp_path / "x.bpat", ts, 0)     # v0 cannot be written
+    finally:
+        ctx.destroy()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,header", [("v2f16", 4), ("v2bf16", 5)])
+def test_save_16bit_is_byte_identical_and_round_trips(tmp_path, fmt, header):
+    # io/headers.rs:60-98: the same layout as v2-f32 with 2-byte elements; 16-bit tensors in, 16-bit tensors out
+    from ferrograd_b200 import FgError, GpuContext, bpat  # noqa: F401
+    ctx = GpuContext.new()
+    try:
+        if fmt == "v2f16":
+            ts = [ctx.init_tensor_f16(a.shape, a.astype(np.float16)) for a in fx.tensors()]
+        else:
+            ts = [ctx.init_tensor_bf16(a.shape, a) for a in fx.tensors()]
+        p = tmp_path / f"out_{fmt}.bpat"
+        ctx.save_tensors(p, ts, header)
+        assert p.read_bytes() == fx.encode(fmt, fx.tensors())
+        back = ctx.load_tensors(p)
+        for t, src in zip(back, ts):
+            assert np.array_equal(ctx.to_numpy(t).view(np.uint16), ctx.to_numpy(src).view(np.uint16))
+        f32 = [ctx.init_tensor_f32(a.shape, a) for a in fx.tensors()]
+        with pytest.raises(FgError):
+            ctx.save_tensors(tmp_path / "x.bpat", f32, header)   # f32 tensors do not fit a 16-bit file
     finally:
         ctx.destroy()
