@@ -576,8 +576,10 @@ def run_ours(args, rank, world, local_rank):
             line["cpu_baseline"] = cpu_baseline(args.workload)
         emit(line)
     barrier()
+    net.destroy()           # the recorded dispatches hold the communicator: they go before it
     if world > 1:
         dist.destroy_process_group()
+    ctx.destroy()
 
 
 def cpu_baseline(workload):

@@ -487,6 +487,7 @@ int32_t fg_plan_begin(fg_ctx* ctx) {
     FG_CUDA(ctx, FG_ERR_INCONSISTENT_CAPTURE, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
     ctx->capture_launches = 0;
+    ctx->capture_has_comm = false;
     return FG_OK;
 }
 
@@ -507,6 +508,9 @@ int32_t fg_plan_end(fg_ctx* ctx, fg_plan** out) {
     p->graph = graph;
     p->launches = ctx->capture_launches;
     p->ws_generation = ctx->ws_generation;
+    p->ctx = ctx;
+    p->has_comm = ctx->capture_has_comm;
+    if (p->has_comm) ctx->comm_plans++;
     e = cudaGraphInstantiate(&p->exec, graph, 0);
     if (e != cudaSuccess) { cudaGraphDestroy(graph); delete p; return fg_fail_cuda(ctx, FG_ERR_INTERNAL, "cudaGraphInstantiate", e); }
     *out = p;
@@ -531,6 +535,7 @@ int32_t fg_plan_launch(fg_ctx* ctx, fg_plan* plan) {
 
 int32_t fg_plan_destroy(fg_plan* plan) {
     if (!plan) return FG_OK;
+    if (plan->has_comm && plan->ctx && plan->ctx->comm_plans > 0) plan->ctx->comm_plans--;
     cudaGraphExecDestroy(plan->exec);
     cudaGraphDestroy(plan->graph);
     delete plan;
@@ -622,7 +627,7 @@ int32_t fg_allreduce_sum_f32(fg_ctx* ctx, float* buf, uint64_t count) {
         return FG_ERR_PEER_ACCESS;
     }
     ctx->comm_pending = true;
-    if (ctx->capturing) ctx->capture_launches++; else ctx->launches++;
+    if (ctx->capturing) { ctx->capture_launches++; ctx->capture_has_comm = true; } else ctx->launches++;
     return FG_OK;
 }
 
@@ -700,8 +705,14 @@ int32_t fg_comm_sync(fg_ctx* ctx, uint32_t timeout_ms) {
 int32_t fg_comm_destroy(fg_ctx* ctx) {
     if (!ctx) return FG_ERR_NOT_INITIALIZED;
     if (ctx->comm && ctx->nccl_lib) {
-        auto d = (pfn_ncclCommDestroy)dlsym(ctx->nccl_lib, "ncclCommDestroy");
-        if (d) d(ctx->comm);
+        // A recorded plan that contains an exchange keeps the communicator in use: tearing the communicator down
+        // waits for the plan to be destroyed, i.e. for ever if the caller destroys things in the other order
+        // (seen with ncclCommDestroy and with ncclCommAbort).  With such plans still alive the communicator is
+        // left to the end of the process instead.
+        if (ctx->comm_plans == 0) {
+            auto d = (pfn_ncclCommDestroy)dlsym(ctx->nccl_lib, "ncclCommDestroy");
+            if (d) d(ctx->comm);
+        }
     }
     ctx->comm = nullptr;
     return FG_OK;

@@ -25,6 +25,8 @@ struct fg_plan {
     cudaGraphExec_t exec;
     uint64_t launches;  // kernels recorded in the graph
     uint64_t ws_generation;   // the scratch arena whose addresses the recorded kernels carry
+    fg_ctx* ctx;
+    bool has_comm;            // the recording contains an exchange: it holds the communicator until it is destroyed
 };
 
 // One timed launch: events on the launching stream around a single kernel.
@@ -76,6 +78,8 @@ struct fg_ctx {
     int opt_comm_max_ctas;      // CTAs the communicator may use (fg_comm_init)
     uint64_t opt_min_exchange;  // elements: the graph engine starts an exchange once this much is complete
     uint64_t ws_generation;     // bumped whenever the scratch arena is reallocated
+    bool capture_has_comm;      // an exchange was recorded since fg_plan_begin
+    int comm_plans;             // live plans that contain an exchange
 };
 
 inline int32_t fg_fail(fg_ctx* ctx, int32_t code, const char* msg) {

@@ -502,6 +502,9 @@ int32_t fg_comm_wait(fg_ctx* ctx, int32_t slot);
  * without waiting for its peers. */
 int32_t fg_comm_sync(fg_ctx* ctx, uint32_t timeout_ms);
 int32_t fg_comm_abort(fg_ctx* ctx);
+/* Destroy the plans that recorded an exchange (fg_plan_destroy, fg_exec_destroy) before the communicator or the
+ * context: a live plan keeps the communicator in use, and tearing it down would wait for the plan for ever.  If
+ * such plans are still alive the communicator is not torn down at all (it lasts until the process ends). */
 int32_t fg_comm_destroy(fg_ctx* ctx);
 
 /* Library / build information. */

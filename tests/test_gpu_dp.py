@@ -83,11 +83,13 @@ def _rank_graph_api(rank, world, port, out_dir):
     for s in range(GSTEPS):
         net.upload_batch(*dp.synth_batch(dict(dims=GDIMS, batch=BATCH, loss="ce"), rank, s))
         net.step()
+        ctx.comm_sync(20000)          # a rank that waits for a peer that never comes ends with FG_ERR_TIMEOUT, not a hang
     ctx.sync()
     assert ctx.device_status() == 0
     W, b = net.get_params()
     np.savez(os.path.join(out_dir, f"graph_rank{rank}.npz"), *W, *b)
     dist.barrier()
+    net.destroy()                 # the recorded dispatches hold the communicator: they go first
     dist.destroy_process_group()
     ctx.destroy()
 
