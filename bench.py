@@ -473,15 +473,16 @@ def run_ours(args, rank, world, local_rank):
     adam_n, adam_ms, adam_bytes = ctx.timing_read("adamw")
     ctx.timing_enable(False)
 
-    # ---- every dispatch recorded as a CUDA graph on its second call and replayed from then on (the
-    #      reference's Schedule is a captured graph too: rocm/mod.rs:324-389) ----
-    ctx.set_option("exec_plans", "1")
+    # ---- the engine's own choice between plain launches and recorded CUDA graphs per dispatch (the reference's
+    #      Schedule is a captured graph: rocm/mod.rs:324-389; here only launch-bound graphs are recorded) ----
+    ctx.set_option("exec_plans", "auto")
     for _ in range(4):
         net.step()
     barrier()
-    mode = ("dispatch_forward + dispatch_loss + dispatch_backward + dispatch_optim through the graph API, each "
-            "replayed as a recorded CUDA graph" + ("; gradients summed over the ranks inside dispatch_backward / "
-                                                   "dispatch_optim (NCCL)" if world > 1 else ""))
+    mode = ("dispatch_forward + dispatch_loss + dispatch_backward + dispatch_optim through the graph API, "
+            + ("each replayed as a recorded CUDA graph" if net.tensors.plans_active() else
+               "plain asynchronous launches (the engine records CUDA graphs only for launch-bound graphs)")
+            + ("; gradients summed over the ranks inside dispatch_backward / dispatch_optim (NCCL)" if world > 1 else ""))
 
     # ---- timed region 2 (headline): K steps, inputs resident in HBM ----
     launches0 = ctx.launch_count()

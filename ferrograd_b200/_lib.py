@@ -25,6 +25,11 @@ class AdamWHyper(C.Structure):
     _fields_ = [("lr", f32), ("beta1", f32), ("beta2", f32), ("eps", f32), ("weight_decay", f32)]
 
 
+class UpdateTensor(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("g", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p), ("w_pairs", C.c_void_p),
+                ("pairs_stride", C.c_uint64), ("n", C.c_uint64)]
+
+
 class EwInstr(C.Structure):
     _fields_ = [("op", i32), ("a", i32), ("b", i32), ("imm", f32)]
 
@@ -93,6 +98,8 @@ SIGNATURES = {
     "fg_sgd_step_paired": (i32, [c_ctx, c_dev, c_dev, u64, f32, f32, i32, c_dev, u64]),
     "fg_adamw_step_paired": (i32, [c_ctx, c_dev, c_dev, c_dev, c_dev, u64, C.POINTER(AdamWHyper), u32, c_dev, f32, i32,
                                    c_dev, u64]),
+    "fg_adamw_step_multi": (i32, [c_ctx, C.POINTER(UpdateTensor), u32, C.POINTER(AdamWHyper), u32, c_dev, f32, i32]),
+    "fg_sgd_step_multi": (i32, [c_ctx, C.POINTER(UpdateTensor), u32, f32, f32, i32]),
     "fg_counter_increment": (i32, [c_ctx, c_dev]),
     "fg_eltwise_chain_fwd": (i32, [c_ctx, u64, C.POINTER(EwInstr), i32, C.POINTER(C.c_void_p), i32, c_dev,
                                    C.POINTER(C.c_void_p)]),
@@ -130,6 +137,7 @@ SIGNATURES = {
     "fg_exec_num_grads": (u32, [C.c_void_p]),
     "fg_exec_grad": (c_buf, [C.c_void_p, u32, C.POINTER(i32)]),
     "fg_exec_forward_steps": (u32, [C.c_void_p]),
+    "fg_exec_plans_active": (i32, [C.c_void_p]),
     "fg_bpat_save": (i32, [c_ctx, C.c_char_p, i32, u32, C.POINTER(c_buf), C.POINTER(u32),
                            C.POINTER(C.POINTER(u32))]),
     "fg_bpat_open": (i32, [C.c_char_p, C.POINTER(C.c_void_p)]),

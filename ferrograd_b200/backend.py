@@ -373,6 +373,24 @@ class GpuContext:
                                                   int(step), _ptr(step_dev), grad_scale, int(zero_grad), _ptr(w_pairs),
                                                   pairs_stride))
 
+    def _update_tensors(self, tensors):
+        arr = (_lib.UpdateTensor * len(tensors))()
+        for i, t in enumerate(tensors):
+            arr[i] = _lib.UpdateTensor(_ptr(t["w"]), _ptr(t["g"]), _ptr(t.get("m")), _ptr(t.get("v")), _ptr(t.get("w_pairs")),
+                                       int(t.get("pairs_stride", 0)), int(t["n"]))
+        return arr
+
+    def adamw_step_multi(self, tensors, lr, beta1, beta2, eps, weight_decay, step=1, step_dev=None, grad_scale=1.0,
+                         zero_grad=True):
+        """tensors: dicts with w, g, m, v, n and optionally w_pairs, pairs_stride; one launch for all of them."""
+        h = _lib.AdamWHyper(lr, beta1, beta2, eps, weight_decay)
+        self._check(self.lib.fg_adamw_step_multi(self.handle, self._update_tensors(tensors), len(tensors), C.byref(h),
+                                                 int(step), _ptr(step_dev), grad_scale, int(zero_grad)))
+
+    def sgd_step_multi(self, tensors, lr, grad_scale=1.0, zero_grad=True):
+        self._check(self.lib.fg_sgd_step_multi(self.handle, self._update_tensors(tensors), len(tensors), lr, grad_scale,
+                                               int(zero_grad)))
+
     def counter_increment(self, counter):
         self._check(self.lib.fg_counter_increment(self.handle, _ptr(counter)))
 

@@ -116,7 +116,13 @@ int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value) {
     }
     if (!strcmp(name, "gemm_split_k")) return truth(&ctx->opt_split_k);
     if (!strcmp(name, "gemm_pairs")) return truth(&ctx->opt_pairs);
-    if (!strcmp(name, "exec_plans")) return truth(&ctx->opt_exec_plans);
+    if (!strcmp(name, "exec_plans")) {
+        if (!strcmp(value, "auto")) { ctx->opt_exec_plans = -1; return FG_OK; }
+        bool on = false;
+        const int32_t s = truth(&on);
+        if (s == FG_OK) ctx->opt_exec_plans = on ? 1 : 0;
+        return s;
+    }
     if (!strcmp(name, "comm_min_exchange")) {
         char* end = nullptr;
         const unsigned long long v = strtoull(value, &end, 10);
@@ -153,7 +159,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     c->opt_tile_pair = -1;
     c->opt_split_k = true;
     c->opt_pairs = true;
-    c->opt_exec_plans = true;
+    c->opt_exec_plans = -1;
     c->opt_comm_max_ctas = 12;
     c->opt_min_exchange = 1ull << 20;
     c->comm_reserved_sms = 16;
@@ -161,7 +167,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     if (const char* e = getenv("FG_GEMM_TILE")) fg_ctx_set_option(c, "gemm_tile", e);
     if (getenv("FG_GEMM_NO_SPLITK")) c->opt_split_k = false;
     if (getenv("FG_GEMM_NO_PAIRS")) c->opt_pairs = false;
-    if (getenv("FG_EXEC_NO_PLANS")) c->opt_exec_plans = false;
+    if (getenv("FG_EXEC_NO_PLANS")) c->opt_exec_plans = 0;
     if (const char* e = getenv("NCCL_MAX_CTAS")) fg_ctx_set_option(c, "comm_max_ctas", e);
     if (const char* e = getenv("FG_COMM_SMS")) fg_ctx_set_option(c, "comm_sms", e);
     if (cuda_stream) {

@@ -74,7 +74,7 @@ struct fg_ctx {
     int opt_tile_bn, opt_tile_bk;
     bool opt_split_k;           // split-K tail of the pair kernel
     bool opt_pairs;             // multiply f32 tensors as they lie (bf16 pairs) where the shape allows
-    bool opt_exec_plans;        // the graph engine records each dispatch as a CUDA graph
+    int opt_exec_plans;         // the graph engine records each dispatch as a CUDA graph: 1 always, 0 never, -1 when launch-bound
     int opt_comm_max_ctas;      // CTAs the communicator may use (fg_comm_init)
     uint64_t opt_min_exchange;  // elements: the graph engine starts an exchange once this much is complete
     uint64_t ws_generation;     // bumped whenever the scratch arena is reallocated

@@ -942,6 +942,47 @@ static int32_t optim_one(fg_exec* e, uint32_t slot, fg_buf* weight) {
 
 // Updates every bound tensor that is marked trainable (the reference updates all of them:
 // dispatch/mod.rs:735-748) and zeroes its gradient.
+// Updates the given input slots in one launch (f32 graphs), or one by one (16-bit storage).
+static int32_t optim_many(fg_exec* e, const std::vector<int>& slots) {
+    if (slots.empty()) return FG_OK;
+    if (e->dtype != FG_DTYPE_F32) {
+        for (int slot : slots) {
+            const int32_t s = optim_one(e, (uint32_t)slot, e->n[e->inputs[slot]].value);
+            if (s != FG_OK) return s;
+        }
+        return FG_OK;
+    }
+    float lr;
+    memcpy(&lr, &e->meta[0], 4);
+    std::vector<fg_update_tensor> t;
+    for (int slot : slots) {
+        const int node = e->inputs[slot];
+        ENode& en = e->n[node];
+        fg_update_tensor u{};
+        u.w = (float*)en.value->ptr;
+        u.g = gptr(e, node);
+        if (e->g.optim == FG_OPTIM_ADAMW) { u.m = (float*)e->m[slot]->ptr; u.v = (float*)e->v[slot]->ptr; }
+        u.w_pairs = en.pairs ? en.pairs->ptr : nullptr;      // the updated weights' pairs, same pass
+        u.pairs_stride = pstride(e, node);
+        u.n = en.numel;
+        t.push_back(u);
+    }
+    int32_t s;
+    if (e->g.optim == FG_OPTIM_SGD) s = fg_sgd_step_multi(e->ctx, t.data(), (uint32_t)t.size(), lr, 1.0f, 1);
+    else {
+        fg_adamw_hyper h = e->hyper;
+        h.lr = lr;
+        s = fg_adamw_step_multi(e->ctx, t.data(), (uint32_t)t.size(), &h, 0, (const uint32_t*)e->step_counter->ptr, 1.0f, 1);
+    }
+    if (s != FG_OK) return s;
+    for (int slot : slots)
+        if (e->n[e->inputs[slot]].pairs) {
+            e->pairs_fresh[slot] = 1;
+            e->pairs_version[slot] = e->n[e->inputs[slot]].value->version;
+        }
+    return FG_OK;
+}
+
 static int32_t optim_eager(fg_exec* e) {
     int32_t s;
     if (e->g.optim == FG_OPTIM_ADAMW && (s = fg_counter_increment(e->ctx, (uint32_t*)e->step_counter->ptr)) != FG_OK) return s;
@@ -951,20 +992,32 @@ static int32_t optim_eager(fg_exec* e) {
         // beside it, the others when it has arrived.
         const uint64_t lo = e->optim_lo, hi = ready_end(e, INT_MAX - 1);
         if (hi > lo && (s = fg_allreduce_sum_f32(e->ctx, (float*)e->grad_arena->ptr + lo, hi - lo)) != FG_OK) return s;
+        std::vector<int> early, late;
         for (int slot : e->arena_order)
-            if (e->trainable[slot] && e->arena_off[slot] + e->n[e->inputs[slot]].numel <= lo &&
-                (s = optim_one(e, (uint32_t)slot, e->n[e->inputs[slot]].value)) != FG_OK)
-                return s;
+            if (e->trainable[slot]) (e->arena_off[slot] + e->n[e->inputs[slot]].numel <= lo ? early : late).push_back(slot);
+        if ((s = optim_many(e, early)) != FG_OK) return s;
         if ((s = fg_comm_join(e->ctx)) != FG_OK) return s;
-        for (int slot : e->arena_order)
-            if (e->trainable[slot] && e->arena_off[slot] + e->n[e->inputs[slot]].numel > lo &&
-                (s = optim_one(e, (uint32_t)slot, e->n[e->inputs[slot]].value)) != FG_OK)
-                return s;
-        return FG_OK;
+        return optim_many(e, late);
     }
-    for (uint32_t k = 0; k < e->inputs.size(); ++k)
-        if (e->trainable[k] && (s = optim_one(e, k, e->n[e->inputs[k]].value)) != FG_OK) return s;
-    return FG_OK;
+    std::vector<int> all;
+    for (int slot : e->arena_order)
+        if (e->trainable[slot]) all.push_back(slot);
+    return optim_many(e, all);
+}
+
+// Are this graph's dispatches recorded and replayed?  With option exec_plans = auto: when the graph is launch-bound,
+// i.e. its estimated device time per launch is under ten microseconds (one forward + backward pass estimated at
+// 300 TFLOP/s for the matmuls and 5 TB/s for every tensor touched three times, over about three launches per step of
+// the forward pass).
+static bool plans_wanted(const fg_exec* e) {
+    if (!e->use_plans || e->ctx->opt_exec_plans == 0) return false;
+    if (e->ctx->opt_exec_plans == 1) return true;
+    double flop = 0.0, bytes = 0.0;
+    for (const GemmStep& gs : e->gemms) flop += 3.0 * 2.0 * gs.batch * (double)gs.M * gs.N * gs.K;
+    for (const ENode& en : e->n) bytes += 3.0 * (double)en.numel * (double)e->esize;
+    const double est_us = flop / 300e6 + bytes / 5e6;
+    const double launches = 3.0 * (double)std::max<size_t>(e->fwd.size(), 1);
+    return est_us / launches < 10.0;
 }
 
 // Runs one dispatch: eagerly the first time (which also sizes the scratch arena), recorded as a plan the
@@ -973,7 +1026,7 @@ static int32_t optim_eager(fg_exec* e) {
 // simply enqueued, so that it becomes part of the caller's plan.
 static int32_t run_planned(fg_exec* e, int which, const void* key, const std::function<int32_t()>& eager) {
     fg_ctx* ctx = e->ctx;
-    if (!e->use_plans || !ctx->opt_exec_plans || ctx->capturing) return eager();
+    if (!plans_wanted(e) || ctx->capturing) return eager();
     if (e->plan[which] && e->plan_key[which] == key && e->plan_ws[which] == (const void*)ctx->ws)
         return fg_plan_launch(ctx, e->plan[which]);
     if (e->calls[which]++ == 0) return eager();
@@ -1069,5 +1122,6 @@ fg_buf* fg_exec_grad(fg_exec* e, uint32_t i, int32_t* node) {
 }
 // Number of kernels the forward pass launches per dispatch (how much was fused).
 uint32_t fg_exec_forward_steps(fg_exec* e) { return e ? (uint32_t)e->fwd.size() : 0; }
+int32_t fg_exec_plans_active(fg_exec* e) { return e && plans_wanted(e) ? 1 : 0; }
 
 }  // extern "C"

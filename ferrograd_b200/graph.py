@@ -186,6 +186,10 @@ class AllocTensors:
         self.loss_sum = wrap(lib.fg_exec_loss_sum(handle))      # one f32: sum over loss_t (this backend's addition)
         self.state = []
 
+    def plans_active(self):
+        """True when the engine records this graph's dispatches as CUDA graphs and replays them."""
+        return bool(self.ctx.lib.fg_exec_plans_active(self.handle))
+
     def forward_steps(self):
         return int(self.ctx.lib.fg_exec_forward_steps(self.handle))
 

@@ -64,7 +64,7 @@ def test_two_gpus_match_one_gpu_on_the_global_batch(tmp_path):
         assert np.max(np.abs(got - ref)) <= 2e-5 + 1e-4 * np.max(np.abs(ref)), float(np.max(np.abs(got - ref)))
 
 
-def _rank_graph_api(rank, world, port, out_dir):
+def _rank_graph_api(rank, world, port, out_dir, plans):
     """The reference's training loop (dispatch_forward / loss / backward / optim) on two ranks: the graph engine
     itself sums the gradients over the ranks.  A small exchange threshold makes the backward pass start exchanges
     of its own, as it does for large layers; four steps cover the eager, the recorded and the replayed dispatch."""
@@ -78,6 +78,7 @@ def _rank_graph_api(rank, world, port, out_dir):
     ctx = GpuContext(rank)
     ctx.comm_init(world, rank, dp.exchange_unique_id(ctx, dist, rank))
     ctx.set_option("comm_min_exchange", 20000)
+    ctx.set_option("exec_plans", plans)             # recorded and replayed dispatches, or plain launches
     net = GraphMLP(ctx, GDIMS, BATCH, "gelu", "ce", OPT)
     net.set_params(*MLPTrainer.init_params(GDIMS, "he_normal", 21))
     for s in range(GSTEPS):
@@ -97,14 +98,15 @@ def _rank_graph_api(rank, world, port, out_dir):
 GDIMS, GSTEPS = [64, 256, 192, 10], 4
 
 
-def test_graph_api_two_gpus_match_one_gpu_on_the_global_batch(tmp_path):
+@pytest.mark.parametrize("plans", ["1", "0"])
+def test_graph_api_two_gpus_match_one_gpu_on_the_global_batch(tmp_path, plans):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     from ferrograd_b200 import GpuContext, dp
     from ferrograd_b200.mlp import GraphMLP, MLPTrainer
-    mp.spawn(_rank_graph_api, args=(2, 29900 + os.getpid() % 300, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_rank_graph_api, args=(2, 29900 + os.getpid() % 300 + int(plans), str(tmp_path), plans), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "graph_rank0.npz"), np.load(tmp_path / "graph_rank1.npz")
     for k in r0.files:
         assert np.array_equal(r0[k], r1[k])           # replicas stay bit-identical

@@ -472,7 +472,7 @@ def test_replayed_dispatches_equal_eager(ctx):
             assert np.array_equal(got, ref)
         assert not np.array_equal(train(eager=False)[0], W[0])       # and training moved the weights
     finally:
-        ctx.set_option("exec_plans", "1")
+        ctx.set_option("exec_plans", "auto")
 
 
 def test_binary_cross_entropy_graph(ctx, oracle):

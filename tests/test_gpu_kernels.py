@@ -79,6 +79,46 @@ def test_adamw_vs_oracle(ctx, oracle, n):
     check(ctx.to_numpy(dv), v, TOL_EW, "adamw v")
 
 
+@pytest.mark.parametrize("kind", ["adamw", "sgd"])
+def test_multi_tensor_update_equals_one_call_per_tensor(ctx, kind):
+    # one launch over several tensors (ragged sizes, more than 16 of them): bit-identical to one call each,
+    # pairs included
+    from ferrograd_b200.backend import to_bf16_bits
+    r = rng(404)
+    sizes = [5, 4096, 8193, 1, 100003, 8192, 12] + [33] * 12
+    hp = (1e-3, 0.9, 0.999, 1e-8, 0.01)
+    tensors, singles = [], []
+    for n in sizes:
+        w, g = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
+        m, v = r.standard_normal(n, np.float32) * 0.1, np.abs(r.standard_normal(n, np.float32)) * 0.01
+        stride = (n + 7) // 8 * 8
+        a = dict(w=up(ctx, w), g=up(ctx, g), m=up(ctx, m), v=up(ctx, v), w_pairs=ctx.alloc_zeroed(4 * stride), pairs_stride=stride, n=n)
+        b = dict(w=up(ctx, w), g=up(ctx, g), m=up(ctx, m), v=up(ctx, v), w_pairs=ctx.alloc_zeroed(4 * stride), pairs_stride=stride, n=n)
+        tensors.append(a)
+        singles.append(b)
+    if kind == "adamw":
+        ctx.adamw_step_multi(tensors, *hp, step=3, grad_scale=0.5)
+        for b in singles:
+            ctx.adamw_step_paired(b["w"], b["g"], b["m"], b["v"], b["n"], *hp, b["w_pairs"], b["pairs_stride"], step=3, grad_scale=0.5)
+    else:
+        ctx.sgd_step_multi(tensors, 0.1, grad_scale=0.5)
+        for b in singles:
+            ctx.sgd_step_paired(b["w"], b["g"], b["n"], 0.1, b["w_pairs"], b["pairs_stride"], grad_scale=0.5)
+    ctx.sync()
+    for a, b in zip(tensors, singles):
+        for key in ("w", "g") + (("m", "v") if kind == "adamw" else ()):
+            assert np.array_equal(ctx.to_numpy(a[key]), ctx.to_numpy(b[key])), key
+        pa = ctx.download(a["w_pairs"], np.empty(2 * a["pairs_stride"], np.uint16))
+        pb = ctx.download(b["w_pairs"], np.empty(2 * a["pairs_stride"], np.uint16))
+        assert np.array_equal(pa, pb)
+        # the pairs are those of the updated weights: plane 0 = bf16(w), plane 1 = bf16(w - trunc_tf32(w))
+        w = ctx.to_numpy(a["w"])
+        hi = (w.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
+        assert np.array_equal(pa[:a["n"]], to_bf16_bits(w))
+        assert np.array_equal(pa[a["pairs_stride"]:a["pairs_stride"] + a["n"]], to_bf16_bits(w - hi))
+        assert (ctx.to_numpy(a["g"]) == 0).all()
+
+
 def test_adamw_device_step_counter(ctx, oracle):
     n = 1000
     r = rng(33)
@@ -460,6 +500,77 @@ def test_gemm_tensor_core_transposes(ctx, oracle, tA, tB, mode):
     Cd = ctx.new_tensor((M, N))
     ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K, transA=tA, transB=tB, mode=mode)
     check(ctx.to_numpy(Cd), oracle.gemm(A, B, transA=tA, transB=tB), TOL_GEMM, f"{mode} transposed")
+
+
+def _pairs_of(x):
+    """What the library defines as a tensor's bf16 pairs: bf16(x) and bf16(x - trunc_tf32(x))."""
+    from ferrograd_b200.backend import to_bf16_bits
+    x = np.ascontiguousarray(x, np.float32)
+    hi = (x.view(np.uint32) & np.uint32(0xffffe000)).view(np.float32)
+    return to_bf16_bits(x).reshape(x.shape), to_bf16_bits(x - hi).reshape(x.shape)
+
+
+# (M, N, K): the pair kernel on the tensors themselves; a ragged shape that goes through operand planes; a narrow layer
+PAIRED_SHAPES = [(512, 384, 256), (640, 520, 1032), (300, 130, 100), (512, 10, 256)]
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "tanh", "gelu"])
+@pytest.mark.parametrize("M,N,K", PAIRED_SHAPES)
+@pytest.mark.parametrize("own_pairs", [True, False])
+def test_gemm_paired_forward(ctx, oracle, M, N, K, act, own_pairs):
+    r = rng(M * 7 + N * 3 + K + len(act))
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32) * 0.1
+    bias = r.standard_normal(N, np.float32)
+    Ad, Bd, Cd, Pd = up(ctx, A), up(ctx, B), ctx.new_tensor((M, N)), ctx.new_tensor((M, N))
+    sa, sb, sc = (M * K + 7) // 8 * 8, (K * N + 7) // 8 * 8, (M * N + 7) // 8 * 8
+    ap = bp = None
+    if own_pairs:       # the caller keeps the operands' pairs; otherwise the call makes them
+        ap, bp = ctx.alloc(4 * sa), ctx.alloc(4 * sb)
+        ctx.pairs_from_f32(Ad, M * K, ap, sa)
+        ctx.pairs_from_f32(Bd, K * N, bp, sb)
+    cp = ctx.alloc_zeroed(4 * sc)
+    ctx.gemm_paired(Ad, Bd, Cd, M, N, K, A_pairs=ap, B_pairs=bp, bias=up(ctx, bias), act=act, preact_out=Pd, C_pairs=cp,
+                    A_stride=sa, B_stride=sb, C_stride=sc)
+    got, pre = ctx.to_numpy(Cd), ctx.to_numpy(Pd)
+    assert ctx.device_status() == 0
+    yref, zref = oracle.bias_act_fwd(oracle.gemm(A, B), bias, act)
+    check(pre, zref, TOL_GEMM, "pre-activation")
+    check(got, yref, TOL_GEMM, "output")
+    pairs = ctx.download(cp, np.empty(2 * sc, np.uint16))
+    hb, lo = _pairs_of(got)
+    assert np.array_equal(pairs[:M * N].reshape(M, N), hb)                  # the pairs are exact functions of what was stored
+    assert np.array_equal(pairs[sc:sc + M * N].reshape(M, N), lo)
+
+
+@pytest.mark.parametrize("below", ["none", "relu", "tanh", "gelu"])
+@pytest.mark.parametrize("M,N,K", PAIRED_SHAPES)
+def test_gemm_paired_backward(ctx, oracle, M, N, K, below):
+    # dB = A^T dZ; dA = (dZ B^T) * act'(saved of the layer below), with its pairs and column sums; dbias = column sums of dZ
+    r = rng(M + N * 5 + K * 11 + len(below))
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32) * 0.1
+    dZ = r.standard_normal((M, N), np.float32)
+    z_below = r.standard_normal((M, K), np.float32)                  # pre-activation of the layer below
+    y_below, _ = oracle.bias_act_fwd(z_below, None, below)
+    saved = z_below if below == "gelu" else y_below                    # GELU saves the pre-activation, the others the output
+    Ad, Bd, Zd = up(ctx, A), up(ctx, B), up(ctx, dZ)
+    dB, dA = ctx.new_tensor((K, N)), ctx.new_tensor((M, K))
+    dbias, dbias_below = ctx.new_tensor((N,)), ctx.new_tensor((K,))
+    sa = (M * K + 7) // 8 * 8
+    dap = ctx.alloc_zeroed(4 * sa)
+    ctx.gemm_bwd_paired(Ad, Bd, Zd, M, N, K, dB=dB, dbias=dbias, dA=dA, below_act=below,
+                        below_saved=up(ctx, saved) if below != "none" else None, dA_pairs=dap, dA_stride=sa,
+                        below_dbias=dbias_below)
+    got_dA, got_dB = ctx.to_numpy(dA), ctx.to_numpy(dB)
+    assert ctx.device_status() == 0
+    check(got_dB, oracle.gemm(A, dZ, transA=True), TOL_GEMM, "dB")
+    ref_dA = oracle.act_bwd(oracle.gemm(dZ, B, transB=True), saved, below)
+    check(got_dA, ref_dA, TOL_GEMM, "dA with the activation factor of the layer below")
+    check(ctx.to_numpy(dbias), oracle.colsum(dZ), TOL_EW, "dbias")
+    check(ctx.to_numpy(dbias_below), oracle.colsum(got_dA), TOL_EW, "bias gradient of the layer below = column sums of dA")
+    pairs = ctx.download(dap, np.empty(2 * sa, np.uint16))
+    hb, lo = _pairs_of(got_dA)
+    assert np.array_equal(pairs[:M * K].reshape(M, K), hb)
+    assert np.array_equal(pairs[sa:sa + M * K].reshape(M, K), lo)
 
 
 @pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
