@@ -49,6 +49,7 @@ SIGNATURES = {
     "fg_ctx_reserve_workspace": (i32, [c_ctx, u64]),
     "fg_ctx_workspace_bytes": (u64, [c_ctx]),
     "fg_ctx_set_option": (i32, [c_ctx, C.c_char_p, C.c_char_p]),
+    "fg_selftest_bounded_wait": (i32, [c_ctx, u32]),
     "fg_ctx_device_status": (i32, [c_ctx, C.POINTER(i32)]),
     "fg_ctx_timing_enable": (i32, [c_ctx, i32]),
     "fg_ctx_timing_read": (i32, [c_ctx, i32, C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double)]),

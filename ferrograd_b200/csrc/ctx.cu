@@ -189,6 +189,13 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
         !create_events(c->ev_ckpt, 8) ||
         cudaMalloc((void**)&c->dev_status, 256) != cudaSuccess ||
         cudaMemset(c->dev_status, 0, 256) != cudaSuccess) {
+        // release whatever was created before the failure (the struct was zeroed: untouched members are NULL)
+        if (c->comm_stream) cudaStreamDestroy(c->comm_stream);
+        if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+        for (cudaEvent_t ev : {c->ev_copy_done, c->ev_main_mark, c->ev_fork, c->ev_join}) if (ev) cudaEventDestroy(ev);
+        for (cudaEvent_t ev : c->ev_ckpt) if (ev) cudaEventDestroy(ev);
+        if (c->dev_status) cudaFree(c->dev_status);
+        if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
         delete c;
         return FG_ERR_INTERNAL;
     }

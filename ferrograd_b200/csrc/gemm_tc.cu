@@ -2173,6 +2173,27 @@ int32_t fg_gemm_bwd_lowp(fg_ctx* ctx, int32_t dtype, uint32_t M, uint32_t N, uin
 
 }  // extern "C"
 
+// ---- self-test of the bounded waits ----
+namespace {
+__global__ void bounded_wait_selftest_kernel(int* dev_status, long long max_cycles) {
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+        // nobody arrives on this barrier: the wait must give up after max_cycles and report it
+        if (!mbar_wait_bounded(smem_u32(&bar), 0, max_cycles)) atomicOr(dev_status, FG_DEVERR_EPI_WAIT);
+    }
+}
+}  // namespace
+
+extern "C" int32_t fg_selftest_bounded_wait(fg_ctx* ctx, uint32_t max_cycles) {
+    FG_ENTER(ctx);
+    const long long limit = max_cycles > 1000000u ? 1000000ll : (long long)max_cycles;
+    bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, limit);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
 #ifdef FG_GEMM_PROFILE
 extern "C" int32_t fg_gemm_profile_read(unsigned long long out[8]) {
     unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};

@@ -22,10 +22,13 @@
 //     larger inputs are refused with FG_ERR_INVALID_ARGUMENT before anything is launched.
 //   * The device address of the array is looked up with cudaGetSymbolAddress once per
 //     device, by the first call made with that device's context.  Make that first call
-//     outside any stream capture.
+//     outside any stream capture; inside a recording started with fg_plan_begin it is refused
+//     (FG_ERR_INCONSISTENT_CAPTURE) rather than attempted.
 //   * All calls on one GPU share the array.  Each call overwrites the entries it uses before
 //     reading them, so nothing has to be cleared between calls, but two calls that run
 //     concurrently on the same GPU (different streams or contexts) race on it.
+#include <atomic>
+
 #include "fg_internal.cuh"
 
 #define FG_MSE_NOALLOC_CHUNK 65536u
@@ -39,7 +42,9 @@ static __device__ __align__(256) float g_mse_partials[FG_MSE_NOALLOC_MAX_PARTIAL
 namespace {
 
 constexpr int kMaxDevices = 64;
-float* s_partials_addr[kMaxDevices] = {};   // device address of g_mse_partials, per device
+// Device address of g_mse_partials, per device.  Several host threads (each with its own context) may make the
+// first call on one device at the same time; they all look up and store the same value.
+std::atomic<float*> s_partials_addr[kMaxDevices];
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -93,14 +98,19 @@ __global__ void __launch_bounds__(256) mse_fold_kernel(const float* __restrict__
 int32_t partials_address(fg_ctx* ctx, float** out) {
     if (ctx->device < 0 || ctx->device >= kMaxDevices)
         return fg_fail(ctx, FG_ERR_INVALID_DEVICE, "fg_mse_loss_grad_noalloc: device index out of range");
-    if (!s_partials_addr[ctx->device]) {
-        float* p = nullptr;
+    float* p = s_partials_addr[ctx->device].load(std::memory_order_acquire);
+    if (!p) {
+        // The look-up is a runtime call that does not belong inside a stream capture: refuse instead of risking
+        // the caller's recording.
+        if (ctx->capturing)
+            return fg_fail(ctx, FG_ERR_INCONSISTENT_CAPTURE,
+                           "fg_mse_loss_grad_noalloc: the first call on a device must be made outside a recording");
         cudaError_t e = cudaGetSymbolAddress((void**)&p, g_mse_partials);
         if (e != cudaSuccess || !p)
             return fg_fail_cuda(ctx, FG_ERR_INTERNAL, "cudaGetSymbolAddress(g_mse_partials)", e);
-        s_partials_addr[ctx->device] = p;
+        s_partials_addr[ctx->device].store(p, std::memory_order_release);
     }
-    *out = s_partials_addr[ctx->device];
+    *out = p;
     return FG_OK;
 }
 

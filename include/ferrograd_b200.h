@@ -96,8 +96,10 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  *                   allows; "0" sends every shape through operand planes written by a pre-pass
  *   "exec_plans"    "auto" (default) | "1" | "0": the graph engine records each dispatch as a CUDA graph and
  *                   replays it.  "auto" does so for graphs whose kernels are short (launch-bound: the tiny MLP gains
- *                   several times); for large layers plain launches keep the GPU fed, and four graph launches per
- *                   step cost more than they save (measured: 1.87 against 1.82 ms per step on 784-4096-4096-10)
+ *                   several times) and whenever the context has a communicator (the host-side cost of enqueueing
+ *                   collectives every step is avoided); for large layers on one GPU plain launches keep the GPU fed,
+ *                   and four graph launches per step cost more than they save (measured: 1.87 against 1.82 ms per
+ *                   step on 784-4096-4096-10)
  *   "comm_max_ctas" CTAs the communicator may use (default 12; read by fg_comm_init)
  *   "comm_sms"      SMs the persistent GEMM leaves free while an exchange is in flight (default 16; 0 = none)
  *   "comm_min_exchange"  the graph engine starts a gradient exchange during the backward pass once this many
@@ -105,6 +107,11 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  * The environment variables FG_GEMM_TILE, FG_GEMM_NO_SPLITK, FG_GEMM_NO_PAIRS, FG_EXEC_NO_PLANS,
  * NCCL_MAX_CTAS and FG_COMM_SMS give the initial values; they are read once, when the context is created. */
 int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value);
+/* Self-test of the bounded device-side waits (no counterpart in the reference).  Launches one tiny kernel that
+ * waits, for at most max_cycles SM clock cycles (clamped to 1,000,000), on an mbarrier nobody ever arrives on,
+ * with the same wait routine the GEMM kernels use.  The wait runs out, the kernel records it in the device error
+ * word and returns: fg_sync then reports FG_ERR_TIMEOUT once and the context stays usable.  Nothing faults or hangs. */
+int32_t fg_selftest_bounded_wait(fg_ctx* ctx, uint32_t max_cycles);
 /* Reads and clears the device-side error word (bounded waits that expired). */
 int32_t fg_ctx_device_status(fg_ctx* ctx, int32_t* status_word);
 
@@ -302,7 +309,8 @@ int32_t fg_bce_loss_grad(fg_ctx* ctx, const float* pred, const float* target, ui
  * context's scratch arena, so no cudaMalloc/cudaFree happens on any call.
  *   - n must not exceed FG_MSE_NOALLOC_MAX_N; larger n returns FG_ERR_INVALID_ARGUMENT.
  *   - The first call made on a device looks up the array's address; make it outside any
- *     stream capture.
+ *     stream capture (inside a recording started with fg_plan_begin it is refused with
+ *     FG_ERR_INCONSISTENT_CAPTURE).
  *   - Calls on the same GPU share the array: do not let two of them run concurrently.
  * loss_sum agrees with fg_mse_loss_grad to rounding (a different, SM-count-independent
  * summation order); loss_elem and grad are identical. */

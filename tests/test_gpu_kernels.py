@@ -769,3 +769,53 @@ def test_plan_capture_and_replay(ctx, oracle):
     assert ctx.launch_count() == before + 3
     assert np.array_equal(ctx.to_numpy(dw), w)
     plan.destroy()
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_context_survives(ctx, oracle):
+    # the wait routine of the GEMM kernels, on a barrier nobody arrives on, with a short limit: the kernel returns,
+    # fg_sync reports FG_ERR_TIMEOUT once, the status word is clear afterwards and a GEMM runs normally
+    from ferrograd_b200 import FgError
+    assert ctx.device_status() == 0
+    ctx._check(ctx.lib.fg_selftest_bounded_wait(ctx.handle, 20000))
+    with pytest.raises(FgError) as e:
+        ctx.sync()
+    assert e.value.kind == "FG_ERR_TIMEOUT"
+    ctx.sync()                                   # reported once, then clear
+    assert ctx.device_status() == 0
+    M, N, K = 256, 384, 512
+    r = rng(9)
+    A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
+    Cd = ctx.new_tensor((M, N))
+    ctx.gemm(up(ctx, A), up(ctx, B), Cd, M, N, K)
+    check(ctx.to_numpy(Cd), oracle.gemm(A, B), TOL_GEMM, "GEMM after an expired wait")
+    assert ctx.device_status() == 0
+
+
+def test_a_plan_recorded_before_the_scratch_arena_moved_is_refused(oracle):
+    # A recorded plan carries addresses inside the scratch arena.  A later, larger eager call reallocates the arena;
+    # replaying the old plan would touch freed memory, so fg_plan_launch refuses it.
+    from ferrograd_b200 import FgError, GpuContext
+    c = GpuContext(0)
+    try:
+        r = rng(10)
+        M, N, K = 200, 72, 100                                      # a shape that goes through operand planes (scratch)
+        A, B = r.standard_normal((M, K), np.float32), r.standard_normal((K, N), np.float32)
+        Ad, Bd, Cd = up(c, A), up(c, B), c.new_tensor((M, N))
+        c.gemm(Ad, Bd, Cd, M, N, K, mode="3xtf32")                  # sizes the arena
+        c.plan_begin()
+        c.gemm(Ad, Bd, Cd, M, N, K, mode="3xtf32")
+        plan = c.plan_end()
+        plan.launch()
+        c.sync()
+        check(c.to_numpy(Cd), oracle.gemm(A, B), TOL_GEMM, "replayed GEMM")
+        big = 1024
+        X, Y = up(c, r.standard_normal((big, big), np.float32)), up(c, r.standard_normal((big, big), np.float32))
+        c.gemm(X, Y, c.new_tensor((big, big)), big, big, big, mode="3xtf32")    # needs a larger arena: it is reallocated
+        with pytest.raises(FgError) as e:
+            plan.launch()
+        assert e.value.kind == "FG_ERR_INCONSISTENT_CAPTURE"
+        c.sync()
+        assert c.device_status() == 0
+        plan.destroy()
+    finally:
+        c.destroy()

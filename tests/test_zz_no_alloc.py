@@ -21,7 +21,9 @@ def test_noalloc_matches_regular_entry_point_twice():
     ctx = GpuContext(0)
     try:
         r = np.random.Generator(np.random.Philox(2024))
-        for n in (70_001, 1_300_000):         # two calls in a row; the second needs more partial sums
+        # calls in a row on the shared array; sizes around the 65,536-element chunk edge, then ones that need
+        # several partial sums
+        for n in (65_536, 65_537, 70_001, 1_300_000):
             p, t = r.standard_normal(n, np.float32), r.standard_normal(n, np.float32)
             dp_, dt_ = ctx.init_tensor_f32((n,), p), ctx.init_tensor_f32((n,), t)
             ref = [ctx.new_tensor((n,)), ctx.new_tensor((1,)), ctx.new_tensor((n,))]
@@ -38,6 +40,11 @@ def test_noalloc_matches_regular_entry_point_twice():
             # and both agree with a float64 sum on the host
             exact = float(np.sum((p.astype(np.float64) - t) ** 2))
             assert abs(float(ctx.to_numpy(got[1])[0]) - exact) <= 1e-5 * exact
+        # nothing to sum: the result is zero and nothing is launched
+        z = ctx.init_tensor_f32((1,), np.array([7.0], np.float32))
+        ctx.mse_loss_grad_noalloc(dp_, dt_, 0, loss_sum=z)
+        ctx.sync()
+        assert float(ctx.to_numpy(z)[0]) == 0.0
         # sum only (no per-element outputs), then a size beyond the maximum
         s = ctx.new_tensor((1,))
         ctx.mse_loss_grad_noalloc(dp_, dt_, n, loss_sum=s)
