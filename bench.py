@@ -289,6 +289,50 @@ def _kernel_lines(torch, stream, ctx, peaks):
                                        "frac_of_bf16_peak": work / ms / 1e9 / peaks["bf16_tflops"],
                                        "call_ms_with_transpose": e_ms,
                                        "call_tflops_with_transpose": 2.0 * N ** 3 / e_ms / 1e9}
+    del A16, B16, C16, A, B, C
+    # Streaming elementwise kernels on 32 Mi elements per tensor (128 MB each, so nothing fits the L2), and the three
+    # kernels of a 10-class output layer on 32768 x 4096 activations (512 MB)
+    n_el = 32 << 20
+    t = [torch.rand(n_el, device="cuda", generator=g) * 0.8 + 0.1 for _ in range(2)] + \
+        [torch.empty(n_el, device="cuda") for _ in range(2)]
+    one = torch.empty(1, device="cuda")
+    bias_v = torch.randn(4096, device="cuda", generator=g)
+    gelu_chain = [("input", 0, 0, 0.0), ("input", 1, 0, 0.0), ("mul", 0, 1, 0.0), ("gelu", 2, 0, 0.0),
+                  ("add", 3, 0, 0.0)]                                                            # gelu(x*y) + x
+    ew = {
+        "bias_gelu_fwd": lambda: ctx.bias_act_fwd(t[0].data_ptr(), bias_v.data_ptr(), "gelu", t[2].data_ptr(), n_el // 4096, 4096),
+        "gelu_bwd": lambda: ctx.act_bwd(t[0].data_ptr(), t[1].data_ptr(), t[2].data_ptr(), n_el, "gelu"),
+        "mse_loss_grad": lambda: ctx.mse_loss_grad(t[0].data_ptr(), t[1].data_ptr(), n_el, 0.5, loss_elem=t[2].data_ptr(),
+                                                   loss_sum=one.data_ptr(), grad=t[3].data_ptr()),
+        "bce_loss_grad": lambda: ctx.bce_loss_grad(t[0].data_ptr(), t[1].data_ptr(), n_el, 0.5, loss_elem=t[2].data_ptr(),
+                                                   loss_sum=one.data_ptr(), grad=t[3].data_ptr()),
+        "chain_fwd_5_instr": lambda: ctx.eltwise_chain_fwd(gelu_chain, [t[0].data_ptr(), t[1].data_ptr()], t[2].data_ptr(), n_el),
+        "chain_bwd_5_instr": lambda: ctx.eltwise_chain_bwd(gelu_chain, [t[0].data_ptr(), t[1].data_ptr()], t[2].data_ptr(),
+                                                           [t[3].data_ptr(), None], n_el),
+    }
+    for name, fn in ew.items():
+        for _ in range(3):
+            fn()
+        n, ms, work = per_launch("eltwise", fn, 5)
+        out[name] = {"ms": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm, "bytes": work, "elements": n_el}
+    del t
+    Ms, Ks, Ns = 32768, 4096, 10
+    h = torch.randn(Ms, Ks, device="cuda", generator=g)
+    w_s = torch.randn(Ks, Ns, device="cuda", generator=g) * 0.02
+    dz = torch.randn(Ms, Ns, device="cuda", generator=g)
+    z_s, dw_s, dh = torch.empty(Ms, Ns, device="cuda"), torch.empty(Ks, Ns, device="cuda"), torch.empty(Ms, Ks, device="cuda")
+    sk = {
+        "skinny_fwd": lambda: ctx.gemm(h.data_ptr(), w_s.data_ptr(), z_s.data_ptr(), Ms, Ns, Ks),
+        "skinny_bwd_dW_dX": lambda: ctx.gemm_bwd(h.data_ptr(), w_s.data_ptr(), dz.data_ptr(), Ms, Ns, Ks, dA=dh.data_ptr(),
+                                                 dB=dw_s.data_ptr()),
+    }
+    for name, fn in sk.items():
+        for _ in range(3):
+            fn()
+        n, ms, work = per_launch("skinny", fn, 5)
+        out[name] = {"ms_per_kernel": ms, "gbs": work / ms / 1e6, "frac_of_hbm": work / ms / 1e6 / hbm,
+                     "bytes_per_kernel": work, "shape": [Ms, Ns, Ks], "kernels_per_call": n // 5}
+    del h, dh
     # C1: the reference's own CPU-scale case (MLP 2-16-2, batch 64, MSE, SGD), 1000 steps replayed as a plan;
     # launch-bound, so the figure is steps per second
     from ferrograd_b200 import dp

@@ -15,7 +15,7 @@ from . import _lib
 
 ACT = {"none": 0, None: 0, "relu": 1, "tanh": 2, "gelu": 3}
 GEMM_MODE = {"auto": 0, "simt": 1, "3xtf32": 2, "tf32_bf16x2": 3}
-KERNEL_KIND = {"gemm_tc": 0, "softmax_ce": 1, "adamw": 2, "sgd": 3, "split": 4}
+KERNEL_KIND = {"gemm_tc": 0, "softmax_ce": 1, "adamw": 2, "sgd": 3, "split": 4, "eltwise": 5, "skinny": 6}
 EW = {"input": 0, "const": 1, "add": 2, "sub": 3, "mul": 4, "div": 5, "neg": 6, "abs": 7,
       "exp": 8, "log": 9, "tanh": 10, "relu": 11, "gelu": 12, "elu": 13}
 

@@ -39,8 +39,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
             print(out)
         if p.returncode != 0:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
-    link = [nvcc, "-shared", "-cudart", "static", "-o", OUT] + objs + ["-ldl"]
+    # link beside the target and move into place: a reader (a loader, a copy of the tree) sees a whole file
+    tmp = OUT + ".tmp"
+    link = [nvcc, "-shared", "-cudart", "static", "-o", tmp] + objs + ["-ldl"]
     subprocess.run(link, check=True)
+    os.replace(tmp, OUT)
     return OUT
 
 

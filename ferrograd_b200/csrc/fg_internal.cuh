@@ -1,5 +1,6 @@
 // Internal definitions shared by the translation units of libferrograd_b200.
 #pragma once
+#include <nvtx3/nvToolsExt.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -106,6 +107,16 @@ inline int32_t fg_fail_cuda(fg_ctx* ctx, int32_t code, const char* what, cudaErr
     do { if (!(ctx)) return FG_ERR_NOT_INITIALIZED; \
          FG_CUDA(ctx, FG_ERR_INVALID_DEVICE, cudaSetDevice((ctx)->device)); \
          (ctx)->ws_used = 0; } while (0)
+
+// A named range on the calling host thread for timeline tools (NVTX, header-only: without a tool attached a
+// range costs one pointer test).  The four dispatches of a training step, plan replays and gradient exchanges
+// carry one each.
+struct FgRange {
+    explicit FgRange(const char* name) { nvtxRangePushA(name); }
+    ~FgRange() { nvtxRangePop(); }
+    FgRange(const FgRange&) = delete;
+    FgRange& operator=(const FgRange&) = delete;
+};
 
 // After a kernel launch: count it and surface launch-configuration errors.
 #define FG_LAUNCHED(ctx) \
@@ -269,6 +280,10 @@ __device__ __forceinline__ void fg_store_pairs1(__nv_bfloat16* pairs, uint64_t p
 int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uint32_t N, uint32_t K,
                             const float* A, const float* B, float* C, const float* bias, int act,
                             float* preact_out);
+// The same for `batch` matrices in one launch (grid z = matrix; strides in elements).
+int32_t fg_gemm_simt_batched_launch(fg_ctx* ctx, int transA, int transB, uint32_t batch, uint32_t M, uint32_t N, uint32_t K,
+                                    const float* A, uint64_t sA, const float* B, uint64_t sB, float* C, uint64_t sC,
+                                    const float* bias, int act, float* preact_out);
 uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K);   // enough for any one skinny launch
 int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
                                 const float* bias, int act, float* preact_out);

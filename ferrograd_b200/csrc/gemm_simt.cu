@@ -19,9 +19,15 @@ template <bool TA, bool TB>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(uint32_t M, uint32_t N, uint32_t K,
                                                         const float* __restrict__ A, const float* __restrict__ B,
                                                         float* __restrict__ C, const float* __restrict__ bias, int act,
-                                                        float* __restrict__ preact) {
+                                                        float* __restrict__ preact, uint64_t sA, uint64_t sB, uint64_t sC) {
     __shared__ float As[TK][TM + 4];
     __shared__ float Bs[TK][TN + 4];
+    // blockIdx.z is the matrix of a batch (the reference puts the batch index in the grid's z too:
+    // crates/fused_gpu/src/dispatch/backend/kernel/forward.rs:159-190); the strides are in elements
+    A += blockIdx.z * sA;
+    B += blockIdx.z * sB;
+    C += blockIdx.z * sC;
+    if (preact) preact += blockIdx.z * sC;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const uint32_t m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
     float acc[4][4];
@@ -273,8 +279,10 @@ __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_
         if (vec) {
             if (ex.mul_saved) {
                 const float4 sv = __ldcs(reinterpret_cast<const float4*>(ex.mul_saved + off));
-                o[0] *= fg_act_grad(ex.mul_act, sv.x); o[1] *= fg_act_grad(ex.mul_act, sv.y);
-                o[2] *= fg_act_grad(ex.mul_act, sv.z); o[3] *= fg_act_grad(ex.mul_act, sv.w);
+                // the short forms the tensor-core epilogues use (one exponential, one reciprocal): the libm tanh of
+                // the plain form made this kernel compute-bound
+                o[0] *= fg_act_grad_sel(ex.mul_act, sv.x); o[1] *= fg_act_grad_sel(ex.mul_act, sv.y);
+                o[2] *= fg_act_grad_sel(ex.mul_act, sv.z); o[3] *= fg_act_grad_sel(ex.mul_act, sv.w);
             }
             const float4 v = make_float4(o[0], o[1], o[2], o[3]);
             *reinterpret_cast<float4*>(dA + off) = v;
@@ -283,7 +291,7 @@ __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_
 #pragma unroll
             for (int q = 0; q < 4; ++q)
                 if (k0 + q < K) {
-                    if (ex.mul_saved) o[q] *= fg_act_grad(ex.mul_act, ex.mul_saved[off + q]);
+                    if (ex.mul_saved) o[q] *= fg_act_grad_sel(ex.mul_act, ex.mul_saved[off + q]);
                     dA[off + q] = o[q];
                     if (ex.pairs) fg_store_pairs1(ex.pairs, ex.pairs_stride, off + q, o[q]);
                 } else o[q] = 0.0f;
@@ -337,10 +345,12 @@ int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K,
     FG_LAUNCHED(ctx);
     const uint32_t blocks = (M + 7) / 8;
     const bool vec = (K % 4 == 0) && fg_aligned16(A);
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * K);                 // A read once
     FG_SKINNY_DISPATCH(N, {
         if (vec) gemm_skinny_n_kernel<NT, true><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);
         else gemm_skinny_n_kernel<NT, false><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);
     });
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
@@ -352,7 +362,10 @@ int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N
     dim3 grid((K + 511) / 512, (M + 31) / 32);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
     const fg_skinny_extras ex = extras ? *extras : fg_skinny_extras{nullptr, 0, nullptr, 0, nullptr};
+    // dA written once; with extras also the saved tensor read and the pairs (as many bytes again) written
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * K * (1.0 + (ex.mul_saved ? 1.0 : 0.0) + (ex.pairs ? 1.0 : 0.0)));
     FG_SKINNY_DISPATCH(N, (gemm_skinny_nt_kernel<NT><<<grid, 128, 0, ctx->stream>>>(M, K, N, dZ, B, dA, ex)));
+    fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
@@ -368,6 +381,7 @@ int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t 
     dim3 grid((Kd + 511) / 512, nchunks);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
     const bool vec = (Kd % 4 == 0) && fg_aligned16(A);
+    fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * Kd);                // A read once
     FG_SKINNY_DISPATCH(N, {
         if (vec) gemm_skinny_tn_partial_kernel<NT, true><<<grid, 128, 0, ctx->stream>>>(M, Kd, N, A, dZ, (float*)part);
         else gemm_skinny_tn_partial_kernel<NT, false><<<grid, 128, 0, ctx->stream>>>(M, Kd, N, A, dZ, (float*)part);
@@ -375,18 +389,27 @@ int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t 
     FG_LAUNCHED(ctx);
     const uint64_t n = (uint64_t)Kd * N;
     fold_chunks_kernel<<<fg_stream_grid(ctx, n, 256, 8), 256, 0, ctx->stream>>>(n, nchunks, (const float*)part, dB);
+    fg_time_end(ctx, tr);
+    FG_LAUNCHED(ctx);
+    return FG_OK;
+}
+
+int32_t fg_gemm_simt_batched_launch(fg_ctx* ctx, int transA, int transB, uint32_t batch, uint32_t M, uint32_t N, uint32_t K,
+                                    const float* A, uint64_t sA, const float* B, uint64_t sB, float* C, uint64_t sC,
+                                    const float* bias, int act, float* preact_out) {
+    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
+    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "SIMT GEMM: M too large");
+    if (batch > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "SIMT GEMM: more than 65535 matrices in a batch");
+    if (batch == 0) return FG_OK;
+    if (!transA && !transB) gemm_simt_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out, sA, sB, sC);
+    else if (transA && !transB) gemm_simt_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out, sA, sB, sC);
+    else if (!transA && transB) gemm_simt_kernel<false, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out, sA, sB, sC);
+    else gemm_simt_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out, sA, sB, sC);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
 
 int32_t fg_gemm_simt_launch(fg_ctx* ctx, int transA, int transB, uint32_t M, uint32_t N, uint32_t K, const float* A,
                             const float* B, float* C, const float* bias, int act, float* preact_out) {
-    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
-    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "SIMT GEMM: M too large");
-    if (!transA && !transB) gemm_simt_kernel<false, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out);
-    else if (transA && !transB) gemm_simt_kernel<true, false><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out);
-    else if (!transA && transB) gemm_simt_kernel<false, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out);
-    else gemm_simt_kernel<true, true><<<grid, 256, 0, ctx->stream>>>(M, N, K, A, B, C, bias, act, preact_out);
-    FG_LAUNCHED(ctx);
-    return FG_OK;
+    return fg_gemm_simt_batched_launch(ctx, transA, transB, 1, M, N, K, A, 0, B, 0, C, 0, bias, act, preact_out);
 }

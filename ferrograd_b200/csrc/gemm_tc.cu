@@ -23,6 +23,7 @@
 // plane 1 = lo; ld = contraction length rounded up to 4 so row pitches are 16-byte
 // multiples).  One 3-D tensor map per operand: dims {contraction, rows, 2},
 // box {32, tile rows, 2}, so one load brings the hi and the lo tile of a k-block.
+#include <atomic>
 #include <cuda_bf16.h>
 #include <stdlib.h>
 
@@ -1247,11 +1248,13 @@ int32_t launch_tc(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const Epilo
         tmA16 = tmA;
         tmB16 = tmB;
     }
-    static uint64_t attr_done = 0;   // one bit per device
-    if (!(attr_done >> (ctx->device & 63) & 1ull)) {
+    // one bit per device; several host threads (one context each) may arrive here together, and setting the
+    // attribute twice is harmless
+    static std::atomic<uint64_t> attr_done{0};
+    if (!(attr_done.load(std::memory_order_acquire) >> (ctx->device & 63) & 1ull)) {
         FG_CUDA(ctx, FG_ERR_INTERNAL,
                 cudaFuncSetAttribute(gemm_tc_kernel<BN, BK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_done |= 1ull << (ctx->device & 63);
+        attr_done.fetch_or(1ull << (ctx->device & 63), std::memory_order_release);
     }
     dim3 grid((ep.N + BN - 1) / BN, (ep.M + BM - 1) / BM);
     if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: M too large");
@@ -1292,18 +1295,20 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
             tmB16 = tmB;
         }
     }
-    static uint64_t attr_done = 0;   // one bit per device
-    if (!(attr_done >> (ctx->device & 63) & 1ull)) {
+    // one bit per device; several host threads (one context each) may arrive here together, and setting the
+    // attribute twice is harmless
+    static std::atomic<uint64_t> attr_done{0};
+    if (!(attr_done.load(std::memory_order_acquire) >> (ctx->device & 63) & 1ull)) {
         FG_CUDA(ctx, FG_ERR_INTERNAL,
                 cudaFuncSetAttribute(gemm_tc_pair_kernel<BK, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-        attr_done |= 1ull << (ctx->device & 63);
+        attr_done.fetch_or(1ull << (ctx->device & 63), std::memory_order_release);
     }
     const uint64_t ntiles = (uint64_t)((ep.M + 2 * BM - 1) / (2 * BM)) * ((ep.N + Cfg::kBN - 1) / Cfg::kBN);
     if (ntiles > (1ull << 30)) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "GEMM: too many tiles");
     // persistent: one CTA pair per SM pair, each walking tiles pair, pair + P, ...
     // How many pairs can be resident at once is asked of the runtime (not every SM need be pairable).
-    static int max_clusters[64] = {0};
-    if (max_clusters[ctx->device & 63] == 0) {
+    static std::atomic<int> max_clusters[64];       // zero-initialised; the same value whoever computes it
+    if (max_clusters[ctx->device & 63].load(std::memory_order_acquire) == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)ctx->sm_count & ~1u);
         cfg.blockDim = dim3(kPairThreads);
@@ -1318,9 +1323,9 @@ int32_t launch_tc_pair(fg_ctx* ctx, const PlaneSet& a, const PlaneSet& b, const 
             cudaGetLastError();
             n = ctx->sm_count / 2;
         }
-        max_clusters[ctx->device & 63] = n;
+        max_clusters[ctx->device & 63].store(n, std::memory_order_release);
     }
-    uint64_t slots = (uint64_t)max_clusters[ctx->device & 63];
+    uint64_t slots = (uint64_t)max_clusters[ctx->device & 63].load(std::memory_order_acquire);
     if (ctx->comm_pending && ctx->comm_reserved_sms > 0) {
         // leave room for the gradient exchange that runs beside this GEMM (see fg_comm_init)
         const uint64_t lim = (uint64_t)(ctx->sm_count - ctx->comm_reserved_sms) / 2;
@@ -1934,16 +1939,53 @@ int32_t fg_gemm_bwd_paired_f32(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, 
 
 // Batched forms: `batch` independent products, operand t at base + t*stride (strides in elements).
 // The reference steps A, B and C by one matrix per Z index of a rank-3 matmul (kernel/forward.rs:159-190).
+// Rank-3 products.  Small matrices (the SIMT path's range) run as ONE launch with the matrix index in the grid's
+// z, as the reference's generated kernel does (kernel/forward.rs:159-190).  Larger ones use the tensor cores: the
+// bf16 pairs of the whole batch are made by one pass per operand, then one GEMM launch per matrix reads its slice
+// (batch + 2 launches, and a launch that fills the GPU gains nothing from being merged with its neighbours).
 int32_t fg_gemm_batched_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t M, uint32_t N, uint32_t K, const float* A,
                             uint64_t strideA, const float* B, uint64_t strideB, float* C, uint64_t strideC,
                             const float* bias, int32_t act, float* preact_out) {
-    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, A && B && C, "fg_gemm_batched_f32: NULL pointer");
+    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_batched_f32: unknown activation");
     FG_REQUIRE(ctx, strideA >= (uint64_t)M * K && strideB >= (uint64_t)K * N && strideC >= (uint64_t)M * N,
                "fg_gemm_batched_f32: a stride is smaller than its matrix (for one B shared by all products, "
                "call fg_gemm_f32 with batch*M rows)");
+    if (batch == 0 || (uint64_t)M * N == 0) return FG_OK;
+    if (pick_path(ctx, mode, M, N, K) == 0 && batch <= 65535 && K > 0)
+        return fg_gemm_simt_batched_launch(ctx, 0, 0, batch, M, N, K, A, strideA, B, strideB, C, strideC, bias, act, preact_out);
+    const bool dense = strideA == (uint64_t)M * K && strideB == (uint64_t)K * N;
+    // the condition under which every per-matrix call below takes the path that reads pairs
+    const bool shared_pairs = dense && mode == FG_GEMM_AUTO && N > 16 && N % 4 == 0 && strideC % 4 == 0 && fg_aligned16(A) &&
+                              fg_aligned16(B) && fg_aligned16(C) && (!preact_out || fg_aligned16(preact_out)) &&
+                              paired_shape_ok(ctx, M, N, K, K, N);
+    __nv_bfloat16 *pa = nullptr, *pb = nullptr;
+    const uint64_t na = (uint64_t)batch * M * K, nb = (uint64_t)batch * K * N;
+    if (shared_pairs) {
+        void* p;
+        int32_t s = fg_ws_ensure(ctx, (na + nb) * 4 + 2 * kPairPartialBytes + 8192);
+        if (s != FG_OK) return s;
+        if ((s = fg_ws_alloc(ctx, na * 4, &p)) != FG_OK) return s;
+        pa = (__nv_bfloat16*)p;
+        if ((s = fg_ws_alloc(ctx, nb * 4, &p)) != FG_OK) return s;
+        pb = (__nv_bfloat16*)p;
+        if ((s = launch_pairs(ctx, A, na, pa, na)) != FG_OK) return s;
+        if ((s = launch_pairs(ctx, B, nb, pb, nb)) != FG_OK) return s;
+    }
     for (uint32_t t = 0; t < batch; ++t) {
-        int32_t s = fg_gemm_f32(ctx, mode, 0, 0, M, N, K, A + t * strideA, B + t * strideB, C + t * strideC, bias, act,
-                                preact_out ? preact_out + t * strideC : nullptr);
+        int32_t s;
+        if (shared_pairs) {
+            // carve nothing more from the arena: the slices above stay valid for every matrix
+            const uint64_t keep = ctx->ws_used;
+            s = gemm_fwd_core(ctx, mode, 0, 0, M, N, K, PairedArg{A + t * strideA, pa + t * strideA, na},
+                              PairedArg{B + t * strideB, pb + t * strideB, nb}, C + t * strideC, bias, act,
+                              preact_out ? preact_out + t * strideC : nullptr, nullptr, 0);
+            ctx->ws_used = keep;
+        } else {
+            s = fg_gemm_f32(ctx, mode, 0, 0, M, N, K, A + t * strideA, B + t * strideB, C + t * strideC, bias, act,
+                            preact_out ? preact_out + t * strideC : nullptr);
+        }
         if (s != FG_OK) return s;
     }
     return FG_OK;
@@ -1952,9 +1994,33 @@ int32_t fg_gemm_batched_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t 
 int32_t fg_gemm_batched_bwd_f32(fg_ctx* ctx, int32_t mode, uint32_t batch, uint32_t M, uint32_t N, uint32_t K,
                                 const float* A, uint64_t strideA, const float* B, uint64_t strideB, const float* dY,
                                 uint64_t strideC, int32_t act, const float* saved, float* dA, float* dB) {
-    if (!ctx) return FG_ERR_NOT_INITIALIZED;
+    FG_ENTER(ctx);
+    FG_REQUIRE(ctx, dY != nullptr, "fg_gemm_batched_bwd_f32: dY is NULL");
+    FG_REQUIRE(ctx, act >= FG_ACT_NONE && act <= FG_ACT_GELU, "fg_gemm_batched_bwd_f32: unknown activation");
+    FG_REQUIRE(ctx, act == FG_ACT_NONE || saved, "fg_gemm_batched_bwd_f32: saved tensor required");
+    FG_REQUIRE(ctx, (!dA || B) && (!dB || A), "fg_gemm_batched_bwd_f32: dA needs B, dB needs A");
     FG_REQUIRE(ctx, strideA >= (uint64_t)M * K && strideB >= (uint64_t)K * N && strideC >= (uint64_t)M * N,
                "fg_gemm_batched_bwd_f32: a stride is smaller than its matrix");
+    if (batch == 0 || (uint64_t)M * N == 0 || (!dA && !dB)) return FG_OK;
+    if (pick_path(ctx, mode, M, N, K) == 0 && batch <= 65535 && strideC == (uint64_t)M * N) {
+        // three launches for the whole batch: dZ = dY * act'(saved), dB[t] = A[t]^T dZ[t], dA[t] = dZ[t] B[t]^T
+        const float* dz = dY;
+        if (act != FG_ACT_NONE) {
+            const uint64_t n = (uint64_t)batch * M * N;
+            void* p;
+            int32_t s = fg_ws_ensure(ctx, n * 4 + 512);
+            if (s != FG_OK) return s;
+            if ((s = fg_ws_alloc(ctx, n * 4, &p)) != FG_OK) return s;
+            if ((s = fg_act_bwd_launch(ctx, n, act, dY, saved, (float*)p)) != FG_OK) return s;
+            dz = (const float*)p;
+        }
+        int32_t s;
+        if (dB && (s = fg_gemm_simt_batched_launch(ctx, 1, 0, batch, K, N, M, A, strideA, dz, strideC, dB, strideB, nullptr,
+                                                   FG_ACT_NONE, nullptr)) != FG_OK) return s;
+        if (dA && (s = fg_gemm_simt_batched_launch(ctx, 0, 1, batch, M, K, N, dz, strideC, B, strideB, dA, strideA, nullptr,
+                                                   FG_ACT_NONE, nullptr)) != FG_OK) return s;
+        return FG_OK;
+    }
     for (uint32_t t = 0; t < batch; ++t) {
         int32_t s = fg_gemm_bwd_f32(ctx, mode, M, N, K, A ? A + t * strideA : nullptr, B ? B + t * strideB : nullptr,
                                     dY + t * strideC, act, saved ? saved + t * strideC : nullptr,

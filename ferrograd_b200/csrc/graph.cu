@@ -1053,6 +1053,7 @@ static int32_t run_planned(fg_exec* e, int which, const void* key, const std::fu
 
 int32_t fg_exec_dispatch_forward(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
+    FgRange range("ferrograd dispatch_forward");
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_forward: bind the input tensors first");
     if (e->paired) {
         // A recorded forward pass does not contain the pairs of the weights (the optimizer keeps them current).
@@ -1071,6 +1072,7 @@ int32_t fg_exec_dispatch_forward(fg_exec* e) {
 
 int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
+    FgRange range("ferrograd dispatch_loss");
     FG_REQUIRE(e->ctx, target != nullptr, "dispatch_loss: target is NULL");
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_loss: bind the input tensors first");
     return run_planned(e, 1, target->ptr, [&] { return loss_eager(e, target); });
@@ -1078,6 +1080,7 @@ int32_t fg_exec_dispatch_loss(fg_exec* e, const fg_buf* target) {
 
 int32_t fg_exec_dispatch_backward(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
+    FgRange range("ferrograd dispatch_backward");
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_backward: bind the input tensors first");
     const int32_t s = run_planned(e, 2, nullptr, [&] { return backward_eager(e); });
     if (s == FG_OK) e->backward_done = true;
@@ -1086,6 +1089,7 @@ int32_t fg_exec_dispatch_backward(fg_exec* e) {
 
 int32_t fg_exec_dispatch_optim(fg_exec* e) {
     if (!e) return FG_ERR_NOT_INITIALIZED;
+    FgRange range("ferrograd dispatch_optim");
     if (!e->bound) return fail(e, FG_ERR_NOT_INITIALIZED, "dispatch_optim: bind the input tensors first");
     // With a communicator, the range of the gradient arena that is still to be summed over the ranks depends on
     // whether a backward pass came before (it has exchanged everything below final_lo already); a recorded

@@ -17,6 +17,8 @@
 //     for the row sizes it is used for).
 #include <math_constants.h>
 
+#include <atomic>
+
 #include "fg_internal.cuh"
 
 namespace {
@@ -408,11 +410,11 @@ int32_t launch_rows(fg_ctx* ctx, const CeArgs& a) {
                                 : ((!a.dlogits || fg_aligned16(a.dlogits)) && (!a.probs || fg_aligned16(a.probs))));
     const size_t smem = (size_t)a.cols * 4;
     if (vec && a.cols >= 8192 && a.cols <= (uint32_t)(kRowT * kRowNV * 4) && smem <= 200 * 1024) {
-        static uint64_t attr_done = 0;   // one bit per device (static per MODE instantiation)
-        if (!(attr_done >> (ctx->device & 63) & 1ull)) {
+        static std::atomic<uint64_t> attr_done{0};   // one bit per device (static per MODE instantiation)
+        if (!(attr_done.load(std::memory_order_acquire) >> (ctx->device & 63) & 1ull)) {
             FG_CUDA(ctx, FG_ERR_INTERNAL,
                     cudaFuncSetAttribute(softmax_rowreg_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            attr_done |= 1ull << (ctx->device & 63);
+            attr_done.fetch_or(1ull << (ctx->device & 63), std::memory_order_release);
         }
         int grid = (int)(a.rows < (uint32_t)ctx->sm_count ? a.rows : (uint32_t)ctx->sm_count);
         fg_time_rec* tr = MODE == 1 ? fg_time_begin(ctx, FG_KERNEL_SOFTMAX_CE, ce_bytes(a)) : nullptr;

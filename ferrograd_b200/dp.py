@@ -8,7 +8,7 @@ replicated, and sums gradients once per step.
 """
 import numpy as np
 
-# BASELINE configurations that train an MLP.  `batch` is per GPU (weak scaling).
+# Benchmark workloads that train an MLP.  `batch` is per GPU (weak scaling).
 WORKLOADS = {
     "c1": dict(name="C1: MLP 2-16-2 tanh, MSE, SGD lr 0.1, batch 64", dims=[2, 16, 2], batch=64, act="tanh",
                loss="mse", opt=("sgd", 0.1), init="xavier_uniform", seed=0, steps=1000),

@@ -125,7 +125,11 @@ enum fg_kernel_kind {
     FG_KERNEL_SOFTMAX_CE = 1, /* work = 2*rows*cols*4 bytes (+probs)       */
     FG_KERNEL_ADAMW = 2,      /* work = 28 (or 32 with zero_grad) bytes/param */
     FG_KERNEL_SGD = 3,        /* work = 12 (or 16 with zero_grad) bytes/param */
-    FG_KERNEL_SPLIT = 4       /* work = bytes read + written by the operand pre-pass */
+    FG_KERNEL_SPLIT = 4,      /* work = bytes read + written by the operand pre-pass */
+    FG_KERNEL_ELTWISE = 5,    /* bias+activation, activation backward, MSE/BCE, chains, conversions:
+                                 work = bytes of the tensors read + written, each once */
+    FG_KERNEL_SKINNY = 6      /* GEMMs with N <= 16: work = bytes of the large operand (and of the outputs
+                                 that are as large) moved once */
 };
 int32_t fg_ctx_timing_enable(fg_ctx* ctx, int32_t on);
 int32_t fg_ctx_timing_read(fg_ctx* ctx, int32_t kind, uint64_t* launches, double* total_ms,

@@ -1,4 +1,4 @@
-"""BASELINE configurations 2 and 3 at their full sizes, checked through size-independent
+"""The softmax-CE (8192 x 32000) and GEMM (8192^3) benchmark workloads at their full sizes, checked through size-independent
 properties plus sampled rows against the CPU oracle; and the edge cases of the C ABI (empty and
 degenerate inputs)."""
 import numpy as np

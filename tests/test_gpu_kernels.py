@@ -684,6 +684,52 @@ def test_gemm_batched(ctx, oracle, mode):
         ctx.gemm_batched(up(ctx, A), up(ctx, B), Cd, T, M, N, K, strides=(M * K, 0, M * N))
 
 
+def test_gemm_batched_small_matrices_run_as_one_launch(ctx, oracle):
+    # 64 small products: one launch with the matrix index in the grid (forward), three launches for the backward
+    # pass (dY * act', dB, dA); the exact path, so the results equal the oracle's sequential fma chain bit for bit
+    T, M, N, K = 64, 24, 40, 56
+    r = rng(2718)
+    A, B = r.standard_normal((T, M, K), np.float32), r.standard_normal((T, K, N), np.float32)
+    bias, dY = r.standard_normal(N, np.float32), r.standard_normal((T, M, N), np.float32)
+    Ad, Bd, Cd, Pd = up(ctx, A), up(ctx, B), ctx.new_tensor((T, M, N)), ctx.new_tensor((T, M, N))
+    ctx.sync()
+    before = ctx.launch_count()
+    ctx.gemm_batched(Ad, Bd, Cd, T, M, N, K, bias=up(ctx, bias), act="relu", preact_out=Pd)
+    assert ctx.launch_count() - before == 1
+    got, pre = ctx.to_numpy(Cd), ctx.to_numpy(Pd)
+    dA, dB = ctx.new_tensor((T, M, K)), ctx.new_tensor((T, K, N))
+    before = ctx.launch_count()
+    ctx.gemm_batched_bwd(Ad, Bd, up(ctx, dY), T, M, N, K, act="relu", saved=Cd, dA=dA, dB=dB)
+    assert ctx.launch_count() - before == 3
+    gA, gB = ctx.to_numpy(dA), ctx.to_numpy(dB)
+    for t in range(T):
+        z = oracle.gemm(A[t], B[t])
+        y, p = oracle.bias_act_fwd(z, bias, "relu")
+        assert np.array_equal(got[t], y) and np.array_equal(pre[t], p), t
+        dz = oracle.act_bwd(dY[t], y, "relu")
+        assert np.array_equal(gA[t], oracle.gemm(dz, B[t], transB=True)), t
+        assert np.array_equal(gB[t], oracle.gemm(A[t], dz, transA=True)), t
+
+
+def test_gemm_batched_large_matrices_share_one_pairs_pass(ctx, oracle):
+    # tensor-core sized products: the bf16 pairs of both operands are made once for the whole batch
+    # (two launches), then one GEMM launch (+ its split-K fold, if any) per matrix
+    T, M, N, K = 3, 512, 384, 256
+    r = rng(1618)
+    A, B = r.standard_normal((T, M, K), np.float32), r.standard_normal((T, K, N), np.float32) * 0.1
+    bias = r.standard_normal(N, np.float32)
+    Cd = ctx.new_tensor((T, M, N))
+    Ad, Bd, bd = up(ctx, A), up(ctx, B), up(ctx, bias)
+    ctx.sync()
+    before = ctx.launch_count()
+    ctx.gemm_batched(Ad, Bd, Cd, T, M, N, K, bias=bd, act="gelu")
+    assert ctx.launch_count() - before <= 2 + 2 * T
+    got = ctx.to_numpy(Cd)
+    for t in range(T):
+        y, _ = oracle.bias_act_fwd(oracle.gemm(A[t], B[t]), bias, "gelu")
+        check(got[t], y, TOL_GEMM, f"batched output {t}")
+
+
 @pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_reference_matmul_known_answers(ctx, mode):
     # crates/ferrograd/tests/std_wgsl.rs:268-373 (matmul_add) and :376-520 (matmul_chain3): constant

@@ -96,7 +96,7 @@ def run_case(ctx, oracle, dims, batch, act, loss, opt, init, steps, mode, tol=TO
 
 
 def test_c1_tiny_mlp_1000_steps(ctx, oracle):
-    # BASELINE config 1: 2 -> 16 -> 2, tanh, MSE, SGD lr 0.1, batch 64, 1000 steps.
+    # Benchmark workload C1 (the reference's own CPU-scale case): 2 -> 16 -> 2, tanh, MSE, SGD lr 0.1, batch 64, 1000 steps.
     from ferrograd_b200 import dp
     w = dp.WORKLOADS["c1"]
     from ferrograd_b200.mlp import MLPTrainer
@@ -128,7 +128,7 @@ def test_c1_tiny_mlp_1000_steps(ctx, oracle):
 
 @pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_c4_reduced(ctx, oracle, mode):
-    # BASELINE config 4 at reduced width: GELU hidden layers, softmax-CE, AdamW.
+    # Benchmark workload C4 at reduced width: GELU hidden layers, softmax-CE, AdamW.
     opt = ("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01)
     tr, W, b, drift = run_case(ctx, oracle, [784, 256, 320, 10], 512, "gelu", "ce", opt, "he_normal", 5, mode)
     assert max(drift) < 1e-4, f"loss drift over 5 steps: {drift}"
@@ -136,7 +136,7 @@ def test_c4_reduced(ctx, oracle, mode):
 
 @pytest.mark.parametrize("mode", ["simt", "3xtf32", "tf32_bf16x2"])
 def test_c5_reduced(ctx, oracle, mode):
-    # BASELINE config 5 at reduced width/depth: tanh, MSE, AdamW.
+    # Benchmark workload C5 at reduced width/depth: tanh, MSE, AdamW.
     opt = ("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01)
     tr, W, b, drift = run_case(ctx, oracle, [512] * 5, 256, "tanh", "mse", opt, "normal_fan_in", 3, mode)
     assert max(drift) < 1e-4, f"loss drift over 3 steps: {drift}"
@@ -148,11 +148,21 @@ def test_relu_sgd_odd_shapes(ctx, oracle):
 
 
 def test_c4_full_size_one_step(ctx, oracle):
-    # BASELINE config 4 at its real size: 784 -> 4096 -> 4096 -> 10, batch 4096, one step.
+    # Benchmark workload C4 at its real size: 784 -> 4096 -> 4096 -> 10, batch 4096, one step.
     from ferrograd_b200 import dp
     w = dp.WORKLOADS["c4"]
     tr, W, b, drift = run_case(ctx, oracle, w["dims"], w["batch"], w["act"], w["loss"], w["opt"], w["init"], 1, "auto")
     assert drift[0] < 1e-5
+
+
+def test_c5_full_size_one_step(ctx, oracle):
+    # Benchmark workload C5 at its real size: eight 8192 x 8192 layers, tanh, MSE, AdamW, batch 2048, one step
+    # (6.6 TFLOP in the oracle: about a minute of host time).
+    from ferrograd_b200 import dp
+    w = dp.WORKLOADS["c5"]
+    tr, W, b, drift = run_case(ctx, oracle, w["dims"], w["batch"], w["act"], w["loss"], w["opt"], w["init"], 1, "auto")
+    assert drift[0] < 1e-5
+    tr.destroy()
 
 
 def test_plan_replay_matches_eager(ctx, oracle):
