@@ -10,6 +10,8 @@
 // (crates/fused_gpu/src/dispatch/backend/kernel/forward.rs:298-464); a chain here is the
 // same idea with the program interpreted per element: every input is read once, every
 // output written once.
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -252,127 +254,218 @@ struct ChainArgs {
     const void* seed;
     void* out;
     int ninstr, ninputs, accumulate, vec;
+    uint32_t keep;                  // forward: bit k set = value k is read by an instruction other than k + 1
     uint64_t n;
 };
 
-// One instruction on one element.
-template <int DT>
-__device__ __forceinline__ float ew_op(int op, float imm, float x, float y) {
+// One instruction on W elements: the op-code is decoded once, the lanes loop inside each case.
+#define FG_EW_LANES(expr)                      \
+    do {                                       \
+        _Pragma("unroll") for (int w = 0; w < W; ++w) { const float xx = x[w], yy = y[w]; (void)yy; r[w] = (expr); } \
+    } while (0)
+template <int DT, int W>
+__device__ __forceinline__ void ew_op(int op, float imm, const float* x, const float* y, float* r) {
     typedef Stored<DT> S;
     switch (op) {
-        case FG_EW_CONST: return S::r(imm);
-        case FG_EW_ADD: return S::r(x + y);
-        case FG_EW_SUB: return S::r(x - y);
-        case FG_EW_MUL: return S::r(x * y);
-        case FG_EW_DIV: return S::r(__fdiv_rn(x, y));
-        case FG_EW_NEG: return -x;
-        case FG_EW_ABS: return fabsf(x);
-        case FG_EW_EXP: return S::r(expf(x));
-        case FG_EW_LOG: return S::r(logf(x));
-        case FG_EW_TANH: return S::r(tanhf(x));
-        case FG_EW_RELU: return x > 0.0f ? x : 0.0f;
-        case FG_EW_GELU: return S::r(fg_gelu_fwd(x, nullptr));
-        case FG_EW_ELU: return x >= 0.0f ? x : S::r(expf(x) - 1.0f);
-        default: return 0.0f;
+        case FG_EW_CONST: FG_EW_LANES(((void)xx, S::r(imm))); break;
+        case FG_EW_ADD: FG_EW_LANES(S::r(xx + yy)); break;
+        case FG_EW_SUB: FG_EW_LANES(S::r(xx - yy)); break;
+        case FG_EW_MUL: FG_EW_LANES(S::r(xx * yy)); break;
+        case FG_EW_DIV: FG_EW_LANES(S::r(__fdiv_rn(xx, yy))); break;
+        case FG_EW_NEG: FG_EW_LANES(-xx); break;
+        case FG_EW_ABS: FG_EW_LANES(fabsf(xx)); break;
+        case FG_EW_EXP: FG_EW_LANES(S::r(expf(xx))); break;
+        case FG_EW_LOG: FG_EW_LANES(S::r(logf(xx))); break;
+        case FG_EW_TANH: FG_EW_LANES(S::r(tanhf(xx))); break;
+        case FG_EW_RELU: FG_EW_LANES(xx > 0.0f ? xx : 0.0f); break;
+        case FG_EW_GELU: FG_EW_LANES(S::r(fg_gelu_fwd(xx, nullptr))); break;
+        case FG_EW_ELU: FG_EW_LANES(xx >= 0.0f ? xx : S::r(expf(xx) - 1.0f)); break;
+        default: FG_EW_LANES(((void)xx, 0.0f)); break;
     }
 }
+#undef FG_EW_LANES
 
-// The program on W consecutive elements starting at i: the decode of an instruction is shared by the W lanes.
+// Where a chain's intermediate values live.  A program is only known at run time, so its values cannot be
+// named registers; as a per-thread array they would sit in local memory (with four lanes per thread the arrays
+// overflowed the L1 and the backward kernel ran at a tenth of the HBM rate).  They live in shared memory
+// instead: slot s, lane w of thread t is word (s * W + w) * 256 + t, so a warp's access to one slot is 32
+// consecutive words.  The value of the previous instruction is also kept in registers, which serves the common
+// "operand = the instruction just before" without a shared-memory read.
+template <int W> struct Slots {
+    float* base;   // this thread's word of slot 0, lane 0
+    __device__ __forceinline__ void ld(int slot, float* o) const {
+#pragma unroll
+        for (int w = 0; w < W; ++w) o[w] = base[(slot * W + w) * 256];
+    }
+    __device__ __forceinline__ void st(int slot, const float* v) const {
+#pragma unroll
+        for (int w = 0; w < W; ++w) base[(slot * W + w) * 256] = v[w];
+    }
+};
+
+__device__ __forceinline__ bool ew_two_operands(int op) { return op >= FG_EW_ADD && op <= FG_EW_DIV; }
+
+// The program on W consecutive elements starting at i; the decode of an instruction is shared by the W lanes.
+// On return `last` holds the value of the final instruction; values are stored to their slots when store_all is
+// set (the backward pass needs them) or when a later instruction other than the next one reads them.
 template <int DT, int W>
-__device__ __forceinline__ void ew_forward(const ChainArgs& a, uint64_t i, float (*v)[W]) {
+__device__ __forceinline__ void ew_forward(const ChainArgs& a, uint64_t i, const Slots<W>& v, bool store_all, bool write_saved,
+                                           float* last) {
     for (int k = 0; k < a.ninstr; ++k) {
         const fg_ew_instr in = a.prog[k];
+        float r[W];
         if (in.op == FG_EW_INPUT) {
-            ldw<DT, W>(a.in[in.a], i, v[k]);
+            ldw<DT, W>(a.in[in.a], i, r);
         } else {
-            const int ia = in.op == FG_EW_CONST ? 0 : in.a, ib = (in.op >= FG_EW_ADD && in.op <= FG_EW_DIV) ? in.b : ia;
+            float x[W], y[W];
 #pragma unroll
-            for (int w = 0; w < W; ++w) v[k][w] = ew_op<DT>(in.op, in.imm, v[ia][w], v[ib][w]);
+            for (int w = 0; w < W; ++w) x[w] = y[w] = 0.0f;
+            if (in.op != FG_EW_CONST) {
+                if (in.a == k - 1) {
+#pragma unroll
+                    for (int w = 0; w < W; ++w) x[w] = last[w];
+                } else {
+                    v.ld(in.a, x);
+                }
+                if (ew_two_operands(in.op)) {
+                    if (in.b == k - 1) {
+#pragma unroll
+                        for (int w = 0; w < W; ++w) y[w] = last[w];
+                    } else if (in.b == in.a) {
+#pragma unroll
+                        for (int w = 0; w < W; ++w) y[w] = x[w];
+                    } else {
+                        v.ld(in.b, y);
+                    }
+                }
+            }
+            ew_op<DT, W>(in.op, in.imm, x, y, r);
         }
+        if (store_all || (a.keep >> k & 1u)) v.st(k, r);
+        if (write_saved && a.saved[k]) stw<DT, W>(a.saved[k], i, r);
+#pragma unroll
+        for (int w = 0; w < W; ++w) last[w] = r[w];
     }
 }
 
 template <int DT, int W>
-__device__ __forceinline__ void chain_fwd_at(const ChainArgs& a, uint64_t i) {
-    float v[FG_EW_MAX_INSTR][W];
-    ew_forward<DT, W>(a, i, v);
-    for (int k = 0; k < a.ninstr; ++k)
-        if (a.saved[k]) stw<DT, W>(a.saved[k], i, v[k]);
-    stw<DT, W>(a.out, i, v[a.ninstr - 1]);
+__device__ __forceinline__ void chain_fwd_at(const ChainArgs& a, uint64_t i, float* smem) {
+    const Slots<W> v{smem + threadIdx.x};
+    float last[W];
+    ew_forward<DT, W>(a, i, v, false, true, last);
+    stw<DT, W>(a.out, i, last);
 }
 
 template <int DT>
 __global__ void __launch_bounds__(256) chain_fwd_kernel(const __grid_constant__ ChainArgs a) {
+    extern __shared__ float chain_smem[];
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t nv = a.vec ? a.n >> 2 : 0;
-    for (uint64_t i = g; i < nv; i += stride) chain_fwd_at<DT, 4>(a, i << 2);
-    for (uint64_t i = (nv << 2) + g; i < a.n; i += stride) chain_fwd_at<DT, 1>(a, i);
+    for (uint64_t i = g; i < nv; i += stride) chain_fwd_at<DT, 4>(a, i << 2, chain_smem);
+    for (uint64_t i = (nv << 2) + g; i < a.n; i += stride) chain_fwd_at<DT, 1>(a, i, chain_smem);
 }
 
-// Adjoint of one instruction on one element: adds to the adjoints of its operands.
-template <int DT>
-__device__ __forceinline__ void ew_adjoint(int op, float g, float va, float vb, float vk, float& ga, float& gb) {
+// Adjoint of one instruction on W elements: adds to the adjoints of its operands.  ga and gb may be one and the
+// same array (x * x): the two updates then apply in order, as they would on one array element.
+#define FG_EW_LANES(stmt)                                                                          \
+    do {                                                                                           \
+        _Pragma("unroll") for (int w = 0; w < W; ++w) {                                            \
+            const float g = gk[w], a_ = va[w], b_ = vb[w], k_ = vk[w];                             \
+            (void)a_; (void)b_; (void)k_;                                                          \
+            stmt;                                                                                  \
+        }                                                                                          \
+    } while (0)
+template <int DT, int W>
+__device__ __forceinline__ void ew_adjoint(int op, const float* gk, const float* va, const float* vb, const float* vk,
+                                           float* ga, float* gb) {
     typedef Stored<DT> S;
     switch (op) {
-        case FG_EW_ADD: ga = S::r(ga + g); gb = S::r(gb + g); break;
-        case FG_EW_SUB: ga = S::r(ga + g); gb = S::r(gb - g); break;
-        case FG_EW_MUL: ga = S::r(ga + S::r(g * vb)); gb = S::r(gb + S::r(g * va)); break;
-        case FG_EW_DIV: ga = S::r(ga + S::r(__fdiv_rn(g, vb)));
-                        gb = S::r(gb - S::r(__fdiv_rn(S::r(g * va), S::r(vb * vb)))); break;
-        case FG_EW_NEG: ga = S::r(ga - g); break;
-        case FG_EW_ABS: ga = S::r(ga + (va >= 0.0f ? g : -g)); break;
-        case FG_EW_EXP: ga = S::r(ga + S::r(g * vk)); break;
-        case FG_EW_LOG: ga = S::r(ga + S::r(__fdiv_rn(g, va))); break;
-        case FG_EW_TANH: ga = S::r(ga + S::r(g * S::r(1.0f - S::r(vk * vk)))); break;
-        case FG_EW_RELU: ga = S::r(ga + g * fg_act_grad(FG_ACT_RELU, vk)); break;
-        case FG_EW_GELU: ga = S::r(ga + S::r(g * S::r(fg_act_grad(FG_ACT_GELU, va)))); break;
-        case FG_EW_ELU: ga = S::r(ga + (vk >= 0.0f ? g : S::r(g * S::r(vk + 1.0f)))); break;
+        case FG_EW_ADD: FG_EW_LANES(ga[w] = S::r(ga[w] + g); gb[w] = S::r(gb[w] + g)); break;
+        case FG_EW_SUB: FG_EW_LANES(ga[w] = S::r(ga[w] + g); gb[w] = S::r(gb[w] - g)); break;
+        case FG_EW_MUL: FG_EW_LANES(ga[w] = S::r(ga[w] + S::r(g * b_)); gb[w] = S::r(gb[w] + S::r(g * a_))); break;
+        case FG_EW_DIV: FG_EW_LANES(ga[w] = S::r(ga[w] + S::r(__fdiv_rn(g, b_)));
+                                    gb[w] = S::r(gb[w] - S::r(__fdiv_rn(S::r(g * a_), S::r(b_ * b_))))); break;
+        case FG_EW_NEG: FG_EW_LANES(ga[w] = S::r(ga[w] - g)); break;
+        case FG_EW_ABS: FG_EW_LANES(ga[w] = S::r(ga[w] + (a_ >= 0.0f ? g : -g))); break;
+        case FG_EW_EXP: FG_EW_LANES(ga[w] = S::r(ga[w] + S::r(g * k_))); break;
+        case FG_EW_LOG: FG_EW_LANES(ga[w] = S::r(ga[w] + S::r(__fdiv_rn(g, a_)))); break;
+        case FG_EW_TANH: FG_EW_LANES(ga[w] = S::r(ga[w] + S::r(g * S::r(1.0f - S::r(k_ * k_))))); break;
+        case FG_EW_RELU: FG_EW_LANES(ga[w] = S::r(ga[w] + g * fg_act_grad(FG_ACT_RELU, k_))); break;
+        case FG_EW_GELU: FG_EW_LANES(ga[w] = S::r(ga[w] + S::r(g * S::r(fg_act_grad(FG_ACT_GELU, a_))))); break;
+        case FG_EW_ELU: FG_EW_LANES(ga[w] = S::r(ga[w] + (k_ >= 0.0f ? g : S::r(g * S::r(k_ + 1.0f))))); break;
         default: break;
     }
 }
+#undef FG_EW_LANES
 
+// Forward values in slots [0, ninstr), adjoints in slots [ninstr, 2 ninstr).  An adjoint slot that nothing has
+// added to yet counts as zero without being read (`touched`), so no slot is ever cleared.
 template <int DT, int W>
-__device__ __forceinline__ void chain_bwd_at(const ChainArgs& a, uint64_t i) {
+__device__ __forceinline__ void chain_bwd_at(const ChainArgs& a, uint64_t i, float* smem) {
     typedef Stored<DT> S;
-    float v[FG_EW_MAX_INSTR][W], adj[FG_EW_MAX_INSTR][W], gin[FG_EW_MAX_INPUTS][W];
-    ew_forward<DT, W>(a, i, v);
-    for (int k = 0; k < a.ninstr; ++k)
-#pragma unroll
-        for (int w = 0; w < W; ++w) adj[k][w] = 0.0f;
-    for (int k = 0; k < a.ninputs; ++k)
-#pragma unroll
-        for (int w = 0; w < W; ++w) gin[k][w] = 0.0f;
-    ldw<DT, W>(a.seed, i, adj[a.ninstr - 1]);
+    const Slots<W> v{smem + threadIdx.x};
+    const Slots<W> adj{smem + threadIdx.x + a.ninstr * W * 256};
+    float g[W];
+    ew_forward<DT, W>(a, i, v, true, false, g);
+    ldw<DT, W>(a.seed, i, g);
+    adj.st(a.ninstr - 1, g);
+    uint32_t touched = 1u << (a.ninstr - 1);
     for (int k = a.ninstr - 1; k >= 0; --k) {
         const fg_ew_instr in = a.prog[k];
-        if (in.op == FG_EW_INPUT) {
+        if (in.op == FG_EW_INPUT || in.op == FG_EW_CONST || !(touched >> k & 1u)) continue;   // nothing flows through
+        adj.ld(k, g);
+        const bool two = ew_two_operands(in.op);
+        const int ia = in.a, ib = two ? in.b : in.a;
+        const bool need_a = in.op == FG_EW_MUL || in.op == FG_EW_DIV || in.op == FG_EW_ABS || in.op == FG_EW_LOG ||
+                            in.op == FG_EW_GELU;
+        const bool need_k = in.op == FG_EW_EXP || in.op == FG_EW_TANH || in.op == FG_EW_RELU || in.op == FG_EW_ELU;
+        float va[W], vb[W], vk[W], ga[W], gb[W];
 #pragma unroll
-            for (int w = 0; w < W; ++w) gin[in.a][w] = S::r(gin[in.a][w] + adj[k][w]);
-        } else if (in.op != FG_EW_CONST) {
-            const int ia = in.a, ib = (in.op >= FG_EW_ADD && in.op <= FG_EW_DIV) ? in.b : in.a;
-#pragma unroll
-            for (int w = 0; w < W; ++w)   // the two adjoint slots may be one and the same (x * x): updated in order
-                ew_adjoint<DT>(in.op, adj[k][w], v[ia][w], v[ib][w], v[k][w], adj[ia][w], adj[ib][w]);
+        for (int w = 0; w < W; ++w) va[w] = vb[w] = vk[w] = ga[w] = gb[w] = 0.0f;
+        if (need_a) v.ld(ia, va);
+        if (need_a && two) v.ld(ib, vb);
+        if (need_k) v.ld(k, vk);
+        if (touched >> ia & 1u) adj.ld(ia, ga);
+        if (two && ib != ia) {
+            if (touched >> ib & 1u) adj.ld(ib, gb);
+            ew_adjoint<DT, W>(in.op, g, va, vb, vk, ga, gb);
+            adj.st(ib, gb);
+        } else if (two) {
+            ew_adjoint<DT, W>(in.op, g, va, vb, vk, ga, ga);
+        } else {
+            ew_adjoint<DT, W>(in.op, g, va, vb, vk, ga, gb);
         }
+        adj.st(ia, ga);
+        touched |= (1u << ia) | (1u << ib);
     }
-    for (int k = 0; k < a.ninputs; ++k) {
-        if (!a.grads[k]) continue;
-        if (a.accumulate) {
-            float old[W];
-            ldw<DT, W>(a.grads[k], i, old);
+    // the gradient of input j: the adjoints of the instructions that read it, from the last one down
+    for (int j = 0; j < a.ninputs; ++j) {
+        if (!a.grads[j]) continue;
+        float gin[W];
 #pragma unroll
-            for (int w = 0; w < W; ++w) gin[k][w] = S::r(old[w] + gin[k][w]);
+        for (int w = 0; w < W; ++w) gin[w] = 0.0f;
+        for (int k = a.ninstr - 1; k >= 0; --k) {
+            if (a.prog[k].op != FG_EW_INPUT || a.prog[k].a != j || !(touched >> k & 1u)) continue;
+            adj.ld(k, g);
+#pragma unroll
+            for (int w = 0; w < W; ++w) gin[w] = S::r(gin[w] + g[w]);
         }
-        stw<DT, W>(a.grads[k], i, gin[k]);
+        if (a.accumulate) {
+            ldw<DT, W>(a.grads[j], i, g);
+#pragma unroll
+            for (int w = 0; w < W; ++w) gin[w] = S::r(g[w] + gin[w]);
+        }
+        stw<DT, W>(a.grads[j], i, gin);
     }
 }
 
 template <int DT>
 __global__ void __launch_bounds__(256) chain_bwd_kernel(const __grid_constant__ ChainArgs a) {
+    extern __shared__ float chain_smem[];
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t nv = a.vec ? a.n >> 2 : 0;
-    for (uint64_t i = g; i < nv; i += stride) chain_bwd_at<DT, 4>(a, i << 2);
-    for (uint64_t i = (nv << 2) + g; i < a.n; i += stride) chain_bwd_at<DT, 1>(a, i);
+    for (uint64_t i = g; i < nv; i += stride) chain_bwd_at<DT, 4>(a, i << 2, chain_smem);
+    for (uint64_t i = (nv << 2) + g; i < a.n; i += stride) chain_bwd_at<DT, 1>(a, i, chain_smem);
 }
 
 // dst[i] = (type of dst) src[i], round to nearest even; four elements per access when both ends allow it
@@ -386,6 +479,34 @@ __global__ void __launch_bounds__(256) convert_kernel(const void* __restrict__ s
         Stored<DD>::st4w(dst, i << 2, v);
     }
     for (uint64_t i = (nv << 2) + g; i < n; i += stride) Stored<DD>::st(dst, i, Stored<DS>::ld(src, i));
+}
+
+// The chain kernels may need more than the default 48 KB of dynamic shared memory (24 instructions x four lanes:
+// 96 KB forward, 192 KB backward): the limit is raised once per device and kernel.
+constexpr int kChainSmemMax = 2 * FG_EW_MAX_INSTR * 4 * 256 * 4;
+int32_t chain_smem_attr(fg_ctx* ctx, int dtype, bool bwd) {
+    static std::atomic<uint64_t> done[6];
+    const int which = (bwd ? 3 : 0) + dtype;
+    const uint64_t bit = 1ull << (ctx->device & 63);
+    if (done[which].load(std::memory_order_acquire) & bit) return FG_OK;
+    cudaError_t e;
+    if (!bwd) {
+        e = dtype == FG_DTYPE_F32 ? cudaFuncSetAttribute(chain_fwd_kernel<FG_DTYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemMax / 2)
+          : dtype == FG_DTYPE_F16 ? cudaFuncSetAttribute(chain_fwd_kernel<FG_DTYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemMax / 2)
+                                  : cudaFuncSetAttribute(chain_fwd_kernel<FG_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemMax / 2);
+    } else {
+        e = dtype == FG_DTYPE_F32 ? cudaFuncSetAttribute(chain_bwd_kernel<FG_DTYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemMax)
+          : dtype == FG_DTYPE_F16 ? cudaFuncSetAttribute(chain_bwd_kernel<FG_DTYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemMax)
+                                  : cudaFuncSetAttribute(chain_bwd_kernel<FG_DTYPE_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kChainSmemMax);
+    }
+    if (e != cudaSuccess) return fg_fail_cuda(ctx, FG_ERR_INTERNAL, "cudaFuncSetAttribute(chain kernel)", e);
+    done[which].fetch_or(bit, std::memory_order_release);
+    return FG_OK;
+}
+// Resident CTAs per SM that the shared memory allows (of at most eight).
+int chain_ctas_per_sm(size_t smem) {
+    const size_t fit = (220u * 1024u) / (smem + 1024);
+    return (int)(fit < 1 ? 1 : fit > 8 ? 8 : fit);
 }
 
 int32_t check_prog(fg_ctx* ctx, const fg_ew_instr* prog, int32_t ninstr, int32_t ninputs) {
@@ -567,13 +688,22 @@ int32_t fg_eltwise_chain_fwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg
     for (int k = 0; k < ninputs; ++k) bits |= reinterpret_cast<uintptr_t>(a.in[k]);
     for (int k = 0; k < ninstr; ++k) bits |= reinterpret_cast<uintptr_t>(a.saved[k]);
     a.vec = (bits & mask) == 0;
-    int grid = fg_stream_grid(ctx, a.vec ? (n + 3) / 4 : n, 256, 8);
+    for (int k = 1; k < ninstr; ++k) {
+        const fg_ew_instr& in = prog[k];
+        if (in.op == FG_EW_INPUT || in.op == FG_EW_CONST) continue;
+        if (in.a != k - 1) a.keep |= 1u << in.a;
+        if (in.op >= FG_EW_ADD && in.op <= FG_EW_DIV && in.b != k - 1 && in.b != in.a) a.keep |= 1u << in.b;
+    }
+    const size_t smem = (size_t)ninstr * (a.vec ? 4 : 1) * 256 * sizeof(float);
+    int32_t st = chain_smem_attr(ctx, dtype, false);
+    if (st != FG_OK) return st;
+    int grid = fg_stream_grid(ctx, a.vec ? (n + 3) / 4 : n, 256, chain_ctas_per_sm(smem));
     int tensors = ninputs + 1;
     for (int k = 0; k < ninstr; ++k) tensors += a.saved[k] != nullptr;
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_ELTWISE, (dtype == FG_DTYPE_F32 ? 4.0 : 2.0) * tensors * n);
-    if (dtype == FG_DTYPE_F32) chain_fwd_kernel<FG_DTYPE_F32><<<grid, 256, 0, ctx->stream>>>(a);
-    else if (dtype == FG_DTYPE_F16) chain_fwd_kernel<FG_DTYPE_F16><<<grid, 256, 0, ctx->stream>>>(a);
-    else chain_fwd_kernel<FG_DTYPE_BF16><<<grid, 256, 0, ctx->stream>>>(a);
+    if (dtype == FG_DTYPE_F32) chain_fwd_kernel<FG_DTYPE_F32><<<grid, 256, smem, ctx->stream>>>(a);
+    else if (dtype == FG_DTYPE_F16) chain_fwd_kernel<FG_DTYPE_F16><<<grid, 256, smem, ctx->stream>>>(a);
+    else chain_fwd_kernel<FG_DTYPE_BF16><<<grid, 256, smem, ctx->stream>>>(a);
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
@@ -601,13 +731,16 @@ int32_t fg_eltwise_chain_bwd_dt(fg_ctx* ctx, int32_t dtype, uint64_t n, const fg
     uintptr_t bits = reinterpret_cast<uintptr_t>(seed);
     for (int k = 0; k < ninputs; ++k) bits |= reinterpret_cast<uintptr_t>(a.in[k]) | reinterpret_cast<uintptr_t>(a.grads[k]);
     a.vec = (bits & mask) == 0;
-    int grid = fg_stream_grid(ctx, a.vec ? (n + 3) / 4 : n, 256, 8);
+    const size_t smem = (size_t)2 * ninstr * (a.vec ? 4 : 1) * 256 * sizeof(float);
+    int32_t st = chain_smem_attr(ctx, dtype, true);
+    if (st != FG_OK) return st;
+    int grid = fg_stream_grid(ctx, a.vec ? (n + 3) / 4 : n, 256, chain_ctas_per_sm(smem));
     int tensors = ninputs + 1;
     for (int k = 0; k < ninputs; ++k) tensors += a.grads[k] ? 1 + (accumulate != 0) : 0;
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_ELTWISE, (dtype == FG_DTYPE_F32 ? 4.0 : 2.0) * tensors * n);
-    if (dtype == FG_DTYPE_F32) chain_bwd_kernel<FG_DTYPE_F32><<<grid, 256, 0, ctx->stream>>>(a);
-    else if (dtype == FG_DTYPE_F16) chain_bwd_kernel<FG_DTYPE_F16><<<grid, 256, 0, ctx->stream>>>(a);
-    else chain_bwd_kernel<FG_DTYPE_BF16><<<grid, 256, 0, ctx->stream>>>(a);
+    if (dtype == FG_DTYPE_F32) chain_bwd_kernel<FG_DTYPE_F32><<<grid, 256, smem, ctx->stream>>>(a);
+    else if (dtype == FG_DTYPE_F16) chain_bwd_kernel<FG_DTYPE_F16><<<grid, 256, smem, ctx->stream>>>(a);
+    else chain_bwd_kernel<FG_DTYPE_BF16><<<grid, 256, smem, ctx->stream>>>(a);
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;

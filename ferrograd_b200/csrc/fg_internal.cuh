@@ -287,8 +287,9 @@ int32_t fg_gemm_simt_batched_launch(fg_ctx* ctx, int transA, int transB, uint32_
 uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K);   // enough for any one skinny launch
 int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
                                 const float* bias, int act, float* preact_out);
-// Optional extras of the dA kernel: dA = (dZ·Bᵀ) * act'(mul_saved), its bf16 pairs, and the column sums of each
-// 32-row block ([ceil(M/32)][K], the partials of the bias gradient of the layer below).
+// Optional extras of the dA kernel: dA = (dZ·Bᵀ) * act'(mul_saved), its bf16 pairs, and partial column sums
+// (the partials of the bias gradient of the layer below): room for [ceil(M/32)][K]; the launch reports how many
+// rows it wrote.
 struct fg_skinny_extras {
     const float* mul_saved;
     int mul_act;
@@ -297,7 +298,7 @@ struct fg_skinny_extras {
     float* colsum_part;
 };
 int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N, const float* dZ, const float* B,
-                                 float* dA, const fg_skinny_extras* extras = nullptr);
+                                 float* dA, const fg_skinny_extras* extras = nullptr, uint32_t* colsum_rows = nullptr);
 int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t N, const float* A, const float* dZ,
                                  float* dB);
 int32_t fg_convert_launch(fg_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, uint64_t n);

@@ -128,11 +128,19 @@ __global__ void __launch_bounds__(256, 2) gemm_skinny_n_kernel(uint32_t M, uint3
 #pragma unroll
     for (int r = 0; r < 4; ++r) a[r] = A + (size_t)min(row0 + r, M - 1) * K;     // rows past the end are not stored
     if (VEC) {
-#pragma unroll 1
-        for (uint32_t k = (ks * 32 + lane) * 4; k < K; k += 512) {
-            float4 x[4];
+        // The rows of the next k-step are requested before the FMAs of this one, so that two steps' worth of
+        // loads (eight 16-byte loads per thread) are in flight: with 128 registers only 16 warps fit an SM, and
+        // one step's worth left the memory system half idle (long-scoreboard stalls, 29 % of the DRAM rate).
+        uint32_t k = (ks * 32 + lane) * 4;
+        float4 x[4], nx[4];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) x[r] = *reinterpret_cast<const float4*>(a[r] + k);
+        for (int r = 0; r < 4; ++r) x[r] = k < K ? __ldcs(reinterpret_cast<const float4*>(a[r] + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (; k < K; k += 512) {
+            const uint32_t kn = k + 512;
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                nx[r] = kn < K ? __ldcs(reinterpret_cast<const float4*>(a[r] + kn)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const float4 w = *reinterpret_cast<const float4*>(Bt + (size_t)n * Kp + k);
@@ -140,6 +148,8 @@ __global__ void __launch_bounds__(256, 2) gemm_skinny_n_kernel(uint32_t M, uint3
                 for (int r = 0; r < 4; ++r)
                     acc[r][n] = fmaf(x[r].w, w.w, fmaf(x[r].z, w.z, fmaf(x[r].y, w.y, fmaf(x[r].x, w.x, acc[r][n]))));
             }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) x[r] = nx[r];
         }
     } else {
 #pragma unroll 2
@@ -180,12 +190,94 @@ __global__ void __launch_bounds__(256, 2) gemm_skinny_n_kernel(uint32_t M, uint3
     }
 }
 
+// ---- forward, sliced: part[s][m][0..15] = sum over k-slice s of A[m][k] * B[k][n] ----
+// The kernel above fetches the transposed small operand through the L1 cache, where the streamed rows of A keep
+// evicting it (L1 hit rate 57 %: every miss is an L2 round trip in the middle of the FMA chain, and the kernel ran
+// at 29 % of the DRAM rate).  Here a block owns one 512-wide slice of k: the slice of B (NT x 512 floats) sits in
+// shared memory, transposed, for the whole block, and the block streams its rows' 2 KB segments of A past it.
+// A warp takes four rows at a time, all sixteen 16-byte loads in flight before the first FMA; a lane owns 16 of
+// the 512 k-values; the 4 x 16 partial sums meet by a halving exchange (62 shuffles, each lane ends with two sums).
+// The slices are added, in order, by skinny_fold_slices_kernel, which also applies bias and activation.
+constexpr int SK_SLICE = 512;
+
+template <int NT>
+__global__ void __launch_bounds__(256, 2) gemm_skinny_n_slice_kernel(uint32_t M, uint32_t N, uint32_t K, uint32_t rows_per_block,
+                                                                     const float* __restrict__ A, const float* __restrict__ B,
+                                                                     float* __restrict__ part) {
+    __shared__ __align__(16) float bt[NT][SK_SLICE];
+    const uint32_t k0 = blockIdx.x * SK_SLICE, kw = min((uint32_t)SK_SLICE, K - k0);
+    for (uint32_t e = threadIdx.x; e < NT * SK_SLICE; e += 256) (&bt[0][0])[e] = 0.0f;
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < kw * N; e += 256) bt[e % N][e / N] = B[(size_t)k0 * N + e];   // B as it lies: [k][n]
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t row_end = min(M, (blockIdx.y + 1) * rows_per_block);
+    for (uint32_t r0 = blockIdx.y * rows_per_block + warp * 4; r0 < row_end; r0 += 32) {
+        float4 x[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float* a = A + (size_t)min(r0 + r, M - 1) * K + k0;      // rows past the end are not stored
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t k = c * 128 + lane * 4;
+                x[r][c] = k < kw ? __ldcs(reinterpret_cast<const float4*>(a + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        float v[64];      // [row][16]: columns NT..15 stay zero
+#pragma unroll
+        for (int i = 0; i < 64; ++i) v[i] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const float4 w = *reinterpret_cast<const float4*>(&bt[n][c * 128 + lane * 4]);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    v[r * 16 + n] = fmaf(x[r][c].w, w.w, fmaf(x[r][c].z, w.z, fmaf(x[r][c].y, w.y, fmaf(x[r][c].x, w.x, v[r * 16 + n]))));
+            }
+        }
+        // halving exchange: at each step a lane keeps one half of its values and adds the partner's copy of them
+#pragma unroll
+        for (int step = 0; step < 5; ++step) {
+            const int off = 16 >> step, half = 32 >> step;
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < half; ++i) {
+                const float send = upper ? v[i] : v[i + half];
+                const float keep = upper ? v[i + half] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+        }
+        // lane bits (16, 8, 4, 2, 1) chose halves of 64, 32, 16, 8, 4: the lane holds values 2*lane' and 2*lane' + 1
+        const int idx = ((lane >> 4) & 1) * 32 + ((lane >> 3) & 1) * 16 + ((lane >> 2) & 1) * 8 + ((lane >> 1) & 1) * 4 + (lane & 1) * 2;
+        const uint32_t row = r0 + (idx >> 4);
+        if (row < row_end)
+            *reinterpret_cast<float2*>(part + ((size_t)blockIdx.x * M + row) * 16 + (idx & 15)) = make_float2(v[0], v[1]);
+    }
+}
+
+// C[m][n] = act(sum over slices of part[s][m][n] + bias[n]); optional copy of the pre-activation.
+__global__ void __launch_bounds__(256) skinny_fold_slices_kernel(uint32_t M, uint32_t N, uint32_t nslices,
+                                                                 const float* __restrict__ part, const float* __restrict__ bias,
+                                                                 int act, float* __restrict__ C, float* __restrict__ preact) {
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;      // over M x 16
+    if (i >= M * 16) return;
+    const uint32_t m = i >> 4, n = i & 15;
+    if (n >= N) return;
+    float z = 0.0f;
+    for (uint32_t s = 0; s < nslices; ++s) z += part[(size_t)s * M * 16 + i];
+    if (bias) z += bias[n];
+    const size_t o = (size_t)m * N + n;
+    if (preact) preact[o] = z;
+    C[o] = fg_act_fwd(act, z);
+}
+
 constexpr int TN_ROWS = 64;   // rows of A per partial sum in the dB kernel
 
-// part[chunk][j][n] = sum over the chunk's rows m of A[m][j] * dZ[m][n]   (A is [M, Kd], dZ is [M, N]).
+// part[chunk][n][j] = sum over the chunk's rows m of A[m][j] * dZ[m][n]   (A is [M, Kd], dZ is [M, N]).
 // A thread owns four consecutive j; the chunk's rows of dZ sit in shared memory and are broadcast.
 template <int NT, bool VEC>
-__global__ void __launch_bounds__(128) gemm_skinny_tn_partial_kernel(uint32_t M, uint32_t Kd, uint32_t N,
+__global__ void __launch_bounds__(128, 4) gemm_skinny_tn_partial_kernel(uint32_t M, uint32_t Kd, uint32_t N,
                                                                      const float* __restrict__ A,
                                                                      const float* __restrict__ dZ,
                                                                      float* __restrict__ part) {
@@ -204,19 +296,25 @@ __global__ void __launch_bounds__(128) gemm_skinny_tn_partial_kernel(uint32_t M,
 #pragma unroll
         for (int n = 0; n < NT; ++n) acc[q][n] = 0.0f;
     const float* a = A + (size_t)m0 * Kd + j0;
-    for (uint32_t r0 = 0; r0 < rows; r0 += 8) {
-        float x[8][4];
+    // Eight rows are multiplied while the next eight are on their way (16 loads of 16 bytes in flight per thread:
+    // with eight, and a grid that fills 70 % of the thread slots, the kernel ran at 23 % of the DRAM rate).
+    float x[8][4], nx[8][4];
+    auto fetch = [&](uint32_t r0, float (*dst)[4]) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const uint32_t r = min(r0 + u, rows - 1);     // rows past the end reload the last one; their dZ is zero
             if (VEC) {
-                const float4 t = *reinterpret_cast<const float4*>(a + (size_t)r * Kd);
-                x[u][0] = t.x; x[u][1] = t.y; x[u][2] = t.z; x[u][3] = t.w;
+                const float4 t = __ldcs(reinterpret_cast<const float4*>(a + (size_t)r * Kd));
+                dst[u][0] = t.x; dst[u][1] = t.y; dst[u][2] = t.z; dst[u][3] = t.w;
             } else {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) x[u][q] = (j0 + q < Kd) ? a[(size_t)r * Kd + q] : 0.0f;
+                for (int q = 0; q < 4; ++q) dst[u][q] = (j0 + q < Kd) ? a[(size_t)r * Kd + q] : 0.0f;
             }
         }
+    };
+    fetch(0, x);
+    for (uint32_t r0 = 0; r0 < rows; r0 += 8) {
+        if (r0 + 8 < rows) fetch(r0 + 8, nx);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (r0 + u < rows) {
@@ -228,35 +326,44 @@ __global__ void __launch_bounds__(128) gemm_skinny_tn_partial_kernel(uint32_t M,
                 }
             }
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) x[u][q] = nx[u][q];
     }
+    // part[chunk][n][j]: for one n a thread's four j are one 16-byte store and a warp's are 512 contiguous bytes
+    // (as [chunk][j][n] every store instruction touched 32 sectors, and 10 MB of partials cost more L2 write
+    // bandwidth than the 67 MB read cost DRAM bandwidth)
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        if (j0 + q < Kd) {
-            float* p = part + ((size_t)blockIdx.y * Kd + j0 + q) * N;
+    for (int n = 0; n < NT; ++n) {
+        if (n >= (int)N) break;
+        float* p = part + ((size_t)blockIdx.y * N + n) * Kd + j0;
+        if (VEC) {
+            *reinterpret_cast<float4*>(p) = make_float4(acc[0][n], acc[1][n], acc[2][n], acc[3][n]);
+        } else {
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
-                if (n < (int)N) p[n] = acc[q][n];
+            for (int q = 0; q < 4; ++q)
+                if (j0 + q < Kd) p[q] = acc[q][n];
         }
     }
 }
 
 // dA[m][k] = sum_n dZ[m][n] * B[k][n]   (dZ is [M, N], B is [K, N]): bound by writing dA once.
-// A thread owns four consecutive k and keeps their rows of B in registers while it walks 32 rows of dZ.
+// A thread owns four consecutive k and keeps their rows of B in registers; a block walks 8-row chunks of dZ
+// (chunk = blockIdx.y, + gridDim.y, ...: the grid is sized to the SMs' thread slots, so every block has the
+// same number of chunks to within one).
 // With extras: the product is multiplied by act'(mul_saved) (the layer below's backward factor), its bf16
-// pairs are written beside it, and the thread's own column sums over the 32 rows go to colsum_part.
+// pairs are written beside it, and the thread's column sums over all of the block's rows go to
+// colsum_part[blockIdx.y][k] (the partials of the bias gradient of the layer below).
+constexpr int NT_ROWS = 8;
+
 template <int NT>
 __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_t K, uint32_t N,
                                                              const float* __restrict__ dZ, const float* __restrict__ B,
                                                              float* __restrict__ dA, fg_skinny_extras ex) {
-    __shared__ float zs[32][NT];
-    const uint32_t m0 = blockIdx.y * 32, rows = min(32u, M - m0);
-    for (uint32_t e = threadIdx.x; e < 32 * NT; e += 128) {
-        const uint32_t r = e / NT, n = e % NT;
-        zs[r][n] = (r < rows && n < N) ? dZ[(size_t)(m0 + r) * N + n] : 0.0f;
-    }
-    __syncthreads();
+    __shared__ float zs[NT_ROWS][NT];
     const uint32_t k0 = (blockIdx.x * 128 + threadIdx.x) * 4;
-    if (k0 >= K) return;
+    const bool active = k0 < K;
     float b[4][NT];
 #pragma unroll
     for (int q = 0; q < 4; ++q)
@@ -265,54 +372,89 @@ __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_
     const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15u) == 0) &&
                      (!ex.mul_saved || (reinterpret_cast<uintptr_t>(ex.mul_saved) & 15u) == 0) &&
                      (!ex.pairs || ((reinterpret_cast<uintptr_t>(ex.pairs) & 15u) == 0 && ex.pairs_stride % 4 == 0));
+    const bool vsaved = vec && ex.mul_saved != nullptr;
     float cs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-    for (uint32_t r = 0; r < rows; ++r) {
-        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // Four rows at a time, and the saved tensor's slices of the next four (of this chunk or of the block's next
+    // chunk) are requested before these four are stored: inside a one-row loop the compiler may not move those
+    // loads above the previous row's stores (the pointers could alias), and every row waited a full memory latency.
+    float4 sv[4], nsv[4];
+    auto fetch = [&](uint32_t m0, uint32_t r0, float4* dst) {
+        const uint32_t last = min((uint32_t)NT_ROWS, M - m0) - 1;
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            const float z = zs[r][n];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) o[q] = fmaf(z, b[q][n], o[q]);
+        for (int u = 0; u < 4; ++u)
+            dst[u] = __ldcs(reinterpret_cast<const float4*>(ex.mul_saved + (size_t)(m0 + min(r0 + u, last)) * K + k0));
+    };
+    const uint32_t step = gridDim.y * NT_ROWS;
+    if (vsaved && active && blockIdx.y * NT_ROWS < M) fetch(blockIdx.y * NT_ROWS, 0, sv);
+    for (uint32_t m0 = blockIdx.y * NT_ROWS; m0 < M; m0 += step) {
+        const uint32_t rows = min((uint32_t)NT_ROWS, M - m0);
+        __syncthreads();                                    // the previous chunk's rows of dZ are no longer read
+        for (uint32_t e = threadIdx.x; e < NT_ROWS * NT; e += 128) {
+            const uint32_t r = e / NT, n = e % NT;
+            zs[r][n] = (r < rows && n < N) ? dZ[(size_t)(m0 + r) * N + n] : 0.0f;
         }
-        const size_t off = (size_t)(m0 + r) * K + k0;
-        if (vec) {
-            if (ex.mul_saved) {
-                const float4 sv = __ldcs(reinterpret_cast<const float4*>(ex.mul_saved + off));
-                // the short forms the tensor-core epilogues use (one exponential, one reciprocal): the libm tanh of
-                // the plain form made this kernel compute-bound
-                o[0] *= fg_act_grad_sel(ex.mul_act, sv.x); o[1] *= fg_act_grad_sel(ex.mul_act, sv.y);
-                o[2] *= fg_act_grad_sel(ex.mul_act, sv.z); o[3] *= fg_act_grad_sel(ex.mul_act, sv.w);
+        __syncthreads();
+        if (!active) continue;
+        for (uint32_t r0 = 0; r0 < rows; r0 += 4) {
+            if (vsaved) {
+                if (r0 + 4 < rows) fetch(m0, r0 + 4, nsv);
+                else if (m0 + step < M) fetch(m0 + step, 0, nsv);
             }
-            const float4 v = make_float4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<float4*>(dA + off) = v;
-            if (ex.pairs) fg_store_pairs4(ex.pairs, ex.pairs_stride, off, v);
-        } else {
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-                if (k0 + q < K) {
-                    if (ex.mul_saved) o[q] *= fg_act_grad_sel(ex.mul_act, ex.mul_saved[off + q]);
-                    dA[off + q] = o[q];
-                    if (ex.pairs) fg_store_pairs1(ex.pairs, ex.pairs_stride, off + q, o[q]);
-                } else o[q] = 0.0f;
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t r = r0 + u;
+                if (r >= rows) break;
+                float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const float z = zs[r][n];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) o[q] = fmaf(z, b[q][n], o[q]);
+                }
+                const size_t off = (size_t)(m0 + r) * K + k0;
+                if (vec) {
+                    if (ex.mul_saved) {
+                        // the short forms the tensor-core epilogues use (one exponential, one reciprocal): the libm
+                        // tanh of the plain form made this kernel compute-bound
+                        o[0] *= fg_act_grad_sel(ex.mul_act, sv[u].x); o[1] *= fg_act_grad_sel(ex.mul_act, sv[u].y);
+                        o[2] *= fg_act_grad_sel(ex.mul_act, sv[u].z); o[3] *= fg_act_grad_sel(ex.mul_act, sv[u].w);
+                    }
+                    const float4 v = make_float4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<float4*>(dA + off) = v;
+                    if (ex.pairs) fg_store_pairs4(ex.pairs, ex.pairs_stride, off, v);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (k0 + q < K) {
+                            if (ex.mul_saved) o[q] *= fg_act_grad_sel(ex.mul_act, ex.mul_saved[off + q]);
+                            dA[off + q] = o[q];
+                            if (ex.pairs) fg_store_pairs1(ex.pairs, ex.pairs_stride, off + q, o[q]);
+                        } else o[q] = 0.0f;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) cs[q] += o[q];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) sv[u] = nsv[u];
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) cs[q] += o[q];
     }
-    if (ex.colsum_part) {
+    if (ex.colsum_part && active) {
 #pragma unroll
         for (int q = 0; q < 4; ++q)
             if (k0 + q < K) ex.colsum_part[(size_t)blockIdx.y * K + k0 + q] = cs[q];
     }
 }
 
-__global__ void __launch_bounds__(256) fold_chunks_kernel(uint64_t n, uint32_t nchunks, const float* __restrict__ part,
+// dB[j][n] = sum over chunks of part[c][n][j]; thread i = n * Kd + j, so the reads are contiguous.
+__global__ void __launch_bounds__(256) fold_chunks_kernel(uint32_t Kd, uint32_t N, uint32_t nchunks, const float* __restrict__ part,
                                                           float* __restrict__ out) {
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t total = (uint64_t)Kd * N;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         float s = 0.0f;
-#pragma unroll 8
-        for (uint32_t c = 0; c < nchunks; ++c) s += part[(size_t)c * n + i];
-        out[i] = s;
+#pragma unroll 16
+        for (uint32_t c = 0; c < nchunks; ++c) s += part[(size_t)c * total + i];
+        const uint32_t n = (uint32_t)(i / Kd), j = (uint32_t)(i % Kd);
+        out[(size_t)j * N + n] = s;
     }
 }
 
@@ -329,7 +471,9 @@ __global__ void __launch_bounds__(256) fold_chunks_kernel(uint64_t n, uint32_t n
 
 uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K) {
     const uint64_t kp = (K + 3) / 4 * 4;
-    const uint64_t fwd = 16 * kp * 4 + 256;                                              // transposed B
+    const uint64_t fwd_t = 16 * kp * 4 + 256;                                            // transposed B
+    const uint64_t fwd_s = (uint64_t)((K + SK_SLICE - 1) / SK_SLICE) * M * 16 * 4 + 256;  // per-slice partial sums
+    const uint64_t fwd = fwd_t > fwd_s ? fwd_t : fwd_s;
     const uint64_t bwd = (uint64_t)((M + TN_ROWS - 1) / TN_ROWS) * K * N * 4 + 256;      // dB partials
     return fwd > bwd ? fwd : bwd;
 }
@@ -337,6 +481,31 @@ uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K) {
 int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, const float* A, const float* B, float* C,
                                 const float* bias, int act, float* preact_out) {
     if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
+    if ((K % 4 == 0) && fg_aligned16(A) && M < (1u << 27)) {
+        // sliced: one block per (512-wide k-slice, group of rows); then the slices are folded
+        const uint32_t nslices = (K + SK_SLICE - 1) / SK_SLICE;
+        void* part;
+        int32_t s = fg_ws_alloc(ctx, (uint64_t)nslices * M * 16 * 4, &part);
+        if (s != FG_OK) return s;
+        // rows per block: 32, 64 or 128, whichever ends soonest on two resident blocks per SM
+        const uint64_t slots = 2ull * ctx->sm_count;
+        uint32_t rpb = 32;
+        uint64_t best = ~0ull;
+        for (uint32_t cand = 32; cand <= 128; cand *= 2) {
+            const uint64_t blocks = (uint64_t)nslices * ((M + cand - 1) / cand);
+            const uint64_t span = ((blocks + slots - 1) / slots) * (cand + 12);     // + the cost of loading the slice of B
+            if (span < best) { best = span; rpb = cand; }
+        }
+        dim3 grid(nslices, (M + rpb - 1) / rpb);
+        if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
+        fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * K);                 // A read once
+        FG_SKINNY_DISPATCH(N, (gemm_skinny_n_slice_kernel<NT><<<grid, 256, 0, ctx->stream>>>(M, N, K, rpb, A, B, (float*)part)));
+        FG_LAUNCHED(ctx);
+        skinny_fold_slices_kernel<<<(M * 16 + 255) / 256, 256, 0, ctx->stream>>>(M, N, nslices, (const float*)part, bias, act, C, preact_out);
+        fg_time_end(ctx, tr);
+        FG_LAUNCHED(ctx);
+        return FG_OK;
+    }
     const uint32_t Kp = (K + 3) / 4 * 4, NTr = (N + 3) / 4 * 4;
     void* bt;
     int32_t s = fg_ws_alloc(ctx, (uint64_t)NTr * Kp * 4, &bt);
@@ -344,24 +513,36 @@ int32_t fg_gemm_skinny_n_launch(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K,
     skinny_transpose_kernel<<<(NTr * Kp + 255) / 256, 256, 0, ctx->stream>>>(K, N, Kp, NTr, B, (float*)bt);
     FG_LAUNCHED(ctx);
     const uint32_t blocks = (M + 7) / 8;
-    const bool vec = (K % 4 == 0) && fg_aligned16(A);
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * K);                 // A read once
-    FG_SKINNY_DISPATCH(N, {
-        if (vec) gemm_skinny_n_kernel<NT, true><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);
-        else gemm_skinny_n_kernel<NT, false><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out);
-    });
+    FG_SKINNY_DISPATCH(N, (gemm_skinny_n_kernel<NT, false><<<blocks, 256, 0, ctx->stream>>>(M, N, K, Kp, A, (const float*)bt, C, bias, act, preact_out)));
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
 
-// dA[M, K] = dZ · B^T with dZ [M, N], B [K, N], N <= 16.
+// dA[M, K] = dZ · B^T with dZ [M, N], B [K, N], N <= 16.  With extras->colsum_part, *colsum_rows receives the
+// number of partial rows written (at most ceil(M / 32), which is what the caller must have room for).
 int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N, const float* dZ, const float* B,
-                                 float* dA, const fg_skinny_extras* extras) {
+                                 float* dA, const fg_skinny_extras* extras, uint32_t* colsum_rows) {
     if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
-    dim3 grid((K + 511) / 512, (M + 31) / 32);
-    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
     const fg_skinny_extras ex = extras ? *extras : fg_skinny_extras{nullptr, 0, nullptr, 0, nullptr};
+    // as many blocks as the SMs hold at once (four or five of 128 threads each, by registers), each walking its
+    // share of the 16-row chunks
+    const uint32_t gx = (K + 511) / 512, chunks = (M + NT_ROWS - 1) / NT_ROWS;
+    int per_sm = 4;
+    FG_SKINNY_DISPATCH(N, {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_nt_kernel<NT>, 128, 0) != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            per_sm = 4;
+        }
+    });
+    uint32_t gy = (uint32_t)((uint64_t)per_sm * ctx->sm_count / gx);
+    if (gy < 1) gy = 1;
+    if (gy > chunks) gy = chunks;
+    if (gy > (M + 31) / 32) gy = (M + 31) / 32;       // the caller's room for column-sum partials
+    if (gy > 65535) gy = 65535;
+    if (colsum_rows) *colsum_rows = gy;
+    dim3 grid(gx, gy);
     // dA written once; with extras also the saved tensor read and the pairs (as many bytes again) written
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * K * (1.0 + (ex.mul_saved ? 1.0 : 0.0) + (ex.pairs ? 1.0 : 0.0)));
     FG_SKINNY_DISPATCH(N, (gemm_skinny_nt_kernel<NT><<<grid, 128, 0, ctx->stream>>>(M, K, N, dZ, B, dA, ex)));
@@ -388,7 +569,7 @@ int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t 
     });
     FG_LAUNCHED(ctx);
     const uint64_t n = (uint64_t)Kd * N;
-    fold_chunks_kernel<<<fg_stream_grid(ctx, n, 256, 8), 256, 0, ctx->stream>>>(n, nchunks, (const float*)part, dB);
+    fold_chunks_kernel<<<fg_stream_grid(ctx, n, 256, 8), 256, 0, ctx->stream>>>(Kd, N, nchunks, (const float*)part, dB);
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;

@@ -1787,8 +1787,9 @@ int32_t gemm_bwd_paired_core(fg_ctx* ctx, uint32_t M, uint32_t N, uint32_t K, Pa
         if (exch_buf && (s = fg_allreduce_sum_f32(ctx, exch_buf, exch_count)) != FG_OK) return s;
         if (dA) {
             const fg_skinny_extras ex{o.mul_saved, o.mul_act, o.pairs, o.stride, cs_part};
-            if ((s = fg_gemm_skinny_nt_launch(ctx, M, K, N, dZ.x, B.x, dA, &ex)) != FG_OK) return s;
-            if (cs_part && (s = fg_colsum_fold_launch(ctx, K, cs_chunks, cs_part, dbias_prev)) != FG_OK) return s;
+            uint32_t cs_rows = 0;
+            if ((s = fg_gemm_skinny_nt_launch(ctx, M, K, N, dZ.x, B.x, dA, &ex, &cs_rows)) != FG_OK) return s;
+            if (cs_part && (s = fg_colsum_fold_launch(ctx, K, cs_rows, cs_part, dbias_prev)) != FG_OK) return s;
         }
         return FG_OK;
     }
