@@ -61,5 +61,37 @@ def load_tensors(ctx, path):
         lib.fg_bpat_close(h)
 
 
+def save_adamw_state(ctx, path, m, v, step):
+    """The optimizer state of a run, to be kept beside a parameter checkpoint.
+
+    This is NOT one of the reference's formats (its SGD has no state and it has no AdamW): the container is an
+    ordinary v2-f32 `.bpat` file, so every reader of the format can open it, whose tensor list is by convention
+    m_0 .. m_{n-1}, v_0 .. v_{n-1} (shapes of the parameters), then one [2] tensor holding the step count as two
+    16-bit halves (low, high), each exact in f32.  m and v are lists of Tensors."""
+    if len(m) != len(v):
+        raise ValueError("m and v must list the same tensors")
+    step = int(step)
+    if not 0 <= step < (1 << 32):
+        raise ValueError("step count out of range")
+    count = ctx.init_tensor_f32((2,), np.array([step & 0xffff, step >> 16], np.float32))
+    try:
+        save_tensors(ctx, path, list(m) + list(v) + [count], V2_F32)
+    finally:
+        count.data.free()
+
+
+def load_adamw_state(ctx, path):
+    """Inverse of save_adamw_state: (m, v, step)."""
+    ts = load_tensors(ctx, path)
+    if len(ts) % 2 != 1 or ts[-1].shape != (2,):
+        for t in ts:
+            t.data.free()
+        raise ValueError(f"{path} is not an optimizer-state container (2n + 1 tensors, the last of shape [2])")
+    n = (len(ts) - 1) // 2
+    halves = ctx.to_numpy(ts[-1])
+    ts[-1].data.free()
+    return ts[:n], ts[n:2 * n], int(halves[0]) | (int(halves[1]) << 16)
+
+
 GpuContext.save_tensors = lambda self, path, tensors, header=V2_F32: save_tensors(self, path, tensors, header)
 GpuContext.load_tensors = lambda self, path: load_tensors(self, path)

@@ -2,7 +2,7 @@
 than the 126 MB L2 so DRAM counters mean something, but well under a few GB on the device
 and only a handful of launches.
 
-    python -m ferrograd_b200.cases gemm|gemm_bwd|gemm_bf16|layer|softmax_ce|adamw|sgd|eltwise|skinny|mlp|graph_mlp [--iters N]
+    python -m ferrograd_b200.cases gemm|gemm_bwd|gemm_bf16|layer|softmax|softmax_ce|adamw|sgd|eltwise|skinny|mlp|graph_mlp [--iters N]
 
 mlp runs training steps of a benchmark workload (--workload c4|c5|c5s) through MLPTrainer, graph_mlp the same
 through the graph API (dispatch_forward / loss / backward / optim); c5s is the eight-layer workload at 4096-wide
@@ -22,7 +22,7 @@ from .mlp import MLPTrainer
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_bwd", "gemm_bf16", "layer", "softmax_ce", "adamw", "sgd", "eltwise", "skinny",
+    ap.add_argument("case", choices=["gemm", "gemm_bwd", "gemm_bf16", "layer", "softmax", "softmax_ce", "adamw", "sgd", "eltwise", "skinny",
                                      "mlp", "graph_mlp"])
     ap.add_argument("--workload", default="c4", choices=["c4", "c5", "c5s"])
     ap.add_argument("--m", type=int, default=2048)
@@ -71,6 +71,15 @@ def main():
             ctx.gemm_paired(x, w, y, M, N, K, A_pairs=pairs["x"], B_pairs=pairs["w"], bias=bias, act="tanh", C_pairs=pairs["y"])
             ctx.gemm_bwd_paired(x, w, dz, M, N, K, A_pairs=pairs["x"], B_pairs=pairs["w"], dZ_pairs=pairs["dz"], dB=dw, dA=dx,
                                 below_act="tanh", below_saved=saved_below, dA_pairs=pairs["dx"], below_dbias=db_below)
+    elif a.case == "softmax":
+        # row softmax alone, forward and backward, on rows too short for the row-in-registers kernel
+        rows, cols = a.n or 16384, 4096
+        x = ctx.init_tensor_f32((rows, cols), 2.0 * r.standard_normal((rows, cols), np.float32))
+        dy = ctx.init_tensor_f32((rows, cols), r.standard_normal((rows, cols), np.float32))
+        y, dx = ctx.new_tensor((rows, cols)), ctx.new_tensor((rows, cols))
+        for _ in range(a.iters):
+            ctx.softmax_fwd(x, y, rows, cols)
+            ctx.softmax_bwd(y, dy, dx, rows, cols)
     elif a.case == "softmax_ce":
         rows, cols = a.n or 2048, 32000
         x = ctx.init_tensor_f32((rows, cols), 2.0 * r.standard_normal((rows, cols), np.float32))

@@ -113,6 +113,66 @@ class MLPTrainer:
         if self.paired:
             self.ctx.pairs_from_f32(self.params, self.n_arena, self.w_pairs, self.n_arena)
 
+    # ---- checkpoints ----
+    def _arena_tensors(self, host_arena):
+        """[W0, b0, W1, b1, ...] as device tensors made from a host copy of an arena."""
+        out = []
+        for l in range(self.L):
+            k, n = self.dims[l], self.dims[l + 1]
+            out.append(self.ctx.init_tensor_f32((k, n), host_arena[self.w_off[l]:self.w_off[l] + k * n]))
+            out.append(self.ctx.init_tensor_f32((n,), host_arena[self.b_off[l]:self.b_off[l] + n]))
+        return out
+
+    def save_checkpoint(self, path):
+        """Parameters as a v2-f32 `.bpat` file in the reference's order (W0, b0, W1, b1, ...), readable by the
+        reference's load_tensors; with AdamW, its moments and step count go to `path + ".adamw"`
+        (bpat.save_adamw_state: not a reference format)."""
+        from . import bpat
+        self.ctx.sync()
+        arena = lambda buf: self.ctx.download(buf, np.empty(self.n_arena, np.float32))
+        ts = self._arena_tensors(arena(self.params))
+        try:
+            bpat.save_tensors(self.ctx, path, ts)
+        finally:
+            for t in ts:
+                t.data.free()
+        if self.opt[0] == "adamw":
+            m, v = self._arena_tensors(arena(self.m)), self._arena_tensors(arena(self.v))
+            try:
+                bpat.save_adamw_state(self.ctx, str(path) + ".adamw", m, v, self.steps_done)
+            finally:
+                for t in m + v:
+                    t.data.free()
+
+    def load_checkpoint(self, path):
+        """Inverse of save_checkpoint; training continues with the step count it had."""
+        import os
+        from . import bpat
+        ts = bpat.load_tensors(self.ctx, path)
+        try:
+            if [t.shape for t in ts] != [s for l in range(self.L) for s in ((self.dims[l], self.dims[l + 1]), (self.dims[l + 1],))]:
+                raise ValueError(f"{path}: tensor shapes do not match this network")
+            host = [self.ctx.to_numpy(t) for t in ts]
+        finally:
+            for t in ts:
+                t.data.free()
+        self.set_params(host[0::2], host[1::2])
+        if self.opt[0] == "adamw" and os.path.exists(str(path) + ".adamw"):
+            m, v, step = bpat.load_adamw_state(self.ctx, str(path) + ".adamw")
+            try:
+                for buf, lst in ((self.m, m), (self.v, v)):
+                    a = np.zeros(self.n_arena, np.float32)
+                    for l in range(self.L):
+                        w, bb = self.ctx.to_numpy(lst[2 * l]), self.ctx.to_numpy(lst[2 * l + 1])
+                        a[self.w_off[l]:self.w_off[l] + w.size] = w.ravel()
+                        a[self.b_off[l]:self.b_off[l] + bb.size] = bb.ravel()
+                    self.ctx.upload(buf, a)
+            finally:
+                for t in m + v:
+                    t.data.free()
+            self.ctx.upload(self.step_counter, np.array([step], np.uint32))
+            self.steps_done = step
+
     def destroy(self):
         """Frees every device buffer of the trainer."""
         from .backend import Buffer

@@ -122,3 +122,47 @@ def test_save_16bit_is_byte_identical_and_round_trips(tmp_path, fmt, header):
             ctx.save_tensors(tmp_path / "x.bpat", f32, header)   # f32 tensors do not fit a 16-bit file
     finally:
         ctx.destroy()
+
+
+@pytest.mark.gpu
+def test_trainer_checkpoint_resumes_bit_for_bit(tmp_path):
+    """Parameters in the reference's v2-f32 format, AdamW moments and step count in the sidecar container
+    (not a reference format): a run resumed from them continues exactly as the uninterrupted run does."""
+    from ferrograd_b200 import GpuContext, bpat, dp
+    from ferrograd_b200.mlp import MLPTrainer
+    dims, batch = [96, 160, 10], 192
+    opt = ("adamw", 1e-3, 0.9, 0.999, 1e-8, 0.01)
+    wl = dict(dims=dims, batch=batch, loss="ce")
+    ctx = GpuContext(0)
+    try:
+        def run(tr, first, last):
+            for s in range(first, last):
+                tr.upload_batch(*dp.synth_batch(wl, 0, s, batch))
+                tr.step()
+            ctx.sync()
+
+        a = MLPTrainer(ctx, dims, batch, "gelu", "ce", opt)
+        a.set_params(*MLPTrainer.init_params(dims, "he_normal", 9))
+        run(a, 0, 3)
+        path = tmp_path / "net.bpat"
+        a.save_checkpoint(path)
+        shapes, fmt = bpat.inspect(path)
+        assert fmt == bpat.V2_F32 and shapes == [(96, 160), (160,), (160, 10), (10,)]
+        m, v, step = bpat.load_adamw_state(ctx, str(path) + ".adamw")
+        assert step == 3 and [t.shape for t in m] == shapes and [t.shape for t in v] == shapes
+        for t in m + v:
+            t.data.free()
+        run(a, 3, 6)
+        Wa, ba = a.get_params()
+
+        b = MLPTrainer(ctx, dims, batch, "gelu", "ce", opt)
+        b.load_checkpoint(path)
+        run(b, 3, 6)
+        Wb, bb = b.get_params()
+        for x, y in zip(Wa + ba, Wb + bb):
+            assert np.array_equal(x, y)
+        with pytest.raises(ValueError):
+            bpat.load_adamw_state(ctx, path)            # a parameter file is not a state container (even count)
+    finally:
+        ctx.sync()
+        ctx.destroy()
