@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(256) skinny_fold_slices_kernel(uint32_t M, uin
 
 constexpr int TN_ROWS = 64;   // rows of A per partial sum in the dB kernel
 
-// part[chunk][n][j] = sum over the chunk's rows m of A[m][j] * dZ[m][n]   (A is [M, Kd], dZ is [M, N]).
+// part[block row][n][j] = sum over the block row's chunks' rows m of A[m][j] * dZ[m][n]   (A is [M, Kd], dZ is [M, N]).
 // A thread owns four consecutive j; the chunk's rows of dZ sit in shared memory and are broadcast.
 template <int NT, bool VEC>
 __global__ void __launch_bounds__(128, 4) gemm_skinny_tn_partial_kernel(uint32_t M, uint32_t Kd, uint32_t N,
@@ -282,55 +282,62 @@ __global__ void __launch_bounds__(128, 4) gemm_skinny_tn_partial_kernel(uint32_t
                                                                      const float* __restrict__ dZ,
                                                                      float* __restrict__ part) {
     __shared__ float zs[TN_ROWS][NT];
-    const uint32_t m0 = blockIdx.y * TN_ROWS, rows = min((uint32_t)TN_ROWS, M - m0);
-    for (uint32_t e = threadIdx.x; e < TN_ROWS * NT; e += 128) {
-        const uint32_t r = e / NT, n = e % NT;
-        zs[r][n] = (r < rows && n < N) ? dZ[(size_t)(m0 + r) * N + n] : 0.0f;
-    }
-    __syncthreads();
     const uint32_t j0 = (blockIdx.x * 128 + threadIdx.x) * 4;
-    if (j0 >= Kd) return;
+    const bool active = j0 < Kd;
     float acc[4][NT];
 #pragma unroll
     for (int q = 0; q < 4; ++q)
 #pragma unroll
         for (int n = 0; n < NT; ++n) acc[q][n] = 0.0f;
-    const float* a = A + (size_t)m0 * Kd + j0;
-    // Eight rows are multiplied while the next eight are on their way (16 loads of 16 bytes in flight per thread:
-    // with eight, and a grid that fills 70 % of the thread slots, the kernel ran at 23 % of the DRAM rate).
-    float x[8][4], nx[8][4];
-    auto fetch = [&](uint32_t r0, float (*dst)[4]) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const uint32_t r = min(r0 + u, rows - 1);     // rows past the end reload the last one; their dZ is zero
-            if (VEC) {
-                const float4 t = __ldcs(reinterpret_cast<const float4*>(a + (size_t)r * Kd));
-                dst[u][0] = t.x; dst[u][1] = t.y; dst[u][2] = t.z; dst[u][3] = t.w;
-            } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) dst[u][q] = (j0 + q < Kd) ? a[(size_t)r * Kd + q] : 0.0f;
-            }
+    // A block walks the 64-row chunks blockIdx.y, + gridDim.y, ... and keeps its sums in registers across them:
+    // the number of partial results is the number of block rows (at most what the SMs hold at once), whatever M is.
+    for (uint32_t m0 = blockIdx.y * TN_ROWS; m0 < M; m0 += gridDim.y * TN_ROWS) {
+        const uint32_t rows = min((uint32_t)TN_ROWS, M - m0);
+        __syncthreads();                                    // the previous chunk's rows of dZ are no longer read
+        for (uint32_t e = threadIdx.x; e < TN_ROWS * NT; e += 128) {
+            const uint32_t r = e / NT, n = e % NT;
+            zs[r][n] = (r < rows && n < N) ? dZ[(size_t)(m0 + r) * N + n] : 0.0f;
         }
-    };
-    fetch(0, x);
-    for (uint32_t r0 = 0; r0 < rows; r0 += 8) {
-        if (r0 + 8 < rows) fetch(r0 + 8, nx);
+        __syncthreads();
+        if (!active) continue;
+        const float* a = A + (size_t)m0 * Kd + j0;
+        // Eight rows are multiplied while the next eight are on their way (16 loads of 16 bytes in flight per
+        // thread: with eight, and a grid that fills 70 % of the thread slots, the kernel ran at 23 % of the DRAM rate).
+        float x[8][4], nx[8][4];
+        auto fetch = [&](uint32_t r0, float (*dst)[4]) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (r0 + u < rows) {
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t r = min(r0 + u, rows - 1);     // rows past the end reload the last one; their dZ is zero
+                if (VEC) {
+                    const float4 t = __ldcs(reinterpret_cast<const float4*>(a + (size_t)r * Kd));
+                    dst[u][0] = t.x; dst[u][1] = t.y; dst[u][2] = t.z; dst[u][3] = t.w;
+                } else {
 #pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    const float z = zs[r0 + u][n];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) acc[q][n] = fmaf(x[u][q], z, acc[q][n]);
+                    for (int q = 0; q < 4; ++q) dst[u][q] = (j0 + q < Kd) ? a[(size_t)r * Kd + q] : 0.0f;
                 }
             }
+        };
+        fetch(0, x);
+        for (uint32_t r0 = 0; r0 < rows; r0 += 8) {
+            if (r0 + 8 < rows) fetch(r0 + 8, nx);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < rows) {
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+                        const float z = zs[r0 + u][n];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) acc[q][n] = fmaf(x[u][q], z, acc[q][n]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) x[u][q] = nx[u][q];
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) x[u][q] = nx[u][q];
     }
+    if (!active) return;
     // part[chunk][n][j]: for one n a thread's four j are one 16-byte store and a warp's are 512 contiguous bytes
     // (as [chunk][j][n] every store instruction touched 32 sectors, and 10 MB of partials cost more L2 write
     // bandwidth than the 67 MB read cost DRAM bandwidth)
@@ -555,12 +562,15 @@ int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N
 int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t N, const float* A, const float* dZ,
                                  float* dB) {
     if (N > SKN) return fg_fail(ctx, FG_ERR_INTERNAL, "skinny GEMM: N too large");
-    const uint32_t nchunks = (M + TN_ROWS - 1) / TN_ROWS;
+    // block rows: as many as the SMs hold at once (four blocks of 128 threads per SM), at most one per 64-row chunk
+    const uint32_t gx = (Kd + 511) / 512;
+    uint32_t nchunks = (uint32_t)(4ull * ctx->sm_count / gx);
+    if (nchunks < 1) nchunks = 1;
+    if (nchunks > (M + TN_ROWS - 1) / TN_ROWS) nchunks = (M + TN_ROWS - 1) / TN_ROWS;
     void* part;
     int32_t s = fg_ws_alloc(ctx, (uint64_t)nchunks * Kd * N * 4, &part);
     if (s != FG_OK) return s;
-    dim3 grid((Kd + 511) / 512, nchunks);
-    if (grid.y > 65535) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "skinny GEMM: too many rows");
+    dim3 grid(gx, nchunks);
     const bool vec = (Kd % 4 == 0) && fg_aligned16(A);
     fg_time_rec* tr = fg_time_begin(ctx, FG_KERNEL_SKINNY, 4.0 * M * Kd);                // A read once
     FG_SKINNY_DISPATCH(N, {
