@@ -477,11 +477,16 @@ __global__ void __launch_bounds__(256) fold_chunks_kernel(uint32_t Kd, uint32_t 
 }  // namespace
 
 uint64_t fg_gemm_skinny_scratch_bytes(uint32_t M, uint32_t N, uint32_t K) {
+    if (N > SKN) return 0;                                                               // not a narrow layer: these kernels do not run
     const uint64_t kp = (K + 3) / 4 * 4;
     const uint64_t fwd_t = 16 * kp * 4 + 256;                                            // transposed B
     const uint64_t fwd_s = (uint64_t)((K + SK_SLICE - 1) / SK_SLICE) * M * 16 * 4 + 256;  // per-slice partial sums
     const uint64_t fwd = fwd_t > fwd_s ? fwd_t : fwd_s;
-    const uint64_t bwd = (uint64_t)((M + TN_ROWS - 1) / TN_ROWS) * K * N * 4 + 256;      // dB partials
+    // dB partials: one [N][K] block per block row, and there are at most as many block rows as 64-row chunks or
+    // as four blocks per SM allow (fewer than 2048 on any GPU)
+    uint64_t rows = (M + TN_ROWS - 1) / TN_ROWS;
+    if (rows > 2048) rows = 2048;
+    const uint64_t bwd = rows * K * N * 4 + 256;
     return fwd > bwd ? fwd : bwd;
 }
 

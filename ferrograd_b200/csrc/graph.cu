@@ -1005,22 +1005,24 @@ static int32_t optim_eager(fg_exec* e) {
     return optim_many(e, all);
 }
 
-// Are this graph's dispatches recorded and replayed?  With option exec_plans = auto: when the context has a
-// communicator, or when the graph is launch-bound,
-// i.e. its estimated device time per launch is under ten microseconds (one forward + backward pass estimated at
+// Are this graph's dispatches recorded and replayed?  With option exec_plans = auto: when the graph is launch-bound,
+// i.e. its estimated device time per launch is under ten microseconds, or under 300 with a communicator (one
+// forward + backward pass estimated at
 // 300 TFLOP/s for the matmuls and 5 TB/s for every tensor touched three times, over about three launches per step of
 // the forward pass).
 static bool plans_wanted(const fg_exec* e) {
     if (!e->use_plans || e->ctx->opt_exec_plans == 0) return false;
     if (e->ctx->opt_exec_plans == 1) return true;
-    // with a communicator every step also enqueues collectives, whose host-side cost a replayed graph avoids
-    // (measured on two GPUs, 784-4096-4096-10: 1.97 ms per step replayed, 2.03 ms with plain launches)
-    if (e->ctx->comm != nullptr && e->ctx->nranks > 1) return true;
     double flop = 0.0, bytes = 0.0;
     for (const GemmStep& gs : e->gemms) flop += 3.0 * 2.0 * gs.batch * (double)gs.M * gs.N * gs.K;
     for (const ENode& en : e->n) bytes += 3.0 * (double)en.numel * (double)e->esize;
     const double est_us = flop / 300e6 + bytes / 5e6;
     const double launches = 3.0 * (double)std::max<size_t>(e->fwd.size(), 1);
+    // With a communicator every step also enqueues collectives, whose host-side cost a replayed graph avoids:
+    // worth it up to a few hundred microseconds per launch (two GPUs, 784-4096-4096-10, about 125 us per launch:
+    // 1.97 ms per step replayed against 2.03 with plain launches; eight 8192-wide layers, about 800 us per
+    // launch: 27.0 against 26.5 ms, so those stay with plain launches).
+    if (e->ctx->comm != nullptr && e->ctx->nranks > 1) return est_us / launches < 300.0;
     return est_us / launches < 10.0;
 }
 

@@ -96,10 +96,10 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  *                   allows; "0" sends every shape through operand planes written by a pre-pass
  *   "exec_plans"    "auto" (default) | "1" | "0": the graph engine records each dispatch as a CUDA graph and
  *                   replays it.  "auto" does so for graphs whose kernels are short (launch-bound: the tiny MLP gains
- *                   several times) and whenever the context has a communicator (the host-side cost of enqueueing
- *                   collectives every step is avoided); for large layers on one GPU plain launches keep the GPU fed,
- *                   and four graph launches per step cost more than they save (measured: 1.87 against 1.82 ms per
- *                   step on 784-4096-4096-10)
+ *                   several times) and, when the context has a communicator, also for graphs of medium-sized
+ *                   kernels (the host-side cost of enqueueing collectives every step is avoided); for large
+ *                   layers plain launches keep the GPU fed, and four graph launches per step cost more than
+ *                   they save (measured: 1.87 against 1.82 ms per step on 784-4096-4096-10 on one GPU)
  *   "comm_max_ctas" CTAs the communicator may use (default 12; read by fg_comm_init)
  *   "comm_sms"      SMs the persistent GEMM leaves free while an exchange is in flight (default 16; 0 = none)
  *   "comm_min_exchange"  the graph engine starts a gradient exchange during the backward pass once this many

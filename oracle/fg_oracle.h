@@ -14,7 +14,9 @@
  * the reference), the CE and MSE loss kernels, tanh/relu/gelu forward and backward,
  * softmax backward with non-zero gradients, and bias broadcast.  For those the
  * oracle follows the cited source lines, or the standard definition where the
- * reference is absent or wrong.
+ * reference is absent or wrong (each such place has a REF_QUIRK_* switch that reproduces
+ * the reference), and every function is compared with an independent float64 formula on
+ * random inputs (tests/test_oracle_crosscheck.py).
  */
 #ifndef FG_ORACLE_H
 #define FG_ORACLE_H

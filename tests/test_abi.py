@@ -66,3 +66,12 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         _lib.load()
+
+
+def test_noalloc_mse_limit_matches_its_static_scratch():
+    # the largest accepted n uses exactly the last of the 4096 static partial sums (65,536 elements each);
+    # checked on the header's constant, so that the 1 GiB inputs need not be allocated
+    m = re.search(r"#define\s+FG_MSE_NOALLOC_MAX_N\s+(\d+)ull", open(os.path.join(ROOT, "include", "ferrograd_b200.h")).read())
+    assert m, "FG_MSE_NOALLOC_MAX_N not found in the header"
+    n = int(m.group(1))
+    assert (n + 65536 - 1) // 65536 == 4096 and (n + 1 + 65536 - 1) // 65536 == 4097
