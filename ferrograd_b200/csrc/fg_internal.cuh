@@ -36,7 +36,7 @@ struct fg_time_rec {
     int kind;
     double work;   // flop for GEMMs, bytes for bandwidth-bound kernels
 };
-#define FG_TIME_MAX_RECS 8192
+#define FG_TIME_MAX_RECS 65536
 
 struct fg_ctx {
     int device;

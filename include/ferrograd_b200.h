@@ -122,7 +122,8 @@ int32_t fg_ctx_device_status(fg_ctx* ctx, int32_t* status_word);
  * launches of one kind since the last read of that kind and forgets them. */
 enum fg_kernel_kind {
     FG_KERNEL_GEMM_TC = 0,    /* work = 2*M*N*K flop                       */
-    FG_KERNEL_SOFTMAX_CE = 1, /* work = 2*rows*cols*4 bytes (+probs)       */
+    FG_KERNEL_SOFTMAX_CE = 1, /* fused CE: work = 2*rows*cols*4 bytes (+probs); softmax forward alone the same;
+                                 softmax backward 3*rows*cols*4 (4* when it accumulates) */
     FG_KERNEL_ADAMW = 2,      /* work = 28 (or 32 with zero_grad) bytes/param */
     FG_KERNEL_SGD = 3,        /* work = 12 (or 16 with zero_grad) bytes/param */
     FG_KERNEL_SPLIT = 4,      /* work = bytes read + written by the operand pre-pass */

@@ -133,8 +133,9 @@ def test_adamw_device_step_counter(ctx, oracle):
 
 
 # ---------------------------------------------------------------- softmax family
-SOFTMAX_SHAPES = [(1, 1), (7, 10), (64, 33), (37, 1000), (5, 4096), (300, 8192), (9, 12345), (40, 32000),
-                  (3, 40000)]
+# 1000, 2000, 4096, 6000 columns: the kernels that hold a row in registers, with 1, 2, 4 and 8 float4 per thread
+SOFTMAX_SHAPES = [(1, 1), (7, 10), (64, 33), (37, 1000), (33, 2000), (5, 4096), (21, 6000), (300, 8192), (9, 12345),
+                  (40, 32000), (3, 40000)]
 
 
 @pytest.mark.parametrize("rows,cols", SOFTMAX_SHAPES)
