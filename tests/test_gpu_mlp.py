@@ -155,6 +155,34 @@ def test_c4_full_size_one_step(ctx, oracle):
     assert drift[0] < 1e-5
 
 
+def test_c4_full_size_one_step_through_the_graph_api(ctx, oracle):
+    # The same workload through the reference's loop (dispatch_forward / loss / backward / optim), which is what the
+    # benchmark times: the loss is unreduced there, so the oracle runs with a gradient scale of one.
+    from ferrograd_b200 import dp
+    from ferrograd_b200.mlp import GraphMLP, MLPTrainer
+    w = dp.WORKLOADS["c4"]
+    dims, batch, opt = w["dims"], w["batch"], w["opt"]
+    net = GraphMLP(ctx, dims, batch, w["act"], w["loss"], opt)
+    W, b = MLPTrainer.init_params(dims, w["init"], 3)
+    net.set_params(W, b)
+    x, t = dp.synth_batch("c4", 0, 0)
+    net.upload_batch(x, t)
+    net.step()
+    ctx.sync()
+    assert ctx.device_status() == 0
+    state = zeros_state(W, b)
+    loss_sum, gW, gb, out = oracle.mlp_step(dims, batch, w["act"], W, b, x, t, "ce", 1.0, opt, step=1, state=state)
+    check(net.get_output(), oracle.softmax_fwd(out), TOL, "forward output (probabilities)")
+    assert abs(net.get_loss() - loss_sum) <= 1e-5 * abs(loss_sum)
+    got_W, got_b = net.get_params()
+    for l in range(len(dims) - 1):
+        for ref_p, ref_g, got, name in ((W[l], gW[l], got_W[l], "W"), (b[l], gb[l], got_b[l], "b")):
+            bound = param_bound(ref_p, ref_g, opt, TOL)
+            worst = float(np.max(np.abs(got.astype(np.float64) - ref_p) / bound))
+            assert worst <= 1.0, f"updated {name}[{l}]: {worst:.3g} x the propagated bound"
+    net.destroy()
+
+
 def test_c5_full_size_one_step(ctx, oracle):
     # Benchmark workload C5 at its real size: eight 8192 x 8192 layers, tanh, MSE, AdamW, batch 2048, one step
     # (6.6 TFLOP in the oracle: about a minute of host time).
