@@ -464,7 +464,11 @@ int32_t fg_exec_dispatch_optim(fg_exec* e);                           /* :790   
 int32_t fg_exec_dispatch_single_optim(fg_exec* e, fg_buf* weight, uint32_t grad_index); /* :794-814 */
 /* AllocTensors (dispatch/mod.rs:835-845).  Saved tensors are the materialised intermediate nodes
  * in node order (a matmul result is always one); gradients exist for every input and every
- * materialised intermediate node, in node order.  `node` (may be NULL) receives the node id. */
+ * materialised intermediate node, in node order.  `node` (may be NULL) receives the node id.
+ * A node that was absorbed into its producer (the add and the activation that follow a matmul run in the GEMM's
+ * epilogue; the members of an elementwise region run in one kernel) is not materialised and has no entry, so
+ * index i here is NOT index i of the reference's compute_saved_nodes (backend/mod.rs:1189): match the entries
+ * by the node id that `node` returns. */
 fg_buf* fg_exec_forward_out(fg_exec* e);
 fg_buf* fg_exec_seed(fg_exec* e);
 fg_buf* fg_exec_loss_t(fg_exec* e);
