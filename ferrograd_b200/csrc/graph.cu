@@ -619,6 +619,14 @@ static int32_t forward_eager(fg_exec* e) {
                 if (s != FG_OK) return s;
                 continue;
             }
+            if (e->dtype == FG_DTYPE_F32 && gs.batch > 1) {
+                // rank-3 product: one launch for small matrices, one pairs pass + one launch per matrix for large ones
+                s = fg_gemm_batched_f32(e->ctx, e->gemm_mode, gs.batch, gs.M, gs.N, gs.K, vptr(e, gs.a), sa, vptr(e, gs.b), sb,
+                                        vptr(e, gs.out), sc, gs.bias >= 0 ? vptr(e, gs.bias) : nullptr, gs.act,
+                                        gs.preact ? (float*)gs.preact->ptr : nullptr);
+                if (s != FG_OK) return s;
+                continue;
+            }
             for (uint32_t t = 0; t < gs.batch && s == FG_OK; ++t) {
                 if (e->dtype != FG_DTYPE_F32) {
                     char* const pa = (char*)vptr(e, gs.a) + t * sa * 2;
@@ -806,6 +814,9 @@ static int32_t backward_eager(fg_exec* e) {
             if (gs.batch > 1) {
                 // one product per Z index: every operand, gradient and saved tensor is stepped by one matrix
                 auto run = [&](float* da_dst, float* db_dst) -> int32_t {
+                    if (e->dtype == FG_DTYPE_F32)
+                        return fg_gemm_batched_bwd_f32(e->ctx, e->gemm_mode, gs.batch, M, Nn, K, vptr(e, gs.a), sa, vptr(e, gs.b), sb,
+                                                       grad_of(gs.out), sc, gs.act, saved, da_dst, db_dst);
                     for (uint32_t t = 0; t < gs.batch; ++t) {
                         int32_t r = gemm_bwd_any(e, M, Nn, K, off(vptr(e, gs.a), t * sa), off(vptr(e, gs.b), t * sb),
                                                  off(grad_of(gs.out), t * sc), gs.act, saved ? off(saved, t * sc) : nullptr,
