@@ -9,6 +9,8 @@
 // for the tensor-core path, and when FG_GEMM_SIMT is requested.
 //
 // 64x64 output tile per CTA, 16x16 threads, 4x4 outputs per thread, k tiles of 16.
+#include <atomic>
+
 #include "fg_internal.cuh"
 
 namespace {
@@ -541,13 +543,19 @@ int32_t fg_gemm_skinny_nt_launch(fg_ctx* ctx, uint32_t M, uint32_t K, uint32_t N
     // as many blocks as the SMs hold at once (four or five of 128 threads each, by registers), each walking its
     // share of the 16-row chunks
     const uint32_t gx = (K + 511) / 512, chunks = (M + NT_ROWS - 1) / NT_ROWS;
-    int per_sm = 4;
-    FG_SKINNY_DISPATCH(N, {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_nt_kernel<NT>, 128, 0) != cudaSuccess || per_sm < 1) {
-            cudaGetLastError();
-            per_sm = 4;
-        }
-    });
+    // resident blocks per SM, asked of the runtime once per device and kernel variant
+    static std::atomic<int> occ[4][64];
+    std::atomic<int>& slot = occ[(N <= 4) ? 0 : (N <= 8) ? 1 : (N <= 12) ? 2 : 3][ctx->device & 63];
+    int per_sm = slot.load(std::memory_order_acquire);
+    if (per_sm == 0) {
+        FG_SKINNY_DISPATCH(N, {
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_nt_kernel<NT>, 128, 0) != cudaSuccess || per_sm < 1) {
+                cudaGetLastError();
+                per_sm = 4;
+            }
+        });
+        slot.store(per_sm, std::memory_order_release);
+    }
     uint32_t gy = (uint32_t)((uint64_t)per_sm * ctx->sm_count / gx);
     if (gy < 1) gy = 1;
     if (gy > chunks) gy = chunks;
