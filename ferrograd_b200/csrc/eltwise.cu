@@ -175,13 +175,24 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(uint32_t rows, uint
         part[(size_t)blockIdx.y * cols + c] = t;
     }
 }
+// out[c] = sum over chunks of part[k][c].  A block covers 32 columns; its eight warps each add every eighth chunk
+// (so the chain of dependent loads is an eighth as long), then the eight sums are added in order.
 __global__ void __launch_bounds__(256) colsum_fold_kernel(uint32_t cols, uint32_t nchunks,
                                                           const float* __restrict__ part, float* __restrict__ out) {
-    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float red[8][33];
+    const uint32_t cx = threadIdx.x & 31u, gy = threadIdx.x >> 5;
+    const uint32_t c = blockIdx.x * 32 + cx;
     float s = 0.0f;
-    for (uint32_t k = 0; k < nchunks; ++k) s += part[(size_t)k * cols + c];
-    out[c] = s;
+    if (c < cols)
+        for (uint32_t k = gy; k < nchunks; k += 8) s += part[(size_t)k * cols + c];
+    red[gy][cx] = s;
+    __syncthreads();
+    if (gy == 0 && c < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w][cx];
+        out[c] = t;
+    }
 }
 
 // ---- chains ----
@@ -541,7 +552,7 @@ int32_t fg_act_bwd_launch(fg_ctx* ctx, uint64_t n, int act, const float* dy, con
 }
 
 int32_t fg_colsum_fold_launch(fg_ctx* ctx, uint32_t cols, uint32_t nchunks, const float* part, float* out) {
-    colsum_fold_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(cols, nchunks, part, out);
+    colsum_fold_kernel<<<(cols + 31) / 32, 256, 0, ctx->stream>>>(cols, nchunks, part, out);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }
@@ -555,7 +566,7 @@ int32_t fg_colsum_launch(fg_ctx* ctx, uint32_t rows, uint32_t cols, const float*
     dim3 grid((cols + 31) / 32, nchunks), block(32, 8);
     colsum_partial_kernel<<<grid, block, 0, ctx->stream>>>(rows, cols, chunk, x, (float*)part);
     FG_LAUNCHED(ctx);
-    colsum_fold_kernel<<<(cols + 255) / 256, 256, 0, ctx->stream>>>(cols, nchunks, (const float*)part, out);
+    colsum_fold_kernel<<<(cols + 31) / 32, 256, 0, ctx->stream>>>(cols, nchunks, (const float*)part, out);
     FG_LAUNCHED(ctx);
     return FG_OK;
 }

@@ -454,16 +454,29 @@ __global__ void __launch_bounds__(128) gemm_skinny_nt_kernel(uint32_t M, uint32_
     }
 }
 
-// dB[j][n] = sum over chunks of part[c][n][j]; thread i = n * Kd + j, so the reads are contiguous.
+// dB[j][n] = sum over chunks of part[c][n][j]; output i = n * Kd + j, so the reads are contiguous.  A block covers
+// 32 outputs; its eight warps each add every eighth chunk (an eighth of the chain of dependent loads), then the
+// eight sums are added in order.
 __global__ void __launch_bounds__(256) fold_chunks_kernel(uint32_t Kd, uint32_t N, uint32_t nchunks, const float* __restrict__ part,
                                                           float* __restrict__ out) {
+    __shared__ float red[8][33];
     const uint64_t total = (uint64_t)Kd * N;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t cx = threadIdx.x & 31u, gy = threadIdx.x >> 5;
+    for (uint64_t i0 = (uint64_t)blockIdx.x * 32; i0 < total; i0 += (uint64_t)gridDim.x * 32) {
+        const uint64_t i = i0 + cx;
         float s = 0.0f;
-#pragma unroll 16
-        for (uint32_t c = 0; c < nchunks; ++c) s += part[(size_t)c * total + i];
-        const uint32_t n = (uint32_t)(i / Kd), j = (uint32_t)(i % Kd);
-        out[(size_t)j * N + n] = s;
+        if (i < total)
+            for (uint32_t c = gy; c < nchunks; c += 8) s += part[(size_t)c * total + i];
+        __syncthreads();                      // the previous round's sums have been read
+        red[gy][cx] = s;
+        __syncthreads();
+        if (gy == 0 && i < total) {
+            float t = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += red[w][cx];
+            const uint32_t n = (uint32_t)(i / Kd), j = (uint32_t)(i % Kd);
+            out[(size_t)j * N + n] = t;
+        }
     }
 }
 
@@ -592,7 +605,7 @@ int32_t fg_gemm_skinny_tn_launch(fg_ctx* ctx, uint32_t M, uint32_t Kd, uint32_t 
     });
     FG_LAUNCHED(ctx);
     const uint64_t n = (uint64_t)Kd * N;
-    fold_chunks_kernel<<<fg_stream_grid(ctx, n, 256, 8), 256, 0, ctx->stream>>>(Kd, N, nchunks, (const float*)part, dB);
+    fold_chunks_kernel<<<fg_stream_grid(ctx, n * 8, 256, 8), 256, 0, ctx->stream>>>(Kd, N, nchunks, (const float*)part, dB);
     fg_time_end(ctx, tr);
     FG_LAUNCHED(ctx);
     return FG_OK;
