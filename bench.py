@@ -579,6 +579,32 @@ def run_ours(args, rank, world, local_rank):
     ctx.timing_enable(False)
     ctx.set_option("exec_plans", "auto")
     clocks = sampler.stop() if sampler else None
+
+    # ---- the gradient exchange of one step alone (no compute beside it): one allreduce per layer's weight range,
+    #      as the backward pass issues them, on the communicator the step uses; outside every timed region ----
+    exchange_alone = None
+    if world > 1:
+        sizes = [w["dims"][l] * w["dims"][l + 1] + w["dims"][l + 1] for l in range(len(w["dims"]) - 1)]
+        with torch.cuda.stream(stream):
+            gbuf = torch.zeros(sum(sizes), device="cuda")
+        ctx.sync()
+
+        def exchange_once(i):
+            off = 0
+            for n_el in sizes:
+                ctx.allreduce_sum(gbuf.data_ptr() + 4 * off, n_el)
+                off += n_el
+            ctx.comm_join()
+
+        for i in range(2):
+            exchange_once(i)
+        barrier()
+        x_ms = max_over_ranks(timed(torch, stream, ctx, exchange_once, 5)) / 5
+        barrier()
+        nbytes = 4.0 * sum(sizes)
+        exchange_alone = {"bytes_per_step": nbytes, "ms": x_ms, "algbw_gbs": nbytes / x_ms / 1e6,
+                          "busbw_gbs": nbytes / x_ms / 1e6 * 2.0 * (world - 1) / world, "allreduces": len(sizes)}
+        del gbuf
     od = w["dims"][-1]
     final_loss = final_loss_sum / (w["batch"] * (od if w["loss"] == "mse" else 1))     # per-sample mean of this rank
 
@@ -632,7 +658,7 @@ def run_ours(args, rank, world, local_rank):
                                         "frac_of_hbm": adam_bytes / adam_ms / 1e6 / peaks["hbm_gbs"] if adam_ms else None,
                                         "frac_of_nominal_hbm": adam_bytes / adam_ms / 1e6 / NOMINAL["hbm_gbs"] if adam_ms else None,
                                         "share_of_step": adam_ms / eager_ms if eager_ms else None}},
-            "final_loss": final_loss, "peaks": peak_src, "dp_check": dp_check,
+            "final_loss": final_loss, "peaks": peak_src, "dp_check": dp_check, "exchange_alone": exchange_alone,
             "model_tflops": net.flops_per_step() * world * args.steps / (ms / 1e3) / 1e12,
         }
         if world == 1 and not args.no_kernels:
