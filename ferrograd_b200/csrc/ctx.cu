@@ -170,6 +170,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     if (getenv("FG_EXEC_NO_PLANS")) c->opt_exec_plans = 0;
     if (const char* e = getenv("NCCL_MAX_CTAS")) fg_ctx_set_option(c, "comm_max_ctas", e);
     if (const char* e = getenv("FG_COMM_SMS")) fg_ctx_set_option(c, "comm_sms", e);
+    if (const char* e = getenv("FG_COMM_MIN_EXCHANGE")) fg_ctx_set_option(c, "comm_min_exchange", e);
     if (cuda_stream) {
         c->stream = (cudaStream_t)cuda_stream;
         c->own_stream = false;

@@ -105,7 +105,8 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  *   "comm_min_exchange"  the graph engine starts a gradient exchange during the backward pass once this many
  *                   elements are complete (default 1048576); smaller ranges wait for the next one
  * The environment variables FG_GEMM_TILE, FG_GEMM_NO_SPLITK, FG_GEMM_NO_PAIRS, FG_EXEC_NO_PLANS,
- * NCCL_MAX_CTAS and FG_COMM_SMS give the initial values; they are read once, when the context is created. */
+ * NCCL_MAX_CTAS, FG_COMM_SMS and FG_COMM_MIN_EXCHANGE give the initial values; they are read once, when the
+ * context is created. */
 int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value);
 /* Self-test of the bounded device-side waits (no counterpart in the reference).  Launches one tiny kernel that
  * waits, for at most max_cycles SM clock cycles (clamped to 1,000,000), on an mbarrier nobody ever arrives on,
