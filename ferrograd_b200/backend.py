@@ -205,7 +205,8 @@ class GpuContext:
 
     # ---- misc ----
     def set_option(self, name, value):
-        """fg_ctx_set_option: "gemm_tile", "gemm_split_k", "gemm_pairs", "exec_plans", "comm_max_ctas", "comm_sms"."""
+        """fg_ctx_set_option: "gemm_tile", "gemm_group", "gemm_split_k", "gemm_pairs", "exec_plans", "comm_max_ctas",
+        "comm_sms", "comm_min_exchange"."""
         self._check(self.lib.fg_ctx_set_option(self.handle, name.encode(), str(value).encode()))
 
     def stream(self):

@@ -123,6 +123,12 @@ int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value) {
         if (s == FG_OK) ctx->opt_exec_plans = on ? 1 : 0;
         return s;
     }
+    if (!strcmp(name, "gemm_group")) {
+        const long v = strtol(value, nullptr, 10);
+        if (v < 0 || v > 64) return fg_fail(ctx, FG_ERR_INVALID_ARGUMENT, "fg_ctx_set_option: gemm_group must be 0 (default) .. 64");
+        ctx->opt_tile_group = (int)v;
+        return FG_OK;
+    }
     if (!strcmp(name, "comm_min_exchange")) {
         char* end = nullptr;
         const unsigned long long v = strtoull(value, &end, 10);
@@ -157,6 +163,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
     c->opt_tile_pair = -1;
+    c->opt_tile_group = 0;
     c->opt_split_k = true;
     c->opt_pairs = true;
     c->opt_exec_plans = -1;
@@ -171,6 +178,7 @@ int32_t fg_ctx_create_on_stream(int32_t device, void* cuda_stream, fg_ctx** out)
     if (const char* e = getenv("NCCL_MAX_CTAS")) fg_ctx_set_option(c, "comm_max_ctas", e);
     if (const char* e = getenv("FG_COMM_SMS")) fg_ctx_set_option(c, "comm_sms", e);
     if (const char* e = getenv("FG_COMM_MIN_EXCHANGE")) fg_ctx_set_option(c, "comm_min_exchange", e);
+    if (const char* e = getenv("FG_GEMM_GROUP")) fg_ctx_set_option(c, "gemm_group", e);
     if (cuda_stream) {
         c->stream = (cudaStream_t)cuda_stream;
         c->own_stream = false;

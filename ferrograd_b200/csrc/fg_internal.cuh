@@ -71,6 +71,7 @@ struct fg_ctx {
     void* comm;
     int nranks, rank;
     // Options (fg_ctx_set_option); the FG_* environment variables give their initial values once, at creation.
+    int opt_tile_group;         // pair kernel: tile rows per group of the tile order (0: the default, eight)
     int opt_tile_pair;          // -1: chosen per shape; 1: CTA pairs whenever the shape allows; 0: opt_tile_bn x opt_tile_bk
     int opt_tile_bn, opt_tile_bk;
     bool opt_split_k;           // split-K tail of the pair kernel

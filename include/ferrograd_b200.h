@@ -92,6 +92,7 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  * CompilationOptions: dispatch/mod.rs:369-455).  Values are strings.
  *   "gemm_tile"     "auto" (default) | "pair" | "256x32" | "256x16" | "128x32" | "128x16": the tensor-core tile
  *   "gemm_split_k"  "1" (default) | "0": cut the tiles of an under-filled last wave into K-shares
+ *   "gemm_group"    "0" (default: by shape) | 1..64: tile rows per group of the pair kernel's tile order
  *   "gemm_pairs"    "1" (default) | "0": multiply f32 tensors as they lie, with bf16 pairs, where the shape
  *                   allows; "0" sends every shape through operand planes written by a pre-pass
  *   "exec_plans"    "auto" (default) | "1" | "0": the graph engine records each dispatch as a CUDA graph and
@@ -105,7 +106,7 @@ uint64_t fg_ctx_workspace_bytes(fg_ctx* ctx);
  *   "comm_min_exchange"  the graph engine starts a gradient exchange during the backward pass once this many
  *                   elements are complete (default 1048576); smaller ranges wait for the next one
  * The environment variables FG_GEMM_TILE, FG_GEMM_NO_SPLITK, FG_GEMM_NO_PAIRS, FG_EXEC_NO_PLANS,
- * NCCL_MAX_CTAS, FG_COMM_SMS and FG_COMM_MIN_EXCHANGE give the initial values; they are read once, when the
+ * FG_GEMM_GROUP, NCCL_MAX_CTAS, FG_COMM_SMS and FG_COMM_MIN_EXCHANGE give the initial values; they are read once, when the
  * context is created. */
 int32_t fg_ctx_set_option(fg_ctx* ctx, const char* name, const char* value);
 /* Self-test of the bounded device-side waits (no counterpart in the reference).  Launches one tiny kernel that
